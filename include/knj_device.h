@@ -1,0 +1,293 @@
+/* knj_device.h -- C-ABI of libknj_device.so: the device layer and the kernel
+ * entry points of the quantized (GGUF Q4_K) MoE expert path, for NVIDIA B200
+ * (sm_100a).
+ *
+ * This is the drop-in boundary. Every entry point replaces one interface of the
+ * reference project (cited per declaration as path:line inside that project):
+ *   - the HIP runtime calls its drivers make directly (hipMalloc, hipMemcpy,
+ *     streams, events) become the thin knj_dev / knj_malloc / knj_stream /
+ *     knj_event functions;
+ *   - each `extern "C" __global__` kernel becomes a host launcher of the same
+ *     name + `_launch`, same arguments in the same order, plus a trailing
+ *     stream (a __global__ symbol cannot be launched by a foreign compiler);
+ *   - the Q4_K bench kernels' argument lists (the de-facto ExpertPlan) become
+ *     knj_q4k_gateup_launch / knj_q4k_down_launch / knj_q4k_proj_launch /
+ *     knj_fuse_gateup_silu_launch;
+ *   - the host routing plan and weighted combine of the benches become device
+ *     kernels (knj_router_topk_launch, knj_moe_permute_launch,
+ *     knj_moe_combine_launch) and the whole layer is one call
+ *     (knj_moe_ffn_decode_launch / knj_moe_ffn_prefill_launch).
+ *
+ * Conventions.
+ *   - Every function returns int: 0 = ok, negative = error (codes below). No
+ *     exception crosses this boundary. knj_last_error_string() describes the
+ *     last error on the calling thread.
+ *   - All buffers are owned by the caller. The library allocates no device
+ *     memory; kernels that need scratch take an explicit workspace whose size a
+ *     *_workspace_bytes function reports.
+ *   - Quantized weights are borrowed and immutable: Q4_K superblocks of 144
+ *     bytes, row-major [expert][row][K/256][144], base address 16-byte aligned
+ *     (KNJ_E_REFUSE otherwise).
+ *   - Launches are asynchronous on the given stream (NULL = default stream).
+ *     Kernels report nothing themselves: callers that want proof of execution
+ *     pre-fill outputs with a sentinel, as the reference's drivers do.
+ *   - Thread model: one thread issues launches per stream; the library keeps
+ *     no global device state beyond the current device.
+ */
+#ifndef KNJ_DEVICE_H
+#define KNJ_DEVICE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes, mapped onto the reference's failure labels
+ * (docs/BUILD-OUTLINE.md:588-598: RETRY / DEGRADE / REFUSE / INVALIDATE / FATAL) */
+#define KNJ_OK 0
+#define KNJ_E_REFUSE (-1)    /* REFUSE: null pointer, bad geometry, misaligned base */
+#define KNJ_E_RUNTIME (-2)   /* FATAL:  a CUDA runtime call failed */
+#define KNJ_E_ARCH (-3)      /* REFUSE: device is not compute capability 10.x */
+#define KNJ_E_WORKSPACE (-4) /* REFUSE: workspace missing or too small */
+#define KNJ_E_TIMEOUT (-5)   /* RETRY:  a bounded device-side wait gave up */
+#define KNJ_E_NOTREADY (-6)  /* event / stream query: work still in flight */
+
+/* Process exit codes of the reference's device drivers
+ * (tests/test_gemm_w4.hip:11-18, tools/bench/q4k_moe_ffn.hip:63). */
+#define KNJ_EXIT_PASS 0
+#define KNJ_EXIT_MISSING_INPUT 3
+#define KNJ_EXIT_FAIL 5
+#define KNJ_EXIT_DECLINED 6 /* built for another arch than the attached device: a skip */
+#define KNJ_EXIT_REFUSED 7  /* KNJ_BUILD_ARCH not set */
+#define KNJ_EXIT_RUNTIME 9
+
+/* element types of activation buffers */
+#define KNJ_DT_F32 0
+#define KNJ_DT_BF16 1
+#define KNJ_DT_F16 2
+
+typedef void *knj_stream_t; /* a cudaStream_t */
+typedef void *knj_event_t;  /* a cudaEvent_t */
+typedef void *knj_graph_t;  /* a cudaGraphExec_t */
+
+/* ======================================================================== */
+/* Device layer (replaces the hip* calls listed per function)               */
+/* ======================================================================== */
+
+/* C mirror of DeviceCaps (src/device/device_caps.h:57-85), runtime fields filled. */
+typedef struct knj_device_caps {
+  char arch[16]; /* "sm_100" */
+  char name[64];
+  int32_t has_mma, has_fp8, has_dot_builtin, wave_size;
+  uint64_t vram_total, vram_usable;
+  int32_t rebar_full_aperture;
+  uint32_t sms, clock_khz, max_streams, num_queue_groups;
+  uint32_t smem_per_block_optin, l2_bytes;
+  int32_t cc_major, cc_minor;
+} knj_device_caps;
+
+const char *knj_last_error_string(void);            /* hipGetErrorString(hipGetLastError()) */
+int knj_dev_count(int *n);                           /* hipGetDeviceCount */
+int knj_dev_open(int idx);                           /* hipSetDevice + arch check; KNJ_E_ARCH if not sm_10x */
+int knj_dev_current(int *idx);                       /* hipGetDevice */
+int knj_dev_caps(int idx, knj_device_caps *out);     /* hipGetDeviceProperties + hipMemGetInfo */
+int knj_dev_sync(void);                              /* hipDeviceSynchronize */
+int knj_mem_info(size_t *free_bytes, size_t *total); /* hipMemGetInfo */
+/* Arch guard of the drivers (tests/test_gemm_w4.hip:124-142): compares env
+ * KNJ_BUILD_ARCH with the compiled arch and the attached device. Returns the
+ * driver exit code: 0 ok, 6 declined (mismatch), 7 refused (unset), 9 no device. */
+int knj_arch_check(void);
+
+int knj_malloc(void **p, size_t bytes);      /* hipMalloc */
+int knj_free(void *p);                       /* hipFree */
+int knj_host_malloc(void **p, size_t bytes); /* hipHostMalloc (pinned) */
+int knj_host_free(void *p);                  /* hipHostFree */
+int knj_memset(void *p, int byte, size_t n, knj_stream_t s); /* hipMemsetAsync */
+int knj_memcpy_h2d(void *dst, const void *src, size_t n);    /* hipMemcpy, blocking */
+int knj_memcpy_d2h(void *dst, const void *src, size_t n);
+int knj_memcpy_d2d(void *dst, const void *src, size_t n);
+int knj_memcpy_h2d_async(void *dst, const void *src, size_t n, knj_stream_t s); /* hipMemcpyAsync */
+int knj_memcpy_d2h_async(void *dst, const void *src, size_t n, knj_stream_t s);
+int knj_memcpy_d2d_async(void *dst, const void *src, size_t n, knj_stream_t s);
+
+int knj_stream_create(knj_stream_t *s); /* hipStreamCreateWithFlags(non-blocking) */
+int knj_stream_destroy(knj_stream_t s);
+int knj_stream_sync(knj_stream_t s);
+int knj_stream_query(knj_stream_t s);                     /* 0 idle, KNJ_E_NOTREADY busy */
+int knj_stream_wait_event(knj_stream_t s, knj_event_t e); /* hipStreamWaitEvent */
+int knj_event_create(knj_event_t *e, int timing);         /* hipEventCreateWithFlags */
+int knj_event_destroy(knj_event_t e);
+int knj_event_record(knj_event_t e, knj_stream_t s);
+int knj_event_query(knj_event_t e);
+int knj_event_sync(knj_event_t e);
+int knj_event_elapsed_ms(float *ms, knj_event_t start, knj_event_t stop);
+
+/* Stream capture into a replayable graph (the resident whole-stack loop,
+ * tools/bench/q4k_stream_ffn.hip:1233-1325, issues the same launches per step). */
+int knj_graph_begin(knj_stream_t s);
+int knj_graph_end(knj_stream_t s, knj_graph_t *g);
+int knj_graph_launch(knj_graph_t g, knj_stream_t s);
+int knj_graph_destroy(knj_graph_t g);
+
+/* ======================================================================== */
+/* Kernels of kernels/knj_kernels.hip                                       */
+/* ======================================================================== */
+
+/* knj_control (kernels/knj_kernels.hip:132-144): out[0] = seed + 1,
+ * out[1] = n_blocks; proves a dispatch happened. */
+int knj_control_launch(uint32_t *out, uint32_t seed, uint32_t n_threads, uint32_t n_blocks, knj_stream_t s);
+
+/* knj_probe_caps (kernels/knj_kernels.hip:282-318), launched <<<1,32>>>.
+ * cap[0] = dp4a(0x01010101, 0x01010101, 0) == 4; cap[1] = two chained packed
+ * half2 fma of 1*1 from zero give 2.0h (0x4000); cap[2] = 1 (dispatched);
+ * cap[3] = in ? in[0] : 0; cap[4] = the observed fp16 pattern.
+ * CUDA additions: cap[5] = a fp16 tensor-core MMA multiplied subnormal-encoded
+ * 4-bit integers exactly (the decode kernels rely on it); cap[6] = a
+ * cp.async.bulk + mbarrier transaction completed within its bounded wait;
+ * cap[7] = 128 TMEM columns were allocated and freed. cap must hold 8 words. */
+int knj_probe_caps_launch(uint32_t *cap, const int32_t *in, knj_stream_t s);
+
+/* knj_build_asum (kernels/knj_kernels.hip:232-260): Asum[m][g] = sum of the
+ * 128 int8 activations of group g of row m; Act is [M][K/8][2] u32. */
+int knj_build_asum_launch(const uint32_t *Act, int32_t *Asum, uint32_t M, uint32_t K, uint32_t n_threads,
+                          uint32_t n_blocks, knj_stream_t s);
+
+/* knj_gemm_w4_i8 (kernels/knj_kernels.hip:176-218): C[m][n] = sum_g scale_g *
+ * (sum_k u_k a_k - 8 * Asum[m][g]); Bq is [N][K/128][68]. */
+int knj_gemm_w4_i8_launch(const uint8_t *Bq, const uint32_t *Act, const int32_t *Asum, float *C, uint32_t M,
+                          uint32_t N, uint32_t K, uint32_t n_threads, uint32_t n_blocks, knj_stream_t s);
+
+/* ======================================================================== */
+/* Q4_K decode (kernels/knj_q4k.h, src/loader/dequant.cpp)                  */
+/* ======================================================================== */
+
+/* Verification kernel: n_blocks Q4_K superblocks -> n_blocks*256 f32, bit-equal
+ * to dequant_q4_k (src/loader/dequant.cpp:102-125) and knj_q4k_weight
+ * (kernels/knj_q4k.h:147-167). Never on a timed path: the hot kernels fuse the
+ * unpack into their consumer. */
+int knj_q4k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks, knj_stream_t s);
+/* Same for Q6_K (src/loader/dequant.cpp:164-191, kernels/knj_q4k.h:170-196). */
+int knj_q6k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks, knj_stream_t s);
+
+/* ======================================================================== */
+/* Routing (src/model/model.cpp:419-460; tools/bench/q4k_stream_ffn.hip:957-1001)
+ * ======================================================================== */
+
+/* RMSNorm rows (src/model/model.cpp:258-271): out = x * rsqrt(mean(x^2)+eps) * w,
+ * w bf16 [H]; out f32 [T][H]. */
+int knj_rmsnorm_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *w_bf16, float eps, int T, int H,
+                       float *out, knj_stream_t s);
+
+/* Router: logits[t][e] = x[t] . Wr[e] (+ bias[e]), softmax over E, exact top-k
+ * (ties to the lowest expert id), renormalised weights. Pair p = t*k + s holds
+ * the s-th most probable expert of token t (the numbering of build_plan).
+ * Wr is bf16 [E][H]; bias f32 [E] or NULL; logits f32 [T][E] scratch (also an
+ * output); pair_exp int32 [T*k]; pair_w f32 [T*k]. E <= 256, k <= 8. */
+int knj_router_topk_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *Wr_bf16, const float *bias, int T,
+                           int H, int E, int k, float *logits, int32_t *pair_exp, float *pair_w, knj_stream_t s);
+
+/* Token permutation: from pair_exp[P] build, per expert, the ascending list of
+ * pair ids routed to it -- pair_idx[E][idx_stride] (-1 padded), pair_cnt[E] --
+ * plus the ascending list of experts that received work, exp_list[E] with
+ * n_active[0] entries used and n_active[1] = max count. Replaces the host loop
+ * tools/bench/q4k_moe_ffn.hip:536-548. */
+int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,
+                           int32_t *exp_list, int32_t *n_active, knj_stream_t s);
+
+/* Weighted combine (tools/bench/q4k_moe_ffn.hip:682-694;
+ * src/model/model.cpp:502-507): out[t] = (residual ? resid[t] : 0) + sum over
+ * the k pairs of token t of pair_w[p] * Y[row_of(p)], summed in ascending
+ * expert order as the CPU path does. Y f32 [rows][H]; row_of = pair_row[p] when
+ * given, else p. out dtype f32 or bf16. */
+int knj_moe_combine_launch(const float *Y, const int32_t *pair_row, const int32_t *pair_exp, const float *pair_w,
+                           const void *resid, int resid_dtype, int64_t ld_resid, void *out, int out_dtype, int64_t ldo,
+                           int T, int H, int k, knj_stream_t s);
+
+/* ======================================================================== */
+/* Expert projections, decode class (f32-accurate, HBM-bound)               */
+/* ======================================================================== */
+
+/* The decode kernels multiply Q4_K codes as exact small integers on the
+ * fp16 tensor cores and apply the per-32 scale/min in f32, so activations are
+ * first split into a "panel": per vector a power-of-two scale, a high and a
+ * low fp16 plane (together ~22 significant bits) and the per-32 sums the min
+ * term needs. One panel vector = 4*K + 4*(K/32) + 16 bytes. */
+size_t knj_panel_bytes(int n_vec, int K);
+/* x [n_vec][K] (f32/bf16/f16, row stride ldx elements) -> panel. */
+int knj_act_prep_launch(const void *x, int x_dtype, int64_t ldx, int n_vec, int K, void *panel, knj_stream_t s);
+
+/* Gate and up in one pass (tools/bench/q4k_moe_ffn.hip:164-241 knj_q4k_gateup):
+ * for every pair p routed to expert e and every n < N
+ *   G[p][n] = x[tok(p)] . Wg[e][n],  U[p][n] = x[tok(p)] . Wu[e][n],
+ *   A[p][n] = silu(G) * U                       (tools/bench/q4k_stream_ffn.hip:1005-1031)
+ * Xpanel holds one prepared vector per TOKEN; tok(p) = pair_tok[p] when given,
+ * else p / top_k. G, U, A are f32 [P][N]; any of them may be NULL (not stored).
+ * Experts are taken from exp_list[0 .. n_active[0]). */
+int knj_q4k_gateup_launch(const void *Xpanel, const uint8_t *Wg, const uint8_t *Wu, const int32_t *pair_idx,
+                          const int32_t *pair_cnt, const int32_t *pair_tok, const int32_t *exp_list,
+                          const int32_t *n_active, float *G, float *U, float *A, int N, int K, int rowBytes,
+                          int64_t idxStride, int n_experts, int top_k, int max_tokens, knj_stream_t s);
+
+/* One projection per pair (tools/bench/q4k_stream_ffn.hip:834-882 knj_q4k_proj;
+ * :780-829 knj_q6k_down with dq4 = 1): Y[p][n] = a[p] . W[e][n]. Apanel holds
+ * one prepared vector per PAIR (row_of as for the combine). Y f32 [P][N]. */
+int knj_q4k_proj_launch(const void *Apanel, const uint8_t *W, const int32_t *pair_idx, const int32_t *pair_cnt,
+                        const int32_t *pair_row, const int32_t *exp_list, const int32_t *n_active, float *Y, int N,
+                        int K, int rowBytes, int64_t idxStride, int n_experts, int max_tokens, knj_stream_t s);
+#define knj_q4k_down_launch knj_q4k_proj_launch
+
+/* A[i] = silu(G[i]) * U[i], n elements (tools/bench/q4k_stream_ffn.hip:1021-1031
+ * knj_fuse_gateup_silu); out dtype f32, bf16 or f16. Uses expf, not the fast
+ * intrinsic, so the f32 path keeps its 1e-5 budget. */
+int knj_fuse_gateup_silu_launch(const float *G, const float *U, void *A, int a_dtype, int64_t n, knj_stream_t s);
+
+/* Single-matrix GEMV/GEMM convenience (the CPU path's Model::matmul,
+ * src/model/model.cpp:326-380): y[m][n_out] = x[m][n_in] . W^T, W Q4_K
+ * [n_out][n_in/256][144]. workspace >= knj_q4k_matmul_workspace_bytes(m, n_in). */
+size_t knj_q4k_matmul_workspace_bytes(int m, int n_in);
+int knj_q4k_matmul_launch(const uint8_t *W, int n_in, int n_out, const void *x, int x_dtype, int64_t ldx, int m,
+                          float *y, int64_t ldy, void *workspace, size_t workspace_bytes, knj_stream_t s);
+
+/* ======================================================================== */
+/* Whole MoE-FFN layer (src/model/model.cpp:399-510 Model::moe)             */
+/* ======================================================================== */
+
+typedef struct knj_moe_ffn_args {
+  int32_t n_tokens, hidden, ffn, n_experts, top_k;
+  int32_t x_dtype;           /* KNJ_DT_F32 or KNJ_DT_BF16 */
+  const void *x;             /* [T][hidden] */
+  int64_t ldx;               /* row stride of x, elements */
+  const uint16_t *w_router;  /* bf16 [E][hidden] */
+  const float *router_bias;  /* f32 [E] or NULL */
+  const uint8_t *w_gate;     /* Q4_K [E][ffn][hidden/256][144] */
+  const uint8_t *w_up;       /* Q4_K [E][ffn][hidden/256][144] */
+  const uint8_t *w_down;     /* Q4_K [E][hidden][ffn/256][144] */
+  const uint16_t *norm_w;    /* bf16 [hidden] RMSNorm weight applied to x first, or NULL */
+  float rms_eps;
+  int32_t residual;          /* 1: out = x + moe(norm(x)); 0: out = moe(norm(x)) */
+  void *out;                 /* [T][hidden] */
+  int32_t out_dtype;         /* KNJ_DT_F32 or KNJ_DT_BF16 */
+  int64_t ldo;
+  void *workspace;           /* >= knj_moe_ffn_workspace_bytes(...) */
+  size_t workspace_bytes;
+  /* optional taps, may be NULL: the routing decision for inspection */
+  int32_t *tap_pair_exp;     /* [T*k] */
+  float *tap_pair_w;         /* [T*k] */
+} knj_moe_ffn_args;
+
+/* mode 0 = decode class (any T, f32-accurate kernels), 1 = prefill class. */
+size_t knj_moe_ffn_workspace_bytes(int n_tokens, int hidden, int ffn, int n_experts, int top_k, int mode);
+
+/* Decode: batch <= 64 tokens, HBM-bound, f32-accurate (<= 1e-5 rel-RMSE vs the
+ * CPU path). Larger T is accepted and stays exact, at decode-class speed. */
+int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s);
+/* Prefill: tokens bucketed per expert, bf16 operands on tcgen05 with f32 TMEM
+ * accumulators (<= 1e-3 rel-RMSE vs the CPU path). */
+int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KNJ_DEVICE_H */

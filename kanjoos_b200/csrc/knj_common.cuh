@@ -1,0 +1,124 @@
+// knj_common.cuh -- shared pieces of the CUDA translation units: status
+// plumbing, PTX wrappers (mbarrier, bulk async copy, warp MMA), bounded waits.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "knj_device.h"
+
+namespace knj {
+
+// ---- host-side status ------------------------------------------------------
+void set_error(const char *fmt, ...);
+int cuda_fail(cudaError_t e, const char *what);
+
+#define KNJ_CUDA(call)                                      \
+  do {                                                      \
+    cudaError_t e_ = (call);                                \
+    if (e_ != cudaSuccess) return ::knj::cuda_fail(e_, #call); \
+  } while (0)
+
+#define KNJ_REQUIRE(cond, ...)       \
+  do {                               \
+    if (!(cond)) {                   \
+      ::knj::set_error(__VA_ARGS__); \
+      return KNJ_E_REFUSE;           \
+    }                                \
+  } while (0)
+
+inline int launch_status(const char *what) {
+  cudaError_t e = cudaGetLastError();
+  return e == cudaSuccess ? KNJ_OK : cuda_fail(e, what);
+}
+
+inline cudaStream_t as_stream(knj_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+int sm_count();  // SMs of the current device (cached per device)
+
+// ---- device helpers --------------------------------------------------------
+#if defined(__CUDACC__)
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t arrivals) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(arrivals) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: every spin in this library gives up after a fixed number of
+// polls (each poll itself blocks for a hardware-chosen interval), so a copy
+// that never lands cannot hang the GPU. Returns false on give-up.
+constexpr uint32_t kMaxPolls = 1u << 22;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kMaxPolls; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// Bulk async copy global -> shared of `bytes` (multiple of 16, both addresses
+// 16-byte aligned), completion counted on `bar`. Never uses cluster multicast.
+__device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+__device__ __forceinline__ float load_as_f32(const void *base, int dtype, int64_t i) {
+  if (dtype == KNJ_DT_F32) return static_cast<const float *>(base)[i];
+  if (dtype == KNJ_DT_BF16) return __bfloat162float(static_cast<const __nv_bfloat16 *>(base)[i]);
+  return __half2float(static_cast<const __half *>(base)[i]);
+}
+__device__ __forceinline__ void store_from_f32(void *base, int dtype, int64_t i, float v) {
+  if (dtype == KNJ_DT_F32) static_cast<float *>(base)[i] = v;
+  else if (dtype == KNJ_DT_BF16) static_cast<__nv_bfloat16 *>(base)[i] = __float2bfloat16_rn(v);
+  else static_cast<__half *>(base)[i] = __float2half_rn(v);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace knj

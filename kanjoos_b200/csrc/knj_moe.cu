@@ -1,0 +1,134 @@
+// knj_moe.cu -- the whole MoE-FFN layer as one C-ABI call: the stage sequence
+// of the reference's CPU branch (src/model/model.cpp:399-510 Model::moe,
+// preceded by the ffn RMSNorm of :631 and followed by the residual add of
+// :652), issued as device kernels on one stream with every intermediate in a
+// caller-provided workspace.
+#include "knj_common.cuh"
+#include "knj_q4k.h"
+
+using namespace knj;
+
+namespace {
+
+inline size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
+
+struct Carve {
+  uint8_t *p;
+  size_t used = 0;
+  explicit Carve(void *base) : p(static_cast<uint8_t *>(base)) {}
+  template <typename T>
+  T *take(size_t bytes) {
+    T *r = p ? reinterpret_cast<T *>(p + used) : nullptr;
+    used += up256(bytes);
+    return r;
+  }
+};
+
+struct DecodeWs {
+  float *xn, *logits, *pair_w, *A, *Y;
+  int32_t *pair_exp, *pair_idx, *pair_cnt, *exp_list, *n_active;
+  void *xpanel, *apanel;
+  size_t bytes;
+};
+
+DecodeWs carve_decode(void *base, int T, int H, int F, int E, int k) {
+  Carve c(base);
+  DecodeWs w;
+  const size_t P = (size_t)T * k;
+  w.xn = c.take<float>((size_t)T * H * 4);
+  w.logits = c.take<float>((size_t)T * E * 4);
+  w.pair_exp = c.take<int32_t>(P * 4);
+  w.pair_w = c.take<float>(P * 4);
+  w.pair_idx = c.take<int32_t>((size_t)E * T * 4);
+  w.pair_cnt = c.take<int32_t>((size_t)E * 4);
+  w.exp_list = c.take<int32_t>((size_t)E * 4);
+  w.n_active = c.take<int32_t>(16);
+  w.xpanel = c.take<void>(knj_panel_bytes(T, H));
+  w.A = c.take<float>(P * F * 4);
+  w.apanel = c.take<void>(knj_panel_bytes((int)P, F));
+  w.Y = c.take<float>(P * H * 4);
+  w.bytes = c.used;
+  return w;
+}
+
+int check_args(const knj_moe_ffn_args *a, const char *who) {
+  KNJ_REQUIRE(a, "%s: null argument block", who);
+  KNJ_REQUIRE(a->x && a->w_router && a->w_gate && a->w_up && a->w_down && a->out, "%s: null tensor pointer", who);
+  KNJ_REQUIRE(a->n_tokens >= 0 && a->hidden > 0 && a->ffn > 0 && a->n_experts > 0, "%s: bad sizes", who);
+  KNJ_REQUIRE(a->hidden % 256 == 0 && a->ffn % 256 == 0, "%s: hidden=%d and ffn=%d must be multiples of 256", who,
+              a->hidden, a->ffn);
+  KNJ_REQUIRE(a->top_k >= 1 && a->top_k <= 8 && a->top_k <= a->n_experts, "%s: top_k=%d out of range", who, a->top_k);
+  KNJ_REQUIRE(a->n_experts <= 256, "%s: at most 256 experts", who);
+  KNJ_REQUIRE(a->x_dtype == KNJ_DT_F32 || a->x_dtype == KNJ_DT_BF16, "%s: x must be f32 or bf16", who);
+  KNJ_REQUIRE(a->out_dtype == KNJ_DT_F32 || a->out_dtype == KNJ_DT_BF16, "%s: out must be f32 or bf16", who);
+  KNJ_REQUIRE(aligned16(a->w_gate) && aligned16(a->w_up) && aligned16(a->w_down) && aligned16(a->w_router),
+              "%s: weight bases must be 16-byte aligned", who);
+  KNJ_REQUIRE(a->ldx >= a->hidden && a->ldo >= a->hidden, "%s: row strides shorter than hidden", who);
+  return KNJ_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t knj_moe_ffn_workspace_bytes(int n_tokens, int hidden, int ffn, int n_experts, int top_k, int mode) {
+  (void)mode;
+  if (n_tokens <= 0) return 256;
+  return carve_decode(nullptr, n_tokens, hidden, ffn, n_experts, top_k).bytes;
+}
+
+int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
+  int rc = check_args(a, "knj_moe_ffn_decode");
+  if (rc) return rc;
+  const int T = a->n_tokens, H = a->hidden, F = a->ffn, E = a->n_experts, k = a->top_k;
+  if (T == 0) return KNJ_OK;
+  const size_t need = knj_moe_ffn_workspace_bytes(T, H, F, E, k, 0);
+  if (!a->workspace || a->workspace_bytes < need) {
+    set_error("knj_moe_ffn_decode: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
+    return KNJ_E_WORKSPACE;
+  }
+  KNJ_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0, "knj_moe_ffn_decode: workspace must be 256-byte aligned");
+  const DecodeWs w = carve_decode(a->workspace, T, H, F, E, k);
+  const int P = T * k;
+
+  // 1. ffn RMSNorm (optional) -> the rows the router and the experts see
+  const void *src = a->x;
+  int src_dt = a->x_dtype;
+  int64_t src_ld = a->ldx;
+  if (a->norm_w) {
+    rc = knj_rmsnorm_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, T, H, w.xn, s);
+    if (rc) return rc;
+    src = w.xn;
+    src_dt = KNJ_DT_F32;
+    src_ld = H;
+  }
+  // 2. route
+  int32_t *pair_exp = a->tap_pair_exp ? a->tap_pair_exp : w.pair_exp;
+  float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
+  rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
+  if (rc) return rc;
+  // 3. permutation tables
+  rc = knj_moe_permute_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, s);
+  if (rc) return rc;
+  // 4. gate, up, silu(g)*u
+  rc = knj_act_prep_launch(src, src_dt, src_ld, T, H, w.xpanel, s);
+  if (rc) return rc;
+  rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
+                             nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, T, s);
+  if (rc) return rc;
+  // 5. down
+  rc = knj_act_prep_launch(w.A, KNJ_DT_F32, F, P, F, w.apanel, s);
+  if (rc) return rc;
+  rc = knj_q4k_proj_launch(w.apanel, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active, w.Y, H, F,
+                           F / 256 * KNJ_Q4K_BYTES, T, E, T, s);
+  if (rc) return rc;
+  // 6. weighted combine (+ residual)
+  return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
+                                a->out, a->out_dtype, a->ldo, T, H, k, s);
+}
+
+// Until the tcgen05 grouped GEMM is wired in, the prefill entry runs the same
+// exact pipeline (f32-accurate, decode-class speed).
+int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) { return knj_moe_ffn_decode_launch(a, s); }
+
+}  // extern "C"

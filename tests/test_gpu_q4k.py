@@ -1,0 +1,121 @@
+"""Q4_K decode and single-matrix products on the GPU against the CPU restatement
+and the golden vectors. Bit-exact for the decode; rel-RMSE <= 1e-5 over every
+output for the f32-accumulate products (the tolerance the task states for the
+GEMV path)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle_lib as ol
+from gpu_util import SENTINEL, dev, report
+from kanjoos_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+
+
+def test_dequant_crafted_blocks_bit_exact(golden):
+    from kanjoos_b200 import ops
+    got = ops.q4k_dequant(dev(golden["q4k_blocks"])).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), golden["q4k_blocks_f32"].view(np.uint32))
+
+
+def test_dequant_cfg1_bit_exact(golden):
+    """Config 1: the whole [768 x 2048] tensor, 1,572,864 weights."""
+    from kanjoos_b200 import ops
+    W = synth.q4k_rows(synth.stream(1, "gate"), synth.FFN, synth.HIDDEN)
+    got = ops.q4k_dequant(dev(W)).cpu().numpy()
+    want = ol.dequant_q4k(W)
+    assert (got == SENTINEL).sum() == 0
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert np.array_equal(got.ravel()[:512].view(np.uint32), golden["cfg1_dequant_head"].view(np.uint32))
+
+
+def test_dequant_empty_and_q6k():
+    from kanjoos_b200 import ops
+    assert ops.q4k_dequant(torch.empty((0, 144), dtype=torch.uint8, device="cuda")).numel() == 0
+    rng = np.random.Generator(np.random.Philox(5))
+    blk = rng.integers(0, 256, size=(64, 210), dtype=np.uint8)
+    blk[:, 208:210] = (np.abs(rng.standard_normal((64, 1))) * 0.01).astype(np.float16).view(np.uint8)
+    want = np.empty((64, 256), np.float32)
+    ol.oracle().knj_or_dequant_q6k(ol.ptr(blk, ol.u8p), ol.ptr(want, ol.f32p), want.size)
+    got = ops.q6k_dequant(dev(blk)).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_cfg1_gemv(golden):
+    """Config 1: y[768] = W[768 x 2048] . x, x f32 ~ N(0,1)."""
+    from kanjoos_b200 import ops
+    W = synth.q4k_rows(synth.stream(1, "gate"), synth.FFN, synth.HIDDEN)
+    x = synth.stream(1, "x").standard_normal(synth.HIDDEN).astype(np.float32)
+    got = ops.q4k_matmul(dev(W), dev(x[None])).cpu().numpy()[0]
+    st = report(got, golden["cfg1_y"], "cfg1 GEMV vs reference dequant_dot_f32")
+    assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_F32
+    # and against an exact (float64) product of the bit-exact decode
+    exact = (ol.dequant_q4k(W).reshape(synth.FFN, -1).astype(np.float64) @ x.astype(np.float64)).astype(np.float32)
+    st = report(got, exact, "cfg1 GEMV vs float64 product")
+    assert st["rel_rmse"] <= TOL_F32
+
+
+@pytest.mark.parametrize("m", [1, 2, 4, 5, 15, 16, 17, 64])
+@pytest.mark.parametrize("n_in,n_out", [(256, 16), (768, 48), (2048, 64)])
+def test_matmul_ragged_row_counts(m, n_in, n_out):
+    from kanjoos_b200 import ops
+    rng = np.random.Generator(np.random.Philox([m, n_in, n_out]))
+    W = synth.q4k_rows(rng, n_out, n_in)
+    x = rng.standard_normal((m, n_in)).astype(np.float32)
+    got = ops.q4k_matmul(dev(W), dev(x)).cpu().numpy()
+    want = ol.matmul_q4k(W, x)
+    st = report(got, want, f"matmul m={m} {n_out}x{n_in}")
+    assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_F32
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_matmul_16bit_activations(dtype):
+    from kanjoos_b200 import ops
+    rng = np.random.Generator(np.random.Philox(11))
+    W = synth.q4k_rows(rng, 32, 1024)
+    x = torch.from_numpy(rng.standard_normal((3, 1024)).astype(np.float32)).to(dtype)
+    got = ops.q4k_matmul(dev(W), x.cuda()).cpu().numpy()
+    want = ol.matmul_q4k(W, x.float().numpy())
+    assert report(got, want, f"matmul {dtype}")["rel_rmse"] <= TOL_F32
+
+
+def test_matmul_wide_dynamic_range():
+    """Activations spanning 12 orders of magnitude, a zero row and tiny rows: the
+    per-vector scaling of the activation planes must keep f32-level accuracy."""
+    from kanjoos_b200 import ops
+    rng = np.random.Generator(np.random.Philox(13))
+    W = synth.q4k_rows(rng, 32, 512)
+    x = rng.standard_normal((6, 512)).astype(np.float32)
+    x[0] *= 1e6
+    x[1] *= 1e-6
+    x[2] = 0.0
+    x[3, ::2] *= 1e4
+    x[4] *= 3e4
+    x[5] *= 1e-20
+    got = ops.q4k_matmul(dev(W), dev(x)).cpu().numpy()
+    want = ol.matmul_q4k(W, x)
+    for r in range(6):
+        if r == 2:
+            assert np.all(got[r] == 0.0)
+            continue
+        assert report(got[r], want[r], f"row {r}")["rel_rmse"] <= 2e-5
+
+
+def test_refusals_do_not_launch():
+    from kanjoos_b200 import _lib, ops
+    W = torch.zeros((16, 1, 144), dtype=torch.uint8, device="cuda")
+    x = torch.zeros((1, 256), dtype=torch.float32, device="cuda")
+    y = torch.zeros((1, 16), dtype=torch.float32, device="cuda")
+    L = _lib.lib()
+    import ctypes as C
+    rc = L.knj_q4k_matmul_launch(C.c_void_p(W.data_ptr()), 256, 16, C.c_void_p(x.data_ptr()), 0, 256, 1,
+                                 C.c_void_p(y.data_ptr()), 16, None, 0, None)
+    assert rc == -4 and b"workspace" in L.knj_last_error_string()
+    rc = L.knj_q4k_matmul_launch(C.c_void_p(W.data_ptr() + 8), 256, 16, C.c_void_p(x.data_ptr()), 0, 256, 1,
+                                 C.c_void_p(y.data_ptr()), 16, C.c_void_p(x.data_ptr()), 1 << 20, None)
+    assert rc in (-1, -4)
+    with pytest.raises(_lib.KnjError):
+        ops.q4k_matmul(torch.zeros((16, 1, 144), dtype=torch.uint8, device="cuda")[1:], x)  # 15 rows: not a multiple of 16
