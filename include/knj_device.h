@@ -196,6 +196,9 @@ int knj_router_topk_launch(const void *x, int x_dtype, int64_t ldx, const uint16
 int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,
                            int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
+/* Second half of the permutation step alone: exp_list / n_active from pair_cnt. */
+int knj_active_list_launch(const int32_t *pair_cnt, int E, int32_t *exp_list, int32_t *n_active, knj_stream_t s);
+
 /* Weighted combine (tools/bench/q4k_moe_ffn.hip:682-694;
  * src/model/model.cpp:502-507): out[t] = (residual ? resid[t] : 0) + sum over
  * the k pairs of token t of pair_w[p] * Y[row_of(p)], summed in ascending
@@ -286,6 +289,30 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s);
 /* Prefill: tokens bucketed per expert, bf16 operands on tcgen05 with f32 TMEM
  * accumulators (<= 1e-3 rel-RMSE vs the CPU path). */
 int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
+
+/* ======================================================================== */
+/* Expert-parallel exchange helpers                                         */
+/* ======================================================================== */
+/* The reference keeps every expert on one device and has no counterpart for
+ * these two (multi-GPU is a declared non-goal there, README.md:104-107,
+ * docs/01-architecture.md:322-325). Experts are split contiguously over ranks,
+ * owner(e) = e / (E / n_ranks). The all-to-all itself is issued by the host
+ * (NCCL); these kernels prepare and consume its buffers.
+ *
+ * knj_ep_pack: copy the hidden row of every pair (row_bytes each, token =
+ * pair / top_k) into send_rows in (expert, pair) order -- which is also
+ * destination-rank order -- and record pair_row[p] = slot of pair p, the index
+ * the combine uses on the returned rows. send_off[E+1] receives the exclusive
+ * scan of pair_cnt. */
+int knj_ep_pack_launch(const void *x, int row_bytes, int top_k, const int32_t *pair_idx, int idx_stride,
+                       const int32_t *pair_cnt, int E, int32_t *send_off, void *send_rows, int32_t *pair_row,
+                       knj_stream_t s);
+/* knj_ep_plan: counts[r][e] = rows source rank r sent for local expert e (rows
+ * of one source are contiguous, experts ascending). Builds the local plan over
+ * received-row indices: pair_idx[E_loc][idx_stride], pair_cnt, exp_list,
+ * n_active, as knj_moe_permute_launch does for local pairs. */
+int knj_ep_plan_launch(const int32_t *counts, int n_ranks, int n_local_experts, int idx_stride, int32_t *pair_idx,
+                       int32_t *pair_cnt, int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
 #ifdef __cplusplus
 }

@@ -86,6 +86,9 @@ SIGNATURES = {
     "knj_rmsnorm_launch": (_i, [_vp, _i, _i64, _vp, _f, _i, _i, _vp, _vp]),
     "knj_router_topk_launch": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "knj_moe_permute_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "knj_ep_pack_launch": (_i, [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]),
+    "knj_ep_plan_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "knj_panel_bytes": (_sz, [_i, _i]),
     "knj_act_prep_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),

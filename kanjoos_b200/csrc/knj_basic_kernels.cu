@@ -236,8 +236,8 @@ int knj_gemm_w4_i8_launch(const uint8_t *Bq, const uint32_t *Act, const int32_t 
 }
 
 int knj_q4k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks, knj_stream_t s) {
-  KNJ_REQUIRE(blocks && out, "knj_q4k_dequant: null pointer");
   if (n_blocks == 0) return KNJ_OK;
+  KNJ_REQUIRE(blocks && out, "knj_q4k_dequant: null pointer");
   KNJ_REQUIRE(aligned16(blocks) && aligned16(out), "knj_q4k_dequant: pointers must be 16-byte aligned");
   const uint64_t quads = n_blocks * 64;
   const unsigned grid = (unsigned)((quads + 255) / 256 < (uint64_t)sm_count() * 16 ? (quads + 255) / 256
@@ -247,8 +247,8 @@ int knj_q4k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks,
 }
 
 int knj_q6k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks, knj_stream_t s) {
-  KNJ_REQUIRE(blocks && out, "knj_q6k_dequant: null pointer");
   if (n_blocks == 0) return KNJ_OK;
+  KNJ_REQUIRE(blocks && out, "knj_q6k_dequant: null pointer");
   const uint64_t n = n_blocks * 256;
   const unsigned grid = (unsigned)((n + 255) / 256 < (uint64_t)sm_count() * 16 ? (n + 255) / 256
                                                                                  : (uint64_t)sm_count() * 16);

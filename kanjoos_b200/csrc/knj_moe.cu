@@ -78,6 +78,7 @@ size_t knj_moe_ffn_workspace_bytes(int n_tokens, int hidden, int ffn, int n_expe
 }
 
 int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
+  if (a && a->n_tokens == 0) return KNJ_OK;  // an empty batch has no rows to point at
   int rc = check_args(a, "knj_moe_ffn_decode");
   if (rc) return rc;
   const int T = a->n_tokens, H = a->hidden, F = a->ffn, E = a->n_experts, k = a->top_k;

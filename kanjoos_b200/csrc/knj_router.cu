@@ -323,6 +323,12 @@ int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride
   return launch_status("active_list_kernel");
 }
 
+int knj_active_list_launch(const int32_t *pair_cnt, int E, int32_t *exp_list, int32_t *n_active, knj_stream_t s) {
+  KNJ_REQUIRE(pair_cnt && exp_list && n_active && E >= 1, "knj_active_list: bad arguments");
+  active_list_kernel<<<1, 256, 0, as_stream(s)>>>(pair_cnt, E, exp_list, n_active);
+  return launch_status("active_list_kernel");
+}
+
 int knj_moe_combine_launch(const float *Y, const int32_t *pair_row, const int32_t *pair_exp, const float *pair_w,
                            const void *resid, int resid_dtype, int64_t ld_resid, void *out, int out_dtype, int64_t ldo,
                            int T, int H, int k, knj_stream_t s) {

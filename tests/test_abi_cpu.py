@@ -56,10 +56,13 @@ def test_null_and_geometry_refusals(L):
     assert L.knj_control_launch(None, 1, 64, 1, None) == -1
     assert L.knj_gemm_w4_i8_launch(None, None, None, None, 1, 1, 128, 64, 1, None) == -1
     assert L.knj_q4k_dequant_launch(None, None, 1, None) == -1
+    assert L.knj_q4k_dequant_launch(None, None, 0, None) == 0
     assert L.knj_router_topk_launch(None, 0, 0, None, None, 1, 256, 8, 2, None, None, None, None) == -1
     assert L.knj_moe_ffn_decode_launch(None, None) == -1
     from kanjoos_b200._lib import MoeFfnArgs
     a = MoeFfnArgs()
+    assert L.knj_moe_ffn_decode_launch(C.byref(a), None) == 0  # zero tokens: nothing to do, nothing to validate
+    a.n_tokens = 1
     assert L.knj_moe_ffn_decode_launch(C.byref(a), None) == -1
     assert b"null tensor pointer" in L.knj_last_error_string()
     one = C.c_void_p(4096)  # never dereferenced: validation fails first

@@ -25,7 +25,7 @@ def test_w4_known_answer(golden, M, N, K):
     asum = ops.build_asum(d_act, M, K).cpu().numpy()
     want_asum = A.reshape(M, K // 128, 128).astype(np.int32).sum(-1)
     assert np.array_equal(asum, want_asum), "Asum differs from the host sums"
-    got = ops.gemm_w4_i8(dev(Bq), d_act, dev(want_asum), M, N, K).cpu().numpy()
+    got = ops.gemm_w4_i8(dev(Bq), d_act, dev(want_asum.astype(np.int32)), M, N, K).cpu().numpy()
     want = np.empty((M, N), np.float32)
     o.knj_or_gemm_w4_reference(ol.ptr(Bq, ol.u8p), ol.ptr(A, ol.i8p), ol.ptr(want, ol.f32p), M, N, K)
     if (M, N, K) == (32, 768, 2048):
