@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4_K MoE-FFN path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                    [--tokens T] [--routing uniform|zipf] [--no-decode]
+
+Workload (all N): the expert-parallel MoE layer of the benchmark configs --
+Qwen3-30B-A3B geometry (hidden 2048, ffn 768, 128 experts, top-8), T tokens per
+step (default 4096, bf16 ~ N(0,1)), random-init Q4_K experts split evenly over
+the N GPUs, token dispatch/combine by all-to-all when N > 1. One step = one pass
+of the layer over the T tokens; value = tokens/s of the whole job. Total work is
+fixed as N grows ("strong" scaling). Successive steps rotate over several
+distinct weight banks so the weights a step reads never sit in L2 from the step
+before. At N = 1 the line also carries the decode numbers (48-layer resident
+stack, batch 1/8/64) with their HBM roofline, and a CPU baseline.
+
+--impl reference times the reference's own CPU code for the same layer
+(oracle/_ref when present, else the C restatement) on the host cores, on a
+bounded sample of the workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, F, E, TOPK, LAYERS = 2048, 768, 128, 8, 48
+EXPERT_BYTES = 3 * F * (H // 256) * 144  # 2,654,208
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["_source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["_source"] = "fallback"
+    return p
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons during the timed region."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=3)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- reference arm
+
+def cpu_layer_tokens_per_s(sample_tokens: int, steps: int, warmup: int, routing: str):
+    """The reference's CPU MoE layer on a bounded sample of the workload."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    from kanjoos_b200 import synth
+    bank = synth.expert_bank(5)
+    wr, bias = synth.router_weight(5, zipf_s=1.1 if routing == "zipf" else None)
+    hx = synth.hidden_rows(5, sample_tokens)
+    r = ol.ref()
+    out = np.empty((sample_tokens, H), np.float32)
+    if r is not None:
+        kind, cores = "reference", r.ref_hardware_threads()
+
+        def run():
+            r.ref_moe(ol.ptr(wr, ol.u16p), ol.ptr(bank["gate"], ol.u8p), ol.ptr(bank["up"], ol.u8p),
+                      ol.ptr(bank["down"], ol.u8p), ol.ptr(hx, ol.f32p), sample_tokens, H, E, TOPK, F,
+                      ol.ptr(out, ol.f32p), None, None, cores)
+    else:
+        kind, cores = "port", ol.oracle().knj_or_num_threads()
+
+        def run():
+            ol.moe(wr, bank, hx, TOPK)
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": sample_tokens / dt, "unit": "tokens/s", "cores": int(cores), "kind": kind,
+            "sample": f"{sample_tokens} tokens of the layer per step (uniform router; the CPU path has no bias input), "
+                      f"{steps} steps, wall clock"}, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cb, dt = cpu_layer_tokens_per_s(args.cpu_sample, max(1, min(args.steps, 5)), min(args.warmup, 1), args.routing)
+    line = {"impl": "reference", "metric": "moe_ffn_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": workload_config(args, 1), "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(args, world):
+    return {"workload": f"ep_moe_layer_T{args.tokens}_{args.routing}", "hidden": H, "ffn": F, "experts": E,
+            "top_k": TOPK, "tokens_per_step": args.tokens, "experts_per_gpu": E // world, "weight_format": "GGUF Q4_K",
+            "l2_policy": "inputs larger than L2: steps rotate over distinct weight banks",
+            "parallelism": f"ep{world}"}
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def decode_section(torch, steps, warmup, pk):
+    """48-layer resident stack, batch 1/8/64: tokens/s and HBM roofline of the decode path."""
+    from kanjoos_b200.moe import ExpertBank, MoeStack
+    banks = [ExpertBank.random(seed=1000 + l) for l in range(LAYERS)]
+    out = {"layers": LAYERS, "resident_weight_gib": round(LAYERS * E * EXPERT_BYTES / 2**30, 2), "batches": {}}
+    for B in (1, 8, 64):
+        stack = MoeStack(banks, top_k=TOPK, max_tokens=B)
+        g = torch.Generator(device="cuda")
+        g.manual_seed(B)
+        x = torch.randn((B, H), device="cuda", generator=g).to(torch.bfloat16)
+        # distinct experts per layer for this input (untimed pass with routing taps)
+        distinct = 0
+        cur = x
+        bufs = (torch.empty_like(x), torch.empty_like(x))
+        for i, layer in enumerate(stack.layers):
+            o, pe, _ = layer.decode(cur, out=bufs[i & 1], return_routing=True)
+            distinct += int(torch.unique(pe).numel())
+            cur = o
+        graph, _ = stack.capture(x)
+        for _ in range(max(3, warmup)):
+            graph.replay()
+        torch.cuda.synchronize()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        ev[0].record()
+        for _ in range(steps):
+            graph.replay()
+        ev[1].record()
+        torch.cuda.synchronize()
+        ms = ev[0].elapsed_time(ev[1]) / steps
+        alg = distinct * EXPERT_BYTES + LAYERS * (E * H * 2 + H * 2 + B * H * 2 * 2)
+        out["batches"][str(B)] = {"tokens_per_s": B / (ms * 1e-3), "ms_per_step": ms,
+                                  "distinct_experts_per_layer": distinct / LAYERS, "algorithmic_bytes": alg,
+                                  "hbm_gbs": alg / (ms * 1e-3) / 1e9,
+                                  "frac_of_" + pk["_source"]: alg / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+        del stack, graph
+    del banks
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from kanjoos_b200 import _lib, ops
+    from kanjoos_b200.ep import CudaCompute, EpMoeLayer
+    from kanjoos_b200.moe import ExpertBank, MoeFfnLayer
+    _lib.check(_lib.lib().knj_dev_open(local))
+    pk = peaks()
+
+    T = args.tokens
+    assert T % world == 0 and E % world == 0
+    T_loc, e_loc = T // world, E // world
+    bank_bytes = e_loc * EXPERT_BYTES
+    n_banks = max(2, math.ceil(400e6 / bank_bytes))
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    router = (torch.randn((E, H), device="cuda", generator=g) * 0.02).to(torch.bfloat16)
+    bias = None
+    if args.routing == "zipf":
+        p = torch.arange(1, E + 1, dtype=torch.float64) ** -1.1
+        perm = torch.randperm(E, generator=torch.Generator().manual_seed(3))
+        b = torch.empty(E, dtype=torch.float32)
+        b[perm] = torch.log(p / p.sum()).float()
+        bias = b.cuda()
+    banks = []
+    for i in range(n_banks):
+        bk = ExpertBank.random(n_experts=e_loc, seed=100 + 17 * i + 1000 * rank, with_norm=False)
+        bk.router, bk.router_bias = router, bias
+        banks.append(bk)
+    gx = torch.Generator(device="cuda")
+    gx.manual_seed(11 + rank)
+    x = torch.randn((T_loc, H), device="cuda", generator=gx).to(torch.bfloat16)
+    out = torch.empty((T_loc, H), dtype=torch.bfloat16, device="cuda")
+
+    if world == 1:
+        layers = [MoeFfnLayer(bk, top_k=TOPK, max_tokens=T_loc, use_norm=False) for bk in banks[:1]]
+        ws = layers[0].workspace
+        layers += [MoeFfnLayer(bk, top_k=TOPK, max_tokens=T_loc, use_norm=False, workspace=ws) for bk in banks[1:]]
+
+        def step(i, xin=x):
+            layers[i % n_banks].prefill(xin, out=out)
+    else:
+        cp = CudaCompute(router, TOPK, bias)
+        eps = [EpMoeLayer(bk, E, cp, None, TOPK) for bk in banks]
+
+        def step(i, xin=x):
+            out.copy_(eps[i % n_banks].forward(xin, out_dtype=torch.bfloat16))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    W = max(3, args.warmup)
+    for i in range(W):
+        step(i)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        step(W + i)
+    e1.record()
+    barrier()
+    ms_step = e0.elapsed_time(e1) / args.steps
+
+    # end to end: pinned host rows in, bf16 result rows out, copies inside the timed region
+    hx = torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory()
+    hx.copy_(x.cpu())
+    hout = torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory()
+    xin = torch.empty_like(x)
+
+    def e2e_step(i):
+        xin.copy_(hx, non_blocking=True)
+        step(i, xin)
+        hout.copy_(out, non_blocking=True)
+
+    for i in range(2):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(W + i)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+
+    t = torch.tensor([ms_step, ms_e2e], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step, ms_e2e = t.tolist()
+
+    # dominant kernel alone (rank 0): gate+up grouped product on this rank's rows, CUDA events on its stream
+    roof = None
+    if rank == 0:
+        _, pe, _ = ops.router_topk(x, router, TOPK, bias)
+        own = (pe // e_loc) == 0 if world > 1 else torch.ones_like(pe, dtype=torch.bool)
+        rows = int(own.sum().item()) if world > 1 else T_loc * TOPK
+        # plan over this rank's experts only, tokens from the local shard stand in for received rows
+        pe_loc = torch.where(own, pe % e_loc, torch.full_like(pe, -1)) if world > 1 else pe
+        pair_idx, pair_cnt, exp_list, n_active = ops.moe_permute(pe_loc.contiguous(), e_loc, T_loc * TOPK)
+        xp = ops.act_prep(x)
+        A = torch.empty((T_loc * TOPK, F), dtype=torch.float32, device="cuda")
+        import ctypes as C
+
+        def gateup(i):
+            bk = banks[i % n_banks]
+            _lib.check(_lib.lib().knj_q4k_gateup_launch(
+                C.c_void_p(xp.data_ptr()), C.c_void_p(bk.gate.data_ptr()), C.c_void_p(bk.up.data_ptr()),
+                C.c_void_p(pair_idx.data_ptr()), C.c_void_p(pair_cnt.data_ptr()), None, C.c_void_p(exp_list.data_ptr()),
+                C.c_void_p(n_active.data_ptr()), None, None, C.c_void_p(A.data_ptr()), F, H, (H // 256) * 144,
+                pair_idx.shape[1], e_loc, TOPK, T_loc, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        for i in range(3):
+            gateup(i)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(args.steps):
+            gateup(3 + i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_k = e0.elapsed_time(e1) / args.steps
+        flops = rows * 2 * 2 * H * F
+        t_tensor = flops / (pk["bf16_tflops"] * 1e12)
+        roof = {"kernel": "q4k gate+up grouped product", "bound": "tensor", "achieved": flops / (ms_k * 1e-3) / 1e12,
+                "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": flops / (ms_k * 1e-3) / 1e12 / pk["bf16_tflops"],
+                "peak_source": pk["_source"], "traffic": None, "ms_per_launch": ms_k,
+                "algorithmic_flops_per_launch": flops,
+                "weight_bytes_per_launch": int((pair_cnt > 0).sum().item()) * 2 * F * (H // 256) * 144,
+                "t_tensor_ms": t_tensor * 1e3}
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    cb = None
+    dec = None
+    if world == 1:
+        cb, _ = cpu_layer_tokens_per_s(args.cpu_sample, 1, 1, "uniform")
+        if not args.no_decode:
+            del banks, layers
+            torch.cuda.empty_cache()
+            dec = decode_section(torch, max(5, args.steps), args.warmup, pk)
+
+    launches = 9 if world == 1 else 13
+    line = {"metric": "moe_ffn_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "f32 accumulate over Q4_K codes x fp16-split activations", "data": "synthetic",
+            "config": workload_config(args, world), "clocks": clocks,
+            "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T_loc * H * 2 * world,
+                    "d2h_bytes_per_step": T_loc * H * 2 * world, "ms_per_step": ms_e2e},
+            "gpu_launches": launches * args.steps, "roofline": roof, "cpu_baseline": cb, "decode": dec,
+            "flops_per_step": T * TOPK * 3 * 2 * H * F + 2 * T * H * E}
+    print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
+    ap.add_argument("--cpu-sample", type=int, default=128, dest="cpu_sample")
+    ap.add_argument("--no-decode", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -254,6 +254,32 @@ int knj_q4k_matmul_launch(const uint8_t *W, int n_in, int n_out, const void *x, 
                           float *y, int64_t ldy, void *workspace, size_t workspace_bytes, knj_stream_t s);
 
 /* ======================================================================== */
+/* Expert projections, prefill class (tcgen05, <= 1e-3)                      */
+/* ======================================================================== */
+
+/* x [rows][K] (f32/bf16/f16, row stride ldx) -> dense fp16 [rows][K], values
+ * saturated to the fp16 range: the token operand of the grouped GEMMs. */
+int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s);
+
+/* Grouped gate+up GEMM over per-expert token buckets on the tensor cores
+ * (tools/bench/q4k_moe_ffn.hip:164-241 knj_q4k_gateup fused with
+ * tools/bench/q4k_stream_ffn.hip:1021-1031 knj_fuse_gateup_silu): for every
+ * pair p of expert e, A[p][n] = silu(x[tok(p)].Wg[e][n]) * (x[tok(p)].Wu[e][n]),
+ * stored as fp16 scaled by 2^-6 (saturating). Xh fp16 [T][K]; tok(p) =
+ * pair_tok[p] when given, else p / top_k. N % 128 == 0. max_pairs bounds the
+ * launch grid (the total number of pairs). status (optional device int) is set
+ * to 1 if a bounded wait inside the kernel gave up. */
+int knj_q4k_gateup_tc_launch(const void *Xh, const uint8_t *Wg, const uint8_t *Wu, const int32_t *pair_idx,
+                             const int32_t *pair_cnt, const int32_t *pair_tok, void *A_f16, int N, int K, int rowBytes,
+                             int64_t idxStride, int n_experts, int top_k, int max_pairs, int *status, knj_stream_t s);
+/* Grouped down GEMM (tools/bench/q4k_stream_ffn.hip:780-829 knj_q6k_down with
+ * dq4 = 1): Y[p][n] = 2^6 * (A[row(p)] . Wd[e][n]), A fp16 as written by the
+ * gate+up kernel, Y f32 [P][N]; row(p) = pair_row[p] when given, else p. */
+int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pair_idx, const int32_t *pair_cnt,
+                           const int32_t *pair_row, float *Y, int N, int K, int rowBytes, int64_t idxStride,
+                           int n_experts, int max_pairs, int *status, knj_stream_t s);
+
+/* ======================================================================== */
 /* Whole MoE-FFN layer (src/model/model.cpp:399-510 Model::moe)             */
 /* ======================================================================== */
 
@@ -280,14 +306,14 @@ typedef struct knj_moe_ffn_args {
   float *tap_pair_w;         /* [T*k] */
 } knj_moe_ffn_args;
 
-/* mode 0 = decode class (any T, f32-accurate kernels), 1 = prefill class. */
+/* mode 0 = decode class (knj_moe_ffn_decode_launch), 1 = prefill class. */
 size_t knj_moe_ffn_workspace_bytes(int n_tokens, int hidden, int ffn, int n_experts, int top_k, int mode);
 
 /* Decode: batch <= 64 tokens, HBM-bound, f32-accurate (<= 1e-5 rel-RMSE vs the
  * CPU path). Larger T is accepted and stays exact, at decode-class speed. */
 int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s);
-/* Prefill: tokens bucketed per expert, bf16 operands on tcgen05 with f32 TMEM
- * accumulators (<= 1e-3 rel-RMSE vs the CPU path). */
+/* Prefill: tokens bucketed per expert, Q4_K unpacked to fp16 operands for
+ * tcgen05.mma with f32 TMEM accumulators (<= 1e-3 rel-RMSE vs the CPU path). */
 int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
 
 /* ======================================================================== */

@@ -95,6 +95,9 @@ SIGNATURES = {
     "knj_q4k_gateup_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i,
                                    _i, _vp]),
     "knj_q4k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp]),
+    "knj_to_f16_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
+    "knj_q4k_gateup_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp]),
+    "knj_q4k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),
     "knj_fuse_gateup_silu_launch": (_i, [_vp, _vp, _vp, _i, _i64, _vp]),
     "knj_q4k_matmul_workspace_bytes": (_sz, [_i, _i]),
     "knj_q4k_matmul_launch": (_i, [_vp, _i, _i, _vp, _i, _i64, _i, _vp, _i64, _vp, _sz, _vp]),

@@ -68,14 +68,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: every spin in this library gives up after a fixed number of
-// polls (each poll itself blocks for a hardware-chosen interval), so a copy
-// that never lands cannot hang the GPU. Returns false on give-up.
-constexpr uint32_t kMaxPolls = 1u << 22;
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kMaxPolls; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
+// Bounded wait: every spin in this library gives up after about a second of
+// SM clock (2^31 cycles), so a copy or an MMA that never completes cannot hang
+// the GPU. Returns false on give-up. `abort_flag` (optional, shared memory) lets
+// the threads of a CTA leave together: the first one to give up raises it and
+// the others stop waiting as soon as they see it.
+constexpr long long kMaxWaitCycles = 1ll << 31;
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag = nullptr) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (abort_flag && *abort_flag) return false;
+    if (clock64() - t0 > kMaxWaitCycles) {
+      if (abort_flag) *abort_flag = 1;
+      return false;
+    }
+  }
 }
 
 // Bulk async copy global -> shared of `bytes` (multiple of 16, both addresses

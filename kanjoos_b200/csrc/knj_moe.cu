@@ -51,6 +51,33 @@ DecodeWs carve_decode(void *base, int T, int H, int F, int E, int k) {
   return w;
 }
 
+struct PrefillWs {
+  float *xn, *logits, *pair_w, *Y;
+  int32_t *pair_exp, *pair_idx, *pair_cnt, *exp_list, *n_active, *status;
+  void *xh, *ah;
+  size_t bytes;
+};
+
+PrefillWs carve_prefill(void *base, int T, int H, int F, int E, int k) {
+  Carve c(base);
+  PrefillWs w;
+  const size_t P = (size_t)T * k;
+  w.xn = c.take<float>((size_t)T * H * 4);
+  w.logits = c.take<float>((size_t)T * E * 4);
+  w.pair_exp = c.take<int32_t>(P * 4);
+  w.pair_w = c.take<float>(P * 4);
+  w.pair_idx = c.take<int32_t>((size_t)E * T * 4);
+  w.pair_cnt = c.take<int32_t>((size_t)E * 4);
+  w.exp_list = c.take<int32_t>((size_t)E * 4);
+  w.n_active = c.take<int32_t>(16);
+  w.status = c.take<int32_t>(16);
+  w.xh = c.take<void>((size_t)T * H * 2);
+  w.ah = c.take<void>(P * F * 2);
+  w.Y = c.take<float>(P * H * 4);
+  w.bytes = c.used;
+  return w;
+}
+
 int check_args(const knj_moe_ffn_args *a, const char *who) {
   KNJ_REQUIRE(a, "%s: null argument block", who);
   KNJ_REQUIRE(a->x && a->w_router && a->w_gate && a->w_up && a->w_down && a->out, "%s: null tensor pointer", who);
@@ -72,8 +99,8 @@ int check_args(const knj_moe_ffn_args *a, const char *who) {
 extern "C" {
 
 size_t knj_moe_ffn_workspace_bytes(int n_tokens, int hidden, int ffn, int n_experts, int top_k, int mode) {
-  (void)mode;
   if (n_tokens <= 0) return 256;
+  if (mode == 1) return carve_prefill(nullptr, n_tokens, hidden, ffn, n_experts, top_k).bytes;
   return carve_decode(nullptr, n_tokens, hidden, ffn, n_experts, top_k).bytes;
 }
 
@@ -128,8 +155,47 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
                                 a->out, a->out_dtype, a->ldo, T, H, k, s);
 }
 
-// Until the tcgen05 grouped GEMM is wired in, the prefill entry runs the same
-// exact pipeline (f32-accurate, decode-class speed).
-int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) { return knj_moe_ffn_decode_launch(a, s); }
+int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
+  if (a && a->n_tokens == 0) return KNJ_OK;
+  int rc = check_args(a, "knj_moe_ffn_prefill");
+  if (rc) return rc;
+  const int T = a->n_tokens, H = a->hidden, F = a->ffn, E = a->n_experts, k = a->top_k;
+  KNJ_REQUIRE(H % 128 == 0 && F % 128 == 0, "knj_moe_ffn_prefill: hidden and ffn must be multiples of 128");
+  const size_t need = knj_moe_ffn_workspace_bytes(T, H, F, E, k, 1);
+  if (!a->workspace || a->workspace_bytes < need) {
+    set_error("knj_moe_ffn_prefill: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
+    return KNJ_E_WORKSPACE;
+  }
+  KNJ_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0, "knj_moe_ffn_prefill: workspace must be 256-byte aligned");
+  const PrefillWs w = carve_prefill(a->workspace, T, H, F, E, k);
+  const int P = T * k;
+
+  const void *src = a->x;
+  int src_dt = a->x_dtype;
+  int64_t src_ld = a->ldx;
+  if (a->norm_w) {
+    rc = knj_rmsnorm_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, T, H, w.xn, s);
+    if (rc) return rc;
+    src = w.xn;
+    src_dt = KNJ_DT_F32;
+    src_ld = H;
+  }
+  int32_t *pair_exp = a->tap_pair_exp ? a->tap_pair_exp : w.pair_exp;
+  float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
+  rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
+  if (rc) return rc;
+  rc = knj_moe_permute_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, s);
+  if (rc) return rc;
+  rc = knj_to_f16_launch(src, src_dt, src_ld, T, H, w.xh, s);
+  if (rc) return rc;
+  rc = knj_q4k_gateup_tc_launch(w.xh, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.ah, F, H,
+                                H / 256 * KNJ_Q4K_BYTES, T, E, k, P, w.status, s);
+  if (rc) return rc;
+  rc = knj_q4k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, E,
+                              P, w.status, s);
+  if (rc) return rc;
+  return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
+                                a->out, a->out_dtype, a->ldo, T, H, k, s);
+}
 
 }  // extern "C"

@@ -1,0 +1,428 @@
+// knj_prefill_tc.cu -- prefill-class grouped expert GEMM on the 5th-generation
+// tensor cores: Q4_K weights are unpacked to fp16 in shared memory and consumed
+// by tcgen05.mma with f32 accumulators in tensor memory.
+//
+// Roles (swap-AB): the MMA "M" side is 128 weight rows of one expert, the "N"
+// side is a bucket of up to 256 routed tokens, K runs over the hidden (or ffn)
+// dimension in slabs of 64. Per CTA one (expert, 128-row tile, token bucket):
+//   warps 0..7  producers: per-row bulk async copies bring the raw 144-byte
+//               superblocks into a staging buffer (one copy per row and
+//               superblock, contiguous in HBM); each slab they rebuild
+//               w = (d*sc)*q - dmin*m in fp16 and store it into the K-major
+//               128-byte-swizzled operand tile, and they gather the token rows
+//               of the slab into the second operand tile;
+//   warp 8      one elected thread issues tcgen05.mma (kind::f16, 128 x N x 16)
+//               over the four 16-wide steps of a slab and commits the stage
+//               back to the producers through an mbarrier;
+//   warps 0..7  epilogue: tcgen05.ld of the accumulators (lane = weight row,
+//               column = token), SiLU(gate)*up or the plain projection, stores.
+// Gate and up share the token operand: two accumulators (columns [0,256) and
+// [256,512)) are fed from two weight tiles per slab.
+//
+// Precision. Operands are fp16, not bf16: a Q4_K weight rounded to fp16 is off
+// by <= 2^-12 relative, which keeps the layer's relative RMSE well inside the
+// 1e-3 budget of the tensor-core path; bf16 operands (2^-9) would not. The
+// activations are converted to fp16 beforehand with a saturating convert, and
+// the SiLU*up intermediate is stored as fp16 after a fixed 2^-6 prescale
+// (undone in the down epilogue), which holds magnitudes up to 4.1e6.
+//
+// Every wait on an mbarrier is bounded; on give-up the kernel raises a status
+// flag, still frees its tensor memory and returns.
+#include "knj_common.cuh"
+#include "knj_q4k.h"
+
+using namespace knj;
+
+namespace {
+
+constexpr int kRowsM = 128;        // weight rows per tile (MMA M)
+constexpr int kMaxTok = 256;       // token bucket (MMA N upper bound)
+constexpr int kSlabK = 64;         // K elements per pipeline stage (one 128-byte swizzle row)
+constexpr int kStages = 2;         // operand stages
+constexpr int kProducerThreads = 256;
+constexpr int kThreads = kProducerThreads + 32;
+constexpr float kActPrescale = 0.015625f;  // 2^-6
+
+struct TcParams {
+  const __half *X;        // activation rows, fp16 [rows][K]
+  const uint8_t *W0;      // gate or the single matrix, Q4_K [E][N][K/256][144]
+  const uint8_t *W1;      // up (dual) or null
+  const int32_t *pair_idx;
+  const int32_t *pair_cnt;
+  const int32_t *row_map;  // pair -> activation row (null: pair / row_div)
+  void *out;               // dual: fp16 act [P][N]; single: f32 Y [P][N]
+  int N, K, rowBytes, row_div, n_experts, m_tiles;
+  int64_t idxStride;
+  float out_scale;
+  int *status;
+};
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D(tmem) (+)= A(smem desc) * B(smem desc), fp16 operands, f32 accumulate
+__device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                           uint32_t accumulate) {
+  const uint32_t zero = 0;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero), "r"(zero), "r"(zero), "r"(zero)
+      : "memory");
+}
+// 16 consecutive f32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// K-major, 128-byte swizzle, rows of 64 fp16 (128 bytes), 8-row groups 1024
+// bytes apart: start address, LBO (unused for swizzled K-major) = 1, SBO = 64
+// (1024 >> 4), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)64 << 32) | ((uint64_t)1 << 46) |
+         ((uint64_t)2 << 61);
+}
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128
+__device__ __forceinline__ uint32_t instr_desc_f16(int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRowsM >> 4) << 24);
+}
+
+__device__ __forceinline__ void producer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); }
+
+template <int NMAT>
+struct Smem {
+  // operand tiles: 1024-byte aligned for the swizzle pattern
+  static constexpr int kATile = kRowsM * 128;    // 16 KB per matrix per stage
+  static constexpr int kBTile = kMaxTok * 128;   // 32 KB per stage
+  static constexpr int kRawBuf = NMAT * kRowsM * KNJ_Q4K_BYTES;
+  static constexpr int kOffA = 0;
+  static constexpr int kOffB = kOffA + kStages * NMAT * kATile;
+  static constexpr int kOffRaw = kOffB + kStages * kBTile;
+  static constexpr int kOffPairs = kOffRaw + 2 * kRawBuf;       // int32 pair id per token of the bucket
+  static constexpr int kOffRows = kOffPairs + kMaxTok * 4;      // int32 activation row per token
+  static constexpr int kOffBars = kOffRows + kMaxTok * 4;       // mbarriers
+  static constexpr int kBytes = kOffBars + 128 + 1024;          // + alignment slack
+};
+
+template <int NMAT>
+__global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcParams p) {
+  using S = Smem<NMAT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- which (expert, token bucket) is this CTA's? scan the counts (E <= 256)
+  const int m_tile = blockIdx.x % p.m_tiles;
+  int want = blockIdx.x / p.m_tiles;
+  int e = -1, tok0 = 0, cnt = 0;
+  for (int i = 0; i < p.n_experts; ++i) {
+    const int c = p.pair_cnt[i];
+    const int nt = (c + kMaxTok - 1) / kMaxTok;
+    if (want < nt) { e = i; tok0 = want * kMaxTok; cnt = c; break; }
+    want -= nt;
+  }
+  if (e < 0) return;  // uniform across the CTA: nothing allocated yet
+  const int ntok = min(kMaxTok, cnt - tok0);
+  const int n_mma = (ntok + 15) & ~15;  // MMA N: multiple of 16
+  const int m0 = m_tile * kRowsM;
+  const int nsb = p.K / KNJ_QK_K, nslab = p.K / kSlabK;
+
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kOffBars);
+  uint64_t *full = bars;               // [kStages] producers -> MMA
+  uint64_t *empty = bars + kStages;    // [kStages] MMA -> producers
+  uint64_t *raw_full = bars + 2 * kStages;  // [2] bulk copies landed
+  uint64_t *acc_full = bars + 2 * kStages + 2;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 3);
+  volatile int *s_fail = reinterpret_cast<volatile int *>(tmem_slot + 1);  // raised by the first wait that gives up
+  int32_t *s_pair = reinterpret_cast<int32_t *>(smem + S::kOffPairs);
+  int32_t *s_row = reinterpret_cast<int32_t *>(smem + S::kOffRows);
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], kProducerThreads); mbar_init(&empty[s], 1); }
+    mbar_init(&raw_full[0], NMAT * kRowsM);
+    mbar_init(&raw_full[1], NMAT * kRowsM);
+    mbar_init(acc_full, 1);
+    *s_fail = 0;
+    mbar_init_fence();
+  }
+  for (int i = tid; i < kMaxTok; i += kThreads) {
+    int pr = -1, rw = -1;
+    if (i < ntok) {
+      pr = p.pair_idx[(size_t)e * p.idxStride + tok0 + i];
+      rw = p.row_map ? p.row_map[pr] : pr / p.row_div;
+    }
+    s_pair[i] = pr;
+    s_row[i] = rw;
+  }
+  constexpr uint32_t kTmemCols = NMAT == 2 ? 512 : 256;
+  if (warp == 8) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;  // once false this thread skips all work and waits but still meets every barrier
+
+  if (warp < 8) {
+    // =========================== producers ===========================
+    const int row = tid & 127, half = tid >> 7;  // weight row, which 16 of the slab's 32 code bytes
+    auto issue_raw = [&](int b) {
+      if (tid < NMAT * kRowsM) {
+        const int mat = tid >> 7;
+        const uint8_t *src = (mat == 0 ? p.W0 : p.W1) + ((size_t)e * p.N + m0 + row) * p.rowBytes + (size_t)b * KNJ_Q4K_BYTES;
+        uint8_t *dst = smem + S::kOffRaw + (b & 1) * S::kRawBuf + (mat * kRowsM + row) * KNJ_Q4K_BYTES;
+        mbar_expect_tx(&raw_full[b & 1], KNJ_Q4K_BYTES);
+        bulk_g2s(dst, src, KNJ_Q4K_BYTES, &raw_full[b & 1]);
+      }
+    };
+    fence_proxy_async();
+    issue_raw(0);
+    for (int b = 0; b < nsb; ++b) {
+      // everyone is done reading the buffer the next superblock lands in
+      producer_sync();
+      if (*s_fail) ok = false;
+      if (!ok) continue;
+      if (b + 1 < nsb) {
+        fence_proxy_async();
+        issue_raw(b + 1);
+      }
+      if (!mbar_wait(&raw_full[b & 1], (b >> 1) & 1, s_fail)) { ok = false; continue; }
+      const uint8_t *raw = smem + S::kOffRaw + (b & 1) * S::kRawBuf;
+
+      for (int G = 0; G < 4 && ok; ++G) {
+        const int ks = b * 4 + G, stage = ks % kStages;
+        if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
+        tc_fence_after();
+
+        // ---- token operand: rows of 64 fp16, 16-byte chunk c of row r stored at chunk c ^ (r & 7)
+        {
+          uint8_t *bt = smem + S::kOffB + stage * S::kBTile;
+          const int c = tid & 7;
+#pragma unroll
+          for (int j = 0; j < kMaxTok / 32; ++j) {
+            const int r = (tid >> 3) + 32 * j;
+            if (r < n_mma) {
+              uint4 v = make_uint4(0u, 0u, 0u, 0u);
+              const int xr = s_row[r];
+              if (xr >= 0) v = __ldg(reinterpret_cast<const uint4 *>(p.X + (size_t)xr * p.K + ks * kSlabK + c * 8));
+              *reinterpret_cast<uint4 *>(bt + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+            }
+          }
+        }
+        // ---- weight operand(s): 16 code bytes -> 16 low-nibble + 16 high-nibble weights of this row
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+          const uint8_t *blk = raw + (mat * kRowsM + row) * KNJ_Q4K_BYTES;
+          const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
+          const uint4 q = *reinterpret_cast<const uint4 *>(blk + KNJ_Q4K_OFF_QS + 32 * G + 16 * half);
+          const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+          const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+          // 6-bit scale / min of sub-blocks 2G (low nibbles) and 2G+1 (high nibbles)
+          uint32_t sc[2], mn[2];
+#pragma unroll
+          for (int par = 0; par < 2; ++par) {
+            const int j = 2 * G + par;
+            if (j < 4) {
+              sc[par] = (hdr.y >> (8 * j)) & 63u;
+              mn[par] = (hdr.z >> (8 * j)) & 63u;
+            } else {
+              const uint32_t hi = (hdr.w >> (8 * (j - 4))) & 0xffu;
+              sc[par] = (hi & 15u) | ((((hdr.y >> (8 * (j - 4))) & 0xffu) >> 6) << 4);
+              mn[par] = (hi >> 4) | ((((hdr.z >> (8 * (j - 4))) & 0xffu) >> 6) << 4);
+            }
+          }
+          uint8_t *at = smem + S::kOffA + (stage * NMAT + mat) * S::kATile + row * 128;
+          const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+          for (int par = 0; par < 2; ++par) {
+            const __half2 d1 = __float2half2_rn(fminf(d * (float)sc[par], 65504.0f));
+            const __half2 m1 = __float2half2_rn(-(dmin * (float)mn[par]));
+            const __half2 k1024 = __float2half2_rn(1024.0f);
+            uint32_t o[8];
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+              const uint32_t src = par ? (qw[w] >> 4) : qw[w];
+              // bytes 0,2 -> (k, k+2) ; bytes 1,3 -> (k+1, k+3): rebuild consecutive pairs below
+              const uint32_t e02 = (src & 0x000f000fu) | 0x64006400u;         // 1024 + q of bytes 0 and 2
+              const uint32_t e13 = ((src >> 8) & 0x000f000fu) | 0x64006400u;  // bytes 1 and 3
+              __half2 h02 = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&e02), k1024), d1, m1);
+              __half2 h13 = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&e13), k1024), d1, m1);
+              const uint32_t u02 = *reinterpret_cast<uint32_t *>(&h02), u13 = *reinterpret_cast<uint32_t *>(&h13);
+              o[2 * w] = __byte_perm(u02, u13, 0x5410);      // (k0, k1)
+              o[2 * w + 1] = __byte_perm(u02, u13, 0x7632);  // (k2, k3)
+            }
+            // 16 weights = two 16-byte chunks: k_local = 32*par + 16*half + [0,16)
+            const int c0 = 4 * par + 2 * half;
+            *reinterpret_cast<uint4 *>(at + (((c0) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+            *reinterpret_cast<uint4 *>(at + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+          }
+        }
+        fence_proxy_async();
+        mbar_arrive(&full[stage]);
+      }
+    }
+  } else if (lane == 0) {
+    // =========================== MMA issue ===========================
+    const uint32_t idesc = instr_desc_f16(n_mma);
+    for (int ks = 0; ks < nslab && ok; ++ks) {
+      const int stage = ks % kStages;
+      if (!mbar_wait(&full[stage], (ks / kStages) & 1, s_fail)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t b_addr = smem_u32(smem + S::kOffB + stage * S::kBTile);
+#pragma unroll
+      for (int mat = 0; mat < NMAT; ++mat) {
+        const uint32_t a_addr = smem_u32(smem + S::kOffA + (stage * NMAT + mat) * S::kATile);
+#pragma unroll
+        for (int k = 0; k < kSlabK / 16; ++k)
+          tc_mma_f16(tmem_base + mat * kMaxTok, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                     (ks > 0 || k > 0) ? 1u : 0u);
+      }
+      tc_commit(&empty[stage]);
+    }
+    if (ok) tc_commit(acc_full);
+  }
+
+  // =========================== epilogue ===========================
+  if (warp < 8) {
+    if (ok && !mbar_wait(acc_full, 0, s_fail)) ok = false;
+    tc_fence_after();
+    if (ok) {
+      const int lane_base = 32 * (warp & 3);
+      const int n = m0 + lane_base + lane;  // output index of this thread's accumulator row
+      for (int c = (warp >> 2); c * 16 < n_mma; c += 2) {
+        float g[16];
+        tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + c * 16, g);
+        if (NMAT == 2) {
+          float u[16];
+          tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + kMaxTok + c * 16, u);
+          __half *A = static_cast<__half *>(p.out);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int pr = s_pair[c * 16 + j];
+            if (pr >= 0) {
+              const float a = (g[j] / (1.0f + __expf(-g[j]))) * u[j] * p.out_scale;
+              A[(size_t)pr * p.N + n] = __float2half_rn(fminf(fmaxf(a, -65504.0f), 65504.0f));
+            }
+          }
+        } else {
+          float *Y = static_cast<float *>(p.out);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int pr = s_pair[c * 16 + j];
+            if (pr >= 0) Y[(size_t)pr * p.N + n] = g[j] * p.out_scale;
+          }
+        }
+      }
+    }
+  }
+  if (!ok && lane == 0 && p.status) atomicExch(p.status, 1);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+}
+
+// x (f32 / bf16 / f16) -> fp16 with saturation, rows dense
+__global__ void to_f16_kernel(const void *__restrict__ x, int dtype, int64_t ldx, int K, int64_t n, __half *__restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / K, c = i - r * K;
+    const float v = load_as_f32(x, dtype, r * ldx + c);
+    out[i] = __float2half_rn(fminf(fmaxf(v, -65504.0f), 65504.0f));
+  }
+}
+
+template <int NMAT>
+int launch_tc(const TcParams &p, int max_pairs, cudaStream_t st) {
+  using S = Smem<NMAT>;
+  int dev = 0;
+  KNJ_CUDA(cudaGetDevice(&dev));
+  auto kern = q4k_grouped_tc_kernel<NMAT>;
+  static bool opted[64] = {false};
+  if (dev >= 0 && dev < 64 && !opted[dev]) {
+    KNJ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
+    opted[dev] = true;
+  }
+  // worst case number of token buckets: every expert has a ragged tail
+  const long long buckets = (long long)max_pairs / kMaxTok + p.n_experts;
+  const long long grid = buckets * p.m_tiles;
+  KNJ_REQUIRE(grid > 0 && grid < (1ll << 31), "grouped GEMM: grid of %lld CTAs out of range", grid);
+  kern<<<(unsigned)grid, kThreads, S::kBytes, st>>>(p);
+  return launch_status("q4k_grouped_tc_kernel");
+}
+
+}  // namespace
+
+extern "C" {
+
+int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s) {
+  KNJ_REQUIRE(x && out_f16, "knj_to_f16: null pointer");
+  KNJ_REQUIRE(x_dtype >= KNJ_DT_F32 && x_dtype <= KNJ_DT_F16 && K > 0, "knj_to_f16: bad dtype / K");
+  if (rows <= 0) return KNJ_OK;
+  const int64_t n = (int64_t)rows * K;
+  const int64_t blocks = (n + 255) / 256, cap = (int64_t)sm_count() * 16;
+  to_f16_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, as_stream(s)>>>(x, x_dtype, ldx, K, n,
+                                                                                  static_cast<__half *>(out_f16));
+  return launch_status("to_f16_kernel");
+}
+
+int knj_q4k_gateup_tc_launch(const void *Xh, const uint8_t *Wg, const uint8_t *Wu, const int32_t *pair_idx,
+                             const int32_t *pair_cnt, const int32_t *pair_tok, void *A_f16, int N, int K, int rowBytes,
+                             int64_t idxStride, int n_experts, int top_k, int max_pairs, int *status, knj_stream_t s) {
+  KNJ_REQUIRE(Xh && Wg && Wu && pair_idx && pair_cnt && A_f16, "knj_q4k_gateup_tc: null pointer");
+  KNJ_REQUIRE(K > 0 && K % 256 == 0 && rowBytes == K / 256 * KNJ_Q4K_BYTES, "knj_q4k_gateup_tc: rowBytes=%d does not match K=%d",
+              rowBytes, K);
+  KNJ_REQUIRE(N > 0 && N % kRowsM == 0, "knj_q4k_gateup_tc: N=%d must be a multiple of 128", N);
+  KNJ_REQUIRE(aligned16(Wg) && aligned16(Wu) && aligned16(Xh), "knj_q4k_gateup_tc: bases must be 16-byte aligned");
+  KNJ_REQUIRE(n_experts >= 1 && n_experts <= 256 && (pair_tok || top_k >= 1) && max_pairs >= 0,
+              "knj_q4k_gateup_tc: bad expert / pair counts");
+  if (max_pairs == 0) return KNJ_OK;
+  TcParams p{};
+  p.X = static_cast<const __half *>(Xh); p.W0 = Wg; p.W1 = Wu; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
+  p.row_map = pair_tok; p.out = A_f16; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = top_k > 0 ? top_k : 1;
+  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = kActPrescale; p.status = status;
+  return launch_tc<2>(p, max_pairs, as_stream(s));
+}
+
+int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pair_idx, const int32_t *pair_cnt,
+                           const int32_t *pair_row, float *Y, int N, int K, int rowBytes, int64_t idxStride,
+                           int n_experts, int max_pairs, int *status, knj_stream_t s) {
+  KNJ_REQUIRE(Ah && Wd && pair_idx && pair_cnt && Y, "knj_q4k_down_tc: null pointer");
+  KNJ_REQUIRE(K > 0 && K % 256 == 0 && rowBytes == K / 256 * KNJ_Q4K_BYTES, "knj_q4k_down_tc: rowBytes=%d does not match K=%d",
+              rowBytes, K);
+  KNJ_REQUIRE(N > 0 && N % kRowsM == 0, "knj_q4k_down_tc: N=%d must be a multiple of 128", N);
+  KNJ_REQUIRE(aligned16(Wd) && aligned16(Ah), "knj_q4k_down_tc: bases must be 16-byte aligned");
+  KNJ_REQUIRE(n_experts >= 1 && n_experts <= 256 && max_pairs >= 0, "knj_q4k_down_tc: bad expert / pair counts");
+  if (max_pairs == 0) return KNJ_OK;
+  TcParams p{};
+  p.X = static_cast<const __half *>(Ah); p.W0 = Wd; p.W1 = nullptr; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
+  p.row_map = pair_row; p.out = Y; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
+  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status;
+  return launch_tc<1>(p, max_pairs, as_stream(s));
+}
+
+}  // extern "C"

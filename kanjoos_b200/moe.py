@@ -85,7 +85,8 @@ class MoeFfnLayer:
                  use_norm: bool = True, workspace: torch.Tensor | None = None):
         self.bank, self.top_k, self.max_tokens, self.residual = bank, top_k, max_tokens, residual
         self.use_norm = use_norm and bank.norm_w is not None
-        need = lib().knj_moe_ffn_workspace_bytes(max_tokens, bank.hidden, bank.ffn, bank.n_experts, top_k, 0)
+        need = max(lib().knj_moe_ffn_workspace_bytes(max_tokens, bank.hidden, bank.ffn, bank.n_experts, top_k, mode)
+                   for mode in (0, 1))
         if workspace is None:
             workspace = torch.empty(need, dtype=torch.uint8, device=bank.gate.device)
         assert workspace.numel() >= need and workspace.data_ptr() % 256 == 0

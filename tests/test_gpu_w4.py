@@ -31,7 +31,8 @@ def test_w4_known_answer(golden, M, N, K):
     if (M, N, K) == (32, 768, 2048):
         assert np.array_equal(want.view(np.uint32), golden["w4_c"].view(np.uint32))
     st = report(got, want, f"gemm_w4_i8 {M}x{N}x{K}")
-    assert st["unwritten"] == 0 and st["rel_rmse"] <= 2e-3
+    # outputs are scaled integers, so the poison value itself can be a legitimate result
+    assert int(((got == -12345.0) & (want != -12345.0)).sum()) == 0 and st["rel_rmse"] <= 2e-3
     if (M, N, K) == (32, 768, 2048):
         assert st["nonzero"] == st["total"]
     # integer inner sums are exact, so the device equals the integer mirror bit for bit
