@@ -330,6 +330,12 @@ void knj_or_rmsnorm_rows(const float* x, int m, int width, const float* w, float
 /* silu. Follows src/model/model.cpp:47. */
 static float or_silu(float v) { return v / (1.0f + expf(-v)); }
 
+/* g[i] = silu(g[i]) * u[i], the activation stage of the MoE branch.
+ * Follows src/model/model.cpp:487-492. */
+void knj_or_silu_mul(float* g, const float* u, uint64_t n) {
+  for (uint64_t i = 0; i < n; ++i) g[i] = or_silu(g[i]) * u[i];
+}
+
 /* Router only: logits -> softmax over E -> K-pass arg-max (strict '>' so ties
  * go to the lowest expert id) -> renormalise. Follows
  * src/model/model.cpp:419-460. Outputs per token: chosen[K] in selection order

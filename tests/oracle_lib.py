@@ -52,6 +52,7 @@ def oracle() -> C.CDLL:
     lib.knj_or_matmul_q4k.argtypes = [u8p, C.c_int, C.c_int, f32p, C.c_int, C.c_int, f32p, C.c_int]
     lib.knj_or_matmul_plain.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, f32p, C.c_int, C.c_int, f32p, C.c_int]
     lib.knj_or_rmsnorm_rows.argtypes = [f32p, C.c_int, C.c_int, f32p, C.c_float, f32p]
+    lib.knj_or_silu_mul.argtypes = [f32p, f32p, C.c_uint64]
     lib.knj_or_route.argtypes = [C.c_void_p, C.c_int, f32p, C.c_int, C.c_int, C.c_int, C.c_int, f32p, i32p, f32p]
     lib.knj_or_moe.argtypes = [C.c_void_p, C.c_int, u8p, u8p, u8p, f32p, C.c_int, C.c_int, C.c_int, C.c_int,
                                C.c_int, f32p, i32p, f32p]
@@ -149,6 +150,14 @@ def route(Wr, wr_type: int, hx: np.ndarray, E: int, top_k: int = 8):
     oracle().knj_or_route(Wr.ctypes.data_as(C.c_void_p), wr_type, ptr(hx, f32p), m, H, E, top_k,
                           ptr(logits, f32p), ptr(chosen, i32p), ptr(weight, f32p))
     return logits, chosen, weight
+
+
+def silu_mul(g: np.ndarray, u: np.ndarray) -> np.ndarray:
+    """silu(g) * u with the CPU path's own expf (element-wise, f32)."""
+    a = np.ascontiguousarray(g, dtype=np.float32).copy()
+    u = np.ascontiguousarray(u, dtype=np.float32)
+    oracle().knj_or_silu_mul(ptr(a, f32p), ptr(u, f32p), a.size)
+    return a
 
 
 def rmsnorm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
