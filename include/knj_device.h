@@ -253,6 +253,21 @@ size_t knj_q4k_matmul_workspace_bytes(int m, int n_in);
 int knj_q4k_matmul_launch(const uint8_t *W, int n_in, int n_out, const void *x, int x_dtype, int64_t ldx, int m,
                           float *y, int64_t ldy, void *workspace, size_t workspace_bytes, knj_stream_t s);
 
+/* Allocation-free form of knj_q4k_matmul_launch. No counterpart in the
+ * reference: it exists for callers that may not allocate device memory when
+ * they call and have no workspace to lend (a serving loop whose pool is fully
+ * committed to resident experts, a plug-in host that only receives input and
+ * output buffers, start-up-only allocation policies). Scratch is a fixed array
+ * inside the library image, knj_q4k_matmul_noalloc_max_scratch() bytes (1 MiB),
+ * held by every GPU that loads the library until the process exits. Returns
+ * KNJ_E_WORKSPACE when knj_q4k_matmul_workspace_bytes(m, n_in) exceeds it. All
+ * calls on a device share the array: calls that overlap on the GPU race and must
+ * be serialised by the caller. The first call on a device resolves the array's
+ * address; make it before any stream capture begins. Calls no allocator. */
+size_t knj_q4k_matmul_noalloc_max_scratch(void);
+int knj_q4k_matmul_noalloc_launch(const uint8_t *W, int n_in, int n_out, const void *x, int x_dtype, int64_t ldx, int m,
+                                  float *y, int64_t ldy, knj_stream_t s);
+
 /* ======================================================================== */
 /* Expert projections, prefill class (tcgen05, <= 1e-3)                      */
 /* ======================================================================== */

@@ -101,6 +101,8 @@ SIGNATURES = {
     "knj_fuse_gateup_silu_launch": (_i, [_vp, _vp, _vp, _i, _i64, _vp]),
     "knj_q4k_matmul_workspace_bytes": (_sz, [_i, _i]),
     "knj_q4k_matmul_launch": (_i, [_vp, _i, _i, _vp, _i, _i64, _i, _vp, _i64, _vp, _sz, _vp]),
+    "knj_q4k_matmul_noalloc_max_scratch": (_sz, []),
+    "knj_q4k_matmul_noalloc_launch": (_i, [_vp, _i, _i, _vp, _i, _i64, _i, _vp, _i64, _vp]),
     "knj_moe_ffn_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "knj_moe_ffn_decode_launch": (_i, [C.POINTER(MoeFfnArgs), _vp]),
     "knj_moe_ffn_prefill_launch": (_i, [C.POINTER(MoeFfnArgs), _vp]),

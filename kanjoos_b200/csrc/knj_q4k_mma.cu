@@ -424,4 +424,67 @@ int knj_q4k_matmul_launch(const uint8_t *W, int n_in, int n_out, const void *x, 
                              n_in / 256 * KNJ_Q4K_BYTES, m, 1, m, s);
 }
 
+// ---------------------------------------------------------------------------
+// Allocation-free variant of knj_q4k_matmul_launch.
+//
+// Who needs it: callers that must not allocate device memory at the point of
+// the call and have no workspace to hand over -- code running inside a
+// latency-critical serving loop whose memory pool is fully committed to the
+// resident experts, plug-in hosts that are only given the input and output
+// buffers, and callers that forbid allocator calls after start-up because an
+// allocation can synchronise the device or fragment a tightly packed HBM budget.
+// For them the scratch lives in a fixed array inside the library image.
+//
+// Cost and limits: every GPU that loads the library carries the array
+// (kNoAllocScratchBytes) until the process exits. Problems whose scratch need
+// exceeds it are refused with KNJ_E_WORKSPACE. All calls on a device share the
+// one array and it keeps whatever the previous call left there; this entry
+// point rewrites every byte it later reads, so nothing needs clearing, but two
+// calls whose kernels overlap on the GPU (different streams, or one stream per
+// thread) race on it -- serialise them.
+//
+// The first call on each device resolves the array's device address (the name
+// of a __device__ array is only a host-side handle in host code; kernels must be
+// given the address cudaGetSymbolAddress returns). Make that first call before
+// starting any stream capture.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr size_t kNoAllocScratchBytes = (size_t)1 << 20;  // 1 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+
+int noalloc_scratch_ptr(void **out) {
+  static void *resolved[64] = {nullptr};
+  int dev = 0;
+  KNJ_CUDA(cudaGetDevice(&dev));
+  KNJ_REQUIRE(dev >= 0 && dev < 64, "no-alloc scratch: device index %d out of range", dev);
+  if (!resolved[dev]) {
+    void *ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);  // with `dev` current
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+    KNJ_REQUIRE(ptr != nullptr, "no-alloc scratch: symbol address resolved to null");
+    resolved[dev] = ptr;
+  }
+  *out = resolved[dev];
+  return KNJ_OK;
+}
+}  // namespace
+
+size_t knj_q4k_matmul_noalloc_max_scratch(void) { return kNoAllocScratchBytes; }
+
+int knj_q4k_matmul_noalloc_launch(const uint8_t *W, int n_in, int n_out, const void *x, int x_dtype, int64_t ldx, int m,
+                                  float *y, int64_t ldy, knj_stream_t s) {
+  KNJ_REQUIRE(m > 0 && n_in > 0, "knj_q4k_matmul_noalloc: m and n_in must be positive");
+  const size_t need = knj_q4k_matmul_workspace_bytes(m, n_in);
+  if (need > kNoAllocScratchBytes) {
+    set_error("knj_q4k_matmul_noalloc: m=%d rows of n_in=%d need %zu bytes of scratch, the built-in array holds %zu; "
+              "use knj_q4k_matmul_launch with a caller workspace",
+              m, n_in, need, kNoAllocScratchBytes);
+    return KNJ_E_WORKSPACE;
+  }
+  void *scratch = nullptr;
+  int rc = noalloc_scratch_ptr(&scratch);
+  if (rc) return rc;
+  return knj_q4k_matmul_launch(W, n_in, n_out, x, x_dtype, ldx, m, y, ldy, scratch, kNoAllocScratchBytes, s);
+}
+
 }  // extern "C"
