@@ -196,6 +196,25 @@ int knj_router_topk_launch(const void *x, int x_dtype, int64_t ldx, const uint16
 int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,
                            int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
+/* Decode front end in one launch (T <= 64): per-row RMSNorm scale (norm_w NULL =
+ * none), router logits + softmax + exact top-k (as knj_router_topk_launch over
+ * the normalised rows), the permutation tables (as knj_moe_permute_launch) and
+ * the prepared activation vector of every token (as knj_act_prep_launch over
+ * the normalised rows). Replaces, for the decode step, rmsnorm_rows + the router
+ * part of Model::moe (src/model/model.cpp:631, :419-460) and the host plan of the
+ * benches. counter: 16 device words of scratch. H <= 2048, rows of x 16-byte
+ * aligned. */
+int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *norm_w, float eps,
+                         const uint16_t *Wr_bf16, const float *bias, int T, int H, int E, int k, float *logits,
+                         int32_t *pair_exp, float *pair_w, int32_t *pair_idx, int idx_stride, int32_t *pair_cnt,
+                         int32_t *exp_list, int32_t *n_active, void *xpanel, uint32_t *counter, knj_stream_t s);
+
+/* Measurement hook (no reference counterpart): a device buffer of 16 uint64 that
+ * receives global-timer stamps (ns) of the front kernel's phases -- start,
+ * logits done, vectors prepared, group complete, top-k done, all groups
+ * complete, tables done -- written by the CTA that finishes last. NULL = off. */
+void knj_moe_front_trace(void *dev_buf);
+
 /* Second half of the permutation step alone: exp_list / n_active from pair_cnt. */
 int knj_active_list_launch(const int32_t *pair_cnt, int E, int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
@@ -216,8 +235,12 @@ int knj_moe_combine_launch(const float *Y, const int32_t *pair_row, const int32_
  * fp16 tensor cores and apply the per-32 scale/min in f32, so activations are
  * first split into a "panel": per vector a power-of-two scale, a high and a
  * low fp16 plane (together ~22 significant bits) and the per-32 sums the min
- * term needs. One panel vector = 4*K + 4*(K/32) + 16 bytes. */
+ * term needs. One panel vector = (K/256) * 1120 + 16 bytes. */
 size_t knj_panel_bytes(int n_vec, int K);
+/* Tuning hook for measurement runs (no reference counterpart): force the
+ * K-split, tiles-per-CTA and 4-token tiles per pass (1, 2 or 4) of the decode
+ * projections; 0 = automatic. */
+void knj_q4k_decode_tuning(int ks, int tg, int nt);
 /* x [n_vec][K] (f32/bf16/f16, row stride ldx elements) -> panel. */
 int knj_act_prep_launch(const void *x, int x_dtype, int64_t ldx, int n_vec, int K, void *panel, knj_stream_t s);
 

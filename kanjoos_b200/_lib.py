@@ -86,10 +86,14 @@ SIGNATURES = {
     "knj_rmsnorm_launch": (_i, [_vp, _i, _i64, _vp, _f, _i, _i, _vp, _vp]),
     "knj_router_topk_launch": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "knj_moe_permute_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "knj_moe_front_launch": (_i, [_vp, _i, _i64, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp,
+                                  _vp, _vp, _vp, _vp]),
+    "knj_moe_front_trace": (None, [_vp]),
     "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
     "knj_ep_pack_launch": (_i, [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "knj_ep_plan_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
+    "knj_q4k_decode_tuning": (None, [_i, _i, _i]),
     "knj_panel_bytes": (_sz, [_i, _i]),
     "knj_act_prep_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i,

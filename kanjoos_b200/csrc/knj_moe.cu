@@ -27,6 +27,7 @@ struct Carve {
 struct DecodeWs {
   float *xn, *logits, *pair_w, *A, *Y;
   int32_t *pair_exp, *pair_idx, *pair_cnt, *exp_list, *n_active;
+  uint32_t *counter;
   void *xpanel, *apanel;
   size_t bytes;
 };
@@ -43,6 +44,7 @@ DecodeWs carve_decode(void *base, int T, int H, int F, int E, int k) {
   w.pair_cnt = c.take<int32_t>((size_t)E * 4);
   w.exp_list = c.take<int32_t>((size_t)E * 4);
   w.n_active = c.take<int32_t>(16);
+  w.counter = c.take<uint32_t>(64);
   w.xpanel = c.take<void>(knj_panel_bytes(T, H));
   w.A = c.take<float>(P * F * 4);
   w.apanel = c.take<void>(knj_panel_bytes((int)P, F));
@@ -119,28 +121,37 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   const DecodeWs w = carve_decode(a->workspace, T, H, F, E, k);
   const int P = T * k;
 
-  // 1. ffn RMSNorm (optional) -> the rows the router and the experts see
-  const void *src = a->x;
-  int src_dt = a->x_dtype;
-  int64_t src_ld = a->ldx;
-  if (a->norm_w) {
-    rc = knj_rmsnorm_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, T, H, w.xn, s);
-    if (rc) return rc;
-    src = w.xn;
-    src_dt = KNJ_DT_F32;
-    src_ld = H;
-  }
-  // 2. route
   int32_t *pair_exp = a->tap_pair_exp ? a->tap_pair_exp : w.pair_exp;
   float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
-  rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
-  if (rc) return rc;
-  // 3. permutation tables
-  rc = knj_moe_permute_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, s);
-  if (rc) return rc;
-  // 4. gate, up, silu(g)*u
-  rc = knj_act_prep_launch(src, src_dt, src_ld, T, H, w.xpanel, s);
-  if (rc) return rc;
+  if (T <= 64 && H <= 2048 && a->ldx % 8 == 0 && aligned16(a->x)) {
+    // decode batch: norm statistics, routing, tables and prepared vectors in one launch
+    rc = knj_moe_front_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, a->w_router, a->router_bias, T, H, E, k,
+                              w.logits, pair_exp, pair_w, w.pair_idx, T, w.pair_cnt, w.exp_list, w.n_active, w.xpanel,
+                              w.counter, s);
+    if (rc) return rc;
+  } else {
+    // 1. ffn RMSNorm (optional) -> the rows the router and the experts see
+    const void *src = a->x;
+    int src_dt = a->x_dtype;
+    int64_t src_ld = a->ldx;
+    if (a->norm_w) {
+      rc = knj_rmsnorm_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, T, H, w.xn, s);
+      if (rc) return rc;
+      src = w.xn;
+      src_dt = KNJ_DT_F32;
+      src_ld = H;
+    }
+    // 2. route
+    rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
+    if (rc) return rc;
+    // 3. permutation tables
+    rc = knj_moe_permute_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, s);
+    if (rc) return rc;
+    // 4. prepared activation vectors
+    rc = knj_act_prep_launch(src, src_dt, src_ld, T, H, w.xpanel, s);
+    if (rc) return rc;
+  }
+  // gate, up, silu(g)*u
   rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
                              nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, T, s);
   if (rc) return rc;

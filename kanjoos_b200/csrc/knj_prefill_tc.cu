@@ -5,15 +5,16 @@
 // Roles (swap-AB): the MMA "M" side is 128 weight rows of one expert, the "N"
 // side is a bucket of up to 256 routed tokens, K runs over the hidden (or ffn)
 // dimension in slabs of 64. Per CTA one (expert, 128-row tile, token bucket):
-//   warps 0..7  producers: per-row bulk async copies bring the raw 144-byte
+//   warps 0..7  unpackers: per-row bulk async copies bring the raw 144-byte
 //               superblocks into a staging buffer (one copy per row and
 //               superblock, contiguous in HBM); each slab they rebuild
 //               w = (d*sc)*q - dmin*m in fp16 and store it into the K-major
-//               128-byte-swizzled operand tile, and they gather the token rows
-//               of the slab into the second operand tile;
+//               128-byte-swizzled operand tile;
 //   warp 8      one elected thread issues tcgen05.mma (kind::f16, 128 x N x 16)
 //               over the four 16-wide steps of a slab and commits the stage
 //               back to the producers through an mbarrier;
+//   warps 9..12 loaders: gather the token rows of the slab (16-byte pieces,
+//               one slab ahead in registers) into the second operand tile;
 //   warps 0..7  epilogue: tcgen05.ld of the accumulators (lane = weight row,
 //               column = token), SiLU(gate)*up or the plain projection, stores.
 // Gate and up share the token operand: two accumulators (columns [0,256) and
@@ -39,8 +40,9 @@ constexpr int kRowsM = 128;        // weight rows per tile (MMA M)
 constexpr int kMaxTok = 256;       // token bucket (MMA N upper bound)
 constexpr int kSlabK = 64;         // K elements per pipeline stage (one 128-byte swizzle row)
 constexpr int kStages = 2;         // operand stages
-constexpr int kProducerThreads = 256;
-constexpr int kThreads = kProducerThreads + 32;
+constexpr int kProducerThreads = 256;  // unpacker warps 0..7
+constexpr int kLoaderThreads = 128;    // loader warps 9..12
+constexpr int kThreads = kProducerThreads + 32 + kLoaderThreads;
 constexpr float kActPrescale = 0.015625f;  // 2^-6
 
 struct TcParams {
@@ -162,7 +164,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
   int32_t *s_row = reinterpret_cast<int32_t *>(smem + S::kOffRows);
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], kProducerThreads); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], kProducerThreads + kLoaderThreads); mbar_init(&empty[s], 1); }
     mbar_init(&raw_full[0], NMAT * kRowsM);
     mbar_init(&raw_full[1], NMAT * kRowsM);
     mbar_init(acc_full, 1);
@@ -220,21 +222,6 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
         if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
         tc_fence_after();
 
-        // ---- token operand: rows of 64 fp16, 16-byte chunk c of row r stored at chunk c ^ (r & 7)
-        {
-          uint8_t *bt = smem + S::kOffB + stage * S::kBTile;
-          const int c = tid & 7;
-#pragma unroll
-          for (int j = 0; j < kMaxTok / 32; ++j) {
-            const int r = (tid >> 3) + 32 * j;
-            if (r < n_mma) {
-              uint4 v = make_uint4(0u, 0u, 0u, 0u);
-              const int xr = s_row[r];
-              if (xr >= 0) v = __ldg(reinterpret_cast<const uint4 *>(p.X + (size_t)xr * p.K + ks * kSlabK + c * 8));
-              *reinterpret_cast<uint4 *>(bt + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-            }
-          }
-        }
         // ---- weight operand(s): 16 code bytes -> 16 low-nibble + 16 high-nibble weights of this row
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
@@ -259,23 +246,22 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
           }
           uint8_t *at = smem + S::kOffA + (stage * NMAT + mat) * S::kATile + row * 128;
           const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
+          const __half2 k1024 = __float2half2_rn(1024.0f);
 #pragma unroll
           for (int par = 0; par < 2; ++par) {
             const __half2 d1 = __float2half2_rn(fminf(d * (float)sc[par], 65504.0f));
             const __half2 m1 = __float2half2_rn(-(dmin * (float)mn[par]));
-            const __half2 k1024 = __float2half2_rn(1024.0f);
             uint32_t o[8];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
-              const uint32_t src = par ? (qw[w] >> 4) : qw[w];
-              // bytes 0,2 -> (k, k+2) ; bytes 1,3 -> (k+1, k+3): rebuild consecutive pairs below
-              const uint32_t e02 = (src & 0x000f000fu) | 0x64006400u;         // 1024 + q of bytes 0 and 2
-              const uint32_t e13 = ((src >> 8) & 0x000f000fu) | 0x64006400u;  // bytes 1 and 3
-              __half2 h02 = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&e02), k1024), d1, m1);
-              __half2 h13 = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&e13), k1024), d1, m1);
-              const uint32_t u02 = *reinterpret_cast<uint32_t *>(&h02), u13 = *reinterpret_cast<uint32_t *>(&h13);
-              o[2 * w] = __byte_perm(u02, u13, 0x5410);      // (k0, k1)
-              o[2 * w + 1] = __byte_perm(u02, u13, 0x7632);  // (k2, k3)
+              // the four codes of this word as bytes, then pairs (k0,k1), (k2,k3) as fp16 1024+q
+              const uint32_t nib = (par ? (qw[w] >> 4) : qw[w]) & 0x0f0f0f0fu;
+              const uint32_t e01 = __byte_perm(nib, 0x64646464u, 0x4140);
+              const uint32_t e23 = __byte_perm(nib, 0x64646464u, 0x4342);
+              const __half2 h01 = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&e01), k1024), d1, m1);
+              const __half2 h23 = __hfma2(__hsub2(*reinterpret_cast<const __half2 *>(&e23), k1024), d1, m1);
+              o[2 * w] = *reinterpret_cast<const uint32_t *>(&h01);
+              o[2 * w + 1] = *reinterpret_cast<const uint32_t *>(&h23);
             }
             // 16 weights = two 16-byte chunks: k_local = 32*par + 16*half + [0,16)
             const int c0 = 4 * par + 2 * half;
@@ -287,7 +273,43 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
         mbar_arrive(&full[stage]);
       }
     }
-  } else if (lane == 0) {
+  } else if (warp >= 9) {
+    // =========================== loaders ===========================
+    // rows of 64 fp16 per slab; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
+    const int lt = tid - (kProducerThreads + 32);
+    const int c = lt & 7, r0 = lt >> 3;  // 16 rows per pass
+    const __half *rowp[kMaxTok / 16];
+#pragma unroll
+    for (int j = 0; j < kMaxTok / 16; ++j) {
+      const int r = r0 + 16 * j;
+      const int xr = r < n_mma ? s_row[r] : -1;
+      rowp[j] = xr >= 0 ? p.X + (size_t)xr * p.K + c * 8 : nullptr;
+    }
+    uint4 v[kMaxTok / 16];
+    auto fetch = [&](int ks) {
+#pragma unroll
+      for (int j = 0; j < kMaxTok / 16; ++j) {
+        v[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (rowp[j]) v[j] = __ldg(reinterpret_cast<const uint4 *>(rowp[j] + ks * kSlabK));
+      }
+    };
+    fetch(0);
+    for (int ks = 0; ks < nslab; ++ks) {
+      const int stage = ks % kStages;
+      if (ok && ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) ok = false;
+      if (!ok) break;  // loaders meet no CTA barrier before the final one
+      tc_fence_after();
+      uint8_t *bt = smem + S::kOffB + stage * S::kBTile;
+#pragma unroll
+      for (int j = 0; j < kMaxTok / 16; ++j) {
+        const int r = r0 + 16 * j;
+        if (r < n_mma) *reinterpret_cast<uint4 *>(bt + r * 128 + ((c ^ (r & 7)) << 4)) = v[j];
+      }
+      if (ks + 1 < nslab) fetch(ks + 1);  // next slab's rows travel while this stage is consumed
+      fence_proxy_async();
+      mbar_arrive(&full[stage]);
+    }
+  } else if (warp == 8 && lane == 0) {
     // =========================== MMA issue ===========================
     const uint32_t idesc = instr_desc_f16(n_mma);
     for (int ks = 0; ks < nslab && ok; ++ks) {

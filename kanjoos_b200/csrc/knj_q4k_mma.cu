@@ -26,7 +26,10 @@
 // form the first k-pair and bytes 1 and 3 the second; the activation planes are
 // stored with every aligned group of four k permuted to (0,2,1,3) so one
 // 16-byte load yields the matching B fragments of both steps.
+#include <type_traits>
+
 #include "knj_common.cuh"
+#include "knj_panel.cuh"
 #include "knj_q4k.h"
 
 using namespace knj;
@@ -35,70 +38,16 @@ namespace {
 
 constexpr int kScalePitch = 18;  // floats per row of the scale table: 8 float2 + 1 pad pair
 
-__host__ __device__ inline size_t panel_vec_bytes(int K) { return (size_t)4 * K + (size_t)K / 8 + 16; }
-
 // ---------------------------------------------------------------------------
-// activation prep: x -> (scale, hi plane, lo plane, per-32 sums)
+// activation prep: x -> (scale, hi plane, lo plane, per-32 sums), see knj_panel.cuh
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(128) act_prep_kernel(const void *__restrict__ x, int dtype, int64_t ldx, int K,
+template <int DT>
+__global__ void __launch_bounds__(128) act_prep_kernel(const void *__restrict__ x, int64_t ldx, int K,
                                                        uint8_t *__restrict__ panel) {
+  __shared__ float red[16];
   const int v = blockIdx.x;
-  const int tid = threadIdx.x;
-  const int nquad = K / 4;
-  __shared__ float red[4];
-
-  float amax = 0.f;
-  for (int q = tid; q < nquad; q += 128)
-#pragma unroll
-    for (int i = 0; i < 4; ++i) amax = fmaxf(amax, fabsf(load_as_f32(x, dtype, (int64_t)v * ldx + 4 * q + i)));
-  amax = warp_max(amax);
-  if ((tid & 31) == 0) red[tid >> 5] = amax;
-  __syncthreads();
-  amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
-
-  // power-of-two scale putting the largest magnitude in [2^13, 2^14)
-  int e = 0;
-  if (amax > 0.f && amax < 3.0e38f) {
-    int ex;
-    frexpf(amax, &ex);  // amax = m * 2^ex, m in [0.5, 1)
-    e = 14 - ex;
-    e = max(-120, min(120, e));
-  }
-  const float s = ldexpf(1.0f, e);
-
-  uint8_t *base = panel + (size_t)v * panel_vec_bytes(K);
-  uint2 *hi = reinterpret_cast<uint2 *>(base);
-  uint2 *lo = reinterpret_cast<uint2 *>(base + (size_t)2 * K);
-  float *sx = reinterpret_cast<float *>(base + (size_t)4 * K);
-  float *inv = reinterpret_cast<float *>(base + (size_t)4 * K + (size_t)K / 8);
-
-  // quads of one 32-wide sub-block sit in 8 consecutive lanes (nquad % 8 == 0, 128 % 8 == 0)
-  for (int q = tid; q < nquad; q += 128) {
-    float f[4], h[4], l[4];
-    float part = 0.f;
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      f[i] = load_as_f32(x, dtype, (int64_t)v * ldx + 4 * q + i) * s;
-      const __half hh = __float2half_rn(f[i]);
-      h[i] = __half2float(hh);
-      const __half ll = __float2half_rn(f[i] - h[i]);
-      l[i] = __half2float(ll);
-      part += h[i] + l[i];
-    }
-    // stored order (k0, k2, k1, k3)
-    __half2 h01 = __floats2half2_rn(h[0], h[2]), h23 = __floats2half2_rn(h[1], h[3]);
-    __half2 l01 = __floats2half2_rn(l[0], l[2]), l23 = __floats2half2_rn(l[1], l[3]);
-    hi[q] = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
-    lo[q] = make_uint2(*reinterpret_cast<uint32_t *>(&l01), *reinterpret_cast<uint32_t *>(&l23));
-    part += __shfl_xor_sync(0xffffffffu, part, 1);
-    part += __shfl_xor_sync(0xffffffffu, part, 2);
-    part += __shfl_xor_sync(0xffffffffu, part, 4);
-    if ((tid & 7) == 0) sx[q >> 3] = part;
-  }
-  if (tid == 0) {
-    inv[0] = ldexpf(1.0f, -e);
-    inv[1] = inv[2] = inv[3] = 0.f;
-  }
+  panel_prep_vector([&](int k) { return load_as_f32(x, DT, (int64_t)v * ldx + k); }, K,
+                    panel + (size_t)v * panel_vec_bytes(K), red);
 }
 
 // ---------------------------------------------------------------------------
@@ -116,175 +65,282 @@ struct ProjParams {
   float *out0;  // dual: G        single: Y
   float *out1;  // dual: U
   float *out2;  // dual: A = silu(G)*U
-  int N, K, rowBytes, pitch, row_div, tiles_per_expert;
+  int N, K, rowBytes, row_div, tiles_per_expert;
+  int ks;         // warps that split the K range of one tile
+  int tg;         // tiles per CTA (blockDim = 32 * tg * ks)
+  int pitch;      // padded bytes per staged row part
+  int tp_alloc;   // token slots per staged activation buffer
+  int resident;   // 1: whole panel vectors of a pass are staged at once (small batch); 0: one superblock chunk per step
   int64_t idxStride;
-  int *status;  // optional: set to 1 when a bounded wait gave up
+  int *status;    // optional: set to 1 when a bounded wait gave up
 };
 
+struct ProjSmem {
+  size_t weights, scales, bbuf, red, bars, total;
+};
+__host__ __device__ inline ProjSmem proj_smem(int warps, int pitch, int ks, int tp_alloc, int nt, int resident, int K) {
+  ProjSmem m;
+  m.weights = 0;
+  m.scales = m.weights + (size_t)warps * 16 * pitch;
+  m.bbuf = m.scales + (size_t)warps * 16 * kScalePitch * sizeof(float);
+  m.red = m.bbuf + (resident ? (size_t)tp_alloc * panel_vec_bytes(K) : (size_t)2 * ks * tp_alloc * kChunkBytes);
+  m.bars = m.red + (size_t)warps * 32 * 2 * nt * sizeof(float);
+  m.total = m.bars + (size_t)(warps + 2) * 8 + 16;
+  return m;
+}
+
+// One CTA = `tg` tiles of one expert x `ks` K-parts; warp w owns tile w / ks and
+// the superblocks [part * nsb/ks, (part+1) * nsb/ks) with part = w % ks.
 // DUAL: the m16 tile is 8 gate rows (fragment rows 0..7) + the 8 up rows of the
 // same output indices (fragment rows 8..15), so silu(g)*u pairs up in-thread.
 // Otherwise the tile is 16 consecutive rows of one matrix.
+// All warps of the CTA walk the K steps in lockstep because they share the
+// staged activation chunks (double buffered, one bulk copy per token and part).
 template <bool DUAL, int NT>
 __global__ void __launch_bounds__(512) q4k_proj_kernel(const ProjParams p) {
+  constexpr int TP = 4 * NT;  // tokens per pass
   extern __shared__ __align__(128) uint8_t smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int nsb = p.K / KNJ_QK_K;
+  const int ks = p.ks, tile_slot = warp / ks, part = warp - tile_slot * ks;
+  const int nsb = p.K / KNJ_QK_K, nsb_part = nsb / ks;
+  const int part_bytes = nsb_part * KNJ_Q4K_BYTES;
 
-  const size_t per_warp = (size_t)16 * p.pitch + 16 * kScalePitch * sizeof(float) + 16;
-  uint8_t *wbase = smem + (size_t)warp * per_warp;
-  float *scales = reinterpret_cast<float *>(wbase + (size_t)16 * p.pitch);
-  uint64_t *bar = reinterpret_cast<uint64_t *>(wbase + (size_t)16 * p.pitch + 16 * kScalePitch * sizeof(float));
+  const ProjSmem lay = proj_smem(nwarp, p.pitch, ks, p.tp_alloc, NT, p.resident, p.K);
+  uint8_t *wbase = smem + lay.weights + (size_t)warp * 16 * p.pitch;
+  float *scales = reinterpret_cast<float *>(smem + lay.scales) + warp * 16 * kScalePitch;
+  uint8_t *bbuf = smem + lay.bbuf;
+  float *red = reinterpret_cast<float *>(smem + lay.red);
+  uint64_t *wbar = reinterpret_cast<uint64_t *>(smem + lay.bars) + warp;
+  uint64_t *bbar = reinterpret_cast<uint64_t *>(smem + lay.bars) + nwarp;
+  volatile int *s_fail = reinterpret_cast<volatile int *>(bbar + 2);
 
-  if (lane == 0) {
-    mbar_init(bar, 1);
-    mbar_init_fence();
+  if (lane == 0) mbar_init(wbar, 1);
+  if (threadIdx.x == 0) {
+    mbar_init(&bbar[0], 1);
+    mbar_init(&bbar[1], 1);
+    *s_fail = 0;
   }
-  __syncwarp();
-  uint32_t phase = 0;
+  mbar_init_fence();
+  __syncthreads();
+  uint32_t wphase = 0, bphase0 = 0, bphase1 = 0;
+  bool ok = true;  // false: skip work and waits, but keep meeting the CTA barriers
+  int staged_vec = -2;  // warp 0, lane i: the vector sitting in resident slot i
 
   const int n_act = p.n_active[0];
-  const int total = n_act * p.tiles_per_expert;
+  const int groups = p.tiles_per_expert / p.tg;
+  const int total = n_act * groups;
   const size_t vec_bytes = panel_vec_bytes(p.K);
   const int rows_per_tile = DUAL ? 8 : 16;
 
-  for (int it = blockIdx.x * nwarp + warp; it < total; it += gridDim.x * nwarp) {
-    const int a = it / p.tiles_per_expert, tile = it - a * p.tiles_per_expert;
+  for (int it = blockIdx.x; it < total; it += gridDim.x) {
+    const int a = it / groups, grp = it - a * groups;
     const int e = p.exp_list[a];
     const int cnt = p.pair_cnt[e];
-    const int n0 = tile * rows_per_tile;
+    const int n0 = (grp * p.tg + tile_slot) * rows_per_tile;
 
-    // ---- stream the 16 weight rows of this tile into shared memory
-    fence_proxy_async();
-    if (lane == 0) mbar_expect_tx(bar, 16u * (uint32_t)p.rowBytes);
-    __syncwarp();
-    if (lane < 16) {
-      const uint8_t *src;
-      if (DUAL)
-        src = (lane < 8 ? p.W0 : p.W1) + ((size_t)e * p.N + n0 + (lane & 7)) * p.rowBytes;
-      else
-        src = p.W0 + ((size_t)e * p.N + n0 + lane) * p.rowBytes;
-      bulk_g2s(wbase + (size_t)lane * p.pitch, src, (uint32_t)p.rowBytes, bar);
+    // ---- stream this warp's part of the 16 weight rows into shared memory
+    if (ok) {
+      fence_proxy_async();
+      if (lane == 0) mbar_expect_tx(wbar, 16u * (uint32_t)part_bytes);
+      __syncwarp();
+      if (lane < 16) {
+        const uint8_t *src;
+        if (DUAL)
+          src = (lane < 8 ? p.W0 : p.W1) + ((size_t)e * p.N + n0 + (lane & 7)) * p.rowBytes;
+        else
+          src = p.W0 + ((size_t)e * p.N + n0 + lane) * p.rowBytes;
+        bulk_g2s(wbase + (size_t)lane * p.pitch, src + (size_t)part * part_bytes, (uint32_t)part_bytes, wbar);
+      }
     }
-    if (!mbar_wait(bar, phase)) {
-      if (lane == 0 && p.status) atomicExch(p.status, 1);
-      mbar_wait(bar, phase);  // one more bounded wait for the copies in flight, then leave
-      return;
-    }
-    phase ^= 1u;
-
+    bool w_ready = false;
     const uint8_t *rowA = wbase + (size_t)g * p.pitch;
     const uint8_t *rowB = wbase + (size_t)(g + 8) * p.pitch;
 
-    for (int tok0 = 0; tok0 < cnt; tok0 += 4 * NT) {
-      // pair ids of this token group: lane i holds the pair of token tok0 + i
-      int my_pair = -1;
-      if (lane < 4 * NT && tok0 + lane < cnt) my_pair = p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
-      int my_vec = -1;
-      if (my_pair >= 0) my_vec = p.row_map ? p.row_map[my_pair] : my_pair / p.row_div;
+    for (int tok0 = 0; tok0 < cnt; tok0 += min(TP, p.tp_alloc)) {
+      const int n_valid = min(min(TP, p.tp_alloc), cnt - tok0);
+      // pair ids of this pass: lane i holds the pair of token tok0 + i
+      int my_pair = -1, my_vec = -1;
+      if (lane < n_valid) {
+        my_pair = p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
+        my_vec = p.row_map ? p.row_map[my_pair] : my_pair / p.row_div;
+      }
+      // staged activation chunks: buffer b, part pp, token i
+      auto stage_chunks = [&](int j) {
+        if (warp == 0) {
+          const int i = lane % p.tp_alloc, pp = lane / p.tp_alloc;
+          const int vec = __shfl_sync(0xffffffffu, my_vec, i);
+          uint64_t *bar = &bbar[j & 1];
+          fence_proxy_async();
+          if (lane == 0) mbar_expect_tx(bar, (uint32_t)(n_valid * ks) * kChunkBytes);
+          __syncwarp();
+          if (pp < ks && i < n_valid)
+            bulk_g2s(bbuf + ((size_t)((j & 1) * ks + pp) * p.tp_alloc + i) * kChunkBytes,
+                     p.panel + (size_t)vec * vec_bytes + (size_t)(pp * nsb_part + j) * kChunkBytes, kChunkBytes, bar);
+        }
+      };
 
-      const uint8_t *bptr[NT];  // B fragments: token g/2 of the tile, plane g&1
-      const float *sxptr[NT];   // per-32 sums + inverse scale: token t of the tile
-      int out_pair[NT];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int vb = __shfl_sync(0xffffffffu, my_vec, nt * 4 + (g >> 1));
-        const int vo = __shfl_sync(0xffffffffu, my_vec, nt * 4 + t);
-        out_pair[nt] = __shfl_sync(0xffffffffu, my_pair, nt * 4 + t);
-        bptr[nt] = vb >= 0 ? p.panel + (size_t)vb * vec_bytes + (size_t)(g & 1) * 2 * p.K + 16 * t : nullptr;
-        sxptr[nt] = vo >= 0 ? reinterpret_cast<const float *>(p.panel + (size_t)vo * vec_bytes + (size_t)4 * p.K)
-                            : nullptr;
+      // resident mode: restage only when the vectors in shared memory are not the ones this pass needs.
+      // The barrier doubles as "every warp is done with the activation buffers and the reduction scratch".
+      bool restage = false;
+      if (p.resident && warp == 0) restage = !__all_sync(0xffffffffu, lane >= n_valid || my_vec == staged_vec);
+      const int any_restage = __syncthreads_or(restage ? 1 : 0);
+      if (*s_fail) ok = false;
+      bool have_b = false;
+      if (p.resident) {
+        have_b = any_restage == 0;
+        if (ok && !have_b && warp == 0) {
+          // one bulk copy per token: the whole prepared vector
+          fence_proxy_async();
+          if (lane == 0) mbar_expect_tx(&bbar[0], (uint32_t)n_valid * (uint32_t)(vec_bytes - 16));
+          __syncwarp();
+          if (lane < n_valid)
+            bulk_g2s(bbuf + (size_t)lane * vec_bytes, p.panel + (size_t)my_vec * vec_bytes, (uint32_t)(vec_bytes - 16), &bbar[0]);
+          staged_vec = lane < n_valid ? my_vec : -2;
+        }
+      } else if (ok) {
+        stage_chunks(0);
       }
 
       float acc0[NT], acc1[NT];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) acc0[nt] = acc1[nt] = 0.f;
 
-      for (int b = 0; b < nsb; ++b) {
-        // ---- (d*sc, dmin*m) of the 16 rows x 8 sub-blocks of this superblock
+      for (int j = 0; j < nsb_part; ++j) {
+        if (!p.resident) {
+          if (j + 1 < nsb_part) {
+            __syncthreads();  // buffer (j+1)&1 was last read at step j-1
+            if (ok) stage_chunks(j + 1);
+          }
+          if (ok) {
+            uint32_t &bph = (j & 1) ? bphase1 : bphase0;
+            if (!mbar_wait(&bbar[j & 1], bph, s_fail)) ok = false;
+            bph ^= 1u;
+          }
+        } else if (ok && !have_b) {
+          if (!mbar_wait(&bbar[0], bphase0, s_fail)) ok = false;
+          bphase0 ^= 1u;
+          have_b = true;
+        }
+        if (ok && !w_ready) {
+          if (!mbar_wait(wbar, wphase, s_fail)) ok = false;
+          wphase ^= 1u;
+          w_ready = true;
+        }
+        if (!ok) continue;
+
+        // ---- (d*sc, dmin*m) of 16 rows x 8 sub-blocks: lane -> row lane%16, sub-blocks 4*(lane/16)..+3
         __syncwarp();
-        if (lane < 16) {
-          const uint4 h = *reinterpret_cast<const uint4 *>(wbase + (size_t)lane * p.pitch + (size_t)b * KNJ_Q4K_BYTES);
+        {
+          const int r = lane & 15, hb = lane >> 4;
+          const uint4 h = *reinterpret_cast<const uint4 *>(wbase + (size_t)r * p.pitch + (size_t)j * KNJ_Q4K_BYTES);
           const float d = __half2float(__ushort_as_half((unsigned short)(h.x & 0xffffu)));
           const float dmin = __half2float(__ushort_as_half((unsigned short)(h.x >> 16)));
-          const uint32_t sc_lo = h.y & 0x3f3f3f3fu, mn_lo = h.z & 0x3f3f3f3fu;
-          const uint32_t sc_hi = (h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u);
-          const uint32_t mn_hi = ((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u);
-          float2 *dst = reinterpret_cast<float2 *>(scales + lane * kScalePitch);
+          const uint32_t sc4 = hb ? ((h.w & 0x0f0f0f0fu) | ((h.y >> 2) & 0x30303030u)) : (h.y & 0x3f3f3f3fu);
+          const uint32_t mn4 = hb ? (((h.w >> 4) & 0x0f0f0f0fu) | ((h.z >> 2) & 0x30303030u)) : (h.z & 0x3f3f3f3fu);
+          float2 *dst = reinterpret_cast<float2 *>(scales + r * kScalePitch) + 4 * hb;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint32_t sc = ((j < 4 ? sc_lo : sc_hi) >> (8 * (j & 3))) & 0xffu;
-            const uint32_t mn = ((j < 4 ? mn_lo : mn_hi) >> (8 * (j & 3))) & 0xffu;
+          for (int i = 0; i < 4; ++i) {
+            const float sc = (float)((sc4 >> (8 * i)) & 0xffu), mn = (float)((mn4 >> (8 * i)) & 0xffu);
             // even sub-blocks hold q*2^-24, odd ones q*2^-20
-            dst[j] = make_float2(d * (float)sc * ((j & 1) ? 1048576.0f : 16777216.0f), dmin * (float)mn);
+            dst[i] = make_float2(d * sc * ((i & 1) ? 1048576.0f : 16777216.0f), dmin * mn);
           }
         }
         __syncwarp();
 
+        // chunk of (token slot, this step); unused slots alias the last staged one (their columns are discarded)
+        const size_t slot_stride = p.resident ? vec_bytes : (size_t)kChunkBytes;
+        const uint8_t *chunks = p.resident ? bbuf + (size_t)(part * nsb_part + j) * kChunkBytes
+                                           : bbuf + (size_t)((j & 1) * ks + part) * p.tp_alloc * kChunkBytes;
+        const int last_slot = p.tp_alloc - 1;
         float sx[NT][8];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          if (sxptr[nt]) {
-            const float4 s0 = __ldg(reinterpret_cast<const float4 *>(sxptr[nt] + b * 8));
-            const float4 s1 = __ldg(reinterpret_cast<const float4 *>(sxptr[nt] + b * 8 + 4));
-            sx[nt][0] = s0.x; sx[nt][1] = s0.y; sx[nt][2] = s0.z; sx[nt][3] = s0.w;
-            sx[nt][4] = s1.x; sx[nt][5] = s1.y; sx[nt][6] = s1.z; sx[nt][7] = s1.w;
-          } else {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) sx[nt][j] = 0.f;
-          }
+          const float4 *sp = reinterpret_cast<const float4 *>(chunks + (size_t)min(nt * 4 + t, last_slot) * slot_stride + kChunkSx);
+          const float4 s0 = sp[0], s1 = sp[1];
+          sx[nt][0] = s0.x; sx[nt][1] = s0.y; sx[nt][2] = s0.z; sx[nt][3] = s0.w;
+          sx[nt][4] = s1.x; sx[nt][5] = s1.y; sx[nt][6] = s1.z; sx[nt][7] = s1.w;
         }
+        const uint8_t *bfrag[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+          bfrag[nt] = chunks + (size_t)min(nt * 4 + (g >> 1), last_slot) * slot_stride + (g & 1) * kChunkLo + 16 * t;
 
+        // the inner loop, specialised on how many 4-token tiles of this pass hold tokens
+        auto run = [&](auto nta_tag) {
+          constexpr int NTA = decltype(nta_tag)::value;
 #pragma unroll
-        for (int G = 0; G < 4; ++G) {
-          const size_t off = (size_t)b * KNJ_Q4K_BYTES + KNJ_Q4K_OFF_QS + 32 * G + 8 * t;
-          const uint2 wa = *reinterpret_cast<const uint2 *>(rowA + off);
-          const uint2 wb = *reinterpret_cast<const uint2 *>(rowB + off);
+          for (int G = 0; G < 4; ++G) {
+            const size_t off = (size_t)j * KNJ_Q4K_BYTES + KNJ_Q4K_OFF_QS + 32 * G + 8 * t;
+            const uint2 wa = *reinterpret_cast<const uint2 *>(rowA + off);
+            const uint2 wb = *reinterpret_cast<const uint2 *>(rowB + off);
 #pragma unroll
-          for (int par = 0; par < 2; ++par) {
-            const int j = 2 * G + par;
-            const uint32_t M = par ? 0x00f000f0u : 0x000f000fu;
-            const float2 sa = *reinterpret_cast<const float2 *>(scales + g * kScalePitch + 2 * j);
-            const float2 sb = *reinterpret_cast<const float2 *>(scales + (g + 8) * kScalePitch + 2 * j);
-            const uint32_t a00 = wa.x & M, a01 = wb.x & M, a02 = (wa.x >> 8) & M, a03 = (wb.x >> 8) & M;
-            const uint32_t a10 = wa.y & M, a11 = wb.y & M, a12 = (wa.y >> 8) & M, a13 = (wb.y >> 8) & M;
+            for (int par = 0; par < 2; ++par) {
+              const int sb = 2 * G + par;
+              const uint32_t M = par ? 0x00f000f0u : 0x000f000fu;
+              const float2 sa = *reinterpret_cast<const float2 *>(scales + g * kScalePitch + 2 * sb);
+              const float2 sb2 = *reinterpret_cast<const float2 *>(scales + (g + 8) * kScalePitch + 2 * sb);
+              const uint32_t a00 = wa.x & M, a01 = wb.x & M, a02 = (wa.x >> 8) & M, a03 = (wb.x >> 8) & M;
+              const uint32_t a10 = wa.y & M, a11 = wb.y & M, a12 = (wa.y >> 8) & M, a13 = (wb.y >> 8) & M;
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              uint4 bf = make_uint4(0u, 0u, 0u, 0u);
-              if (bptr[nt]) bf = __ldg(reinterpret_cast<const uint4 *>(bptr[nt] + (size_t)(b * 256 + 64 * G + 32 * par) * 2));
-              float c[4] = {0.f, 0.f, 0.f, 0.f};
-              mma_f16_16816(c, a00, a01, a02, a03, bf.x, bf.y);
-              mma_f16_16816(c, a10, a11, a12, a13, bf.z, bf.w);
-              // columns 2t / 2t+1 are the high / low plane of the same token
-              acc0[nt] = fmaf(sa.x, c[0] + c[1], acc0[nt]);
-              acc0[nt] = fmaf(-sa.y, sx[nt][j], acc0[nt]);
-              acc1[nt] = fmaf(sb.x, c[2] + c[3], acc1[nt]);
-              acc1[nt] = fmaf(-sb.y, sx[nt][j], acc1[nt]);
+              for (int nt = 0; nt < NTA; ++nt) {
+                const uint4 bf = *reinterpret_cast<const uint4 *>(bfrag[nt] + (64 * G + 32 * par) * 2);
+                float c[4];
+                mma_f16_16816_zero(c, a00, a01, a02, a03, bf.x, bf.y);
+                mma_f16_16816(c, a10, a11, a12, a13, bf.z, bf.w);
+                // columns 2t / 2t+1 are the high / low plane of the same token
+                acc0[nt] = fmaf(sa.x, c[0] + c[1], acc0[nt]);
+                acc0[nt] = fmaf(-sa.y, sx[nt][sb], acc0[nt]);
+                acc1[nt] = fmaf(sb2.x, c[2] + c[3], acc1[nt]);
+                acc1[nt] = fmaf(-sb2.y, sx[nt][sb], acc1[nt]);
+              }
             }
+          }
+        };
+        const int tiles = (n_valid + 3) >> 2;
+        if (NT == 1 || tiles == 1) run(std::integral_constant<int, 1>{});
+        else if (NT == 2 || tiles == 2) run(std::integral_constant<int, (NT >= 2 ? 2 : 1)>{});
+        else if (tiles == 3) run(std::integral_constant<int, (NT >= 4 ? 3 : 1)>{});
+        else run(std::integral_constant<int, NT>{});
+      }
+
+      // ---- combine the K parts (fixed order), undo the activation scale, store
+      if (ks > 1) {
+        float *mine = red + (size_t)(warp * 32 + lane) * 2 * NT;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) { mine[2 * nt] = acc0[nt]; mine[2 * nt + 1] = acc1[nt]; }
+        __syncthreads();
+        if (part == 0) {
+          for (int pp = 1; pp < ks; ++pp) {
+            const float *other = red + (size_t)((warp + pp) * 32 + lane) * 2 * NT;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) { acc0[nt] += other[2 * nt]; acc1[nt] += other[2 * nt + 1]; }
           }
         }
       }
-
-      // ---- epilogue: undo the activation scale, store
+      if (part == 0 && ok) {
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        const int pp = out_pair[nt];
-        if (pp < 0) continue;
-        const float inv = __ldg(sxptr[nt] + p.K / 32);
-        const float v0 = acc0[nt] * inv, v1 = acc1[nt] * inv;
-        if (DUAL) {
-          const size_t o = (size_t)pp * p.N + n0 + g;
-          if (p.out0) p.out0[o] = v0;
-          if (p.out1) p.out1[o] = v1;
-          if (p.out2) p.out2[o] = (v0 / (1.0f + expf(-v0))) * v1;
-        } else {
-          p.out0[(size_t)pp * p.N + n0 + g] = v0;
-          p.out0[(size_t)pp * p.N + n0 + g + 8] = v1;
+        for (int nt = 0; nt < NT; ++nt) {
+          const int pp = __shfl_sync(0xffffffffu, my_pair, nt * 4 + t);
+          const int vo = __shfl_sync(0xffffffffu, my_vec, nt * 4 + t);
+          if (pp < 0) continue;
+          const float inv = __ldg(reinterpret_cast<const float *>(p.panel + (size_t)vo * vec_bytes + (size_t)nsb * kChunkBytes));
+          const float v0 = acc0[nt] * inv, v1 = acc1[nt] * inv;
+          if (DUAL) {
+            const size_t o = (size_t)pp * p.N + n0 + g;
+            if (p.out0) p.out0[o] = v0;
+            if (p.out1) p.out1[o] = v1;
+            if (p.out2) p.out2[o] = (v0 / (1.0f + expf(-v0))) * v1;
+          } else {
+            p.out0[(size_t)pp * p.N + n0 + g] = v0;
+            p.out0[(size_t)pp * p.N + n0 + g + 8] = v1;
+          }
         }
       }
     }
     __syncwarp();
   }
+  if (!ok && threadIdx.x == 0 && p.status) atomicExch(p.status, 1);
 }
 
 __global__ void iota_plan_kernel(int32_t *pair_idx, int32_t *pair_cnt, int32_t *exp_list, int32_t *n_active, int m) {
@@ -304,17 +360,42 @@ int pad_pitch(int rowBytes) {
   return pitch;
 }
 
+// Experiment hook: 0 = choose automatically.
+int g_force_ks = 0, g_force_tg = 0, g_force_nt = 0;
+
 template <bool DUAL, int NT>
-int launch_proj(const ProjParams &p, int n_experts_max, cudaStream_t st) {
-  const size_t per_warp = (size_t)16 * p.pitch + 16 * kScalePitch * sizeof(float) + 16;
+int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st) {
+  const int nsb = p.K / KNJ_QK_K;
+  const int TP = 4 * NT;
+  // small batches: split K over the warps of a CTA so every SM has many warps in flight,
+  // and keep the whole prepared vectors of a pass resident in shared memory
+  p.tp_alloc = max_tokens < TP ? (max_tokens < 1 ? 1 : max_tokens) : TP;
+  p.resident = (size_t)p.tp_alloc * panel_vec_bytes(p.K) <= 40 * 1024 ? 1 : 0;
+  int ks = 1;
+  if (max_tokens <= 8) {
+    for (int c : {4, 3, 2})
+      if (nsb % c == 0 && (p.resident || p.tp_alloc * c <= 32)) { ks = c; break; }
+  }
+  if (g_force_ks > 0 && nsb % g_force_ks == 0 && (p.resident || p.tp_alloc * g_force_ks <= 32)) ks = g_force_ks;
+  int tg = ks >= 4 ? 1 : (ks >= 3 ? 2 : 8);
+  if (g_force_tg > 0) tg = g_force_tg;
+  while (tg > 1 && (p.tiles_per_expert % tg != 0 || tg * ks > 16)) tg >>= 1;
+  p.ks = ks;
+  p.tg = tg;
+  p.pitch = pad_pitch(nsb / ks * KNJ_Q4K_BYTES);
+
   int dev = 0;
   KNJ_CUDA(cudaGetDevice(&dev));
   int smem_max = 0;
   KNJ_CUDA(cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-  int warps = (int)((size_t)(smem_max - 1024) / per_warp);
-  if (warps > 16) warps = 16;
-  KNJ_REQUIRE(warps >= 1, "q4k projection: a %d-byte row does not fit the shared memory tile", p.rowBytes);
-  const size_t smem = per_warp * warps;
+  size_t smem = proj_smem(p.tg * ks, p.pitch, ks, p.tp_alloc, NT, p.resident, p.K).total;
+  while (smem > (size_t)smem_max && p.tg > 1) {  // very long rows: fewer tiles per CTA
+    p.tg >>= 1;
+    smem = proj_smem(p.tg * ks, p.pitch, ks, p.tp_alloc, NT, p.resident, p.K).total;
+  }
+  KNJ_REQUIRE(smem <= (size_t)smem_max && p.tiles_per_expert % p.tg == 0,
+              "q4k projection: rows of %d bytes do not fit the shared memory tile", p.rowBytes);
+  const int threads = p.tg * ks * 32;
   auto kern = q4k_proj_kernel<DUAL, NT>;
   // opt in to the large dynamic shared memory once per device and instantiation
   // (kept out of later launches so they are plain stream work, capturable in a graph)
@@ -323,25 +404,39 @@ int launch_proj(const ProjParams &p, int n_experts_max, cudaStream_t st) {
     KNJ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     opted[dev] = smem;
   }
-  const long long max_items = (long long)n_experts_max * p.tiles_per_expert;
-  long long grid = (max_items + warps - 1) / warps;
-  const long long cap = (long long)sm_count();
+  int per_sm = (int)((size_t)(smem_max + 1024) / (smem + 1024));
+  if (per_sm > 2048 / threads) per_sm = 2048 / threads;
+  if (per_sm > 16) per_sm = 16;
+  if (per_sm < 1) per_sm = 1;
+  const long long max_items = (long long)n_experts_max * (p.tiles_per_expert / p.tg);
+  long long grid = max_items;
+  const long long cap = (long long)sm_count() * per_sm;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  kern<<<(unsigned)grid, warps * 32, smem, st>>>(p);
+  kern<<<(unsigned)grid, threads, smem, st>>>(p);
   return launch_status("q4k_proj_kernel");
 }
 
 template <bool DUAL>
 int launch_proj_nt(const ProjParams &p, int n_experts_max, int max_tokens, cudaStream_t st) {
-  if (max_tokens <= 4) return launch_proj<DUAL, 1>(p, n_experts_max, st);
-  if (max_tokens <= 8) return launch_proj<DUAL, 2>(p, n_experts_max, st);
-  return launch_proj<DUAL, 4>(p, n_experts_max, st);
+  int nt = max_tokens <= 4 ? 1 : (max_tokens <= 8 ? 2 : 4);
+  if (g_force_nt > 0) nt = g_force_nt;
+  if (nt == 1) return launch_proj<DUAL, 1>(p, n_experts_max, max_tokens, st);
+  if (nt == 2) return launch_proj<DUAL, 2>(p, n_experts_max, max_tokens, st);
+  return launch_proj<DUAL, 4>(p, n_experts_max, max_tokens, st);
 }
 
 }  // namespace
 
 extern "C" {
+
+// Experiment hook for tuning runs: force the K-split and tiles-per-CTA of the
+// decode projections (0 = automatic). Not part of the reference surface.
+void knj_q4k_decode_tuning(int ks, int tg, int nt) {
+  g_force_ks = ks;
+  g_force_tg = tg;
+  g_force_nt = nt;
+}
 
 size_t knj_panel_bytes(int n_vec, int K) { return (size_t)(n_vec > 0 ? n_vec : 0) * panel_vec_bytes(K); }
 
@@ -351,7 +446,10 @@ int knj_act_prep_launch(const void *x, int x_dtype, int64_t ldx, int n_vec, int 
   KNJ_REQUIRE(x_dtype >= KNJ_DT_F32 && x_dtype <= KNJ_DT_F16, "knj_act_prep: unknown dtype %d", x_dtype);
   KNJ_REQUIRE(aligned16(panel), "knj_act_prep: panel must be 16-byte aligned");
   if (n_vec <= 0) return KNJ_OK;
-  act_prep_kernel<<<n_vec, 128, 0, as_stream(s)>>>(x, x_dtype, ldx, K, static_cast<uint8_t *>(panel));
+  uint8_t *pn = static_cast<uint8_t *>(panel);
+  if (x_dtype == KNJ_DT_F32) act_prep_kernel<KNJ_DT_F32><<<n_vec, 128, 0, as_stream(s)>>>(x, ldx, K, pn);
+  else if (x_dtype == KNJ_DT_BF16) act_prep_kernel<KNJ_DT_BF16><<<n_vec, 128, 0, as_stream(s)>>>(x, ldx, K, pn);
+  else act_prep_kernel<KNJ_DT_F16><<<n_vec, 128, 0, as_stream(s)>>>(x, ldx, K, pn);
   return launch_status("act_prep_kernel");
 }
 
@@ -370,7 +468,7 @@ int knj_q4k_gateup_launch(const void *Xpanel, const uint8_t *Wg, const uint8_t *
   p.W0 = Wg; p.W1 = Wu; p.panel = static_cast<const uint8_t *>(Xpanel);
   p.pair_idx = pair_idx; p.pair_cnt = pair_cnt; p.row_map = pair_tok; p.exp_list = exp_list; p.n_active = n_active;
   p.out0 = G; p.out1 = U; p.out2 = A;
-  p.N = N; p.K = K; p.rowBytes = rowBytes; p.pitch = pad_pitch(rowBytes); p.row_div = top_k > 0 ? top_k : 1;
+  p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = top_k > 0 ? top_k : 1;
   p.tiles_per_expert = N / 8; p.idxStride = idxStride; p.status = nullptr;
   return launch_proj_nt<true>(p, n_experts, max_tokens, as_stream(s));
 }
@@ -388,7 +486,7 @@ int knj_q4k_proj_launch(const void *Apanel, const uint8_t *W, const int32_t *pai
   p.W0 = W; p.W1 = nullptr; p.panel = static_cast<const uint8_t *>(Apanel);
   p.pair_idx = pair_idx; p.pair_cnt = pair_cnt; p.row_map = pair_row; p.exp_list = exp_list; p.n_active = n_active;
   p.out0 = Y; p.out1 = nullptr; p.out2 = nullptr;
-  p.N = N; p.K = K; p.rowBytes = rowBytes; p.pitch = pad_pitch(rowBytes); p.row_div = 1;
+  p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
   p.tiles_per_expert = N / 16; p.idxStride = idxStride; p.status = nullptr;
   return launch_proj_nt<false>(p, n_experts, max_tokens, as_stream(s));
 }

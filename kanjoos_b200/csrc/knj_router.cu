@@ -5,6 +5,7 @@
 // tools/bench/q4k_stream_ffn.hip:957-1001 and :1305-1313 between the device
 // kernels of the benches).
 #include "knj_common.cuh"
+#include "knj_panel.cuh"
 
 using namespace knj;
 
@@ -82,6 +83,121 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const void *__restri
   }
 }
 
+// eight consecutive activations starting at element idx (a multiple of 8; rows 16-byte aligned)
+__device__ __forceinline__ void load8_as_f32(const void *base, int dtype, int64_t idx, float (&v)[8]) {
+  if (dtype == KNJ_DT_F32) {
+    const float4 a = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(base) + idx));
+    const float4 b = __ldg(reinterpret_cast<const float4 *>(static_cast<const float *>(base) + idx) + 1);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  } else {
+    const uint4 r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(base) + idx));
+    const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (dtype == KNJ_DT_BF16) {
+        v[2 * j] = __uint_as_float(u[j] << 16);
+        v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+      } else {
+        const __half2 h = *reinterpret_cast<const __half2 *>(&u[j]);
+        v[2 * j] = __low2float(h);
+        v[2 * j + 1] = __high2float(h);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Router logits for large token counts on the warp-level tensor cores
+// (mma.sync m16n8k16, bf16 x bf16 -> f32). A warp owns 16 tokens x 64 experts.
+// bf16 rows are used as they are; f32 / f16 rows are split on the fly into
+// three bf16 planes (hi + mid + lo = 24 significant bits), so every product is
+// exact and only the f32 accumulation order differs from the CPU path.
+// Both operands are read with one 16-byte load per two k-steps: lane t of a
+// quad takes k = 8t..8t+7 of a 32-wide span for its row, and the same mapping
+// is used for the router row, so the k-slots of A and B agree.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// eight values -> bf16 pairs (plane 0), and the residual planes for non-bf16 input
+template <int DT>
+__device__ __forceinline__ void load_planes(const void *x, int64_t idx, bool valid, uint32_t (&p0)[4], uint32_t (&p1)[4],
+                                            uint32_t (&p2)[4]) {
+  if (DT == KNJ_DT_BF16) {
+    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+    if (valid) r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + idx));
+    p0[0] = r.x; p0[1] = r.y; p0[2] = r.z; p0[3] = r.w;
+  } else {
+    float v[8];
+    if (valid) load8_as_f32(x, DT, idx, v);
+    else
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float a = v[2 * j], b = v[2 * j + 1];
+      const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      a -= __low2float(h); b -= __high2float(h);
+      const __nv_bfloat162 m = __floats2bfloat162_rn(a, b);
+      a -= __low2float(m); b -= __high2float(m);
+      const __nv_bfloat162 l = __floats2bfloat162_rn(a, b);
+      p0[j] = *reinterpret_cast<const uint32_t *>(&h);
+      p1[j] = *reinterpret_cast<const uint32_t *>(&m);
+      p2[j] = *reinterpret_cast<const uint32_t *>(&l);
+    }
+  }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(128) router_logits_mma_kernel(const void *__restrict__ x, int64_t ldx,
+                                                                const __nv_bfloat16 *__restrict__ Wr,
+                                                                const float *__restrict__ bias, int T, int H, int E,
+                                                                float *__restrict__ logits) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int tok0 = blockIdx.y * 64 + warp * 16;
+  const int e0 = blockIdx.x * 64;
+  float acc[8][4];
+#pragma unroll
+  for (int n = 0; n < 8; ++n)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+  const int ra = tok0 + g, rb = tok0 + g + 8;
+  for (int k0 = 0; k0 < H; k0 += 32) {
+    uint32_t a0[4], a1[4], a2[4], b0[4], b1[4], b2[4];  // rows g and g+8: planes
+    load_planes<DT>(x, (int64_t)ra * ldx + k0 + 8 * t, ra < T, a0, a1, a2);
+    load_planes<DT>(x, (int64_t)rb * ldx + k0 + 8 * t, rb < T, b0, b1, b2);
+#pragma unroll
+    for (int n = 0; n < 8; ++n) {
+      const int e = e0 + n * 8 + g;
+      uint4 w = make_uint4(0u, 0u, 0u, 0u);
+      if (e < E) w = __ldg(reinterpret_cast<const uint4 *>(Wr + (size_t)e * H + k0 + 8 * t));
+      mma_bf16_16816(acc[n], a0[0], b0[0], a0[1], b0[1], w.x, w.y);
+      mma_bf16_16816(acc[n], a0[2], b0[2], a0[3], b0[3], w.z, w.w);
+      if (DT != KNJ_DT_BF16) {
+        mma_bf16_16816(acc[n], a1[0], b1[0], a1[1], b1[1], w.x, w.y);
+        mma_bf16_16816(acc[n], a1[2], b1[2], a1[3], b1[3], w.z, w.w);
+        mma_bf16_16816(acc[n], a2[0], b2[0], a2[1], b2[1], w.x, w.y);
+        mma_bf16_16816(acc[n], a2[2], b2[2], a2[3], b2[3], w.z, w.w);
+      }
+    }
+  }
+#pragma unroll
+  for (int n = 0; n < 8; ++n) {
+    const int e = e0 + n * 8 + 2 * t;
+    const float bb0 = (bias && e < E) ? bias[e] : 0.f, bb1 = (bias && e + 1 < E) ? bias[e + 1] : 0.f;
+    if (ra < T && e < E) logits[(size_t)ra * E + e] = acc[n][0] + bb0;
+    if (ra < T && e + 1 < E) logits[(size_t)ra * E + e + 1] = acc[n][1] + bb1;
+    if (rb < T && e < E) logits[(size_t)rb * E + e] = acc[n][2] + bb0;
+    if (rb < T && e + 1 < E) logits[(size_t)rb * E + e + 1] = acc[n][3] + bb1;
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Softmax + exact top-k + renormalise: one warp per token. Selection is by
 // (value descending, expert id ascending), the tie rule of the CPU path's
@@ -89,23 +205,20 @@ __global__ void __launch_bounds__(256) router_logits_kernel(const void *__restri
 // ---------------------------------------------------------------------------
 constexpr int kMaxEPerLane = 8;  // E <= 256
 
-__global__ void __launch_bounds__(128) router_topk_kernel(const float *__restrict__ logits, int T, int E, int k,
-                                                          int32_t *__restrict__ pair_exp,
-                                                          float *__restrict__ pair_w) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (t >= T) return;
+// One warp: softmax over the E logits of a token, exact top-k, renormalised
+// weights. Lane 0 ends up holding the k (expert, weight) pairs in sel_e / sel_w.
+__device__ __forceinline__ void warp_topk(const float *__restrict__ lg, int E, int k, int lane, int (&sel_e)[8],
+                                          float (&sel_w)[8]) {
   const int per = (E + 31) / 32;
-  float v[kMaxEPerLane];
+  float v[kMaxEPerLane], pr[kMaxEPerLane];
   float mx = -INFINITY;
 #pragma unroll
   for (int i = 0; i < kMaxEPerLane; ++i) {
     const int e = i * 32 + lane;
-    v[i] = (i < per && e < E) ? logits[(size_t)t * E + e] : -INFINITY;
+    v[i] = (i < per && e < E) ? __ldcg(lg + e) : -INFINITY;
     mx = fmaxf(mx, v[i]);
   }
   mx = warp_max(mx);
-  float pr[kMaxEPerLane];
   float sum = 0.f;
 #pragma unroll
   for (int i = 0; i < kMaxEPerLane; ++i) {
@@ -115,44 +228,56 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float *__restric
   sum = warp_sum(sum);
 #pragma unroll
   for (int i = 0; i < kMaxEPerLane; ++i) pr[i] = pr[i] / sum;
-
+  // order-preserving integer keys: larger float <=> larger unsigned key
+  unsigned key[kMaxEPerLane];
+#pragma unroll
+  for (int i = 0; i < kMaxEPerLane; ++i) {
+    const unsigned u = __float_as_uint(v[i]);
+    key[i] = (v[i] == -INFINITY) ? 0u : ((u & 0x80000000u) ? ~u : (u | 0x80000000u));
+  }
   float keep = 0.f;
-  float sel_p[8];
-  int sel_e[8];
 #pragma unroll
   for (int s = 0; s < 8; ++s) {
     if (s >= k) break;
-    // lane-local best, then a butterfly that prefers the larger value and, on
-    // equal values, the smaller expert id
-    float bv = -INFINITY, bp = 0.f;
+    // lane-local best (ascending id inside a lane: strict '>' keeps the lowest id), a hardware max over
+    // the warp, then the smallest expert id among the lanes that hold that maximum
+    unsigned bk = 0u;
+    float bp = 0.f;
     int be = 0x7fffffff;
 #pragma unroll
-    for (int i = 0; i < kMaxEPerLane; ++i) {
-      const int e = i * 32 + lane;
-      if (v[i] > bv) { bv = v[i]; be = e; bp = pr[i]; }  // ascending e inside a lane: strict '>' keeps the lowest id
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-      const int oe = __shfl_xor_sync(0xffffffffu, be, o);
-      const float op = __shfl_xor_sync(0xffffffffu, bp, o);
-      if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; bp = op; }
-    }
-    sel_e[s] = be;
-    sel_p[s] = bp;
-    keep += bp;
-    // retire the winner
+    for (int i = 0; i < kMaxEPerLane; ++i)
+      if (key[i] > bk) { bk = key[i]; be = i * 32 + lane; bp = pr[i]; }
+    const unsigned top = __reduce_max_sync(0xffffffffu, bk);
+    const int win = __reduce_min_sync(0xffffffffu, (bk == top && bk != 0u) ? be : 0x7fffffff);
+    const int src = win & 31;  // expert id = i*32 + lane
+    sel_e[s] = win;
+    sel_w[s] = __shfl_sync(0xffffffffu, bp, src);
+    keep += sel_w[s];
 #pragma unroll
     for (int i = 0; i < kMaxEPerLane; ++i)
-      if (i * 32 + lane == be) v[i] = -INFINITY;
+      if (i * 32 + lane == win) key[i] = 0u;
   }
   const float inv = keep > 0.f ? 1.0f / keep : 0.f;
+#pragma unroll
+  for (int s = 0; s < 8; ++s)
+    if (s < k) sel_w[s] *= inv;
+}
+
+__global__ void __launch_bounds__(128) router_topk_kernel(const float *__restrict__ logits, int T, int E, int k,
+                                                          int32_t *__restrict__ pair_exp,
+                                                          float *__restrict__ pair_w) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  int sel_e[8];
+  float sel_w[8];
+  warp_topk(logits + (size_t)t * E, E, k, lane, sel_e, sel_w);
   if (lane == 0) {
 #pragma unroll
     for (int s = 0; s < 8; ++s) {
       if (s >= k) break;
       pair_exp[(size_t)t * k + s] = sel_e[s];
-      pair_w[(size_t)t * k + s] = sel_p[s] * inv;
+      pair_w[(size_t)t * k + s] = sel_w[s];
     }
   }
 }
@@ -168,29 +293,48 @@ __global__ void __launch_bounds__(256) permute_kernel(const int32_t *__restrict_
   const int e = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   __shared__ int wsum[8];
-  __shared__ int base_s;
-  if (threadIdx.x == 0) base_s = 0;
-  __syncthreads();
   int32_t *row = pair_idx + (size_t)e * idx_stride;
-  for (int p0 = 0; p0 < P; p0 += 256) {
-    const int p = p0 + threadIdx.x;
-    const bool hit = p < P && pair_exp[p] == e;
-    const unsigned m = __ballot_sync(0xffffffffu, hit);
-    if (lane == 0) wsum[warp] = __popc(m);
-    __syncthreads();
-    int off = base_s;
-    for (int w = 0; w < warp; ++w) off += wsum[w];
-    const int rank = off + __popc(m & ((1u << lane) - 1u));
-    if (hit && rank < idx_stride) row[rank] = p;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      int tot = 0;
-      for (int w = 0; w < 8; ++w) tot += wsum[w];
-      base_s += tot;
+  int base = 0;  // identical in every thread
+  // eight consecutive pairs per thread and pass: count, block-wide exclusive scan, write in order
+  for (int p0 = 0; p0 < P; p0 += 2048) {
+    const int first = p0 + threadIdx.x * 8;
+    int v[8];
+    if (first + 8 <= P && (P & 3) == 0) {
+      const int4 a = __ldg(reinterpret_cast<const int4 *>(pair_exp + first));
+      const int4 b = __ldg(reinterpret_cast<const int4 *>(pair_exp + first) + 1);
+      v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = first + i < P ? pair_exp[first + i] : -1;
     }
+    int c = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) c += (v[i] == e);
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    int off = base, tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) off += wsum[w];
+      tot += wsum[w];
+    }
+    int rank = off + incl - c;
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (v[i] == e) {
+        if (rank < idx_stride) row[rank] = first + i;
+        ++rank;
+      }
+    base += tot;
     __syncthreads();
   }
-  const int cnt = min(base_s, idx_stride);
+  const int cnt = min(base, idx_stride);
   for (int i = cnt + threadIdx.x; i < idx_stride; i += 256) row[i] = -1;
   if (threadIdx.x == 0) pair_cnt[e] = cnt;
 }
@@ -237,9 +381,20 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
   const int t = blockIdx.x;
   __shared__ int s_row[8];
   __shared__ float s_w[8];
+  __shared__ int s_ex[8];
+  __shared__ float s_wraw[8];
+  __shared__ int s_rraw[8];
+  if ((int)threadIdx.x < k) {  // the k slots' metadata in parallel
+    const int pp = t * k + threadIdx.x;
+    s_ex[threadIdx.x] = pair_exp[pp];
+    s_wraw[threadIdx.x] = pair_w[pp];
+    s_rraw[threadIdx.x] = pair_row ? pair_row[pp] : pp;
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
     int ex[8], ord[8];
-    for (int s = 0; s < k; ++s) { ex[s] = pair_exp[(size_t)t * k + s]; ord[s] = s; }
+#pragma unroll
+    for (int s = 0; s < 8; ++s) { ex[s] = s < k ? s_ex[s] : 0x7fffffff; ord[s] = s; }
     for (int a = 1; a < k; ++a) {  // insertion sort by expert id
       const int o = ord[a];
       int b = a - 1;
@@ -247,21 +402,26 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
       ord[b + 1] = o;
     }
     for (int s = 0; s < k; ++s) {
-      const int p = t * k + ord[s];
-      s_row[s] = pair_row ? pair_row[p] : p;
-      s_w[s] = pair_w[p];
+      s_row[s] = s_rraw[ord[s]];
+      s_w[s] = s_wraw[ord[s]];
     }
   }
   __syncthreads();
   for (int h = threadIdx.x * 4; h < H; h += 1024) {
+    float4 y[8];
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (s < k) y[s] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)s_row[s] * H + h));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < k; ++s) {
-      const float4 y = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)s_row[s] * H + h));
-      const float w = s_w[s];
-      acc.x = __fadd_rn(acc.x, __fmul_rn(w, y.x));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(w, y.y));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(w, y.z));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(w, y.w));
+#pragma unroll
+    for (int s = 0; s < 8; ++s) {
+      if (s < k) {
+        const float w = s_w[s];
+        acc.x = __fadd_rn(acc.x, __fmul_rn(w, y[s].x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(w, y[s].y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(w, y[s].z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(w, y[s].w));
+      }
     }
     float r[4] = {acc.x, acc.y, acc.z, acc.w};
 #pragma unroll
@@ -269,6 +429,277 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
       float v = r[i];
       if (resid) v = __fadd_rn(load_as_f32(resid, resid_dtype, (int64_t)t * ld_resid + h + i), v);
       store_from_f32(out, out_dtype, (int64_t)t * ldo + h + i, v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Decode front end (T <= 64): RMSNorm statistics, router logits, softmax,
+// top-k, permutation tables and the prepared activation vectors in ONE launch.
+// CTA b computes the logits of expert b for every token (the row's sum of
+// squares falls out of the same pass over x) and, if b < T, prepares token b's
+// vector; the CTA that finishes last does the per-token top-k and the tables.
+// logit = rsqrt(mean(x^2)+eps) * sum_h (Wr[e][h]*wn[h]) * x[h]: the same value as
+// the CPU path's router over the normalised row up to f32 summation order.
+// ---------------------------------------------------------------------------
+struct FrontParams {
+  const void *x;
+  int x_dtype;
+  int64_t ldx;
+  const __nv_bfloat16 *norm_w;  // null: no normalisation
+  float eps;
+  const __nv_bfloat16 *Wr;
+  const float *bias;
+  int T, H, E, k, idx_stride;
+  float *logits;
+  int32_t *pair_exp;
+  float *pair_w;
+  int32_t *pair_idx, *pair_cnt, *exp_list, *n_active;
+  uint8_t *xpanel;
+  unsigned int *counter;  // [1 + token groups] words, zero before the launch
+  unsigned long long *trace;  // optional [8]: global-timer stamps of the phases of the CTA that finishes last
+};
+
+__device__ __forceinline__ unsigned long long gtime_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+constexpr int kFrontMaxT = 64;
+constexpr int kFrontMaxSlices = 8;  // H <= 2048
+constexpr int kFrontTok = 8;        // tokens per CTA
+
+// Grid (ceil(E/8), ceil(T/8)): CTA (eg, tg) computes the logits of experts
+// 8eg..8eg+7 (one per warp) for tokens 8tg..8tg+7 and prepares the vectors of
+// some of those tokens. The CTA that completes a token group does that group's
+// top-k (one warp per token); the CTA that completes the last group builds the
+// permutation tables.
+template <int DT>
+__global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
+  __shared__ float s_scale[kFrontTok];
+  __shared__ float s_red[16];
+  __shared__ int s_flag;
+  __shared__ int32_t s_pe[kFrontMaxT * 8];
+  __shared__ int32_t s_cc[16][256];  // per 32-pair chunk and expert: count, then exclusive base
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int eg = blockIdx.x, tg = blockIdx.y, n_eg = gridDim.x, n_tg = gridDim.y;
+  const int nslice = p.H / 256;
+  const int e = eg * 8 + warp;
+  const int t0 = tg * kFrontTok;
+  unsigned long long stamp[9];
+  stamp[6] = stamp[7] = stamp[8] = 0;
+  stamp[0] = gtime_ns();
+
+  // ---- logits (and the rows' scales)
+  {
+    const int ee = e < p.E ? e : p.E - 1;
+    float wr[kFrontMaxSlices][8];
+#pragma unroll
+    for (int i = 0; i < kFrontMaxSlices; ++i) {
+      if (i < nslice) {
+        load8_as_f32(p.Wr, KNJ_DT_BF16, (int64_t)ee * p.H + 256 * i + 8 * lane, wr[i]);
+        if (p.norm_w) {
+          float nw[8];
+          load8_as_f32(p.norm_w, KNJ_DT_BF16, 256 * i + 8 * lane, nw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) wr[i][j] *= nw[j];
+        }
+      }
+    }
+    const float bias = (p.bias && e < p.E) ? p.bias[e] : 0.f;
+    // the whole row of a token is fetched before it is used and the next token's row
+    // travels meanwhile, so a token costs one trip to L2 instead of one per slice
+    constexpr int NV = DT == KNJ_DT_F32 ? 2 : 1;  // 16-byte loads per 8 activations
+    uint4 ra[kFrontMaxSlices][NV], rb[kFrontMaxSlices][NV];
+    auto fetch = [&](int t, uint4 (&r)[kFrontMaxSlices][NV]) {
+#pragma unroll
+      for (int sl = 0; sl < kFrontMaxSlices; ++sl)
+        if (sl < nslice) {
+          const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(p.x) +
+                                                             ((int64_t)t * p.ldx + 256 * sl + 8 * lane) * (DT == KNJ_DT_F32 ? 4 : 2));
+#pragma unroll
+          for (int q = 0; q < NV; ++q) r[sl][q] = __ldg(src + q);
+        }
+    };
+    auto unpack = [&](const uint4 (&r)[NV], float (&v)[8]) {
+      if (DT == KNJ_DT_F32) {
+        v[0] = __uint_as_float(r[0].x); v[1] = __uint_as_float(r[0].y); v[2] = __uint_as_float(r[0].z); v[3] = __uint_as_float(r[0].w);
+        v[4] = __uint_as_float(r[NV - 1].x); v[5] = __uint_as_float(r[NV - 1].y); v[6] = __uint_as_float(r[NV - 1].z); v[7] = __uint_as_float(r[NV - 1].w);
+      } else {
+        const uint32_t u[4] = {r[0].x, r[0].y, r[0].z, r[0].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (DT == KNJ_DT_BF16) {
+            v[2 * j] = __uint_as_float(u[j] << 16);
+            v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2 *>(&u[j]);
+            v[2 * j] = __low2float(h);
+            v[2 * j + 1] = __high2float(h);
+          }
+        }
+      }
+    };
+    auto reduce_store = [&](int i, const uint4 (&r)[kFrontMaxSlices][NV]) {
+      float d0 = 0.f, d1 = 0.f, s0 = 0.f, s1 = 0.f;
+#pragma unroll
+      for (int sl = 0; sl < kFrontMaxSlices; ++sl) {
+        if (sl < nslice) {
+          float v[8];
+          unpack(r[sl], v);
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            d0 = fmaf(wr[sl][j], v[j], d0);
+            d1 = fmaf(wr[sl][j + 1], v[j + 1], d1);
+            s0 = fmaf(v[j], v[j], s0);
+            s1 = fmaf(v[j + 1], v[j + 1], s1);
+          }
+        }
+      }
+      const float dot = warp_sum(d0 + d1), ss = warp_sum(s0 + s1);
+      if (lane == 0) {
+        const float scale = p.norm_w ? 1.0f / sqrtf(ss / (float)p.H + p.eps) : 1.0f;
+        if (warp == 0) s_scale[i] = scale;
+        if (e < p.E) p.logits[(size_t)(t0 + i) * p.E + e] = dot * scale + bias;
+      }
+    };
+    const int nt = min(kFrontTok, p.T - t0);
+    stamp[6] = gtime_ns();
+    if (nt > 0) fetch(t0, ra);
+    for (int i = 0; i < nt; i += 2) {
+      if (i + 1 < nt) fetch(t0 + i + 1, rb);
+      reduce_store(i, ra);
+      if (i == 0) stamp[7] = gtime_ns();
+      if (i + 1 < nt) {
+        if (i + 2 < nt) fetch(t0 + i + 2, ra);
+        reduce_store(i + 1, rb);
+      }
+      if (i == 0) stamp[8] = gtime_ns();
+    }
+  }
+  __syncthreads();
+  stamp[1] = gtime_ns();
+
+  // ---- prepared vectors: CTA (eg, tg) takes tokens t0 + eg, t0 + eg + n_eg, ...
+  for (int i = eg; i < kFrontTok; i += n_eg) {
+    const int t = t0 + i;
+    if (t >= p.T) break;
+    const float scale = s_scale[i];
+    if (p.norm_w) {
+      panel_prep_vector(
+          [&](int k) {
+            return __fmul_rn(__fmul_rn(load_as_f32(p.x, DT, (int64_t)t * p.ldx + k), scale),
+                             __bfloat162float(p.norm_w[k]));
+          },
+          p.H, p.xpanel + (size_t)t * panel_vec_bytes(p.H), s_red);
+    } else {
+      panel_prep_vector([&](int k) { return load_as_f32(p.x, DT, (int64_t)t * p.ldx + k); }, p.H,
+                        p.xpanel + (size_t)t * panel_vec_bytes(p.H), s_red);
+    }
+  }
+
+  // ---- did this CTA complete its token group?
+  stamp[2] = gtime_ns();
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_flag = (atomicAdd(p.counter + 1 + tg, 1u) == (unsigned)n_eg - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  stamp[3] = gtime_ns();
+
+  // ---- top-k of the group's tokens, one warp each
+  {
+    const int t = t0 + warp;
+    if (t < p.T) {
+      int sel_e[8];
+      float sel_w[8];
+      warp_topk(p.logits + (size_t)t * p.E, p.E, p.k, lane, sel_e, sel_w);
+      if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < 8; ++s) {
+          if (s >= p.k) break;
+          p.pair_exp[(size_t)t * p.k + s] = sel_e[s];
+          p.pair_w[(size_t)t * p.k + s] = sel_w[s];
+        }
+      }
+    }
+  }
+
+  // ---- did this CTA complete the last group?
+  stamp[4] = gtime_ns();
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) s_flag = (atomicAdd(p.counter, 1u) == (unsigned)n_tg - 1) ? 1 : 0;
+  __syncthreads();
+  if (!s_flag) return;
+  __threadfence();
+  stamp[5] = gtime_ns();
+
+  // ---- permutation tables. Pairs are taken in chunks of 32 (one per warp pass):
+  // count per (chunk, expert), scan over chunks, then every pair knows its rank.
+  const int P = p.T * p.k;
+  const int n_chunk = (P + 31) / 32;  // <= 16
+  for (int i = threadIdx.x; i < P; i += 256) s_pe[i] = __ldcg(p.pair_exp + i);
+  for (int i = threadIdx.x; i < n_chunk * 256; i += 256) (&s_cc[0][0])[i] = 0;
+  __syncthreads();
+  for (int c = warp; c < n_chunk; c += 8) {
+    const int q = c * 32 + lane;
+    const int pe = q < P ? s_pe[q] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, pe);
+    if (pe >= 0 && (peers & ((1u << lane) - 1u)) == 0) s_cc[c][pe] = __popc(peers);  // first lane of each expert
+  }
+  __syncthreads();
+  int cnt = 0;
+  if ((int)threadIdx.x < p.E) {
+    for (int c = 0; c < n_chunk; ++c) {
+      const int n = s_cc[c][threadIdx.x];
+      s_cc[c][threadIdx.x] = cnt;
+      cnt += n;
+    }
+  }
+  __syncthreads();
+  for (int c = warp; c < n_chunk; c += 8) {
+    const int q = c * 32 + lane;
+    const int pe = q < P ? s_pe[q] : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, pe);
+    if (pe >= 0) {
+      const int rank = s_cc[c][pe] + __popc(peers & ((1u << lane) - 1u));
+      if (rank < p.idx_stride) p.pair_idx[(size_t)pe * p.idx_stride + rank] = q;
+    }
+  }
+  if ((int)threadIdx.x < p.E) {
+    const int c2 = min(cnt, p.idx_stride);
+    for (int i = c2; i < p.idx_stride; ++i) p.pair_idx[(size_t)threadIdx.x * p.idx_stride + i] = -1;
+    p.pair_cnt[threadIdx.x] = c2;
+    cnt = c2;
+  }
+  // active experts, ascending
+  __shared__ int s_wsum[8], s_wmax[8];
+  const unsigned m = __ballot_sync(0xffffffffu, cnt > 0);
+  int cm = cnt;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) cm = max(cm, __shfl_xor_sync(0xffffffffu, cm, o));
+  if (lane == 0) { s_wsum[warp] = __popc(m); s_wmax[warp] = cm; }
+  __syncthreads();
+  int off = 0, tot = 0, mxc = 0;
+  for (int w = 0; w < 8; ++w) {
+    if (w < warp) off += s_wsum[w];
+    tot += s_wsum[w];
+    mxc = max(mxc, s_wmax[w]);
+  }
+  if (cnt > 0) p.exp_list[off + __popc(m & ((1u << lane) - 1u))] = threadIdx.x;
+  for (int i = tot + threadIdx.x; i < p.E; i += 256) p.exp_list[i] = -1;
+  if (threadIdx.x == 0) {
+    p.n_active[0] = tot;
+    p.n_active[1] = mxc;
+    if (p.trace) {
+      for (int i = 0; i < 6; ++i) p.trace[i] = stamp[i];
+      p.trace[6] = gtime_ns();
+      p.trace[7] = stamp[6];
+      p.trace[8] = stamp[7];
+      p.trace[9] = stamp[8];
     }
   }
 }
@@ -303,10 +734,20 @@ int knj_router_topk_launch(const void *x, int x_dtype, int64_t ldx, const uint16
   KNJ_REQUIRE(k >= 1 && k <= 8 && k <= E, "knj_router_topk: top_k=%d out of range (1..8, <= E)", k);
   KNJ_REQUIRE(aligned16(Wr_bf16), "knj_router_topk: router weight must be 16-byte aligned");
   if (T <= 0) return KNJ_OK;
-  dim3 grid((E + 7) / 8, (T + kRouterTT - 1) / kRouterTT);
-  router_logits_kernel<<<grid, 256, 0, as_stream(s)>>>(x, x_dtype, ldx, reinterpret_cast<const __nv_bfloat16 *>(Wr_bf16),
-                                                       bias, T, H, E, logits);
-  int rc = launch_status("router_logits_kernel");
+  int rc;
+  if (T >= 32 && H % 32 == 0 && ldx % 8 == 0 && aligned16(x)) {
+    dim3 grid((E + 63) / 64, (T + 63) / 64);
+    const __nv_bfloat16 *wr = reinterpret_cast<const __nv_bfloat16 *>(Wr_bf16);
+    if (x_dtype == KNJ_DT_BF16) router_logits_mma_kernel<KNJ_DT_BF16><<<grid, 128, 0, as_stream(s)>>>(x, ldx, wr, bias, T, H, E, logits);
+    else if (x_dtype == KNJ_DT_F32) router_logits_mma_kernel<KNJ_DT_F32><<<grid, 128, 0, as_stream(s)>>>(x, ldx, wr, bias, T, H, E, logits);
+    else router_logits_mma_kernel<KNJ_DT_F16><<<grid, 128, 0, as_stream(s)>>>(x, ldx, wr, bias, T, H, E, logits);
+    rc = launch_status("router_logits_mma_kernel");
+  } else {
+    dim3 grid((E + 7) / 8, (T + kRouterTT - 1) / kRouterTT);
+    router_logits_kernel<<<grid, 256, 0, as_stream(s)>>>(x, x_dtype, ldx, reinterpret_cast<const __nv_bfloat16 *>(Wr_bf16),
+                                                         bias, T, H, E, logits);
+    rc = launch_status("router_logits_kernel");
+  }
   if (rc) return rc;
   router_topk_kernel<<<(T + 3) / 4, 128, 0, as_stream(s)>>>(logits, T, E, k, pair_exp, pair_w);
   return launch_status("router_topk_kernel");
@@ -321,6 +762,39 @@ int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride
   if (rc) return rc;
   active_list_kernel<<<1, 256, 0, as_stream(s)>>>(pair_cnt, E, exp_list, n_active);
   return launch_status("active_list_kernel");
+}
+
+static unsigned long long *g_front_trace = nullptr;
+// Measurement hook (no reference counterpart): device buffer of 16 u64 that receives
+// global-timer stamps of the front kernel's phases; NULL switches it off.
+void knj_moe_front_trace(void *dev_buf) { g_front_trace = static_cast<unsigned long long *>(dev_buf); }
+
+int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *norm_w, float eps,
+                         const uint16_t *Wr_bf16, const float *bias, int T, int H, int E, int k, float *logits,
+                         int32_t *pair_exp, float *pair_w, int32_t *pair_idx, int idx_stride, int32_t *pair_cnt,
+                         int32_t *exp_list, int32_t *n_active, void *xpanel, uint32_t *counter, knj_stream_t s) {
+  KNJ_REQUIRE(x && Wr_bf16 && logits && pair_exp && pair_w && pair_idx && pair_cnt && exp_list && n_active && xpanel && counter,
+              "knj_moe_front: null pointer");
+  KNJ_REQUIRE(T >= 1 && T <= kFrontMaxT, "knj_moe_front: T=%d out of range (1..%d)", T, kFrontMaxT);
+  KNJ_REQUIRE(H % 256 == 0 && H <= 256 * kFrontMaxSlices, "knj_moe_front: H=%d must be a multiple of 256, <= %d", H,
+              256 * kFrontMaxSlices);
+  KNJ_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= 8 && k <= E && idx_stride >= T, "knj_moe_front: bad E / k / stride");
+  KNJ_REQUIRE(aligned16(Wr_bf16) && aligned16(xpanel) && (!norm_w || aligned16(norm_w)) && aligned16(x) && ldx % 8 == 0,
+              "knj_moe_front: 16-byte alignment of x rows, weights and panel");
+  FrontParams p{};
+  p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.norm_w = reinterpret_cast<const __nv_bfloat16 *>(norm_w); p.eps = eps;
+  p.Wr = reinterpret_cast<const __nv_bfloat16 *>(Wr_bf16); p.bias = bias; p.T = T; p.H = H; p.E = E; p.k = k;
+  p.idx_stride = idx_stride; p.logits = logits; p.pair_exp = pair_exp; p.pair_w = pair_w; p.pair_idx = pair_idx;
+  p.pair_cnt = pair_cnt; p.exp_list = exp_list; p.n_active = n_active; p.xpanel = static_cast<uint8_t *>(xpanel);
+  p.counter = counter;
+  p.trace = g_front_trace;
+  const int n_tg = (T + kFrontTok - 1) / kFrontTok;
+  KNJ_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t) * (1 + n_tg), as_stream(s)));
+  dim3 grid((E + 7) / 8, n_tg);
+  if (x_dtype == KNJ_DT_F32) moe_front_kernel<KNJ_DT_F32><<<grid, 256, 0, as_stream(s)>>>(p);
+  else if (x_dtype == KNJ_DT_BF16) moe_front_kernel<KNJ_DT_BF16><<<grid, 256, 0, as_stream(s)>>>(p);
+  else moe_front_kernel<KNJ_DT_F16><<<grid, 256, 0, as_stream(s)>>>(p);
+  return launch_status("moe_front_kernel");
 }
 
 int knj_active_list_launch(const int32_t *pair_cnt, int E, int32_t *exp_list, int32_t *n_active, knj_stream_t s) {
