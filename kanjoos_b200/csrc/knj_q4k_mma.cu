@@ -371,13 +371,12 @@ int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st
   // and keep the whole prepared vectors of a pass resident in shared memory
   p.tp_alloc = max_tokens < TP ? (max_tokens < 1 ? 1 : max_tokens) : TP;
   p.resident = (size_t)p.tp_alloc * panel_vec_bytes(p.K) <= 40 * 1024 ? 1 : 0;
+  // Defaults measured on B200 (48-layer resident stack, batch 1/8/64): two K-parts per tile for the long
+  // gate/up rows (more warps per SM for the same shared memory), whole rows for the short down rows.
   int ks = 1;
-  if (max_tokens <= 8) {
-    for (int c : {4, 3, 2})
-      if (nsb % c == 0 && (p.resident || p.tp_alloc * c <= 32)) { ks = c; break; }
-  }
+  if (DUAL && nsb % 2 == 0 && (p.resident || p.tp_alloc * 2 <= 32)) ks = 2;
   if (g_force_ks > 0 && nsb % g_force_ks == 0 && (p.resident || p.tp_alloc * g_force_ks <= 32)) ks = g_force_ks;
-  int tg = ks >= 4 ? 1 : (ks >= 3 ? 2 : 8);
+  int tg = (DUAL && max_tokens <= 4) ? 4 : 8;
   if (g_force_tg > 0) tg = g_force_tg;
   while (tg > 1 && (p.tiles_per_expert % tg != 0 || tg * ks > 16)) tg >>= 1;
   p.ks = ks;
@@ -419,7 +418,7 @@ int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st
 
 template <bool DUAL>
 int launch_proj_nt(const ProjParams &p, int n_experts_max, int max_tokens, cudaStream_t st) {
-  int nt = max_tokens <= 4 ? 1 : (max_tokens <= 8 ? 2 : 4);
+  int nt = max_tokens <= 4 ? 1 : 2;  // 8 tokens per pass: experts of a decode batch rarely see more
   if (g_force_nt > 0) nt = g_force_nt;
   if (nt == 1) return launch_proj<DUAL, 1>(p, n_experts_max, max_tokens, st);
   if (nt == 2) return launch_proj<DUAL, 2>(p, n_experts_max, max_tokens, st);

@@ -373,11 +373,12 @@ __global__ void __launch_bounds__(256) active_list_kernel(const int32_t *__restr
 // (src/model/model.cpp:464-508). The residual is added last, as the caller of
 // the MoE branch does (src/model/model.cpp:652).
 // ---------------------------------------------------------------------------
+template <int RDT, int ODT>
 __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ Y, const int32_t *__restrict__ pair_row,
                                                       const int32_t *__restrict__ pair_exp,
                                                       const float *__restrict__ pair_w, const void *__restrict__ resid,
-                                                      int resid_dtype, int64_t ld_resid, void *__restrict__ out,
-                                                      int out_dtype, int64_t ldo, int H, int k) {
+                                                      int64_t ld_resid, void *__restrict__ out, int64_t ldo, int H,
+                                                      int k) {
   const int t = blockIdx.x;
   __shared__ int s_row[8];
   __shared__ float s_w[8];
@@ -424,12 +425,12 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
       }
     }
     float r[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (resid) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float v = r[i];
-      if (resid) v = __fadd_rn(load_as_f32(resid, resid_dtype, (int64_t)t * ld_resid + h + i), v);
-      store_from_f32(out, out_dtype, (int64_t)t * ldo + h + i, v);
+      for (int i = 0; i < 4; ++i) r[i] = __fadd_rn(load_as_f32(resid, RDT, (int64_t)t * ld_resid + h + i), r[i]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) store_from_f32(out, ODT, (int64_t)t * ldo + h + i, r[i]);
   }
 }
 
@@ -810,8 +811,21 @@ int knj_moe_combine_launch(const float *Y, const int32_t *pair_row, const int32_
   KNJ_REQUIRE(H > 0 && H % 4 == 0 && k >= 1 && k <= 8, "knj_moe_combine: H %% 4 == 0 and 1 <= k <= 8 required");
   KNJ_REQUIRE(aligned16(Y), "knj_moe_combine: Y must be 16-byte aligned");
   if (T <= 0) return KNJ_OK;
-  combine_kernel<<<T, 256, 0, as_stream(s)>>>(Y, pair_row, pair_exp, pair_w, resid, resid_dtype, ld_resid, out,
-                                              out_dtype, ldo, H, k);
+  KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_moe_combine: out must be f32 or bf16");
+  KNJ_REQUIRE(!resid || (resid_dtype >= KNJ_DT_F32 && resid_dtype <= KNJ_DT_F16), "knj_moe_combine: unknown residual dtype");
+  cudaStream_t st = as_stream(s);
+#define KNJ_COMBINE(R, O) combine_kernel<R, O><<<T, 256, 0, st>>>(Y, pair_row, pair_exp, pair_w, resid, ld_resid, out, ldo, H, k)
+  const int rd = resid ? resid_dtype : KNJ_DT_F32;
+  if (out_dtype == KNJ_DT_F32) {
+    if (rd == KNJ_DT_F32) KNJ_COMBINE(KNJ_DT_F32, KNJ_DT_F32);
+    else if (rd == KNJ_DT_BF16) KNJ_COMBINE(KNJ_DT_BF16, KNJ_DT_F32);
+    else KNJ_COMBINE(KNJ_DT_F16, KNJ_DT_F32);
+  } else {
+    if (rd == KNJ_DT_F32) KNJ_COMBINE(KNJ_DT_F32, KNJ_DT_BF16);
+    else if (rd == KNJ_DT_BF16) KNJ_COMBINE(KNJ_DT_BF16, KNJ_DT_BF16);
+    else KNJ_COMBINE(KNJ_DT_F16, KNJ_DT_BF16);
+  }
+#undef KNJ_COMBINE
   return launch_status("combine_kernel");
 }
 
