@@ -355,7 +355,8 @@ def run_gpu(args):
     cb = None
     dec = None
     if world == 1:
-        cb, _ = cpu_layer_tokens_per_s(args.cpu_sample, 1, 1, "uniform")
+        if args.cpu_sample > 0:
+            cb, _ = cpu_layer_tokens_per_s(args.cpu_sample, 1, 1, "uniform")
         if not args.no_decode:
             del banks, layers
             torch.cuda.empty_cache()

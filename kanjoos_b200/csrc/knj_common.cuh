@@ -2,6 +2,7 @@
 // plumbing, PTX wrappers (mbarrier, bulk async copy, warp MMA), bounded waits.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -37,6 +38,12 @@ inline int launch_status(const char *what) {
 inline cudaStream_t as_stream(knj_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 int sm_count();  // SMs of the current device (cached per device)
+
+// TMA descriptor over a matrix of `rows` byte rows (`row_bytes` each, a multiple of 16, base 16-byte aligned),
+// seen as 32-bit words; one copy moves a box of box_rows rows x box_bytes bytes (box_bytes <= 1024, multiple
+// of 16) into dense shared memory. No swizzle, no multicast.
+int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t row_bytes, uint32_t box_bytes,
+                        uint32_t box_rows);
 
 // ---- device helpers --------------------------------------------------------
 #if defined(__CUDACC__)
@@ -89,12 +96,53 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   }
 }
 
+// Same contract, but polls with the non-suspending test_wait: lowest wake-up latency,
+// for pipelines whose stage hand-offs sit on the critical path.
+__device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag = nullptr) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_test(bar, parity)) return true;
+    if (abort_flag && *abort_flag) return false;
+    if (clock64() - t0 > kMaxWaitCycles) {
+      if (abort_flag) *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // Bulk async copy global -> shared of `bytes` (multiple of 16, both addresses
 // 16-byte aligned), completion counted on `bar`. Never uses cluster multicast.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(dst_smem)),
                "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// TMA tiled copy of one box: x = first 32-bit word inside the row (a multiple of 4), y = first row.
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ void tma_load_rows(void *dst_smem, const CUtensorMap *map, int x_words, int y_row, uint64_t *bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(reinterpret_cast<uint64_t>(map)), "r"(x_words), "r"(y_row), "r"(smem_u32(bar))
                : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }

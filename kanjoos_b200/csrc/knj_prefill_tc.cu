@@ -57,7 +57,13 @@ struct TcParams {
   int64_t idxStride;
   float out_scale;
   int *status;
+  unsigned long long *trace;  // optional: SM-clock stamps of CTA 0's first slabs (measurement hook)
+  int trace_ctas;             // per-CTA records that fit behind the 64 slab stamps
+  CUtensorMap map0, map1;     // TMA descriptors of W0 / W1, box = one superblock (36 words) x 32 rows
 };
+
+unsigned long long *g_tc_trace = nullptr;
+int g_tc_trace_ctas = 0;
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -113,7 +119,8 @@ __device__ __forceinline__ uint32_t instr_desc_f16(int n) {
   return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRowsM >> 4) << 24);
 }
 
-__device__ __forceinline__ void producer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(kProducerThreads) : "memory"); }
+// the two unpacker warps that own the same 32 weight rows (one per 16-byte half) meet on their own barrier
+__device__ __forceinline__ void pair_sync(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory"); }
 
 template <int NMAT>
 struct Smem {
@@ -127,11 +134,14 @@ struct Smem {
   static constexpr int kOffPairs = kOffRaw + 2 * kRawBuf;       // int32 pair id per token of the bucket
   static constexpr int kOffRows = kOffPairs + kMaxTok * 4;      // int32 activation row per token
   static constexpr int kOffBars = kOffRows + kMaxTok * 4;       // mbarriers
-  static constexpr int kBytes = kOffBars + 128 + 1024;          // + alignment slack
+  static constexpr int kBytes = kOffBars + 192 + 1024;          // + alignment slack
 };
 
-template <int NMAT>
-__global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcParams p) {
+// NMAT = 2 with GATEUP: gate and up tiles of the same 128 output indices (one shared token operand, SiLU*up
+// epilogue). NMAT = 2 without: two consecutive 128-row tiles of one matrix (halves the token-operand traffic
+// of the down projection). NMAT = 1: one tile.
+template <int NMAT, bool GATEUP>
+__global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __grid_constant__ TcParams p) {
   using S = Smem<NMAT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -148,25 +158,31 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
     want -= nt;
   }
   if (e < 0) return;  // uniform across the CTA: nothing allocated yet
+  unsigned long long *cta_rec = (p.trace && (int)blockIdx.x < p.trace_ctas) ? p.trace + 64 + 4 * (size_t)blockIdx.x : nullptr;
+  if (cta_rec && tid == 0) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    cta_rec[0] = global_timer_ns();
+    cta_rec[3] = ((unsigned long long)smid << 32) | (unsigned)(cnt - tok0 < kMaxTok ? cnt - tok0 : kMaxTok);
+  }
   const int ntok = min(kMaxTok, cnt - tok0);
   const int n_mma = (ntok + 15) & ~15;  // MMA N: multiple of 16
-  const int m0 = m_tile * kRowsM;
+  const int m0 = m_tile * kRowsM * (GATEUP ? 1 : NMAT);
   const int nsb = p.K / KNJ_QK_K, nslab = p.K / kSlabK;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kOffBars);
   uint64_t *full = bars;               // [kStages] producers -> MMA
   uint64_t *empty = bars + kStages;    // [kStages] MMA -> producers
-  uint64_t *raw_full = bars + 2 * kStages;  // [2] bulk copies landed
-  uint64_t *acc_full = bars + 2 * kStages + 2;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 3);
+  uint64_t *raw_full = bars + 2 * kStages;  // [2 buffers][4 row groups] bulk copies landed
+  uint64_t *acc_full = bars + 2 * kStages + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 9);
   volatile int *s_fail = reinterpret_cast<volatile int *>(tmem_slot + 1);  // raised by the first wait that gives up
   int32_t *s_pair = reinterpret_cast<int32_t *>(smem + S::kOffPairs);
   int32_t *s_row = reinterpret_cast<int32_t *>(smem + S::kOffRows);
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], kProducerThreads + kLoaderThreads); mbar_init(&empty[s], 1); }
-    mbar_init(&raw_full[0], NMAT * kRowsM);
-    mbar_init(&raw_full[1], NMAT * kRowsM);
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], (kProducerThreads + kLoaderThreads) / 32); mbar_init(&empty[s], 1); }
+    for (int i = 0; i < 8; ++i) mbar_init(&raw_full[i], 1);
     mbar_init(acc_full, 1);
     *s_fail = 0;
     mbar_init_fence();
@@ -194,63 +210,81 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
   if (warp < 8) {
     // =========================== producers ===========================
     const int row = tid & 127, half = tid >> 7;  // weight row, which 16 of the slab's 32 code bytes
+    const int pair = warp & 3;                   // rows 32*pair .. 32*pair+31: this warp and warp ^ 4
+    // one TMA box per matrix and row group: 32 rows x one superblock (a single copy instruction each; per-row
+    // bulk copies cost the copy unit about 25 cycles apiece and stalled every superblock boundary)
     auto issue_raw = [&](int b) {
-      if (tid < NMAT * kRowsM) {
-        const int mat = tid >> 7;
-        const uint8_t *src = (mat == 0 ? p.W0 : p.W1) + ((size_t)e * p.N + m0 + row) * p.rowBytes + (size_t)b * KNJ_Q4K_BYTES;
-        uint8_t *dst = smem + S::kOffRaw + (b & 1) * S::kRawBuf + (mat * kRowsM + row) * KNJ_Q4K_BYTES;
-        mbar_expect_tx(&raw_full[b & 1], KNJ_Q4K_BYTES);
-        bulk_g2s(dst, src, KNJ_Q4K_BYTES, &raw_full[b & 1]);
+      if (warp < 4 && lane == 0) {
+        uint64_t *bar = &raw_full[(b & 1) * 4 + pair];
+        mbar_expect_tx(bar, (uint32_t)NMAT * 32u * KNJ_Q4K_BYTES);
+#pragma unroll
+        for (int mat = 0; mat < NMAT; ++mat) {
+          uint8_t *dst = smem + S::kOffRaw + (b & 1) * S::kRawBuf + (mat * kRowsM + 32 * pair) * KNJ_Q4K_BYTES;
+          const int y = e * p.N + m0 + (GATEUP ? 0 : mat * kRowsM) + 32 * pair;
+          tma_load_rows(dst, (GATEUP && mat == 1) ? &p.map1 : &p.map0, b * (KNJ_Q4K_BYTES / 4), y, bar);
+        }
       }
     };
     fence_proxy_async();
     issue_raw(0);
     for (int b = 0; b < nsb; ++b) {
-      // everyone is done reading the buffer the next superblock lands in
-      producer_sync();
+      // both warps of the row group are done reading the buffer the next superblock lands in
+      pair_sync(pair);
       if (*s_fail) ok = false;
       if (!ok) continue;
       if (b + 1 < nsb) {
         fence_proxy_async();
         issue_raw(b + 1);
       }
-      if (!mbar_wait(&raw_full[b & 1], (b >> 1) & 1, s_fail)) { ok = false; continue; }
+      if (!mbar_wait(&raw_full[(b & 1) * 4 + pair], (b >> 1) & 1, s_fail)) { ok = false; continue; }
       const uint8_t *raw = smem + S::kOffRaw + (b & 1) * S::kRawBuf;
 
-      for (int G = 0; G < 4 && ok; ++G) {
+      // ---- once per superblock: (d*sc, -dmin*m) of this row's eight sub-blocks in fp16.
+      // d*sc is an 11-bit by 6-bit product, so one fp16 multiply rounds it exactly as a
+      // float multiply followed by a conversion would.
+      const __half2 k1024 = __float2half2_rn(1024.0f);
+      __half2 d1h[NMAT][8], m1h[NMAT][8];
+#pragma unroll
+      for (int mat = 0; mat < NMAT; ++mat) {
+        const uint4 hdr = *reinterpret_cast<const uint4 *>(raw + (mat * kRowsM + row) * KNJ_Q4K_BYTES);
+        const __half2 dd = __half2half2(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+        const __half2 dm = __hneg2(__half2half2(__ushort_as_half((unsigned short)(hdr.x >> 16))));
+        const uint32_t sc4[2] = {hdr.y & 0x3f3f3f3fu, (hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u)};
+        const uint32_t mn4[2] = {hdr.z & 0x3f3f3f3fu, ((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u)};
+#pragma unroll
+        for (int hb = 0; hb < 2; ++hb) {
+#pragma unroll
+          for (int pr = 0; pr < 2; ++pr) {
+            // bytes (2pr, 2pr+1) of the four six-bit values -> fp16 pair via 1024 + v
+            const uint32_t es = __byte_perm(sc4[hb], 0x64646464u, pr ? 0x4342 : 0x4140);
+            const uint32_t em = __byte_perm(mn4[hb], 0x64646464u, pr ? 0x4342 : 0x4140);
+            const __half2 s2 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&es), k1024), dd);
+            const __half2 m2 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&em), k1024), dm);
+            d1h[mat][4 * hb + 2 * pr] = __low2half2(s2);
+            d1h[mat][4 * hb + 2 * pr + 1] = __high2half2(s2);
+            m1h[mat][4 * hb + 2 * pr] = __low2half2(m2);
+            m1h[mat][4 * hb + 2 * pr + 1] = __high2half2(m2);
+          }
+        }
+      }
+
+#pragma unroll
+      for (int G = 0; G < 4; ++G) {
+        if (!ok) break;
         const int ks = b * 4 + G, stage = ks % kStages;
+        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 16) p.trace[4 * ks + 0] = clock64();
         if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
         tc_fence_after();
-
+        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 16) p.trace[4 * ks + 1] = clock64();
         // ---- weight operand(s): 16 code bytes -> 16 low-nibble + 16 high-nibble weights of this row
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
-          const uint8_t *blk = raw + (mat * kRowsM + row) * KNJ_Q4K_BYTES;
-          const uint4 hdr = *reinterpret_cast<const uint4 *>(blk);
-          const uint4 q = *reinterpret_cast<const uint4 *>(blk + KNJ_Q4K_OFF_QS + 32 * G + 16 * half);
-          const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
-          const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
-          // 6-bit scale / min of sub-blocks 2G (low nibbles) and 2G+1 (high nibbles)
-          uint32_t sc[2], mn[2];
-#pragma unroll
-          for (int par = 0; par < 2; ++par) {
-            const int j = 2 * G + par;
-            if (j < 4) {
-              sc[par] = (hdr.y >> (8 * j)) & 63u;
-              mn[par] = (hdr.z >> (8 * j)) & 63u;
-            } else {
-              const uint32_t hi = (hdr.w >> (8 * (j - 4))) & 0xffu;
-              sc[par] = (hi & 15u) | ((((hdr.y >> (8 * (j - 4))) & 0xffu) >> 6) << 4);
-              mn[par] = (hi >> 4) | ((((hdr.z >> (8 * (j - 4))) & 0xffu) >> 6) << 4);
-            }
-          }
+          const uint4 q = *reinterpret_cast<const uint4 *>(raw + (mat * kRowsM + row) * KNJ_Q4K_BYTES + KNJ_Q4K_OFF_QS + 32 * G + 16 * half);
           uint8_t *at = smem + S::kOffA + (stage * NMAT + mat) * S::kATile + row * 128;
           const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-          const __half2 k1024 = __float2half2_rn(1024.0f);
 #pragma unroll
           for (int par = 0; par < 2; ++par) {
-            const __half2 d1 = __float2half2_rn(fminf(d * (float)sc[par], 65504.0f));
-            const __half2 m1 = __float2half2_rn(-(dmin * (float)mn[par]));
+            const __half2 d1 = d1h[mat][2 * G + par], m1 = m1h[mat][2 * G + par];
             uint32_t o[8];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -270,7 +304,9 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
           }
         }
         fence_proxy_async();
-        mbar_arrive(&full[stage]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full[stage]);
+        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 16) p.trace[4 * ks + 2] = clock64();
       }
     }
   } else if (warp >= 9) {
@@ -307,15 +343,17 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
       }
       if (ks + 1 < nslab) fetch(ks + 1);  // next slab's rows travel while this stage is consumed
       fence_proxy_async();
-      mbar_arrive(&full[stage]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full[stage]);
     }
   } else if (warp == 8 && lane == 0) {
     // =========================== MMA issue ===========================
     const uint32_t idesc = instr_desc_f16(n_mma);
     for (int ks = 0; ks < nslab && ok; ++ks) {
       const int stage = ks % kStages;
-      if (!mbar_wait(&full[stage], (ks / kStages) & 1, s_fail)) { ok = false; break; }
+      if (!mbar_spin(&full[stage], (ks / kStages) & 1, s_fail)) { ok = false; break; }
       tc_fence_after();
+      if (p.trace && blockIdx.x == 0 && ks < 16) p.trace[4 * ks + 3] = clock64();
       const uint32_t b_addr = smem_u32(smem + S::kOffB + stage * S::kBTile);
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
@@ -334,39 +372,66 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const TcPar
   if (warp < 8) {
     if (ok && !mbar_wait(acc_full, 0, s_fail)) ok = false;
     tc_fence_after();
-    if (ok) {
-      const int lane_base = 32 * (warp & 3);
-      const int n = m0 + lane_base + lane;  // output index of this thread's accumulator row
-      for (int c = (warp >> 2); c * 16 < n_mma; c += 2) {
-        float g[16];
-        tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + c * 16, g);
-        if (NMAT == 2) {
-          float u[16];
-          tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + kMaxTok + c * 16, u);
-          __half *A = static_cast<__half *>(p.out);
+    if (cta_rec && tid == 0) cta_rec[1] = global_timer_ns();
+    // The accumulator rows are output indices (one per thread) and the columns tokens, while the outputs are
+    // token-major: transpose through the operand stages (idle now), then write whole 256- or 512-byte row
+    // segments, 16 bytes per lane. Every unpacker thread takes part in the barriers even after a failed wait.
+    const bool tr = p.trace && blockIdx.x == 0 && tid == 0;
+    if (tr) p.trace[48] = clock64();
+    const int lane_base = 32 * (warp & 3);
+    uint8_t *stg = smem + S::kOffA;
+    constexpr int kEpiMats = GATEUP ? 1 : NMAT;
+    constexpr int kRowB = GATEUP ? kRowsM * 2 : kRowsM * 4;  // staged bytes per token
+    static_assert(kMaxTok * kRowB <= S::kOffPairs, "epilogue staging does not fit the operand stages");
+#pragma unroll 1
+    for (int mat = 0; mat < kEpiMats; ++mat) {
+      if (ok) {
+        for (int c = (warp >> 2); c * 16 < n_mma; c += 2) {
+          float g[16];
+          tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + mat * kMaxTok + c * 16, g);
+          if (GATEUP) {
+            float u[16];
+            tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + kMaxTok + c * 16, u);
+            if (tr && c < 4) p.trace[53 + c] = clock64();
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int pr = s_pair[c * 16 + j];
-            if (pr >= 0) {
-              const float a = (g[j] / (1.0f + __expf(-g[j]))) * u[j] * p.out_scale;
-              A[(size_t)pr * p.N + n] = __float2half_rn(fminf(fmaxf(a, -65504.0f), 65504.0f));
+            for (int j = 0; j < 16; ++j) {
+              const float a = __fdividef(g[j], 1.0f + __expf(-g[j])) * u[j] * p.out_scale;
+              *reinterpret_cast<__half *>(stg + (c * 16 + j) * kRowB + (lane_base + lane) * 2) =
+                  __float2half_rn(fminf(fmaxf(a, -65504.0f), 65504.0f));
             }
-          }
-        } else {
-          float *Y = static_cast<float *>(p.out);
+            if (tr && c < 4) p.trace[54 + c] = clock64();
+          } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int pr = s_pair[c * 16 + j];
-            if (pr >= 0) Y[(size_t)pr * p.N + n] = g[j] * p.out_scale;
+            for (int j = 0; j < 16; ++j)
+              *reinterpret_cast<float *>(stg + (c * 16 + j) * kRowB + (lane_base + lane) * 4) = g[j] * p.out_scale;
           }
         }
       }
+      if (tr) p.trace[49 + 2 * mat] = clock64();
+      asm volatile("bar.sync 5, 256;" ::: "memory");
+      if (ok) {
+        constexpr int kLanesPerRow = kRowB / 16;            // 16 (fp16) or 32 (f32)
+        constexpr int kRowsPerInstr = 32 / kLanesPerRow;    // 2 or 1
+        const int sub = lane / kLanesPerRow, l16 = lane % kLanesPerRow;
+        for (int r = warp * kRowsPerInstr + sub; r < ntok; r += 8 * kRowsPerInstr) {
+          const int pr = s_pair[r];
+          const uint4 v = *reinterpret_cast<const uint4 *>(stg + r * kRowB + l16 * 16);
+          uint8_t *dst = GATEUP ? reinterpret_cast<uint8_t *>(static_cast<__half *>(p.out) + (size_t)pr * p.N + m0)
+                                : reinterpret_cast<uint8_t *>(static_cast<float *>(p.out) + (size_t)pr * p.N + m0 + mat * kRowsM);
+          *reinterpret_cast<uint4 *>(dst + l16 * 16) = v;
+        }
+      }
+      if (tr) p.trace[50 + 2 * mat] = clock64();
+      if (mat + 1 < kEpiMats) asm volatile("bar.sync 5, 256;" ::: "memory");
     }
   }
+  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[60] = clock64();
   if (!ok && lane == 0 && p.status) atomicExch(p.status, 1);
   tc_fence_before();
   __syncthreads();
+  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[61] = clock64();
   if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+  if (cta_rec && tid == 0) cta_rec[2] = global_timer_ns();
 }
 
 // x (f32 / bf16 / f16) -> fp16 with saturation, rows dense
@@ -378,16 +443,25 @@ __global__ void to_f16_kernel(const void *__restrict__ x, int dtype, int64_t ldx
   }
 }
 
-template <int NMAT>
-int launch_tc(const TcParams &p, int max_pairs, cudaStream_t st) {
+template <int NMAT, bool GATEUP>
+int launch_tc(TcParams p, int max_pairs, cudaStream_t st) {
   using S = Smem<NMAT>;
   int dev = 0;
   KNJ_CUDA(cudaGetDevice(&dev));
-  auto kern = q4k_grouped_tc_kernel<NMAT>;
+  auto kern = q4k_grouped_tc_kernel<NMAT, GATEUP>;
   static bool opted[64] = {false};
   if (dev >= 0 && dev < 64 && !opted[dev]) {
     KNJ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
     opted[dev] = true;
+  }
+  {
+    const uint64_t rows = (uint64_t)p.n_experts * p.N;
+    int rc = make_row_tensor_map(&p.map0, p.W0, rows, (uint32_t)p.rowBytes, KNJ_Q4K_BYTES, 32);
+    if (rc) return rc;
+    if (GATEUP) {
+      rc = make_row_tensor_map(&p.map1, p.W1, rows, (uint32_t)p.rowBytes, KNJ_Q4K_BYTES, 32);
+      if (rc) return rc;
+    }
   }
   // worst case number of token buckets: every expert has a ragged tail
   const long long buckets = (long long)max_pairs / kMaxTok + p.n_experts;
@@ -400,6 +474,15 @@ int launch_tc(const TcParams &p, int max_pairs, cudaStream_t st) {
 }  // namespace
 
 extern "C" {
+
+// Measurement hook (no reference counterpart): device buffer of 64 + 4 * cta_slots u64. The first 64 receive
+// SM-clock stamps of the first 16 slabs of CTA 0 -- [4k] unpacker starts slab k, [4k+1] stage free, [4k+2] stage
+// published, [4k+3] MMA sees it; then per CTA b < cta_slots: global-timer ns at start, accumulator complete,
+// end, and (SM id << 32 | tokens of its bucket).
+void knj_tc_trace(void *dev_buf, int cta_slots) {
+  g_tc_trace = static_cast<unsigned long long *>(dev_buf);
+  g_tc_trace_ctas = dev_buf ? cta_slots : 0;
+}
 
 int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s) {
   KNJ_REQUIRE(x && out_f16, "knj_to_f16: null pointer");
@@ -426,8 +509,8 @@ int knj_q4k_gateup_tc_launch(const void *Xh, const uint8_t *Wg, const uint8_t *W
   TcParams p{};
   p.X = static_cast<const __half *>(Xh); p.W0 = Wg; p.W1 = Wu; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
   p.row_map = pair_tok; p.out = A_f16; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = top_k > 0 ? top_k : 1;
-  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = kActPrescale; p.status = status;
-  return launch_tc<2>(p, max_pairs, as_stream(s));
+  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = kActPrescale; p.status = status; p.trace = g_tc_trace; p.trace_ctas = g_tc_trace_ctas;
+  return launch_tc<2, true>(p, max_pairs, as_stream(s));
 }
 
 int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pair_idx, const int32_t *pair_cnt,
@@ -443,8 +526,13 @@ int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pai
   TcParams p{};
   p.X = static_cast<const __half *>(Ah); p.W0 = Wd; p.W1 = nullptr; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
   p.row_map = pair_row; p.out = Y; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
-  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status;
-  return launch_tc<1>(p, max_pairs, as_stream(s));
+  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; p.trace = g_tc_trace; p.trace_ctas = g_tc_trace_ctas;
+  if (N % (2 * kRowsM) == 0) {  // two row tiles per CTA share every gathered token tile
+    p.m_tiles = N / (2 * kRowsM);
+    return launch_tc<2, false>(p, max_pairs, as_stream(s));
+  }
+  p.m_tiles = N / kRowsM;
+  return launch_tc<1, false>(p, max_pairs, as_stream(s));
 }
 
 }  // extern "C"

@@ -73,6 +73,7 @@ struct ProjParams {
   int resident;   // 1: whole panel vectors of a pass are staged at once (small batch); 0: one superblock chunk per step
   int64_t idxStride;
   int *status;    // optional: set to 1 when a bounded wait gave up
+  CUtensorMap map0, map1;  // TMA descriptors of W0 / W1: box = this launch's row part x tile rows
 };
 
 struct ProjSmem {
@@ -97,7 +98,7 @@ __host__ __device__ inline ProjSmem proj_smem(int warps, int pitch, int ks, int 
 // All warps of the CTA walk the K steps in lockstep because they share the
 // staged activation chunks (double buffered, one bulk copy per token and part).
 template <bool DUAL, int NT>
-__global__ void __launch_bounds__(512) q4k_proj_kernel(const ProjParams p) {
+__global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ ProjParams p) {
   constexpr int TP = 4 * NT;  // tokens per pass
   extern __shared__ __align__(128) uint8_t smem[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
@@ -139,18 +140,19 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const ProjParams p) {
     const int cnt = p.pair_cnt[e];
     const int n0 = (grp * p.tg + tile_slot) * rows_per_tile;
 
-    // ---- stream this warp's part of the 16 weight rows into shared memory
+    // ---- this warp's part of the 16 weight rows: one TMA box per matrix (rows x part bytes), dense in
+    // shared memory
     if (ok) {
       fence_proxy_async();
-      if (lane == 0) mbar_expect_tx(wbar, 16u * (uint32_t)part_bytes);
-      __syncwarp();
-      if (lane < 16) {
-        const uint8_t *src;
-        if (DUAL)
-          src = (lane < 8 ? p.W0 : p.W1) + ((size_t)e * p.N + n0 + (lane & 7)) * p.rowBytes;
-        else
-          src = p.W0 + ((size_t)e * p.N + n0 + lane) * p.rowBytes;
-        bulk_g2s(wbase + (size_t)lane * p.pitch, src + (size_t)part * part_bytes, (uint32_t)part_bytes, wbar);
+      if (lane == 0) {
+        mbar_expect_tx(wbar, 16u * (uint32_t)part_bytes);
+        const int xw = part * (part_bytes >> 2);
+        if (DUAL) {
+          tma_load_rows(wbase, &p.map0, xw, e * p.N + n0, wbar);
+          tma_load_rows(wbase + 8 * part_bytes, &p.map1, xw, e * p.N + n0, wbar);
+        } else {
+          tma_load_rows(wbase, &p.map0, xw, e * p.N + n0, wbar);
+        }
       }
     }
     bool w_ready = false;
@@ -371,17 +373,31 @@ int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st
   // and keep the whole prepared vectors of a pass resident in shared memory
   p.tp_alloc = max_tokens < TP ? (max_tokens < 1 ? 1 : max_tokens) : TP;
   p.resident = (size_t)p.tp_alloc * panel_vec_bytes(p.K) <= 40 * 1024 ? 1 : 0;
-  // Defaults measured on B200 (48-layer resident stack, batch 1/8/64): two K-parts per tile for the long
-  // gate/up rows (more warps per SM for the same shared memory), whole rows for the short down rows.
-  int ks = 1;
-  if (DUAL && nsb % 2 == 0 && (p.resident || p.tp_alloc * 2 <= 32)) ks = 2;
-  if (g_force_ks > 0 && nsb % g_force_ks == 0 && (p.resident || p.tp_alloc * g_force_ks <= 32)) ks = g_force_ks;
+  // K-split: every part must fit one TMA box (at most 7 superblocks = 1008 bytes per row). Defaults measured
+  // on B200 (48-layer resident stack, batch 1/8/64).
+  auto fits = [&](int c) { return c >= 1 && nsb % c == 0 && nsb / c <= 7 && (p.resident || p.tp_alloc * c <= 32); };
+  int ks = 0;
+  for (int c = DUAL ? 2 : 1; c <= 16 && !ks; ++c)
+    if (fits(c)) ks = c;
+  if (!ks && fits(1)) ks = 1;
+  if (g_force_ks > 0 && fits(g_force_ks)) ks = g_force_ks;
+  KNJ_REQUIRE(ks >= 1, "q4k projection: rows of %d superblocks cannot be split into TMA boxes for this batch", nsb);
   int tg = (DUAL && max_tokens <= 4) ? 4 : 8;
   if (g_force_tg > 0) tg = g_force_tg;
   while (tg > 1 && (p.tiles_per_expert % tg != 0 || tg * ks > 16)) tg >>= 1;
+  KNJ_REQUIRE(tg * ks <= 16, "q4k projection: K-split %d needs more than 16 warps", ks);
   p.ks = ks;
   p.tg = tg;
-  p.pitch = pad_pitch(nsb / ks * KNJ_Q4K_BYTES);
+  p.pitch = nsb / ks * KNJ_Q4K_BYTES;  // dense TMA boxes
+  {
+    const uint64_t rows = (uint64_t)n_experts_max * p.N;
+    int rc = make_row_tensor_map(&p.map0, p.W0, rows, (uint32_t)p.rowBytes, (uint32_t)p.pitch, DUAL ? 8 : 16);
+    if (rc) return rc;
+    if (DUAL) {
+      rc = make_row_tensor_map(&p.map1, p.W1, rows, (uint32_t)p.rowBytes, (uint32_t)p.pitch, 8);
+      if (rc) return rc;
+    }
+  }
 
   int dev = 0;
   KNJ_CUDA(cudaGetDevice(&dev));

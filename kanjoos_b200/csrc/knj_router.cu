@@ -124,59 +124,108 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint3
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// eight values -> bf16 pairs (plane 0), and the residual planes for non-bf16 input
-template <int DT>
-__device__ __forceinline__ void load_planes(const void *x, int64_t idx, bool valid, uint32_t (&p0)[4], uint32_t (&p1)[4],
-                                            uint32_t (&p2)[4]) {
-  if (DT == KNJ_DT_BF16) {
-    uint4 r = make_uint4(0u, 0u, 0u, 0u);
-    if (valid) r = __ldg(reinterpret_cast<const uint4 *>(static_cast<const uint16_t *>(x) + idx));
-    p0[0] = r.x; p0[1] = r.y; p0[2] = r.z; p0[3] = r.w;
-  } else {
-    float v[8];
-    if (valid) load8_as_f32(x, DT, idx, v);
-    else
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = 0.f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      float a = v[2 * j], b = v[2 * j + 1];
-      const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-      a -= __low2float(h); b -= __high2float(h);
-      const __nv_bfloat162 m = __floats2bfloat162_rn(a, b);
-      a -= __low2float(m); b -= __high2float(m);
-      const __nv_bfloat162 l = __floats2bfloat162_rn(a, b);
-      p0[j] = *reinterpret_cast<const uint32_t *>(&h);
-      p1[j] = *reinterpret_cast<const uint32_t *>(&m);
-      p2[j] = *reinterpret_cast<const uint32_t *>(&l);
-    }
-  }
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;  // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(n) : "memory");
 }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
+// CTA = 4 warps = 64 tokens x 64 experts; K in steps of 32 through a 3-stage
+// cp.async pipeline (activation tile + router tile per stage).
 template <int DT>
 __global__ void __launch_bounds__(128) router_logits_mma_kernel(const void *__restrict__ x, int64_t ldx,
                                                                 const __nv_bfloat16 *__restrict__ Wr,
                                                                 const float *__restrict__ bias, int T, int H, int E,
                                                                 float *__restrict__ logits) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int ES = DT == KNJ_DT_F32 ? 4 : 2;      // bytes per activation
+  constexpr int XROW = 32 * ES;                     // bytes per staged activation row
+  constexpr int XTILE = 64 * XROW, WTILE = 64 * 64; // bytes per stage
+  constexpr int STAGES = 3;
+  __shared__ __align__(16) uint8_t sx[STAGES][XTILE];
+  __shared__ __align__(16) uint8_t sw[STAGES][WTILE];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-  const int tok0 = blockIdx.y * 64 + warp * 16;
-  const int e0 = blockIdx.x * 64;
+  const int tok0 = blockIdx.y * 64, e0 = blockIdx.x * 64;
+  const int nk = H / 32;
+
+  auto issue = [&](int kstep, int st) {
+    const int k0 = kstep * 32;
+    // activations: 64 rows x XROW bytes
+#pragma unroll
+    for (int c = tid; c < XTILE / 16; c += 128) {
+      const int r = c / (XROW / 16), cc = c % (XROW / 16);
+      const int tok = tok0 + r;
+      const uint8_t *src = static_cast<const uint8_t *>(x) + ((int64_t)min(tok, T - 1) * ldx + k0) * ES + cc * 16;
+      cp_async16(&sx[st][r * XROW + cc * 16], src, tok < T);
+    }
+    // router rows: 64 experts x 64 bytes
+#pragma unroll
+    for (int c = tid; c < WTILE / 16; c += 128) {
+      const int r = c >> 2, cc = c & 3;
+      const int e = e0 + r;
+      cp_async16(&sw[st][r * 64 + cc * 16], Wr + (size_t)min(e, E - 1) * H + k0 + cc * 8, e < E);
+    }
+  };
+
   float acc[8][4];
 #pragma unroll
   for (int n = 0; n < 8; ++n)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-  const int ra = tok0 + g, rb = tok0 + g + 8;
-  for (int k0 = 0; k0 < H; k0 += 32) {
-    uint32_t a0[4], a1[4], a2[4], b0[4], b1[4], b2[4];  // rows g and g+8: planes
-    load_planes<DT>(x, (int64_t)ra * ldx + k0 + 8 * t, ra < T, a0, a1, a2);
-    load_planes<DT>(x, (int64_t)rb * ldx + k0 + 8 * t, rb < T, b0, b1, b2);
+
+  issue(0, 0);
+  cp_async_commit();
+  if (nk > 1) issue(1, 1);
+  cp_async_commit();
+  for (int ks = 0; ks < nk; ++ks) {
+    cp_async_wait<1>();
+    __syncthreads();
+    if (ks + 2 < nk) issue(ks + 2, (ks + 2) % STAGES);
+    cp_async_commit();
+    const int st = ks % STAGES;
+    // A fragments of rows g and g+8 of this warp's 16 tokens: k = 8t..8t+7 of the 32-wide span
+    uint32_t a0[4], a1[4], a2[4], b0[4], b1[4], b2[4];
+    auto planes = [&](int row, uint32_t (&p0)[4], uint32_t (&p1)[4], uint32_t (&p2)[4]) {
+      const uint8_t *src = &sx[st][(warp * 16 + row) * XROW + 8 * t * ES];
+      if (DT == KNJ_DT_BF16) {
+        const uint4 r = *reinterpret_cast<const uint4 *>(src);
+        p0[0] = r.x; p0[1] = r.y; p0[2] = r.z; p0[3] = r.w;
+      } else {
+        float v[8];
+        if (DT == KNJ_DT_F32) {
+          const float4 u0 = *reinterpret_cast<const float4 *>(src), u1 = *reinterpret_cast<const float4 *>(src + 16);
+          v[0] = u0.x; v[1] = u0.y; v[2] = u0.z; v[3] = u0.w; v[4] = u1.x; v[5] = u1.y; v[6] = u1.z; v[7] = u1.w;
+        } else {
+          const uint4 r = *reinterpret_cast<const uint4 *>(src);
+          const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const __half2 h = *reinterpret_cast<const __half2 *>(&u[j]);
+            v[2 * j] = __low2float(h);
+            v[2 * j + 1] = __high2float(h);
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float a = v[2 * j], b = v[2 * j + 1];
+          const __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          a -= __low2float(h); b -= __high2float(h);
+          const __nv_bfloat162 m = __floats2bfloat162_rn(a, b);
+          a -= __low2float(m); b -= __high2float(m);
+          const __nv_bfloat162 l = __floats2bfloat162_rn(a, b);
+          p0[j] = *reinterpret_cast<const uint32_t *>(&h);
+          p1[j] = *reinterpret_cast<const uint32_t *>(&m);
+          p2[j] = *reinterpret_cast<const uint32_t *>(&l);
+        }
+      }
+    };
+    planes(g, a0, a1, a2);
+    planes(g + 8, b0, b1, b2);
 #pragma unroll
     for (int n = 0; n < 8; ++n) {
-      const int e = e0 + n * 8 + g;
-      uint4 w = make_uint4(0u, 0u, 0u, 0u);
-      if (e < E) w = __ldg(reinterpret_cast<const uint4 *>(Wr + (size_t)e * H + k0 + 8 * t));
+      const uint4 w = *reinterpret_cast<const uint4 *>(&sw[st][(n * 8 + g) * 64 + 16 * t]);
       mma_bf16_16816(acc[n], a0[0], b0[0], a0[1], b0[1], w.x, w.y);
       mma_bf16_16816(acc[n], a0[2], b0[2], a0[3], b0[3], w.z, w.w);
       if (DT != KNJ_DT_BF16) {
@@ -187,6 +236,8 @@ __global__ void __launch_bounds__(128) router_logits_mma_kernel(const void *__re
       }
     }
   }
+  cp_async_wait<0>();
+  const int ra = tok0 + warp * 16 + g, rb = ra + 8;
 #pragma unroll
   for (int n = 0; n < 8; ++n) {
     const int e = e0 + n * 8 + 2 * t;

@@ -36,6 +36,39 @@ int sm_count() {
   return cached[dev];
 }
 
+int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t row_bytes, uint32_t box_bytes,
+                        uint32_t box_rows) {
+  typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static EncodeFn encode = nullptr;
+  if (!encode) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || !fn) {
+      set_error("cuTensorMapEncodeTiled is not available from this driver");
+      return KNJ_E_RUNTIME;
+    }
+    encode = reinterpret_cast<EncodeFn>(fn);
+  }
+  KNJ_REQUIRE(row_bytes % 16 == 0 && box_bytes % 16 == 0 && box_bytes <= 1024 && box_rows >= 1 && box_rows <= 256 &&
+                  aligned16(base),
+              "tensor map: rows of %u bytes / boxes of %u x %u bytes are not TMA-addressable", row_bytes, box_rows, box_bytes);
+  const cuuint64_t dims[2] = {row_bytes / 4, rows};
+  const cuuint64_t strides[1] = {row_bytes};
+  const cuuint32_t box[2] = {box_bytes / 4, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(base), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with driver status %d", (int)r);
+    return KNJ_E_RUNTIME;
+  }
+  return KNJ_OK;
+}
+
 }  // namespace knj
 
 using namespace knj;
