@@ -299,13 +299,19 @@ int knj_q4k_matmul_noalloc_launch(const uint8_t *W, int n_in, int n_out, const v
  * saturated to the fp16 range: the token operand of the grouped GEMMs. */
 int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s);
 
-/* Measurement hook (no reference counterpart): a device buffer of 64 uint64 that
- * receives SM-clock stamps of the first 16 K-slabs of CTA 0 of the grouped GEMMs
- * ([4k] unpacker starts slab k, [4k+1] stage free, [4k+2] stage published,
- * [4k+3] MMA thread sees it), followed by 4 uint64 per CTA b < cta_slots:
- * global-timer ns at start, accumulator complete, end, and
- * (SM id << 32 | tokens of the CTA's bucket). NULL = off. */
+/* Measurement hook (no reference counterpart): a device buffer of
+ * 256 + 4 * cta_slots uint64. SM-clock stamps of CTA 0 of the grouped GEMMs:
+ * [4k..4k+3], k < 12: unpacker starts K-slab k, stage free, stage published,
+ * MMA thread sees the slab; [48..61] epilogue phases; [64+4k..64+4k+3]: loader
+ * reaches slab k, stage free, rows stored, published. From [256] on, 4 uint64
+ * per CTA b < cta_slots: global-timer ns at start, accumulator complete, end,
+ * and (SM id << 32 | tokens of the CTA's bucket). NULL = off. */
 void knj_tc_trace(void *dev_buf, int cta_slots);
+
+/* Experiment hook (no reference counterpart): 1 = run every tile of the grouped
+ * GEMMs on a single SM (tcgen05 cta_group::1) even where CTA pairs apply;
+ * 0 = automatic (pairs whenever a bucket has an even number of row tiles). */
+void knj_tc_tuning(int force_single_sm);
 
 /* Grouped gate+up GEMM over per-expert token buckets on the tensor cores
  * (tools/bench/q4k_moe_ffn.hip:164-241 knj_q4k_gateup fused with

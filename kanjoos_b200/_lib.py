@@ -100,6 +100,7 @@ SIGNATURES = {
                                    _i, _vp]),
     "knj_q4k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp]),
     "knj_tc_trace": (None, [_vp, _i]),
+    "knj_tc_tuning": (None, [_i]),
     "knj_to_f16_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp]),
     "knj_q4k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),

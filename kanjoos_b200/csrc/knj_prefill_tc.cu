@@ -36,10 +36,9 @@ using namespace knj;
 
 namespace {
 
-constexpr int kRowsM = 128;        // weight rows per tile (MMA M)
+constexpr int kRowsM = 128;        // weight rows per tile and CTA (MMA M per CTA)
 constexpr int kMaxTok = 256;       // token bucket (MMA N upper bound)
 constexpr int kSlabK = 64;         // K elements per pipeline stage (one 128-byte swizzle row)
-constexpr int kStages = 2;         // operand stages
 constexpr int kProducerThreads = 256;  // unpacker warps 0..7
 constexpr int kLoaderThreads = 128;    // loader warps 9..12
 constexpr int kThreads = kProducerThreads + 32 + kLoaderThreads;
@@ -64,34 +63,86 @@ struct TcParams {
 
 unsigned long long *g_tc_trace = nullptr;
 int g_tc_trace_ctas = 0;
+int g_tc_force_single = 0;  // experiment hook: 1 = never pair CTAs
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
+// Every tcgen05 instruction of one kernel names the same CTA group: CG = 1 (one SM per tile) or 2 (a pair of
+// CTAs of one cluster works on one 256-row tile: each brings its own 128 weight rows and half of the tokens).
+template <int CG>
 __device__ __forceinline__ void tmem_alloc(uint32_t *slot_smem, uint32_t ncols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols)
-               : "memory");
+  if (CG == 1)
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols) : "memory");
+  else
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(ncols) : "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (CG == 1) asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  else asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
 }
+template <int CG>
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  if (CG == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+  else asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
-__device__ __forceinline__ void tc_commit(uint64_t *bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+// the barrier (a shared::cluster address: this CTA's or the peer's) gets one arrival once every MMA issued so far
+// has completed
+template <int CG>
+__device__ __forceinline__ void tc_commit_addr(uint32_t bar_addr) {
+  if (CG == 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
+  else asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t cluster_addr(const void *smem_ptr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(smem_ptr)), "r"(rank));
+  return r;
+}
+// arrive on a barrier given by its shared::cluster address (this CTA's or the peer's). The data it publishes
+// is read by the tensor core through the async proxy, ordered by the writer's fence.proxy.async.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_addr) : "memory");
+}
+// 16-byte asynchronous copy global -> shared (L2 only); src_bytes = 0 writes zeros
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src), "r"(src_bytes) : "memory");
+}
+// one arrival on the barrier once every cp.async this thread has issued so far has landed
+__device__ __forceinline__ void cp_async_arrive(uint64_t *bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// all threads of both CTAs of the pair
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
 // D(tmem) (+)= A(smem desc) * B(smem desc), fp16 operands, f32 accumulate
+template <int CG>
 __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                            uint32_t accumulate) {
   const uint32_t zero = 0;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero), "r"(zero), "r"(zero), "r"(zero)
-      : "memory");
+  if (CG == 1)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero), "r"(zero), "r"(zero), "r"(zero)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(zero), "r"(zero), "r"(zero), "r"(zero),
+          "r"(zero), "r"(zero), "r"(zero), "r"(zero)
+        : "memory");
 }
 // 16 consecutive f32 columns of this thread's TMEM lane
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float (&v)[16]) {
@@ -114,38 +165,47 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3fffu) | ((uint64_t)1 << 16) | ((uint64_t)64 << 32) | ((uint64_t)1 << 46) |
          ((uint64_t)2 << 61);
 }
-// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128
-__device__ __forceinline__ uint32_t instr_desc_f16(int n) {
-  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kRowsM >> 4) << 24);
+// kind::f16 instruction descriptor: D = f32, A = B = f16, both K-major, M = 128 per CTA of the group
+__device__ __forceinline__ uint32_t instr_desc_f16(int m, int n) {
+  return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
 // the two unpacker warps that own the same 32 weight rows (one per 16-byte half) meet on their own barrier
 __device__ __forceinline__ void pair_sync(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory"); }
 
-template <int NMAT>
+template <int NMAT, int CG>
 struct Smem {
   // operand tiles: 1024-byte aligned for the swizzle pattern
+  static constexpr int kStagesA = CG == 2 ? 3 : 2;  // weight operand stages
+  static constexpr int kStagesB = CG == 2 ? 3 : 2;  // token operand stages
+  static constexpr int kTokCta = kMaxTok / CG;   // token rows this CTA stages per slab
   static constexpr int kATile = kRowsM * 128;    // 16 KB per matrix per stage
-  static constexpr int kBTile = kMaxTok * 128;   // 32 KB per stage
+  static constexpr int kBTile = kTokCta * 128;   // 32 KB (16 KB in a pair) per stage
   static constexpr int kRawBuf = NMAT * kRowsM * KNJ_Q4K_BYTES;
   static constexpr int kOffA = 0;
-  static constexpr int kOffB = kOffA + kStages * NMAT * kATile;
-  static constexpr int kOffRaw = kOffB + kStages * kBTile;
+  static constexpr int kOffB = kOffA + kStagesA * NMAT * kATile;
+  static constexpr int kOffRaw = kOffB + kStagesB * kBTile;
   static constexpr int kOffPairs = kOffRaw + 2 * kRawBuf;       // int32 pair id per token of the bucket
   static constexpr int kOffRows = kOffPairs + kMaxTok * 4;      // int32 activation row per token
   static constexpr int kOffBars = kOffRows + kMaxTok * 4;       // mbarriers
-  static constexpr int kBytes = kOffBars + 192 + 1024;          // + alignment slack
+  static constexpr int kBytes = kOffBars + 256 + 1024;          // + alignment slack
 };
 
 // NMAT = 2 with GATEUP: gate and up tiles of the same 128 output indices (one shared token operand, SiLU*up
 // epilogue). NMAT = 2 without: two consecutive 128-row tiles of one matrix (halves the token-operand traffic
 // of the down projection). NMAT = 1: one tile.
-template <int NMAT, bool GATEUP>
+// CG = 2: CTAs 2i and 2i+1 of the grid form a cluster and run tcgen05.mma.cta_group::2 (M = 256 over the pair):
+// each CTA unpacks its own weight tiles and stages half of the bucket's token rows, so the token operand
+// crosses L2 -> shared memory once per 256 weight rows instead of once per 128. The even CTA issues the MMAs;
+// producers of both CTAs arrive on its "full" barriers, and it commits to the "empty" barriers of both.
+template <int NMAT, bool GATEUP, int CG>
 __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __grid_constant__ TcParams p) {
-  using S = Smem<NMAT>;
+  using S = Smem<NMAT, CG>;
+  constexpr int kStagesA = S::kStagesA, kStagesB = S::kStagesB;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t rank = CG == 2 ? cluster_rank() : 0u;  // == blockIdx.x & 1 (m_tiles is even when CG == 2)
 
   // ---- which (expert, token bucket) is this CTA's? scan the counts (E <= 256)
   const int m_tile = blockIdx.x % p.m_tiles;
@@ -157,8 +217,8 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     if (want < nt) { e = i; tok0 = want * kMaxTok; cnt = c; break; }
     want -= nt;
   }
-  if (e < 0) return;  // uniform across the CTA: nothing allocated yet
-  unsigned long long *cta_rec = (p.trace && (int)blockIdx.x < p.trace_ctas) ? p.trace + 64 + 4 * (size_t)blockIdx.x : nullptr;
+  if (e < 0) return;  // the same for both CTAs of a pair: nothing allocated yet, no barrier touched
+  unsigned long long *cta_rec = (p.trace && (int)blockIdx.x < p.trace_ctas) ? p.trace + 256 + 4 * (size_t)blockIdx.x : nullptr;
   if (cta_rec && tid == 0) {
     unsigned smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
@@ -167,25 +227,31 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   }
   const int ntok = min(kMaxTok, cnt - tok0);
   const int n_mma = (ntok + 15) & ~15;  // MMA N: multiple of 16
+  const int n_cta = n_mma / CG;         // token rows staged by this CTA: [rank * n_cta, (rank + 1) * n_cta)
   const int m0 = m_tile * kRowsM * (GATEUP ? 1 : NMAT);
   const int nsb = p.K / KNJ_QK_K, nslab = p.K / kSlabK;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kOffBars);
-  uint64_t *full = bars;               // [kStages] producers -> MMA
-  uint64_t *empty = bars + kStages;    // [kStages] MMA -> producers
-  uint64_t *raw_full = bars + 2 * kStages;  // [2 buffers][4 row groups] bulk copies landed
-  uint64_t *acc_full = bars + 2 * kStages + 8;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 2 * kStages + 9);
+  uint64_t *fullA = bars;                          // [kStagesA] unpackers -> MMA (the even CTA's are used)
+  uint64_t *emptyA = fullA + kStagesA;             // [kStagesA] MMA -> unpackers
+  uint64_t *fullB = emptyA + kStagesA;             // [kStagesB] this CTA's loaders (asynchronous copies landed)
+  uint64_t *emptyB = fullB + kStagesB;             // [kStagesB] MMA -> loaders
+  uint64_t *peerB = emptyB + kStagesB;             // [kStagesB] even CTA only: the odd CTA's token rows landed
+  uint64_t *raw_full = peerB + kStagesB;           // [2 buffers][4 row groups] TMA boxes landed
+  uint64_t *acc_full = raw_full + 8;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
   volatile int *s_fail = reinterpret_cast<volatile int *>(tmem_slot + 1);  // raised by the first wait that gives up
   int32_t *s_pair = reinterpret_cast<int32_t *>(smem + S::kOffPairs);
   int32_t *s_row = reinterpret_cast<int32_t *>(smem + S::kOffRows);
 
   if (tid == 0) {
-    for (int s = 0; s < kStages; ++s) { mbar_init(&full[s], (kProducerThreads + kLoaderThreads) / 32); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < kStagesA; ++s) { mbar_init(&fullA[s], CG * kProducerThreads / 32); mbar_init(&emptyA[s], 1); }
+    for (int s = 0; s < kStagesB; ++s) { mbar_init(&fullB[s], kLoaderThreads); mbar_init(&emptyB[s], 1); mbar_init(&peerB[s], 1); }
     for (int i = 0; i < 8; ++i) mbar_init(&raw_full[i], 1);
     mbar_init(acc_full, 1);
     *s_fail = 0;
-    mbar_init_fence();
+    if (CG == 2) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    else mbar_init_fence();
   }
   for (int i = tid; i < kMaxTok; i += kThreads) {
     int pr = -1, rw = -1;
@@ -198,11 +264,12 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   }
   constexpr uint32_t kTmemCols = NMAT == 2 ? 512 : 256;
   if (warp == 8) {
-    tmem_alloc(tmem_slot, kTmemCols);
-    tmem_relinquish();
+    tmem_alloc<CG>(tmem_slot, kTmemCols);
+    tmem_relinquish<CG>();
   }
   tc_fence_before();
   __syncthreads();
+  if (CG == 2) cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;  // once false this thread skips all work and waits but still meets every barrier
@@ -271,11 +338,11 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
 #pragma unroll
       for (int G = 0; G < 4; ++G) {
         if (!ok) break;
-        const int ks = b * 4 + G, stage = ks % kStages;
-        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 16) p.trace[4 * ks + 0] = clock64();
-        if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
+        const int ks = b * 4 + G, stage = ks % kStagesA;
+        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 0] = clock64();
+        if (ks >= kStagesA && !mbar_wait(&emptyA[stage], ((ks / kStagesA) - 1) & 1, s_fail)) { ok = false; break; }
         tc_fence_after();
-        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 16) p.trace[4 * ks + 1] = clock64();
+        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 1] = clock64();
         // ---- weight operand(s): 16 code bytes -> 16 low-nibble + 16 high-nibble weights of this row
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
@@ -305,67 +372,87 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
         }
         fence_proxy_async();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&full[stage]);
-        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 16) p.trace[4 * ks + 2] = clock64();
+        if (lane == 0) {
+          if (CG == 2) mbar_arrive_cluster(cluster_addr(&fullA[stage], 0));
+          else mbar_arrive(&fullA[stage]);
+        }
+        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 2] = clock64();
       }
     }
   } else if (warp >= 9) {
     // =========================== loaders ===========================
-    // rows of 64 fp16 per slab; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
+    // rows of 64 fp16 per slab; 16-byte chunk c of row r lands at chunk c ^ (r & 7). Asynchronous copies:
+    // nothing waits for the gathered rows in registers, so as many slabs travel as there are stages, and
+    // the stage's barrier gets this thread's arrival when its copies have landed. (A register path would
+    // stall on the release fence of every hand-off until its prefetched loads return.) In a pair each CTA
+    // gathers half of the bucket's rows.
+    constexpr int kRpt = S::kTokCta / 16;  // rows per thread and slab
     const int lt = tid - (kProducerThreads + 32);
     const int c = lt & 7, r0 = lt >> 3;  // 16 rows per pass
-    const __half *rowp[kMaxTok / 16];
+    const __half *rowp[kRpt];
 #pragma unroll
-    for (int j = 0; j < kMaxTok / 16; ++j) {
+    for (int j = 0; j < kRpt; ++j) {
       const int r = r0 + 16 * j;
-      const int xr = r < n_mma ? s_row[r] : -1;
+      const int xr = r < n_cta ? s_row[rank * n_cta + r] : -1;
       rowp[j] = xr >= 0 ? p.X + (size_t)xr * p.K + c * 8 : nullptr;
     }
-    uint4 v[kMaxTok / 16];
-    auto fetch = [&](int ks) {
-#pragma unroll
-      for (int j = 0; j < kMaxTok / 16; ++j) {
-        v[j] = make_uint4(0u, 0u, 0u, 0u);
-        if (rowp[j]) v[j] = __ldg(reinterpret_cast<const uint4 *>(rowp[j] + ks * kSlabK));
-      }
-    };
-    fetch(0);
-    for (int ks = 0; ks < nslab; ++ks) {
-      const int stage = ks % kStages;
-      if (ok && ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) ok = false;
-      if (!ok) break;  // loaders meet no CTA barrier before the final one
-      tc_fence_after();
+    for (int ks = 0; ks < nslab && ok; ++ks) {  // loaders meet no CTA barrier before the final one
+      const int stage = ks % kStagesB;
+      const bool ltr = p.trace && blockIdx.x == 0 && lt == 0 && ks < 12;
+      if (ltr) p.trace[64 + 4 * ks] = clock64();
+      if (ks >= kStagesB && !mbar_wait(&emptyB[stage], ((ks / kStagesB) - 1) & 1, s_fail)) { ok = false; break; }
+      if (ltr) p.trace[64 + 4 * ks + 1] = clock64();
       uint8_t *bt = smem + S::kOffB + stage * S::kBTile;
 #pragma unroll
-      for (int j = 0; j < kMaxTok / 16; ++j) {
+      for (int j = 0; j < kRpt; ++j) {
         const int r = r0 + 16 * j;
-        if (r < n_mma) *reinterpret_cast<uint4 *>(bt + r * 128 + ((c ^ (r & 7)) << 4)) = v[j];
+        if (r < n_cta)
+          cp_async16(bt + r * 128 + ((c ^ (r & 7)) << 4), rowp[j] ? (const void *)(rowp[j] + ks * kSlabK) : (const void *)p.X,
+                     rowp[j] ? 16u : 0u);
       }
-      if (ks + 1 < nslab) fetch(ks + 1);  // next slab's rows travel while this stage is consumed
-      fence_proxy_async();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&full[stage]);
+      cp_async_arrive(&fullB[stage]);
+      if (ltr) p.trace[64 + 4 * ks + 3] = clock64();
     }
-  } else if (warp == 8 && lane == 0) {
-    // =========================== MMA issue ===========================
-    const uint32_t idesc = instr_desc_f16(n_mma);
+  } else if (CG == 2 && warp == 8 && lane == 0 && rank == 1) {
+    // =========================== relay (odd CTA) ===========================
+    // cp.async completions can only arrive on a barrier of their own CTA: pass them on to the MMA thread
     for (int ks = 0; ks < nslab && ok; ++ks) {
-      const int stage = ks % kStages;
-      if (!mbar_spin(&full[stage], (ks / kStages) & 1, s_fail)) { ok = false; break; }
+      const int sb = ks % kStagesB;
+      if (!mbar_spin(&fullB[sb], (ks / kStagesB) & 1, s_fail)) { ok = false; break; }
+      fence_proxy_async();
+      mbar_arrive_cluster(cluster_addr(&peerB[sb], 0));
+    }
+  } else if (warp == 8 && lane == 0 && rank == 0) {
+    // =========================== MMA issue ===========================
+    const uint32_t idesc = instr_desc_f16(kRowsM * CG, n_mma);
+    for (int ks = 0; ks < nslab && ok; ++ks) {
+      const int sa = ks % kStagesA, sb = ks % kStagesB;
+      if (!mbar_spin(&fullB[sb], (ks / kStagesB) & 1, s_fail)) { ok = false; break; }
+      if (CG == 2 && !mbar_spin(&peerB[sb], (ks / kStagesB) & 1, s_fail)) { ok = false; break; }
+      if (!mbar_spin(&fullA[sa], (ks / kStagesA) & 1, s_fail)) { ok = false; break; }
+      fence_proxy_async();  // the gathered rows were written by asynchronous copies of other threads
       tc_fence_after();
-      if (p.trace && blockIdx.x == 0 && ks < 16) p.trace[4 * ks + 3] = clock64();
-      const uint32_t b_addr = smem_u32(smem + S::kOffB + stage * S::kBTile);
+      if (p.trace && blockIdx.x == 0 && ks < 12) p.trace[4 * ks + 3] = clock64();
+      const uint32_t b_addr = smem_u32(smem + S::kOffB + sb * S::kBTile);
 #pragma unroll
       for (int mat = 0; mat < NMAT; ++mat) {
-        const uint32_t a_addr = smem_u32(smem + S::kOffA + (stage * NMAT + mat) * S::kATile);
+        const uint32_t a_addr = smem_u32(smem + S::kOffA + (sa * NMAT + mat) * S::kATile);
 #pragma unroll
         for (int k = 0; k < kSlabK / 16; ++k)
-          tc_mma_f16(tmem_base + mat * kMaxTok, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                     (ks > 0 || k > 0) ? 1u : 0u);
+          tc_mma_f16<CG>(tmem_base + mat * kMaxTok, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
+                         (ks > 0 || k > 0) ? 1u : 0u);
       }
-      tc_commit(&empty[stage]);
+      tc_commit_addr<CG>(smem_u32(&emptyA[sa]));
+      tc_commit_addr<CG>(smem_u32(&emptyB[sb]));
+      if (CG == 2) {
+        tc_commit_addr<CG>(cluster_addr(&emptyA[sa], 1));
+        tc_commit_addr<CG>(cluster_addr(&emptyB[sb], 1));
+      }
     }
-    if (ok) tc_commit(acc_full);
+    if (ok) {
+      tc_commit_addr<CG>(smem_u32(acc_full));
+      if (CG == 2) tc_commit_addr<CG>(cluster_addr(acc_full, 1));
+    }
   }
 
   // =========================== epilogue ===========================
@@ -392,14 +479,13 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
           if (GATEUP) {
             float u[16];
             tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + kMaxTok + c * 16, u);
-            if (tr && c < 4) p.trace[53 + c] = clock64();
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
+              // fast division: the IEEE one takes its slow path whenever exp(-g) overflows
               const float a = __fdividef(g[j], 1.0f + __expf(-g[j])) * u[j] * p.out_scale;
               *reinterpret_cast<__half *>(stg + (c * 16 + j) * kRowB + (lane_base + lane) * 2) =
                   __float2half_rn(fminf(fmaxf(a, -65504.0f), 65504.0f));
             }
-            if (tr && c < 4) p.trace[54 + c] = clock64();
           } else {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
@@ -425,12 +511,13 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
       if (mat + 1 < kEpiMats) asm volatile("bar.sync 5, 256;" ::: "memory");
     }
   }
-  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[60] = clock64();
   if (!ok && lane == 0 && p.status) atomicExch(p.status, 1);
   tc_fence_before();
   __syncthreads();
-  if (p.trace && blockIdx.x == 0 && tid == 0) p.trace[61] = clock64();
-  if (warp == 8) tmem_dealloc(tmem_base, kTmemCols);
+  // a CTA of a pair may neither free tensor memory nor leave while the peer still reads its accumulators'
+  // operands or arrives on its barriers
+  if (CG == 2) cluster_sync_all();
+  if (warp == 8) tmem_dealloc<CG>(tmem_base, kTmemCols);
   if (cta_rec && tid == 0) cta_rec[2] = global_timer_ns();
 }
 
@@ -443,12 +530,12 @@ __global__ void to_f16_kernel(const void *__restrict__ x, int dtype, int64_t ldx
   }
 }
 
-template <int NMAT, bool GATEUP>
-int launch_tc(TcParams p, int max_pairs, cudaStream_t st) {
-  using S = Smem<NMAT>;
+template <int NMAT, bool GATEUP, int CG>
+int launch_tc_cg(TcParams p, int max_pairs, cudaStream_t st) {
+  using S = Smem<NMAT, CG>;
   int dev = 0;
   KNJ_CUDA(cudaGetDevice(&dev));
-  auto kern = q4k_grouped_tc_kernel<NMAT, GATEUP>;
+  auto kern = q4k_grouped_tc_kernel<NMAT, GATEUP, CG>;
   static bool opted[64] = {false};
   if (dev >= 0 && dev < 64 && !opted[dev]) {
     KNJ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
@@ -467,22 +554,46 @@ int launch_tc(TcParams p, int max_pairs, cudaStream_t st) {
   const long long buckets = (long long)max_pairs / kMaxTok + p.n_experts;
   const long long grid = buckets * p.m_tiles;
   KNJ_REQUIRE(grid > 0 && grid < (1ll << 31), "grouped GEMM: grid of %lld CTAs out of range", grid);
-  kern<<<(unsigned)grid, kThreads, S::kBytes, st>>>(p);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = S::kBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  KNJ_CUDA(cudaLaunchKernelEx(&cfg, kern, p));
   return launch_status("q4k_grouped_tc_kernel");
+}
+
+// pairs of CTAs whenever the row tiles of a bucket come in twos
+template <int NMAT, bool GATEUP>
+int launch_tc(const TcParams &p, int max_pairs, cudaStream_t st) {
+  if (p.m_tiles % 2 == 0 && !g_tc_force_single) return launch_tc_cg<NMAT, GATEUP, 2>(p, max_pairs, st);
+  return launch_tc_cg<NMAT, GATEUP, 1>(p, max_pairs, st);
 }
 
 }  // namespace
 
 extern "C" {
 
-// Measurement hook (no reference counterpart): device buffer of 64 + 4 * cta_slots u64. The first 64 receive
-// SM-clock stamps of the first 16 slabs of CTA 0 -- [4k] unpacker starts slab k, [4k+1] stage free, [4k+2] stage
-// published, [4k+3] MMA sees it; then per CTA b < cta_slots: global-timer ns at start, accumulator complete,
-// end, and (SM id << 32 | tokens of its bucket).
+// Measurement hook (no reference counterpart): device buffer of 256 + 4 * cta_slots u64. SM-clock stamps of
+// CTA 0: [4k..4k+3], k < 12: unpacker starts slab k, stage free, stage published, MMA sees the slab;
+// [48..61] epilogue phases; [64+4k..], k < 12: loader reaches slab k, stage free, rows stored, published.
+// From [256] on, per CTA b < cta_slots: global-timer ns at start, accumulator complete, end, and
+// (SM id << 32 | tokens of its bucket).
 void knj_tc_trace(void *dev_buf, int cta_slots) {
   g_tc_trace = static_cast<unsigned long long *>(dev_buf);
   g_tc_trace_ctas = dev_buf ? cta_slots : 0;
 }
+
+// Experiment hook (no reference counterpart): 1 = run every tile on a single SM (cta_group::1) even where
+// CTA pairs apply; 0 = automatic.
+void knj_tc_tuning(int force_single_sm) { g_tc_force_single = force_single_sm; }
 
 int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s) {
   KNJ_REQUIRE(x && out_f16, "knj_to_f16: null pointer");
