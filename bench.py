@@ -50,50 +50,81 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons during the timed region."""
+    """SM clock and throttle reasons sampled every few milliseconds while the timed regions run
+    (NVML reads only; nvidia-smi polling as the fallback)."""
+    REASONS = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"), (0x4, "sw_power_cap"))
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.sm, self.mx, self.reasons = index, [], None, set()
+        self.proc, self.th, self.stop_flag, self.nvml = None, None, threading.Event(), None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+            phys = int(vis.split(",")[self.index]) if vis and all(v.strip().isdigit() for v in vis.split(",")) else self.index
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(phys)
+            self.mx = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.th = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.th.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.th = threading.Thread(target=self._read, daemon=True)
+            self.th = threading.Thread(target=self._read_smi, daemon=True)
             self.th.start()
         except OSError:
             self.proc = None
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+    def _poll_nvml(self):
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                self.sm.append(float(n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)))
+                mask = int(n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle))
+                for bit, name in self.REASONS:
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.003)
 
-    def stop(self):
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=3)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        for r in self.rows:
+    def _read_smi(self):
+        for line in self.proc.stdout:
+            r = [c.strip() for c in line.split(",")]
             if len(r) < 6:
                 continue
             try:
-                sm.append(float(r[0]))
-                mx = float(r[1])
+                self.sm.append(float(r[0]))
+                self.mx = float(r[1])
             except ValueError:
                 continue
             for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
                 if v.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                    self.reasons.add(name)
+
+    def stop(self):
+        if self.nvml is None and not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["clock query unavailable"], "samples": 0}
+        self.stop_flag.set()
+        if self.proc:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=3)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        if self.th:
+            self.th.join(timeout=3)
+        sm = sorted(self.sm)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.mx, "reasons": sorted(self.reasons),
+                "samples": len(sm), "source": "nvml" if self.nvml else "nvidia-smi"}
 
 
 # --------------------------------------------------------------------------- reference arm
@@ -248,14 +279,14 @@ def run_gpu(args):
         ws = layers[0].workspace
         layers += [MoeFfnLayer(bk, top_k=TOPK, max_tokens=T_loc, use_norm=False, workspace=ws) for bk in banks[1:]]
 
-        def step(i, xin=x):
-            layers[i % n_banks].prefill(xin, out=out)
+        def step(i, xin=x, dst=out):
+            layers[i % n_banks].prefill(xin, out=dst)
     else:
         cp = CudaCompute(router, TOPK, bias)
         eps = [EpMoeLayer(bk, E, cp, None, TOPK) for bk in banks]
 
-        def step(i, xin=x):
-            out.copy_(eps[i % n_banks].forward(xin, out_dtype=torch.bfloat16))
+        def step(i, xin=x, dst=out):
+            dst.copy_(eps[i % n_banks].forward(xin, out_dtype=torch.bfloat16))
 
     def barrier():
         torch.cuda.synchronize()
@@ -279,23 +310,47 @@ def run_gpu(args):
     barrier()
     ms_step = e0.elapsed_time(e1) / args.steps
 
-    # end to end: pinned host rows in, bf16 result rows out, copies inside the timed region
+    # end to end: pinned host rows in, bf16 result rows out, every step's copies inside the timed region.
+    # Three streams and two device buffers per direction: the copy-in of step i+1 and the copy-out of
+    # step i-1 overlap the compute of step i (PCIe is full duplex); nothing is cached across steps.
     hx = torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory()
     hx.copy_(x.cpu())
-    hout = torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory()
-    xin = torch.empty_like(x)
+    hout = [torch.empty((T_loc, H), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    xin = [torch.empty_like(x) for _ in range(2)]
+    dout = [torch.empty_like(out) for _ in range(2)]
+    s_c = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
 
-    def e2e_step(i):
-        xin.copy_(hx, non_blocking=True)
-        step(i, xin)
-        hout.copy_(out, non_blocking=True)
+    def e2e_run(n, first):
+        ev_in = [None, None]     # copy-in of the step that last used buffer b
+        ev_comp = [None, None]   # compute of that step
+        ev_out = [None, None]    # copy-out of that step
+        for k in range(n):
+            b = k & 1
+            with torch.cuda.stream(s_in):
+                if ev_comp[b] is not None:
+                    s_in.wait_event(ev_comp[b])      # the step two back has read xin[b]
+                xin[b].copy_(hx, non_blocking=True)
+                ev_in[b] = torch.cuda.Event()
+                ev_in[b].record(s_in)
+            s_c.wait_event(ev_in[b])
+            if ev_out[b] is not None:
+                s_c.wait_event(ev_out[b])            # dout[b] has been copied out
+            step(first + k, xin[b], dout[b])
+            ev_comp[b] = torch.cuda.Event()
+            ev_comp[b].record(s_c)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_comp[b])
+                hout[b].copy_(dout[b], non_blocking=True)
+                ev_out[b] = torch.cuda.Event()
+                ev_out[b].record(s_out)
+        s_c.wait_stream(s_out)
+        s_c.wait_stream(s_in)
 
-    for i in range(2):
-        e2e_step(i)
+    e2e_run(2, 0)
     barrier()
     e0.record()
-    for i in range(args.steps):
-        e2e_step(W + i)
+    e2e_run(args.steps, W)
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1) / args.steps
@@ -339,9 +394,18 @@ def run_gpu(args):
         flops = rows * 2 * 2 * H * F
         t_tensor = flops / (pk["bf16_tflops"] * 1e12)
         assert int(status.item()) == 0, "a bounded wait inside the grouped GEMM gave up"
-        roof = {"kernel": "q4k_grouped_tc_kernel<2> (gate+up, tcgen05)", "bound": "tensor", "achieved": flops / (ms_k * 1e-3) / 1e12,
+        # DRAM bytes per launch from the ncu capture of the 512-token case (weights 229.55 - 3.06 MB, which do not
+        # depend on the token count while every expert is active, + 3.06 MB read and 7.80 MB written per 512
+        # tokens), scaled to this launch's rows
+        w_bytes = int((pair_cnt > 0).sum().item()) * 2 * F * (H // 256) * 144
+        traffic = None
+        traffic_note = None
+        if world == 1:
+            traffic = w_bytes + (3.06e6 + 7.80e6) * (rows / 4096.0)
+            traffic_note = "ncu dram bytes of the T=512 capture: weight stream as measured, token-proportional part scaled by rows"
+        roof = {"kernel": "q4k_grouped_tc_kernel<2,true,2> (gate+up, tcgen05 cta_group::2)", "bound": "tensor", "achieved": flops / (ms_k * 1e-3) / 1e12,
                 "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": flops / (ms_k * 1e-3) / 1e12 / pk["bf16_tflops"],
-                "peak_source": pk["_source"], "traffic": None, "ms_per_launch": ms_k,
+                "peak_source": pk["_source"], "traffic": traffic, "traffic_note": traffic_note, "ms_per_launch": ms_k,
                 "algorithmic_flops_per_launch": flops,
                 "weight_bytes_per_launch": int((pair_cnt > 0).sum().item()) * 2 * F * (H // 256) * 144,
                 "t_tensor_ms": t_tensor * 1e3}
@@ -356,7 +420,7 @@ def run_gpu(args):
     dec = None
     if world == 1:
         if args.cpu_sample > 0:
-            cb, _ = cpu_layer_tokens_per_s(args.cpu_sample, 1, 1, "uniform")
+            cb, _ = cpu_layer_tokens_per_s(args.cpu_sample, 3, 1, "uniform")
         if not args.no_decode:
             del banks, layers
             torch.cuda.empty_cache()
@@ -380,12 +444,12 @@ def run_gpu(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
-    ap.add_argument("--cpu-sample", type=int, default=128, dest="cpu_sample")
+    ap.add_argument("--cpu-sample", type=int, default=1024, dest="cpu_sample")
     ap.add_argument("--no-decode", action="store_true")
     ap.add_argument("--section", default="all", choices=["all", "decode"])
     ap.add_argument("--decode-layers", type=int, default=LAYERS, dest="decode_layers")
