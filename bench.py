@@ -426,7 +426,7 @@ def run_gpu(args):
             torch.cuda.empty_cache()
             dec = decode_section(torch, max(5, args.steps), args.warmup, pk)
 
-    launches = 8 if world == 1 else 13
+    launches = 8 if world == 1 else 9  # router 2, permute 2, to_f16, gate+up, down, combine (N>1: partial combine + rank reduce)
     line = {"metric": "moe_ffn_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16 operands (Q4_K unpacked), f32 accumulate", "data": "synthetic",
@@ -447,7 +447,7 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=16384)
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--cpu-sample", type=int, default=1024, dest="cpu_sample")
     ap.add_argument("--no-decode", action="store_true")

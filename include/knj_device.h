@@ -392,6 +392,19 @@ int knj_ep_pack_launch(const void *x, int row_bytes, int top_k, const int32_t *p
 int knj_ep_plan_launch(const int32_t *counts, int n_ranks, int n_local_experts, int idx_stride, int32_t *pair_idx,
                        int32_t *pair_cnt, int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
+/* Gather exchange, step 1 (no reference counterpart; the partial form of the
+ * weighted sum at src/model/model.cpp:455-463): out[t][:] = sum over the pairs of
+ * token t whose expert id lies in [exp_lo, exp_hi), ascending expert id, of
+ * pair_w * Y[pair][:], separately rounded multiply and add from zero; zeros for
+ * tokens without such a pair. Y rows are indexed by pair id t*k+s. out f32 [T][H]. */
+int knj_ep_combine_partial_launch(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k,
+                                  int exp_lo, int exp_hi, float *out, knj_stream_t s);
+
+/* Gather exchange, step 2: out[t][:] = (resid[t][:] +) sum over ranks r = 0..n_ranks-1
+ * (ascending) of parts[r*rank_stride + t*H + :]; out f32 or bf16, dense rows. */
+int knj_ep_reduce_launch(const float *parts, int n_ranks, int64_t rank_stride, int T, int H, const void *resid,
+                         int resid_dtype, void *out, int out_dtype, knj_stream_t s);
+
 #ifdef __cplusplus
 }
 #endif

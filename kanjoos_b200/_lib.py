@@ -92,6 +92,8 @@ SIGNATURES = {
     "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
     "knj_ep_pack_launch": (_i, [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "knj_ep_plan_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "knj_ep_combine_partial_launch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
+    "knj_ep_reduce_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _i, _vp, _i, _vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "knj_q4k_decode_tuning": (None, [_i, _i, _i]),
     "knj_panel_bytes": (_sz, [_i, _i]),

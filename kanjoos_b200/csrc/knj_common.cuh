@@ -41,7 +41,7 @@ int sm_count();  // SMs of the current device (cached per device)
 
 // TMA descriptor over a matrix of `rows` byte rows (`row_bytes` each, a multiple of 16, base 16-byte aligned),
 // seen as 32-bit words; one copy moves a box of box_rows rows x box_bytes bytes (box_bytes <= 1024, multiple
-// of 16) into dense shared memory. No swizzle, no multicast.
+// of 16) into dense shared memory. No swizzle; the copy targets this CTA only.
 int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t row_bytes, uint32_t box_bytes,
                         uint32_t box_rows);
 
@@ -125,7 +125,7 @@ __device__ __forceinline__ bool mbar_spin(uint64_t *bar, uint32_t parity, volati
 }
 
 // Bulk async copy global -> shared of `bytes` (multiple of 16, both addresses
-// 16-byte aligned), completion counted on `bar`. Never uses cluster multicast.
+// 16-byte aligned), completion counted on `bar`. The destination is always this CTA's own shared memory.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32_t bytes, uint64_t *bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                    smem_u32(dst_smem)),

@@ -1,7 +1,8 @@
-// knj_ep.cu -- kernels around the expert-parallel exchange: rows are packed in
-// (destination rank, expert, pair) order before the dispatch all-to-all, and the
-// receiving rank turns the per-source expert counts into its local grouped-GEMM
-// plan. The reference has no multi-GPU path (it keeps every expert on one
+// knj_ep.cu -- kernels around the expert-parallel exchange. Two exchanges are served.
+// "dispatch": rows are packed in (destination rank, expert, pair) order before a per-pair all-to-all, and the
+// receiving rank turns the per-source expert counts into its local grouped-GEMM plan.
+// "gather": every rank holds all token rows (all-gather), computes its experts' pairs, forms per-token partial
+// sums over its experts (ep_combine_partial) and the ranks' partial rows are summed in rank order (ep_reduce). The reference has no multi-GPU path (it keeps every expert on one
 // device: docs/01-architecture.md:322-325); these entry points serve the
 // expert-sharded layout this library adds, and follow the pair/plan conventions
 // of the single-device path (tools/bench/q4k_stream_ffn.hip:957-1001).
@@ -84,9 +85,107 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const int32_t *__restrict_
   if (threadIdx.x == 0) pair_cnt[e] = total;
 }
 
+// Partial combine of the gather exchange: for every token of the whole batch the weighted sum over those of
+// its k pairs whose expert lives on this rank ([exp_lo, exp_hi)), in ascending expert order, separately rounded
+// multiply and add from zero (the per-rank prefix of the single-device combine). Tokens without a local expert
+// get zeros. Rows of Y are indexed by the global pair id.
+__global__ void __launch_bounds__(256) ep_combine_partial_kernel(const float *__restrict__ Y,
+                                                                 const int32_t *__restrict__ pair_exp,
+                                                                 const float *__restrict__ pair_w, int exp_lo,
+                                                                 int exp_hi, float *__restrict__ out, int H, int k) {
+  const int t = blockIdx.x;
+  __shared__ int s_row[8];
+  __shared__ float s_w[8];
+  __shared__ int s_n;
+  if (threadIdx.x == 0) {
+    int ex[8], ord[8], n = 0;
+    for (int s = 0; s < k; ++s) {
+      const int e = pair_exp[t * k + s];
+      if (e >= exp_lo && e < exp_hi) { ex[n] = e; ord[n] = s; ++n; }
+    }
+    for (int a = 1; a < n; ++a) {  // insertion sort by expert id
+      const int o = ord[a], eo = ex[a];
+      int b = a - 1;
+      while (b >= 0 && ex[b] > eo) { ord[b + 1] = ord[b]; ex[b + 1] = ex[b]; --b; }
+      ord[b + 1] = o;
+      ex[b + 1] = eo;
+    }
+    for (int s = 0; s < n; ++s) {
+      s_row[s] = t * k + ord[s];
+      s_w[s] = pair_w[t * k + ord[s]];
+    }
+    s_n = n;
+  }
+  __syncthreads();
+  const int n = s_n;
+  for (int h = threadIdx.x * 4; h < H; h += 1024) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n; ++s) {
+      const float4 y = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)s_row[s] * H + h));
+      const float w = s_w[s];
+      acc.x = __fadd_rn(acc.x, __fmul_rn(w, y.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(w, y.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(w, y.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(w, y.w));
+    }
+    *reinterpret_cast<float4 *>(out + (size_t)t * H + h) = acc;
+  }
+}
+
+// Sum of the per-rank partial rows in ascending rank order (experts are contiguous per rank, so this is the
+// single-device expert order with the additions regrouped per rank), then the optional residual, then the store.
+template <int ODT>
+__global__ void __launch_bounds__(256) ep_reduce_kernel(const float *__restrict__ parts, int n_ranks, int64_t rank_stride,
+                                                        const void *__restrict__ resid, int resid_dtype, void *__restrict__ out,
+                                                        int64_t n4) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 acc = __ldg(reinterpret_cast<const float4 *>(parts) + i);
+    for (int r = 1; r < n_ranks; ++r) {
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(parts + r * rank_stride) + i);
+      acc.x = __fadd_rn(acc.x, v.x);
+      acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z);
+      acc.w = __fadd_rn(acc.w, v.w);
+    }
+    float r4[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (resid) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r4[j] = __fadd_rn(load_as_f32(resid, resid_dtype, i * 4 + j), r4[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) store_from_f32(out, ODT, i * 4 + j, r4[j]);
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+int knj_ep_combine_partial_launch(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k,
+                                  int exp_lo, int exp_hi, float *out, knj_stream_t s) {
+  KNJ_REQUIRE(Y && pair_exp && pair_w && out, "knj_ep_combine_partial: null pointer");
+  KNJ_REQUIRE(k >= 1 && k <= 8 && H > 0 && H % 4 == 0 && exp_lo <= exp_hi, "knj_ep_combine_partial: bad k / H / expert range");
+  if (T <= 0) return KNJ_OK;
+  ep_combine_partial_kernel<<<T, 256, 0, as_stream(s)>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, out, H, k);
+  return launch_status("ep_combine_partial_kernel");
+}
+
+int knj_ep_reduce_launch(const float *parts, int n_ranks, int64_t rank_stride, int T, int H, const void *resid,
+                         int resid_dtype, void *out, int out_dtype, knj_stream_t s) {
+  KNJ_REQUIRE(parts && out, "knj_ep_reduce: null pointer");
+  KNJ_REQUIRE(n_ranks >= 1 && H > 0 && H % 4 == 0 && rank_stride % 4 == 0, "knj_ep_reduce: bad sizes");
+  KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_ep_reduce: out must be f32 or bf16");
+  KNJ_REQUIRE(!resid || (resid_dtype >= KNJ_DT_F32 && resid_dtype <= KNJ_DT_F16), "knj_ep_reduce: unknown residual dtype");
+  if (T <= 0) return KNJ_OK;
+  const int64_t n4 = (int64_t)T * H / 4;
+  const int64_t blocks = (n4 + 255) / 256, cap = (int64_t)sm_count() * 16;
+  const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+  if (out_dtype == KNJ_DT_F32)
+    ep_reduce_kernel<KNJ_DT_F32><<<grid, 256, 0, as_stream(s)>>>(parts, n_ranks, rank_stride, resid, resid_dtype, out, n4);
+  else
+    ep_reduce_kernel<KNJ_DT_BF16><<<grid, 256, 0, as_stream(s)>>>(parts, n_ranks, rank_stride, resid, resid_dtype, out, n4);
+  return launch_status("ep_reduce_kernel");
+}
 
 int knj_ep_pack_launch(const void *x, int row_bytes, int top_k, const int32_t *pair_idx, int idx_stride,
                        const int32_t *pair_cnt, int E, int32_t *send_off, void *send_rows, int32_t *pair_row,

@@ -1,18 +1,31 @@
 """Expert-parallel MoE-FFN layer: experts split contiguously over the ranks of
 a torch.distributed group (owner(e) = e // (E / world)), tokens data-parallel.
 
-Per step and rank: route the local tokens -> pack hidden rows in (destination,
-expert, pair) order -> all-to-all #1 (dispatch, bf16 rows) -> grouped expert FFN
-on the received rows -> all-to-all #2 (combine, f32 rows back to their source)
--> ordered weighted sum. torch.distributed carries the exchange (NCCL on GPUs,
-gloo in the CPU tests); every kernel is a C-ABI call of libknj_device.so.
+Two exchanges are implemented behind `EpMoeLayer(exchange=...)`:
 
-With world == 1 the same kernels run with pack and exchange elided (rows are
-gathered straight from the token buffer through the pair->token map).
+"gather" (default when every rank holds the same number of tokens): all-gather
+the token rows and the routing tables (pair_exp, pair_w) -> every rank runs the
+grouped expert FFN for the pairs of ITS experts, reading token rows through the
+pair -> token map (no per-pair copies of rows) -> per-token partial sums over the
+rank's experts -> equal-split all-to-all of the partial rows -> sum over ranks
+in ascending rank order. Per rank and step (N-1)/N * T * (row + 8 k bytes) come
+in and (N-1)/N * T * 4 H bytes go out, independent of k; all sizes are static, so
+the step needs no host synchronisation.
+
+"dispatch": route -> pack hidden rows in (destination, expert, pair) order ->
+all-to-all #1 (one row per routed pair) -> grouped expert FFN on the received
+rows -> all-to-all #2 (one f32 row per pair back) -> ordered weighted sum. Moves
+k rows per token each way and needs the split sizes on the host; kept for ranks
+with unequal token counts and as the bit-exact restatement of the single-device
+order (its result equals the single-process result bit for bit).
+
+torch.distributed carries the exchange (NCCL on GPUs, gloo in the CPU tests);
+every kernel is a C-ABI call of libknj_device.so. With world == 1 the same
+kernels run with the exchange elided.
 
 The arithmetic is delegated to a `LocalCompute` object so the host logic
-(counts, splits, plan, inverse permutation) can be exercised on CPU ranks with
-a stand-in compute in the tests.
+(counts, splits, plans, inverse permutation, partial sums) can be exercised on
+CPU ranks with a stand-in compute in the tests.
 """
 from __future__ import annotations
 
@@ -51,9 +64,13 @@ def plan_from_counts(recv_counts: torch.Tensor):
 class CudaCompute:
     """The kernels of libknj_device.so behind the LocalCompute interface."""
 
-    def __init__(self, router: torch.Tensor, top_k: int, router_bias: torch.Tensor | None = None):
+    def __init__(self, router: torch.Tensor, top_k: int, router_bias: torch.Tensor | None = None,
+                 tc_rows_per_expert: int = 16):
         from . import ops  # deferred: needs the CUDA library
         self.ops, self.router, self.top_k, self.bias = ops, router, top_k, router_bias
+        # received rows per local expert from which the tensor-core grouped GEMMs take over
+        # (below it the f32-accurate GEMV-class kernels run)
+        self.tc_rows_per_expert = tc_rows_per_expert
 
     def route(self, x):
         _, pe, pw = self.ops.router_topk(x, self.router, self.top_k, self.bias)
@@ -92,6 +109,12 @@ class CudaCompute:
         """rows [R][H] -> Y f32 [R][H]; row i of `rows` is pair i of the local plan."""
         pair_idx, pair_cnt, exp_list, n_active = plan
         ops = self.ops
+        if n_rows >= self.tc_rows_per_expert * pair_cnt.shape[0]:
+            xh = ops.to_f16(rows)
+            A, st = ops.q4k_gateup_tc(xh, bank.gate, bank.up, pair_idx, pair_cnt, n_rows, 1, poison=False)
+            Y, st2 = ops.q4k_down_tc(A, bank.down, pair_idx, pair_cnt, n_rows, poison=False)
+            self.last_status = (st, st2)  # device flags: non-zero if a bounded wait inside the kernels gave up
+            return Y
         xp = ops.act_prep(rows)
         A = ops.q4k_gateup(xp, bank.gate, bank.up, pair_idx, pair_cnt, exp_list, n_active, n_rows, 1, max_tokens,
                            want=("A",))["A"]
@@ -101,16 +124,63 @@ class CudaCompute:
     def combine(self, Yback, pair_row, pair_exp, pair_w, T, out_dtype):
         return self.ops.moe_combine(Yback, pair_exp, pair_w, T, self.top_k, out_dtype=out_dtype, pair_row=pair_row)
 
+    # ---- gather exchange
+    def plan_for_experts(self, pair_exp_all, exp_lo, e_loc, stride):
+        """Plan over the global pair list restricted to experts [exp_lo, exp_lo + e_loc): pair ids stay global."""
+        local_ids = pair_exp_all - exp_lo  # ids outside [0, e_loc) match no expert of the plan
+        return self.ops.moe_permute(local_ids, e_loc, stride)
+
+    def expert_ffn_tokens(self, x_all, bank, plan, P, n_local_pairs_hint):
+        """x_all [T][H] -> Y f32 [P][H], rows = global pair ids (rows of other ranks' pairs stay unwritten)."""
+        pair_idx, pair_cnt, exp_list, n_active = plan
+        ops, k = self.ops, self.top_k
+        if n_local_pairs_hint >= self.tc_rows_per_expert * pair_cnt.shape[0]:
+            xh = ops.to_f16(x_all)
+            A, st = ops.q4k_gateup_tc(xh, bank.gate, bank.up, pair_idx, pair_cnt, P, k, poison=False)
+            Y, st2 = ops.q4k_down_tc(A, bank.down, pair_idx, pair_cnt, P, poison=False)
+            self.last_status = (st, st2)
+            return Y
+        xp = ops.act_prep(x_all)
+        T = x_all.shape[0]
+        A = ops.q4k_gateup(xp, bank.gate, bank.up, pair_idx, pair_cnt, exp_list, n_active, P, k, T, want=("A",))["A"]
+        ap = ops.act_prep(A)  # rows of foreign pairs are unwritten and never read back
+        return ops.q4k_proj(ap, bank.down, pair_idx, pair_cnt, exp_list, n_active, P, T)
+
+    def combine_partial(self, Y, pair_exp_all, pair_w_all, T, exp_lo, exp_hi):
+        from ._lib import check, lib
+        H = Y.shape[1]
+        out = torch.empty((T, H), dtype=torch.float32, device=Y.device)
+        check(lib().knj_ep_combine_partial_launch(C.c_void_p(Y.data_ptr()), C.c_void_p(pair_exp_all.data_ptr()),
+                                                  C.c_void_p(pair_w_all.data_ptr()), T, H, self.top_k, exp_lo, exp_hi,
+                                                  C.c_void_p(out.data_ptr()),
+                                                  C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
+    def reduce_parts(self, parts, out_dtype):
+        """parts f32 [world][T_loc][H] -> [T_loc][H], ranks summed in ascending order."""
+        from ._lib import check, lib
+        world, T_loc, H = parts.shape
+        out = torch.empty((T_loc, H), dtype=out_dtype, device=parts.device)
+        dt = {torch.float32: 0, torch.bfloat16: 1}[out_dtype]
+        check(lib().knj_ep_reduce_launch(C.c_void_p(parts.data_ptr()), world, T_loc * H, T_loc, H, None, 0,
+                                         C.c_void_p(out.data_ptr()), dt,
+                                         C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
 
 class EpMoeLayer:
     """One expert-parallel MoE-FFN layer on this rank.
 
     bank: the LOCAL experts (E/world of them, ids rank*E/world ...); the router
     weight inside `compute` covers all E experts and is replicated.
+    exchange: "gather" or "dispatch" (see the module text). "gather" needs the
+    same token count on every rank.
     """
 
-    def __init__(self, bank, n_experts: int, compute, group=None, top_k: int = synth.TOP_K):
+    def __init__(self, bank, n_experts: int, compute, group=None, top_k: int = synth.TOP_K, exchange: str = "gather"):
+        assert exchange in ("gather", "dispatch")
         self.bank, self.E, self.compute, self.group, self.top_k = bank, n_experts, compute, group, top_k
+        self.exchange = exchange
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         assert n_experts % self.world == 0
@@ -118,6 +188,37 @@ class EpMoeLayer:
         self.last_stats = {}
 
     def forward(self, x: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+        if self.exchange == "gather":
+            return self._forward_gather(x, out_dtype)
+        return self._forward_dispatch(x, out_dtype)
+
+    def _forward_gather(self, x: torch.Tensor, out_dtype) -> torch.Tensor:
+        T_loc, H = x.shape
+        world, k, cp = self.world, self.top_k, self.compute
+        T = T_loc * world
+        pair_exp, pair_w = cp.route(x)
+        if world == 1:
+            x_all, pe_all, pw_all = x, pair_exp, pair_w
+        else:
+            x_all = torch.empty((T, H), dtype=x.dtype, device=x.device)
+            pe_all = torch.empty(T * k, dtype=pair_exp.dtype, device=x.device)
+            pw_all = torch.empty(T * k, dtype=pair_w.dtype, device=x.device)
+            dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+            dist.all_gather_into_tensor(pe_all, pair_exp, group=self.group)
+            dist.all_gather_into_tensor(pw_all, pair_w, group=self.group)
+        lo = self.rank * self.e_loc
+        plan = cp.plan_for_experts(pe_all, lo, self.e_loc, max(T, 1))
+        self.last_stats = {"tokens_gathered": int(T)}
+        Y = cp.expert_ffn_tokens(x_all, self.bank, plan, T * k, (T * k) // world)
+        part = cp.combine_partial(Y, pe_all, pw_all, T, lo, lo + self.e_loc)
+        if world == 1:
+            parts = part.view(1, T, H)
+        else:
+            parts = torch.empty((world, T_loc, H), dtype=torch.float32, device=x.device)
+            dist.all_to_all_single(parts.view(T, H), part, group=self.group)  # block j of `part` -> rank j
+        return cp.reduce_parts(parts, out_dtype)
+
+    def _forward_dispatch(self, x: torch.Tensor, out_dtype) -> torch.Tensor:
         T, H = x.shape
         P = T * self.top_k
         cp = self.compute

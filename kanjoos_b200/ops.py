@@ -187,21 +187,24 @@ def to_f16(x: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def q4k_gateup_tc(xh, Wg, Wu, pair_idx, pair_cnt, P: int, top_k: int, pair_tok=None):
-    """Tensor-core grouped gate+up: returns (A fp16 [P][N] scaled by 2^-6, status int32[1])."""
+def q4k_gateup_tc(xh, Wg, Wu, pair_idx, pair_cnt, P: int, top_k: int, pair_tok=None, poison: bool = True):
+    """Tensor-core grouped gate+up: returns (A fp16 [P][N] scaled by 2^-6, status int32[1]).
+    poison=True pre-fills A with NaN so that tests can see unwritten rows."""
     _need(xh, torch.float16)
     E, N, nsb, _ = Wg.shape
-    A = torch.full((P, N), float("nan"), dtype=torch.float16, device="cuda")
+    A = (torch.full((P, N), float("nan"), dtype=torch.float16, device="cuda") if poison
+         else torch.empty((P, N), dtype=torch.float16, device="cuda"))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     check(lib().knj_q4k_gateup_tc_launch(_p(xh), _p(Wg), _p(Wu), _p(pair_idx), _p(pair_cnt), _p(pair_tok), _p(A), N,
                                          nsb * 256, nsb * 144, pair_idx.shape[1], E, top_k, P, _p(status), _stream()))
     return A, status
 
 
-def q4k_down_tc(ah, Wd, pair_idx, pair_cnt, P: int, pair_row=None):
+def q4k_down_tc(ah, Wd, pair_idx, pair_cnt, P: int, pair_row=None, poison: bool = True):
     _need(ah, torch.float16)
     E, N, nsb, _ = Wd.shape
-    Y = torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda")
+    Y = (torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda") if poison
+         else torch.empty((P, N), dtype=torch.float32, device="cuda"))
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     check(lib().knj_q4k_down_tc_launch(_p(ah), _p(Wd), _p(pair_idx), _p(pair_cnt), _p(pair_row), _p(Y), N, nsb * 256,
                                        nsb * 144, pair_idx.shape[1], E, P, _p(status), _stream()))

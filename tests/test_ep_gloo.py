@@ -1,9 +1,14 @@
-"""Host logic of the expert-parallel layer on CPU ranks (gloo, world_size 2 and
-1): split sizes, dispatch/combine all-to-all, the receiving rank's local plan and
-the inverse permutation. The arithmetic is supplied by a stand-in built on the
-CPU restatement of the reference, so the sharded result must equal the
-single-process Model::moe result bit for bit (same per-expert row order, same
-ascending-expert combine)."""
+"""Host logic of the expert-parallel layer on CPU ranks (gloo, world_size 1, 2
+and 4), both exchanges. The arithmetic is supplied by a stand-in built on the CPU
+restatement of the reference.
+"dispatch": split sizes, per-pair all-to-all, the receiving rank's local plan and
+the inverse permutation; the sharded result must equal the single-process
+Model::moe result bit for bit (same per-expert row order, same ascending-expert
+combine).
+"gather": all-gather of rows and routing tables, the plan restricted to the
+rank's experts, per-token partial sums, equal-split all-to-all and the
+rank-ordered sum; bit-equal at world 1, and equal up to the regrouping of the f32
+additions (<= 1e-6 relative RMSE) at world 2 and 4."""
 import os
 import socket
 
@@ -72,6 +77,48 @@ class OracleCompute:
         return torch.from_numpy(out)
 
 
+def _gather_methods():
+    """The gather-exchange half of the stand-in (added to OracleCompute below)."""
+
+    def plan_for_experts(self, pair_exp_all, exp_lo, e_loc, stride):
+        pe = pair_exp_all.numpy()
+        return [[int(p) for p in np.nonzero(pe == exp_lo + e)[0]] for e in range(e_loc)]
+
+    def expert_ffn_tokens(self, x_all, bank, plan, P, hint):
+        xr = x_all.numpy()
+        Y = np.full((P, xr.shape[1]), np.nan, np.float32)  # rows of foreign pairs must never be read
+        for e, pairs in enumerate(plan):
+            if not pairs:
+                continue
+            rows = xr[[p // self.top_k for p in pairs]]
+            g = ol.matmul_q4k(bank["gate"][e], rows)
+            u = ol.matmul_q4k(bank["up"][e], rows)
+            Y[pairs] = ol.matmul_q4k(bank["down"][e], ol.silu_mul(g, u))
+        return torch.from_numpy(Y)
+
+    def combine_partial(self, Y, pair_exp_all, pair_w_all, T_all, exp_lo, exp_hi):
+        pe, pw, Yn = pair_exp_all.numpy(), pair_w_all.numpy(), Y.numpy()
+        out = np.zeros((T_all, Yn.shape[1]), np.float32)
+        for t in range(T_all):
+            slots = [s for s in range(self.top_k) if exp_lo <= pe[t * self.top_k + s] < exp_hi]
+            for s in sorted(slots, key=lambda s: pe[t * self.top_k + s]):
+                p = t * self.top_k + s
+                out[t] = out[t] + np.float32(pw[p]) * Yn[p]
+        return torch.from_numpy(out)
+
+    def reduce_parts(self, parts, out_dtype):
+        acc = parts[0].numpy().copy()
+        for r in range(1, parts.shape[0]):
+            acc = acc + parts[r].numpy()
+        return torch.from_numpy(acc)
+
+    return plan_for_experts, expert_ffn_tokens, combine_partial, reduce_parts
+
+
+(OracleCompute.plan_for_experts, OracleCompute.expert_ffn_tokens, OracleCompute.combine_partial,
+ OracleCompute.reduce_parts) = _gather_methods()
+
+
 def problem():
     bank = synth.expert_bank(CFG, n_experts=E, hidden=H, ffn=F)
     wr, _ = synth.router_weight(CFG, n_experts=E, hidden=H)
@@ -79,18 +126,18 @@ def problem():
     return bank, wr, hx
 
 
-def _rank_main(rank, world, port, out_dir):
+def _rank_main(rank, world, port, out_dir, exchange="dispatch"):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         bank, wr, hx = problem()
         e_loc, t_loc = E // world, T // world
         local = {k: np.ascontiguousarray(v[rank * e_loc:(rank + 1) * e_loc]) for k, v in bank.items()}
-        layer = ep.EpMoeLayer(local, E, OracleCompute(wr, K), None, K)
+        layer = ep.EpMoeLayer(local, E, OracleCompute(wr, K), None, K, exchange=exchange)
         x = torch.from_numpy(hx[rank * t_loc:(rank + 1) * t_loc].copy())
         out = layer.forward(x)
         np.save(os.path.join(out_dir, f"out{rank}.npy"), out.numpy())
-        np.save(os.path.join(out_dir, f"rows{rank}.npy"), np.array([layer.last_stats["rows_received"]]))
+        np.save(os.path.join(out_dir, f"rows{rank}.npy"), np.array([layer.last_stats.get("rows_received", -1)]))
     finally:
         dist.destroy_process_group()
 
@@ -105,7 +152,7 @@ def _free_port():
 def test_sharded_equals_single_process(tmp_path, world):
     bank, wr, hx = problem()
     want, chosen, _ = ol.moe(wr, bank, hx, K)
-    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path), "dispatch"), nprocs=world, join=True)
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
     # every routed pair reached the rank that owns its expert
@@ -114,10 +161,21 @@ def test_sharded_equals_single_process(tmp_path, world):
     assert rows == owner_rows.tolist() and sum(rows) == T * K
 
 
-def test_world_one_takes_the_same_path(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_gather_exchange_matches_single_process(tmp_path, world):
     bank, wr, hx = problem()
     want, _, _ = ol.moe(wr, bank, hx, K)
-    layer = ep.EpMoeLayer(bank, E, OracleCompute(wr, K), None, K)
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path), "gather"), nprocs=world, join=True)
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    st = ol.compare(np.ascontiguousarray(got, dtype=np.float32), want)
+    assert st["rel_rmse"] <= 1e-6, st  # same products, additions regrouped per rank
+
+
+@pytest.mark.parametrize("exchange", ["dispatch", "gather"])
+def test_world_one_takes_the_same_path(tmp_path, exchange):
+    bank, wr, hx = problem()
+    want, _, _ = ol.moe(wr, bank, hx, K)
+    layer = ep.EpMoeLayer(bank, E, OracleCompute(wr, K), None, K, exchange=exchange)
     got = layer.forward(torch.from_numpy(hx.copy())).numpy()
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 

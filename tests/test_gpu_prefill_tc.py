@@ -28,13 +28,24 @@ def ragged_problem(E, F, H, counts, seed):
     return pe, Wg, Wu, Wd, x
 
 
-@pytest.mark.parametrize("E,F,H,counts", [
-    (4, 256, 256, [5, 0, 1, 40]),
-    (3, 256, 512, [16, 300, 0]),
-    (2, 768, 2048, [33, 7]),
+@pytest.mark.parametrize("E,F,H,counts,single_sm", [
+    (4, 256, 256, [5, 0, 1, 40], 0),
+    (3, 256, 512, [16, 300, 0], 0),
+    (2, 768, 2048, [33, 7], 0),
+    (3, 256, 512, [16, 300, 0], 1),   # the same buckets on single SMs (tcgen05 cta_group::1)
+    (2, 256, 768, [130, 9], 0),       # 768 = 3 x 256 rows of the down matrix: odd tile count, single-SM form
+    (2, 256, 256, [256, 255], 0),     # a full bucket and one token short of it, CTA pairs
 ])
-def test_grouped_gemms(E, F, H, counts):
-    from kanjoos_b200 import ops
+def test_grouped_gemms(E, F, H, counts, single_sm):
+    from kanjoos_b200 import ops, _lib
+    _lib.lib().knj_tc_tuning(single_sm)
+    try:
+        _grouped_gemms(ops, E, F, H, counts)
+    finally:
+        _lib.lib().knj_tc_tuning(0)
+
+
+def _grouped_gemms(ops, E, F, H, counts):
     pe, Wg, Wu, Wd, x = ragged_problem(E, F, H, counts, [E, F, H])
     T = len(pe)
     pair_idx, pair_cnt, _, _ = ops.moe_permute(dev(pe), E, T)
