@@ -133,6 +133,13 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src, uint32
                : "memory");
 }
 // TMA tiled copy of one box: x = first 32-bit word inside the row (a multiple of 4), y = first row.
+// Ask for the same box to be brought into L2 only (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_rows(const CUtensorMap *map, int x_words, int y_row) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x_words),
+               "r"(y_row)
+               : "memory");
+}
+
 __device__ __forceinline__ unsigned long long global_timer_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

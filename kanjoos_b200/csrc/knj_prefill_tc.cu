@@ -94,6 +94,14 @@ __device__ __forceinline__ void tc_commit_addr(uint32_t bar_addr) {
   if (CG == 1) asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
   else asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_addr) : "memory");
 }
+// the same, signalled to the barrier at this shared-memory offset in both CTAs of the pair by one instruction
+// (a barrier arrival, not a data copy)
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_addr) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar_addr),
+               "h"(mask)
+               : "memory");
+}
 // shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
 __device__ __forceinline__ uint32_t cluster_addr(const void *smem_ptr, uint32_t rank) {
   uint32_t r;
@@ -176,8 +184,8 @@ __device__ __forceinline__ void pair_sync(int pair) { asm volatile("bar.sync %0,
 template <int NMAT, int CG>
 struct Smem {
   // operand tiles: 1024-byte aligned for the swizzle pattern
-  static constexpr int kStagesA = CG == 2 ? 3 : 2;  // weight operand stages
-  static constexpr int kStagesB = CG == 2 ? 3 : 2;  // token operand stages
+  static constexpr int kStages = CG == 2 ? 3 : 2;   // operand stages (weights and token rows advance together)
+  static constexpr int kStagesA = kStages, kStagesB = kStages;
   static constexpr int kTokCta = kMaxTok / CG;   // token rows this CTA stages per slab
   static constexpr int kATile = kRowsM * 128;    // 16 KB per matrix per stage
   static constexpr int kBTile = kTokCta * 128;   // 32 KB (16 KB in a pair) per stage
@@ -201,7 +209,7 @@ struct Smem {
 template <int NMAT, bool GATEUP, int CG>
 __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __grid_constant__ TcParams p) {
   using S = Smem<NMAT, CG>;
-  constexpr int kStagesA = S::kStagesA, kStagesB = S::kStagesB;
+  constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -232,12 +240,10 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   const int nsb = p.K / KNJ_QK_K, nslab = p.K / kSlabK;
 
   uint64_t *bars = reinterpret_cast<uint64_t *>(smem + S::kOffBars);
-  uint64_t *fullA = bars;                          // [kStagesA] unpackers -> MMA (the even CTA's are used)
-  uint64_t *emptyA = fullA + kStagesA;             // [kStagesA] MMA -> unpackers
-  uint64_t *fullB = emptyA + kStagesA;             // [kStagesB] this CTA's loaders (asynchronous copies landed)
-  uint64_t *emptyB = fullB + kStagesB;             // [kStagesB] MMA -> loaders
-  uint64_t *peerB = emptyB + kStagesB;             // [kStagesB] even CTA only: the odd CTA's token rows landed
-  uint64_t *raw_full = peerB + kStagesB;           // [2 buffers][4 row groups] TMA boxes landed
+  uint64_t *full = bars;                           // [kStages] unpackers + loaders -> MMA (the even CTA's are used)
+  uint64_t *empty = full + kStages;                // [kStages] MMA -> unpackers and loaders
+  uint64_t *locB = empty + kStages;                // [kStages] odd CTA only: its own loaders' copies landed
+  uint64_t *raw_full = locB + kStages;             // [2 buffers][4 row groups] TMA boxes landed
   uint64_t *acc_full = raw_full + 8;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 1);
   volatile int *s_fail = reinterpret_cast<volatile int *>(tmem_slot + 1);  // raised by the first wait that gives up
@@ -245,8 +251,13 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   int32_t *s_row = reinterpret_cast<int32_t *>(smem + S::kOffRows);
 
   if (tid == 0) {
-    for (int s = 0; s < kStagesA; ++s) { mbar_init(&fullA[s], CG * kProducerThreads / 32); mbar_init(&emptyA[s], 1); }
-    for (int s = 0; s < kStagesB; ++s) { mbar_init(&fullB[s], kLoaderThreads); mbar_init(&emptyB[s], 1); mbar_init(&peerB[s], 1); }
+    // one "full" barrier per stage: 8 unpacker warps per CTA, this CTA's loader threads (asynchronous-copy
+    // arrivals) and, in a pair, one relayed arrival for the odd CTA's loaders
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], CG * 8 + kLoaderThreads + (CG == 2 ? 1 : 0));
+      mbar_init(&empty[s], 1);
+      mbar_init(&locB[s], kLoaderThreads);
+    }
     for (int i = 0; i < 8; ++i) mbar_init(&raw_full[i], 1);
     mbar_init(acc_full, 1);
     *s_fail = 0;
@@ -338,9 +349,9 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
 #pragma unroll
       for (int G = 0; G < 4; ++G) {
         if (!ok) break;
-        const int ks = b * 4 + G, stage = ks % kStagesA;
+        const int ks = b * 4 + G, stage = ks % kStages;
         if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 0] = clock64();
-        if (ks >= kStagesA && !mbar_wait(&emptyA[stage], ((ks / kStagesA) - 1) & 1, s_fail)) { ok = false; break; }
+        if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
         tc_fence_after();
         if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 1] = clock64();
         // ---- weight operand(s): 16 code bytes -> 16 low-nibble + 16 high-nibble weights of this row
@@ -373,8 +384,8 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-          if (CG == 2) mbar_arrive_cluster(cluster_addr(&fullA[stage], 0));
-          else mbar_arrive(&fullA[stage]);
+          if (CG == 2) mbar_arrive_cluster(cluster_addr(&full[stage], 0));
+          else mbar_arrive(&full[stage]);
         }
         if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 2] = clock64();
       }
@@ -397,10 +408,10 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
       rowp[j] = xr >= 0 ? p.X + (size_t)xr * p.K + c * 8 : nullptr;
     }
     for (int ks = 0; ks < nslab && ok; ++ks) {  // loaders meet no CTA barrier before the final one
-      const int stage = ks % kStagesB;
+      const int stage = ks % kStages;
       const bool ltr = p.trace && blockIdx.x == 0 && lt == 0 && ks < 12;
       if (ltr) p.trace[64 + 4 * ks] = clock64();
-      if (ks >= kStagesB && !mbar_wait(&emptyB[stage], ((ks / kStagesB) - 1) & 1, s_fail)) { ok = false; break; }
+      if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
       if (ltr) p.trace[64 + 4 * ks + 1] = clock64();
       uint8_t *bt = smem + S::kOffB + stage * S::kBTile;
 #pragma unroll
@@ -410,48 +421,47 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
           cp_async16(bt + r * 128 + ((c ^ (r & 7)) << 4), rowp[j] ? (const void *)(rowp[j] + ks * kSlabK) : (const void *)p.X,
                      rowp[j] ? 16u : 0u);
       }
-      cp_async_arrive(&fullB[stage]);
+      cp_async_arrive(rank == 0 ? &full[stage] : &locB[stage]);
       if (ltr) p.trace[64 + 4 * ks + 3] = clock64();
     }
   } else if (CG == 2 && warp == 8 && lane == 0 && rank == 1) {
     // =========================== relay (odd CTA) ===========================
     // cp.async completions can only arrive on a barrier of their own CTA: pass them on to the MMA thread
     for (int ks = 0; ks < nslab && ok; ++ks) {
-      const int sb = ks % kStagesB;
-      if (!mbar_spin(&fullB[sb], (ks / kStagesB) & 1, s_fail)) { ok = false; break; }
-      fence_proxy_async();
-      mbar_arrive_cluster(cluster_addr(&peerB[sb], 0));
+      const int sb = ks % kStages;
+      if (!mbar_spin(&locB[sb], (ks / kStages) & 1, s_fail)) { ok = false; break; }
+      mbar_arrive_cluster(cluster_addr(&full[sb], 0));
     }
   } else if (warp == 8 && lane == 0 && rank == 0) {
     // =========================== MMA issue ===========================
+    // Every instruction this thread issues (MMA, commit, barrier test) costs it on the order of a hundred
+    // cycles, and the tensor pipe queues little: what is not an MMA here is idle pipe time. Hence one "full"
+    // barrier per stage for both operands and one commit per CTA.
     const uint32_t idesc = instr_desc_f16(kRowsM * CG, n_mma);
     for (int ks = 0; ks < nslab && ok; ++ks) {
-      const int sa = ks % kStagesA, sb = ks % kStagesB;
-      if (!mbar_spin(&fullB[sb], (ks / kStagesB) & 1, s_fail)) { ok = false; break; }
-      if (CG == 2 && !mbar_spin(&peerB[sb], (ks / kStagesB) & 1, s_fail)) { ok = false; break; }
-      if (!mbar_spin(&fullA[sa], (ks / kStagesA) & 1, s_fail)) { ok = false; break; }
-      fence_proxy_async();  // the gathered rows were written by asynchronous copies of other threads
+      const int st = ks % kStages;
+      if (!mbar_spin(&full[st], (ks / kStages) & 1, s_fail)) { ok = false; break; }
+      // No proxy fence here: the unpackers fence their own stores before arriving, the gathered rows are
+      // complete when their copies' arrivals are (the hand-off CUTLASS' cp.async tcgen05 main loop relies on),
+      // and a fence.proxy.async in this thread would wait for the shared-memory reads of every MMA in flight.
       tc_fence_after();
       if (p.trace && blockIdx.x == 0 && ks < 12) p.trace[4 * ks + 3] = clock64();
-      const uint32_t b_addr = smem_u32(smem + S::kOffB + sb * S::kBTile);
+      const uint32_t b_addr = smem_u32(smem + S::kOffB + st * S::kBTile);
+      const uint32_t a_addr = smem_u32(smem + S::kOffA + st * NMAT * S::kATile);
 #pragma unroll
-      for (int mat = 0; mat < NMAT; ++mat) {
-        const uint32_t a_addr = smem_u32(smem + S::kOffA + (sa * NMAT + mat) * S::kATile);
+      for (int k = 0; k < kSlabK / 16; ++k) {
 #pragma unroll
-        for (int k = 0; k < kSlabK / 16; ++k)
-          tc_mma_f16<CG>(tmem_base + mat * kMaxTok, smem_desc_sw128(a_addr + k * 32), smem_desc_sw128(b_addr + k * 32), idesc,
-                         (ks > 0 || k > 0) ? 1u : 0u);
+        for (int mat = 0; mat < NMAT; ++mat)  // consecutive instructions alternate between the two accumulators
+          tc_mma_f16<CG>(tmem_base + mat * kMaxTok, smem_desc_sw128(a_addr + mat * S::kATile + k * 32),
+                         smem_desc_sw128(b_addr + k * 32), idesc, (ks > 0 || k > 0) ? 1u : 0u);
       }
-      tc_commit_addr<CG>(smem_u32(&emptyA[sa]));
-      tc_commit_addr<CG>(smem_u32(&emptyB[sb]));
-      if (CG == 2) {
-        tc_commit_addr<CG>(cluster_addr(&emptyA[sa], 1));
-        tc_commit_addr<CG>(cluster_addr(&emptyB[sb], 1));
-      }
+      if (CG == 2) tc_commit_pair(smem_u32(&empty[st]));
+      else tc_commit_addr<CG>(smem_u32(&empty[st]));
+      if (p.trace && blockIdx.x == 0 && ks < 12) p.trace[128 + ks] = clock64();
     }
     if (ok) {
-      tc_commit_addr<CG>(smem_u32(acc_full));
-      if (CG == 2) tc_commit_addr<CG>(cluster_addr(acc_full, 1));
+      if (CG == 2) tc_commit_pair(smem_u32(acc_full));
+      else tc_commit_addr<CG>(smem_u32(acc_full));
     }
   }
 
@@ -593,7 +603,7 @@ void knj_tc_trace(void *dev_buf, int cta_slots) {
 
 // Experiment hook (no reference counterpart): 1 = run every tile on a single SM (cta_group::1) even where
 // CTA pairs apply; 0 = automatic.
-void knj_tc_tuning(int force_single_sm) { g_tc_force_single = force_single_sm; }
+void knj_tc_tuning(int force_single_sm) { g_tc_force_single = force_single_sm & 1; }
 
 int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s) {
   KNJ_REQUIRE(x && out_f16, "knj_to_f16: null pointer");
