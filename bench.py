@@ -283,7 +283,7 @@ def run_gpu(args):
             layers[i % n_banks].prefill(xin, out=dst)
     else:
         cp = CudaCompute(router, TOPK, bias)
-        eps = [EpMoeLayer(bk, E, cp, None, TOPK) for bk in banks]
+        eps = [EpMoeLayer(bk, E, cp, None, TOPK, exchange=args.exchange) for bk in banks]
 
         def step(i, xin=x, dst=out):
             dst.copy_(eps[i % n_banks].forward(xin, out_dtype=torch.bfloat16))
@@ -426,7 +426,7 @@ def run_gpu(args):
             torch.cuda.empty_cache()
             dec = decode_section(torch, max(5, args.steps), args.warmup, pk)
 
-    launches = 8 if world == 1 else 9  # router 2, permute 2, to_f16, gate+up, down, combine (N>1: partial combine + rank reduce)
+    launches = 8 if world == 1 else 12  # router 2, permute 2, to_f16, gate+up, down, combine (N>1: + 3 peer gathers, partial combine to peers, rank reduce)
     line = {"metric": "moe_ffn_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16 operands (Q4_K unpacked), f32 accumulate", "data": "synthetic",
@@ -451,6 +451,7 @@ def main():
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--cpu-sample", type=int, default=1024, dest="cpu_sample")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "gather", "dispatch"], help="expert-parallel exchange (N > 1)")
     ap.add_argument("--section", default="all", choices=["all", "decode"])
     ap.add_argument("--decode-layers", type=int, default=LAYERS, dest="decode_layers")
     ap.add_argument("--decode-batches", default="1,8,64", dest="decode_batches")

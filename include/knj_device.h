@@ -313,6 +313,12 @@ void knj_tc_trace(void *dev_buf, int cta_slots);
  * 0 = automatic (pairs whenever a bucket has an even number of row tiles). */
 void knj_tc_tuning(int force_single_sm);
 
+/* Launch mode of the kernels of a decode layer (no reference counterpart).
+ * 1 (default): programmatic stream serialization -- each grid may be scheduled
+ * while its predecessor on the stream drains and waits on the device for the
+ * predecessor's completion before reading its results; 0: plain launches. */
+void knj_chain_overlap(int on);
+
 /* Grouped gate+up GEMM over per-expert token buckets on the tensor cores
  * (tools/bench/q4k_moe_ffn.hip:164-241 knj_q4k_gateup fused with
  * tools/bench/q4k_stream_ffn.hip:1021-1031 knj_fuse_gateup_silu): for every
@@ -404,6 +410,27 @@ int knj_ep_combine_partial_launch(const float *Y, const int32_t *pair_exp, const
  * (ascending) of parts[r*rank_stride + t*H + :]; out f32 or bf16, dense rows. */
 int knj_ep_reduce_launch(const float *parts, int n_ranks, int64_t rank_stride, int T, int H, const void *resid,
                          int resid_dtype, void *out, int out_dtype, knj_stream_t s);
+
+/* Peer exchange (no reference counterpart): the gather exchange with the rows
+ * moved by this library's kernels over NVLink peer mappings instead of NCCL
+ * collectives. src_ptrs / parts_ptrs are DEVICE arrays of n_ranks pointers, entry
+ * r = rank r's exchange buffer mapped into this process (entry own-rank = the
+ * local buffer). The caller orders the steps across ranks (a barrier after the
+ * rows are published and one after the partial rows are stored).
+ * knj_ep_peer_gather: dst[r*bytes_per_rank + i] = src_ptrs[r][i].
+ * knj_ep_combine_partial_peer: as knj_ep_combine_partial, but the row of token t
+ * goes to parts_ptrs[t / T_loc][(my_rank*T_loc + t % T_loc)*H ...] and tokens
+ * without an expert in [exp_lo, exp_hi) are skipped.
+ * knj_ep_reduce_sel: out[t] = (resid[t] +) sum, ascending rank r, of
+ * parts[(r*T_loc + t)*H ...] over the ranks that own one of token t's k experts
+ * (rank of expert e = e / experts_per_rank); pair_exp is the LOCAL table [T_loc*k]. */
+int knj_ep_peer_gather_launch(const void *const *src_ptrs, int n_ranks, int64_t bytes_per_rank, void *dst, knj_stream_t s);
+int knj_ep_combine_partial_peer_launch(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k,
+                                       int exp_lo, int exp_hi, float *const *parts_ptrs, int my_rank, int T_loc,
+                                       knj_stream_t s);
+int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, const int32_t *pair_exp, int k,
+                             int experts_per_rank, const void *resid, int resid_dtype, void *out, int out_dtype,
+                             knj_stream_t s);
 
 #ifdef __cplusplus
 }

@@ -94,6 +94,9 @@ SIGNATURES = {
     "knj_ep_plan_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "knj_ep_combine_partial_launch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),
     "knj_ep_reduce_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _i, _vp, _i, _vp]),
+    "knj_ep_peer_gather_launch": (_i, [_vp, _i, _i64, _vp, _vp]),
+    "knj_ep_combine_partial_peer_launch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
+    "knj_ep_reduce_sel_launch": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "knj_q4k_decode_tuning": (None, [_i, _i, _i]),
     "knj_panel_bytes": (_sz, [_i, _i]),
@@ -103,6 +106,7 @@ SIGNATURES = {
     "knj_q4k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp]),
     "knj_tc_trace": (None, [_vp, _i]),
     "knj_tc_tuning": (None, [_i]),
+    "knj_chain_overlap": (None, [_i]),
     "knj_to_f16_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp]),
     "knj_q4k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),

@@ -3,6 +3,7 @@
 #pragma once
 
 #include <cuda.h>
+#include <utility>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -39,6 +40,26 @@ inline cudaStream_t as_stream(knj_stream_t s) { return reinterpret_cast<cudaStre
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 int sm_count();  // SMs of the current device (cached per device)
 
+// Launch of a kernel that belongs to a chain of dependent launches on one stream (the decode layer). With
+// overlap on, the launch carries the programmatic-stream-serialization attribute: the grid may be scheduled
+// while its predecessor drains, and it must call grid_dep_wait() before it touches anything the predecessor
+// wrote. Off (knj_chain_overlap(0)): a plain launch; grid_dep_wait() is then a no-op.
+extern int g_chain_overlap;
+template <class... KArgs, class... Args>
+inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = g_chain_overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
 // TMA descriptor over a matrix of `rows` byte rows (`row_bytes` each, a multiple of 16, base 16-byte aligned),
 // seen as 32-bit words; one copy moves a box of box_rows rows x box_bytes bytes (box_bytes <= 1024, multiple
 // of 16) into dense shared memory. No swizzle; the copy targets this CTA only.
@@ -47,6 +68,13 @@ int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint3
 
 // ---- device helpers --------------------------------------------------------
 #if defined(__CUDACC__)
+
+// Blocks until the grids this launch depends on have completed and their writes are visible; then lets the
+// next launch of the chain be scheduled early. No-ops for a plain launch.
+__device__ __forceinline__ void grid_dep_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

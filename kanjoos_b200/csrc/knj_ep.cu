@@ -157,9 +157,141 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const float *__restrict_
   }
 }
 
+// ---- "peer" exchange: the same two steps with the rows moved by this library's own kernels over NVLink peer
+// mappings (every rank maps every other rank's exchange buffers into its address space).
+
+// dst[r * bytes_per_rank + i] = src[r][i]: pulls the published rows (or routing tables) of every rank into
+// local memory, 16 bytes per thread and step; source r == own rank is a local copy.
+__global__ void __launch_bounds__(256) ep_peer_gather_kernel(const uint4 *const *__restrict__ src, int n_ranks,
+                                                             int64_t u4_per_rank, uint4 *__restrict__ dst) {
+  const int64_t total = (int64_t)n_ranks * u4_per_rank;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / u4_per_rank);
+    const int64_t j = i - (int64_t)r * u4_per_rank;
+    dst[i] = src[r][j];
+  }
+}
+
+// ep_combine_partial with the result row stored straight into the token owner's buffer: parts[owner] points at
+// the owner's [n_ranks][T_loc][H] f32 array, this rank fills slot `my_rank`. Tokens without a local expert are
+// skipped (the owner knows from its own routing table which ranks contribute).
+__global__ void __launch_bounds__(256) ep_combine_partial_peer_kernel(const float *__restrict__ Y,
+                                                                      const int32_t *__restrict__ pair_exp,
+                                                                      const float *__restrict__ pair_w, int exp_lo,
+                                                                      int exp_hi, float *const *__restrict__ parts,
+                                                                      int my_rank, int T_loc, int H, int k) {
+  const int t = blockIdx.x;
+  __shared__ int s_row[8];
+  __shared__ float s_w[8];
+  __shared__ int s_n;
+  if (threadIdx.x == 0) {
+    int ex[8], ord[8], n = 0;
+    for (int s = 0; s < k; ++s) {
+      const int e = pair_exp[t * k + s];
+      if (e >= exp_lo && e < exp_hi) { ex[n] = e; ord[n] = s; ++n; }
+    }
+    for (int a = 1; a < n; ++a) {
+      const int o = ord[a], eo = ex[a];
+      int b = a - 1;
+      while (b >= 0 && ex[b] > eo) { ord[b + 1] = ord[b]; ex[b + 1] = ex[b]; --b; }
+      ord[b + 1] = o;
+      ex[b + 1] = eo;
+    }
+    for (int s = 0; s < n; ++s) {
+      s_row[s] = t * k + ord[s];
+      s_w[s] = pair_w[t * k + ord[s]];
+    }
+    s_n = n;
+  }
+  __syncthreads();
+  const int n = s_n;
+  if (n == 0) return;
+  float *out = parts[t / T_loc] + ((size_t)my_rank * T_loc + (t % T_loc)) * H;
+  for (int h = threadIdx.x * 4; h < H; h += 1024) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n; ++s) {
+      const float4 y = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)s_row[s] * H + h));
+      const float w = s_w[s];
+      acc.x = __fadd_rn(acc.x, __fmul_rn(w, y.x));
+      acc.y = __fadd_rn(acc.y, __fmul_rn(w, y.y));
+      acc.z = __fadd_rn(acc.z, __fmul_rn(w, y.z));
+      acc.w = __fadd_rn(acc.w, __fmul_rn(w, y.w));
+    }
+    *reinterpret_cast<float4 *>(out + h) = acc;
+  }
+}
+
+// Sum over the ranks that own at least one of the token's k experts, ascending rank (the others wrote nothing).
+template <int ODT>
+__global__ void __launch_bounds__(256) ep_reduce_sel_kernel(const float *__restrict__ parts, int n_ranks, int T_loc,
+                                                            const int32_t *__restrict__ pair_exp, int k, int e_loc,
+                                                            const void *__restrict__ resid, int resid_dtype,
+                                                            void *__restrict__ out, int H) {
+  const int t = blockIdx.x;
+  unsigned long long mask = 0;
+  for (int s = 0; s < k; ++s) mask |= 1ull << (pair_exp[t * k + s] / e_loc);
+  for (int h = threadIdx.x * 4; h < H; h += 1024) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!((mask >> r) & 1ull)) continue;
+      const float4 v = __ldg(reinterpret_cast<const float4 *>(parts + ((size_t)r * T_loc + t) * H + h));
+      acc.x = __fadd_rn(acc.x, v.x);
+      acc.y = __fadd_rn(acc.y, v.y);
+      acc.z = __fadd_rn(acc.z, v.z);
+      acc.w = __fadd_rn(acc.w, v.w);
+    }
+    float r4[4] = {acc.x, acc.y, acc.z, acc.w};
+    if (resid) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) r4[j] = __fadd_rn(load_as_f32(resid, resid_dtype, (int64_t)t * H + h + j), r4[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) store_from_f32(out, ODT, (int64_t)t * H + h + j, r4[j]);
+  }
+}
+
 }  // namespace
 
 extern "C" {
+
+int knj_ep_peer_gather_launch(const void *const *src_ptrs, int n_ranks, int64_t bytes_per_rank, void *dst, knj_stream_t s) {
+  KNJ_REQUIRE(src_ptrs && dst, "knj_ep_peer_gather: null pointer");
+  KNJ_REQUIRE(n_ranks >= 1 && bytes_per_rank >= 0 && bytes_per_rank % 16 == 0 && aligned16(dst),
+              "knj_ep_peer_gather: sizes must be 16-byte multiples at 16-byte aligned bases");
+  if (bytes_per_rank == 0) return KNJ_OK;
+  const int64_t total = (int64_t)n_ranks * (bytes_per_rank / 16);
+  const int64_t blocks = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
+  ep_peer_gather_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, as_stream(s)>>>(
+      reinterpret_cast<const uint4 *const *>(src_ptrs), n_ranks, bytes_per_rank / 16, static_cast<uint4 *>(dst));
+  return launch_status("ep_peer_gather_kernel");
+}
+
+int knj_ep_combine_partial_peer_launch(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k,
+                                       int exp_lo, int exp_hi, float *const *parts_ptrs, int my_rank, int T_loc,
+                                       knj_stream_t s) {
+  KNJ_REQUIRE(Y && pair_exp && pair_w && parts_ptrs, "knj_ep_combine_partial_peer: null pointer");
+  KNJ_REQUIRE(k >= 1 && k <= 8 && H > 0 && H % 4 == 0 && exp_lo <= exp_hi && T_loc >= 1 && my_rank >= 0,
+              "knj_ep_combine_partial_peer: bad k / H / expert range / rank");
+  if (T <= 0) return KNJ_OK;
+  ep_combine_partial_peer_kernel<<<T, 256, 0, as_stream(s)>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, H, k);
+  return launch_status("ep_combine_partial_peer_kernel");
+}
+
+int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, const int32_t *pair_exp, int k,
+                             int experts_per_rank, const void *resid, int resid_dtype, void *out, int out_dtype,
+                             knj_stream_t s) {
+  KNJ_REQUIRE(parts && pair_exp && out, "knj_ep_reduce_sel: null pointer");
+  KNJ_REQUIRE(n_ranks >= 1 && n_ranks <= 64 && H > 0 && H % 4 == 0 && k >= 1 && k <= 8 && experts_per_rank >= 1,
+              "knj_ep_reduce_sel: bad sizes");
+  KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_ep_reduce_sel: out must be f32 or bf16");
+  KNJ_REQUIRE(!resid || (resid_dtype >= KNJ_DT_F32 && resid_dtype <= KNJ_DT_F16), "knj_ep_reduce_sel: unknown residual dtype");
+  if (T_loc <= 0) return KNJ_OK;
+  if (out_dtype == KNJ_DT_F32)
+    ep_reduce_sel_kernel<KNJ_DT_F32><<<T_loc, 256, 0, as_stream(s)>>>(parts, n_ranks, T_loc, pair_exp, k, experts_per_rank, resid, resid_dtype, out, H);
+  else
+    ep_reduce_sel_kernel<KNJ_DT_BF16><<<T_loc, 256, 0, as_stream(s)>>>(parts, n_ranks, T_loc, pair_exp, k, experts_per_rank, resid, resid_dtype, out, H);
+  return launch_status("ep_reduce_sel_kernel");
+}
 
 int knj_ep_combine_partial_launch(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k,
                                   int exp_lo, int exp_hi, float *out, knj_stream_t s) {

@@ -46,6 +46,7 @@ __global__ void __launch_bounds__(128) act_prep_kernel(const void *__restrict__ 
                                                        uint8_t *__restrict__ panel) {
   __shared__ float red[16];
   const int v = blockIdx.x;
+  grid_dep_wait();
   panel_prep_vector([&](int k) { return load_as_f32(x, DT, (int64_t)v * ldx + k); }, K,
                     panel + (size_t)v * panel_vec_bytes(K), red);
 }
@@ -123,6 +124,7 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
     *s_fail = 0;
   }
   mbar_init_fence();
+  grid_dep_wait();  // the plan, the prepared vectors (and for the down projection the activations) come from earlier launches
   __syncthreads();
   uint32_t wphase = 0, bphase0 = 0, bphase1 = 0;
   bool ok = true;  // false: skip work and waits, but keep meeting the CTA barriers
@@ -428,7 +430,7 @@ int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st
   const long long cap = (long long)sm_count() * per_sm;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
-  kern<<<(unsigned)grid, threads, smem, st>>>(p);
+  KNJ_CUDA(launch_chain(kern, dim3((unsigned)grid), dim3(threads), smem, st, p));
   return launch_status("q4k_proj_kernel");
 }
 
@@ -462,9 +464,11 @@ int knj_act_prep_launch(const void *x, int x_dtype, int64_t ldx, int n_vec, int 
   KNJ_REQUIRE(aligned16(panel), "knj_act_prep: panel must be 16-byte aligned");
   if (n_vec <= 0) return KNJ_OK;
   uint8_t *pn = static_cast<uint8_t *>(panel);
-  if (x_dtype == KNJ_DT_F32) act_prep_kernel<KNJ_DT_F32><<<n_vec, 128, 0, as_stream(s)>>>(x, ldx, K, pn);
-  else if (x_dtype == KNJ_DT_BF16) act_prep_kernel<KNJ_DT_BF16><<<n_vec, 128, 0, as_stream(s)>>>(x, ldx, K, pn);
-  else act_prep_kernel<KNJ_DT_F16><<<n_vec, 128, 0, as_stream(s)>>>(x, ldx, K, pn);
+  cudaError_t le;
+  if (x_dtype == KNJ_DT_F32) le = launch_chain(act_prep_kernel<KNJ_DT_F32>, dim3(n_vec), dim3(128), 0, as_stream(s), x, ldx, K, pn);
+  else if (x_dtype == KNJ_DT_BF16) le = launch_chain(act_prep_kernel<KNJ_DT_BF16>, dim3(n_vec), dim3(128), 0, as_stream(s), x, ldx, K, pn);
+  else le = launch_chain(act_prep_kernel<KNJ_DT_F16>, dim3(n_vec), dim3(128), 0, as_stream(s), x, ldx, K, pn);
+  KNJ_CUDA(le);
   return launch_status("act_prep_kernel");
 }
 

@@ -436,6 +436,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
   __shared__ int s_ex[8];
   __shared__ float s_wraw[8];
   __shared__ int s_rraw[8];
+  grid_dep_wait();
   if ((int)threadIdx.x < k) {  // the k slots' metadata in parallel
     const int pp = t * k + threadIdx.x;
     s_ex[threadIdx.x] = pair_exp[pp];
@@ -459,7 +460,10 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
     }
   }
   __syncthreads();
-  for (int h = threadIdx.x * 4; h < H; h += 1024) {
+  // gridDim.y column slices per token (small batches: more CTAs shorten the chain of dependent loads)
+  const int h_per = (H / 4 + gridDim.y - 1) / gridDim.y * 4;
+  const int h_lo = blockIdx.y * h_per, h_hi = min(H, h_lo + h_per);
+  for (int h = h_lo + threadIdx.x * 4; h < h_hi; h += 1024) {
     float4 y[8];
 #pragma unroll
     for (int s = 0; s < 8; ++s)
@@ -542,6 +546,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   unsigned long long stamp[9];
   stamp[6] = stamp[7] = stamp[8] = 0;
   stamp[0] = gtime_ns();
+  grid_dep_wait();  // the token rows are the previous layer's output
 
   // ---- logits (and the rows' scales)
   {
@@ -843,9 +848,11 @@ int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t
   const int n_tg = (T + kFrontTok - 1) / kFrontTok;
   KNJ_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t) * (1 + n_tg), as_stream(s)));
   dim3 grid((E + 7) / 8, n_tg);
-  if (x_dtype == KNJ_DT_F32) moe_front_kernel<KNJ_DT_F32><<<grid, 256, 0, as_stream(s)>>>(p);
-  else if (x_dtype == KNJ_DT_BF16) moe_front_kernel<KNJ_DT_BF16><<<grid, 256, 0, as_stream(s)>>>(p);
-  else moe_front_kernel<KNJ_DT_F16><<<grid, 256, 0, as_stream(s)>>>(p);
+  cudaError_t le;
+  if (x_dtype == KNJ_DT_F32) le = launch_chain(moe_front_kernel<KNJ_DT_F32>, grid, dim3(256), 0, as_stream(s), p);
+  else if (x_dtype == KNJ_DT_BF16) le = launch_chain(moe_front_kernel<KNJ_DT_BF16>, grid, dim3(256), 0, as_stream(s), p);
+  else le = launch_chain(moe_front_kernel<KNJ_DT_F16>, grid, dim3(256), 0, as_stream(s), p);
+  KNJ_CUDA(le);
   return launch_status("moe_front_kernel");
 }
 
@@ -865,8 +872,12 @@ int knj_moe_combine_launch(const float *Y, const int32_t *pair_row, const int32_
   KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_moe_combine: out must be f32 or bf16");
   KNJ_REQUIRE(!resid || (resid_dtype >= KNJ_DT_F32 && resid_dtype <= KNJ_DT_F16), "knj_moe_combine: unknown residual dtype");
   cudaStream_t st = as_stream(s);
-#define KNJ_COMBINE(R, O) combine_kernel<R, O><<<T, 256, 0, st>>>(Y, pair_row, pair_exp, pair_w, resid, ld_resid, out, ldo, H, k)
+#define KNJ_COMBINE(R, O) \
+  KNJ_CUDA(launch_chain(combine_kernel<R, O>, dim3(T, slices), dim3(256), 0, st, Y, pair_row, pair_exp, pair_w, resid, ld_resid, out, ldo, H, k))
   const int rd = resid ? resid_dtype : KNJ_DT_F32;
+  // few tokens: split every row over column slices of at least 256 so that the grid has ~64 CTAs
+  int slices = 1;
+  while (slices < 8 && T * slices < 64 && H / (slices * 2) >= 256) slices *= 2;
   if (out_dtype == KNJ_DT_F32) {
     if (rd == KNJ_DT_F32) KNJ_COMBINE(KNJ_DT_F32, KNJ_DT_F32);
     else if (rd == KNJ_DT_BF16) KNJ_COMBINE(KNJ_DT_BF16, KNJ_DT_F32);

@@ -73,7 +73,16 @@ int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint3
 
 using namespace knj;
 
+namespace knj {
+int g_chain_overlap = 1;
+}
+
 extern "C" {
+
+// 1 (default): the kernels of a decode layer are launched with programmatic stream serialization, so each
+// grid is scheduled while its predecessor drains; 0: plain launches.
+void knj_chain_overlap(int on) { g_chain_overlap = on ? 1 : 0; }
+
 
 const char *knj_last_error_string(void) { return g_err; }
 

@@ -12,6 +12,13 @@ in ascending rank order. Per rank and step (N-1)/N * T * (row + 8 k bytes) come
 in and (N-1)/N * T * 4 H bytes go out, independent of k; all sizes are static, so
 the step needs no host synchronisation.
 
+"peer": the gather exchange carried by this library's own kernels over NVLink
+peer mappings (torch symmetric memory gives every rank pointers to every other
+rank's exchange buffers): rows and routing tables are pulled with plain loads
+from the peers, partial rows are stored straight into the token owner's buffer
+and only for tokens that have an expert on the sending rank; two small
+all-reduces serve as barriers. CUDA only.
+
 "dispatch": route -> pack hidden rows in (destination, expert, pair) order ->
 all-to-all #1 (one row per routed pair) -> grouped expert FFN on the received
 rows -> all-to-all #2 (one f32 row per pair back) -> ordered weighted sum. Moves
@@ -130,12 +137,17 @@ class CudaCompute:
         local_ids = pair_exp_all - exp_lo  # ids outside [0, e_loc) match no expert of the plan
         return self.ops.moe_permute(local_ids, e_loc, stride)
 
+    def rows_for_gather(self, x, n_local_pairs_hint, e_loc):
+        if x.dtype == torch.bfloat16 and n_local_pairs_hint >= self.tc_rows_per_expert * e_loc:
+            return self.ops.to_f16(x)
+        return x
+
     def expert_ffn_tokens(self, x_all, bank, plan, P, n_local_pairs_hint):
         """x_all [T][H] -> Y f32 [P][H], rows = global pair ids (rows of other ranks' pairs stay unwritten)."""
         pair_idx, pair_cnt, exp_list, n_active = plan
         ops, k = self.ops, self.top_k
         if n_local_pairs_hint >= self.tc_rows_per_expert * pair_cnt.shape[0]:
-            xh = ops.to_f16(x_all)
+            xh = x_all if x_all.dtype == torch.float16 else ops.to_f16(x_all)
             A, st = ops.q4k_gateup_tc(xh, bank.gate, bank.up, pair_idx, pair_cnt, P, k, poison=False)
             Y, st2 = ops.q4k_down_tc(A, bank.down, pair_idx, pair_cnt, P, poison=False)
             self.last_status = (st, st2)
@@ -156,6 +168,30 @@ class CudaCompute:
                                                   C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return out
 
+    def peer_gather(self, ptr_table, world, bytes_per_rank, dst):
+        from ._lib import check, lib
+        check(lib().knj_ep_peer_gather_launch(C.c_void_p(ptr_table.data_ptr()), world, bytes_per_rank,
+                                              C.c_void_p(dst.data_ptr()),
+                                              C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def combine_partial_peer(self, Y, pair_exp_all, pair_w_all, T, exp_lo, exp_hi, parts_ptrs, rank, T_loc):
+        from ._lib import check, lib
+        check(lib().knj_ep_combine_partial_peer_launch(C.c_void_p(Y.data_ptr()), C.c_void_p(pair_exp_all.data_ptr()),
+                                                       C.c_void_p(pair_w_all.data_ptr()), T, Y.shape[1], self.top_k,
+                                                       exp_lo, exp_hi, C.c_void_p(parts_ptrs.data_ptr()), rank, T_loc,
+                                                       C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def reduce_sel(self, parts, pair_exp_local, k, e_loc, out_dtype):
+        from ._lib import check, lib
+        world, T_loc, H = parts.shape
+        out = torch.empty((T_loc, H), dtype=out_dtype, device=parts.device)
+        dt = {torch.float32: 0, torch.bfloat16: 1}[out_dtype]
+        check(lib().knj_ep_reduce_sel_launch(C.c_void_p(parts.data_ptr()), world, T_loc, H,
+                                             C.c_void_p(pair_exp_local.data_ptr()), k, e_loc, None, 0,
+                                             C.c_void_p(out.data_ptr()), dt,
+                                             C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
     def reduce_parts(self, parts, out_dtype):
         """parts f32 [world][T_loc][H] -> [T_loc][H], ranks summed in ascending order."""
         from ._lib import check, lib
@@ -168,6 +204,42 @@ class CudaCompute:
         return out
 
 
+class PeerBuffers:
+    """Exchange buffers of one rank that every rank of the group maps into its own address space
+    (torch symmetric memory), plus device tables of the ranks' pointers for the peer kernels."""
+
+    def __init__(self, group, world, rank, T_loc, H, k, row_dtype, device):
+        import torch.distributed._symmetric_memory as symm
+        g = group if group is not None else dist.group.WORLD
+        self.group = group
+        self.xpub = symm.empty((T_loc, H), dtype=row_dtype, device=device)
+        self.pepub = symm.empty((T_loc * k,), dtype=torch.int32, device=device)
+        self.pwpub = symm.empty((T_loc * k,), dtype=torch.float32, device=device)
+        self.parts = symm.empty((world, T_loc, H), dtype=torch.float32, device=device)
+        self._handles = [symm.rendezvous(t, g) for t in (self.xpub, self.pepub, self.pwpub, self.parts)]
+
+        def table(h):
+            return torch.tensor([int(p) for p in h.buffer_ptrs], dtype=torch.int64, device=device)
+        self.x_ptrs, self.pe_ptrs, self.pw_ptrs, self.parts_ptrs = (table(h) for h in self._handles)
+        self._token = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def barrier(self):
+        """Stream-ordered barrier over the group: everything the ranks enqueued before it (their stores into
+        peers' buffers included) has completed when work enqueued after it starts."""
+        dist.all_reduce(self._token, group=self.group)
+
+
+_PEER_BUFFERS = {}
+
+
+def peer_buffers(group, world, rank, T_loc, H, k, row_dtype, device) -> PeerBuffers:
+    """One set per (group, shape): allocation is a collective, so every rank asks in the same order."""
+    key = (id(group), world, T_loc, H, k, row_dtype, str(device))
+    if key not in _PEER_BUFFERS:
+        _PEER_BUFFERS[key] = PeerBuffers(group, world, rank, T_loc, H, k, row_dtype, device)
+    return _PEER_BUFFERS[key]
+
+
 class EpMoeLayer:
     """One expert-parallel MoE-FFN layer on this rank.
 
@@ -178,7 +250,7 @@ class EpMoeLayer:
     """
 
     def __init__(self, bank, n_experts: int, compute, group=None, top_k: int = synth.TOP_K, exchange: str = "gather"):
-        assert exchange in ("gather", "dispatch")
+        assert exchange in ("gather", "dispatch", "peer")
         self.bank, self.E, self.compute, self.group, self.top_k = bank, n_experts, compute, group, top_k
         self.exchange = exchange
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -188,15 +260,49 @@ class EpMoeLayer:
         self.last_stats = {}
 
     def forward(self, x: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
-        if self.exchange == "gather":
-            return self._forward_gather(x, out_dtype)
-        return self._forward_dispatch(x, out_dtype)
+        if self.exchange == "dispatch":
+            return self._forward_dispatch(x, out_dtype)
+        if (self.exchange == "peer" and self.world > 1 and x.is_cuda and (x.shape[0] * self.top_k) % 4 == 0):
+            return self._forward_peer(x, out_dtype)
+        return self._forward_gather(x, out_dtype)
+
+    def _forward_peer(self, x: torch.Tensor, out_dtype) -> torch.Tensor:
+        """The gather exchange with this library's own kernels moving the rows over NVLink peer mappings:
+        publish (fp16 rows, routing tables) -> barrier -> pull every rank's rows into local memory -> expert
+        GEMMs -> partial sums stored straight into the token owners' buffers -> barrier -> rank-ordered sum."""
+        T_loc, H = x.shape
+        world, k, cp = self.world, self.top_k, self.compute
+        T = T_loc * world
+        pair_exp, pair_w = cp.route(x)
+        xg = cp.rows_for_gather(x, (T * k) // world, self.e_loc)
+        pb = peer_buffers(self.group, world, self.rank, T_loc, H, k, xg.dtype, x.device)
+        pb.xpub.copy_(xg)
+        pb.pepub.copy_(pair_exp)
+        pb.pwpub.copy_(pair_w)
+        pb.barrier()
+        x_all = torch.empty((T, H), dtype=xg.dtype, device=x.device)
+        pe_all = torch.empty(T * k, dtype=torch.int32, device=x.device)
+        pw_all = torch.empty(T * k, dtype=torch.float32, device=x.device)
+        cp.peer_gather(pb.x_ptrs, world, T_loc * H * xg.element_size(), x_all)
+        cp.peer_gather(pb.pe_ptrs, world, T_loc * k * 4, pe_all)
+        cp.peer_gather(pb.pw_ptrs, world, T_loc * k * 4, pw_all)
+        lo = self.rank * self.e_loc
+        plan = cp.plan_for_experts(pe_all, lo, self.e_loc, max(T, 1))
+        self.last_stats = {"tokens_gathered": int(T)}
+        Y = cp.expert_ffn_tokens(x_all, self.bank, plan, T * k, (T * k) // world)
+        cp.combine_partial_peer(Y, pe_all, pw_all, T, lo, lo + self.e_loc, pb.parts_ptrs, self.rank, T_loc)
+        pb.barrier()
+        return cp.reduce_sel(pb.parts, pair_exp, k, self.e_loc, out_dtype)
 
     def _forward_gather(self, x: torch.Tensor, out_dtype) -> torch.Tensor:
         T_loc, H = x.shape
         world, k, cp = self.world, self.top_k, self.compute
         T = T_loc * world
         pair_exp, pair_w = cp.route(x)
+        # 16-bit rows that the tensor-core GEMMs would convert to fp16 anyway are converted before they travel:
+        # every rank converts its own rows once instead of all rows of all ranks (bf16 -> fp16 is exact in range)
+        if world > 1 and hasattr(cp, "rows_for_gather"):
+            x = cp.rows_for_gather(x, (T * k) // world, self.e_loc)
         if world == 1:
             x_all, pe_all, pw_all = x, pair_exp, pair_w
         else:

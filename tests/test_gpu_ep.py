@@ -53,7 +53,7 @@ def test_world_one_on_gpu(T, tc_rows, tol, exchange):
         assert layer.last_stats["rows_received"] == T * K
 
 
-def _rank_main(rank, world, port, out_dir, T, tc_rows, exchange):
+def _rank_main(rank, world, port, out_dir, T, tc_rows, exchange, bf16=False, repeats=1):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
@@ -63,7 +63,10 @@ def _rank_main(rank, world, port, out_dir, T, tc_rows, exchange):
         e_loc, t_loc = E // world, T // world
         layer = _layer(bank, wr, rank * e_loc, (rank + 1) * e_loc, tc_rows, exchange)
         x = torch.from_numpy(hx[rank * t_loc:(rank + 1) * t_loc].copy()).cuda()
-        out = layer.forward(x)
+        if bf16:
+            x = x.to(torch.bfloat16)
+        for _ in range(repeats):  # repeated steps reuse the exchange buffers
+            out = layer.forward(x)
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, f"out{rank}.npy"), out.cpu().numpy())
         np.save(os.path.join(out_dir, f"rows{rank}.npy"), np.array([layer.last_stats.get("rows_received", -1)]))
@@ -77,7 +80,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-@pytest.mark.parametrize("exchange", ["gather", "dispatch"])
+@pytest.mark.parametrize("exchange", ["gather", "dispatch", "peer"])
 @pytest.mark.parametrize("T,tc_rows,tol", [(12, 1 << 30, TOL_F32), (320, 1, TOL_TC)])
 def test_two_ranks_match_single_process(tmp_path, T, tc_rows, tol, exchange):
     if torch.cuda.device_count() < 2:
@@ -95,3 +98,19 @@ def test_two_ranks_match_single_process(tmp_path, T, tc_rows, tol, exchange):
         rows = [int(np.load(tmp_path / f"rows{r}.npy")[0]) for r in range(world)]
         owner_rows = np.bincount(chosen.ravel() // (E // world), minlength=world)
         assert rows == owner_rows.tolist() and sum(rows) == T * K
+
+
+def test_two_ranks_peer_exchange_fp16_rows_repeated(tmp_path):
+    """bf16 rows converted to fp16 before they are published, three steps over the same exchange buffers."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    from gpu_util import report
+    world, T = 2, 320
+    bank, wr, hx = problem(402, T)
+    hx = synth.bf16_round(hx)
+    want, _, _ = ol.moe(wr, bank, hx, K)
+    mp.spawn(_rank_main, args=(world, _free_port(), str(tmp_path), T, 1, "peer", True, 3), nprocs=world, join=True)
+    got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
+    st = report(got, want, "expert-parallel layer (peer exchange, fp16 rows, 3 steps), 2 NCCL ranks")
+    assert st["rel_rmse"] <= TOL_TC
