@@ -426,7 +426,17 @@ def run_gpu(args):
             torch.cuda.empty_cache()
             dec = decode_section(torch, max(5, args.steps), args.warmup, pk)
 
-    launches = 8 if world == 1 else 12  # router 2, permute 2, to_f16, gate+up, down, combine (N>1: + 3 peer gathers, partial combine to peers, rank reduce)
+    # kernels of this library per layer step: router logits + top-k, permutation (count, scan, scatter for
+    # P >= 8192, else one kernel) + active list, to_f16, gate+up, down, then combine (N = 1) or the exchange kernels
+    n_perm = 4 if T * TOPK >= 8192 else 2
+    if world == 1:
+        launches = 2 + n_perm + 1 + 2 + 1
+    elif args.exchange == "peer":
+        launches = 2 + 1 + 3 + n_perm + 2 + 2      # + 3 peer gathers, partial combine to peers, rank reduce
+    elif args.exchange == "gather":
+        launches = 2 + 1 + n_perm + 2 + 2
+    else:
+        launches = 2 + n_perm + 2 + 2 + 1 + 2 + 1  # pack (2), plan (2)
     line = {"metric": "moe_ffn_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16 operands (Q4_K unpacked), f32 accumulate", "data": "synthetic",

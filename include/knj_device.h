@@ -196,6 +196,13 @@ int knj_router_topk_launch(const void *x, int x_dtype, int64_t ldx, const uint16
 int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,
                            int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
+/* The same tables for long pair lists (P >= 8192) by a counting sort that is
+ * parallel over the pairs; `scratch` holds knj_moe_permute_scratch_bytes(P, E)
+ * bytes. Shorter lists (or scratch == NULL) take knj_moe_permute_launch. */
+size_t knj_moe_permute_scratch_bytes(int P, int E);
+int knj_moe_permute_ws_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,
+                              int32_t *exp_list, int32_t *n_active, void *scratch, size_t scratch_bytes, knj_stream_t s);
+
 /* Decode front end in one launch (T <= 64): per-row RMSNorm scale (norm_w NULL =
  * none), router logits + softmax + exact top-k (as knj_router_topk_launch over
  * the normalised rows), the permutation tables (as knj_moe_permute_launch) and

@@ -86,6 +86,8 @@ SIGNATURES = {
     "knj_rmsnorm_launch": (_i, [_vp, _i, _i64, _vp, _f, _i, _i, _vp, _vp]),
     "knj_router_topk_launch": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "knj_moe_permute_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
+    "knj_moe_permute_scratch_bytes": (_sz, [_i, _i]),
+    "knj_moe_permute_ws_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "knj_moe_front_launch": (_i, [_vp, _i, _i64, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp,
                                   _vp, _vp, _vp, _vp]),
     "knj_moe_front_trace": (None, [_vp]),

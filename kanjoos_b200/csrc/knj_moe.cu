@@ -195,7 +195,9 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
   rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
   if (rc) return rc;
-  rc = knj_moe_permute_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, s);
+  // long pair lists take the counting-sort form; its scratch is the activation buffer, which is written later
+  rc = knj_moe_permute_ws_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.ah,
+                                 (size_t)P * F * 2, s);
   if (rc) return rc;
   rc = knj_to_f16_launch(src, src_dt, src_ld, T, H, w.xh, s);
   if (rc) return rc;

@@ -540,6 +540,24 @@ __global__ void to_f16_kernel(const void *__restrict__ x, int dtype, int64_t ldx
   }
 }
 
+// the common case, bf16 rows whose length and stride are multiples of 8: 16 bytes in, 16 bytes out per thread and step
+__global__ void __launch_bounds__(256) bf16_to_f16_kernel(const uint4 *__restrict__ x, int64_t ldx8, int K8, int64_t n8,
+                                                          uint4 *__restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / K8, c = i - r * K8;
+    const uint4 v = __ldg(x + r * ldx8 + c);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xffff0000u);
+      const __half2 h = __floats2half2_rn(fminf(fmaxf(lo, -65504.0f), 65504.0f), fminf(fmaxf(hi, -65504.0f), 65504.0f));
+      o[j] = *reinterpret_cast<const uint32_t *>(&h);
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 template <int NMAT, bool GATEUP, int CG>
 int launch_tc_cg(TcParams p, int max_pairs, cudaStream_t st) {
   using S = Smem<NMAT, CG>;
@@ -610,6 +628,12 @@ int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, 
   KNJ_REQUIRE(x_dtype >= KNJ_DT_F32 && x_dtype <= KNJ_DT_F16 && K > 0, "knj_to_f16: bad dtype / K");
   if (rows <= 0) return KNJ_OK;
   const int64_t n = (int64_t)rows * K;
+  if (x_dtype == KNJ_DT_BF16 && K % 8 == 0 && ldx % 8 == 0 && aligned16(x) && aligned16(out_f16)) {
+    const int64_t n8 = n / 8, blocks8 = (n8 + 255) / 256, cap8 = (int64_t)sm_count() * 16;
+    bf16_to_f16_kernel<<<(unsigned)(blocks8 < cap8 ? blocks8 : cap8), 256, 0, as_stream(s)>>>(
+        static_cast<const uint4 *>(x), ldx / 8, K / 8, n8, static_cast<uint4 *>(out_f16));
+    return launch_status("bf16_to_f16_kernel");
+  }
   const int64_t blocks = (n + 255) / 256, cap = (int64_t)sm_count() * 16;
   to_f16_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, as_stream(s)>>>(x, x_dtype, ldx, K, n,
                                                                                   static_cast<__half *>(out_f16));

@@ -334,6 +334,89 @@ __global__ void __launch_bounds__(128) router_topk_kernel(const float *__restric
 }
 
 // ---------------------------------------------------------------------------
+// Counting-sort form of the permutation tables for long pair lists.
+// counts[c][e]: pairs of chunk c (256 consecutive pairs) routed to expert e; after the scan, the number of such
+// pairs in earlier chunks. The order inside a chunk is recovered from warp match masks, so every expert's row
+// lists its pairs in ascending pair id exactly as permute_kernel does.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) permute_count_kernel(const int32_t *__restrict__ pair_exp, int P, int E,
+                                                            int32_t *__restrict__ counts) {
+  __shared__ int hist[256];
+  hist[threadIdx.x] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  const int e = p < P ? pair_exp[p] : -1;
+  const bool valid = e >= 0 && e < E;
+  const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : -1 - (int)(threadIdx.x & 31));
+  if (valid && (threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[e], __popc(peers));
+  __syncthreads();
+  if ((int)threadIdx.x < E) counts[(size_t)blockIdx.x * E + threadIdx.x] = hist[threadIdx.x];
+}
+
+__global__ void __launch_bounds__(256) permute_scan_kernel(int32_t *__restrict__ counts, int chunks, int E, int idx_stride,
+                                                           int32_t *__restrict__ pair_cnt) {
+  const int e = blockIdx.x;
+  __shared__ int wsum[8];
+  __shared__ int s_base;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) s_base = 0;
+  __syncthreads();
+  for (int c0 = 0; c0 < chunks; c0 += 256) {
+    const int c = c0 + threadIdx.x;
+    const int v = c < chunks ? counts[(size_t)c * E + e] : 0;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) wsum[warp] = incl;
+    __syncthreads();
+    int off = s_base, tot = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      if (w < warp) off += wsum[w];
+      tot += wsum[w];
+    }
+    if (c < chunks) counts[(size_t)c * E + e] = off + incl - v;
+    __syncthreads();
+    if (threadIdx.x == 0) s_base += tot;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) pair_cnt[e] = min(s_base, idx_stride);
+}
+
+__global__ void __launch_bounds__(256) permute_scatter_kernel(const int32_t *__restrict__ pair_exp, int P, int E,
+                                                              const int32_t *__restrict__ base, int idx_stride,
+                                                              int32_t *__restrict__ pair_idx) {
+  __shared__ int wcnt[8][256];  // per warp and expert: pairs of that expert in the warp, then in the earlier warps
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < 8 * 256; i += 256) (&wcnt[0][0])[i] = 0;
+  __syncthreads();
+  const int p = blockIdx.x * 256 + threadIdx.x;
+  const int e = p < P ? pair_exp[p] : -1;
+  const bool valid = e >= 0 && e < E;
+  const unsigned peers = __match_any_sync(0xffffffffu, valid ? e : -1 - lane);
+  const int in_warp = __popc(peers & ((1u << lane) - 1u));
+  if (valid && lane == __ffs(peers) - 1) wcnt[warp][e] = __popc(peers);
+  __syncthreads();
+  if ((int)threadIdx.x < E) {
+    int run = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int c = wcnt[w][threadIdx.x];
+      wcnt[w][threadIdx.x] = run;
+      run += c;
+    }
+  }
+  __syncthreads();
+  if (valid) {
+    const int pos = base[(size_t)blockIdx.x * E + e] + wcnt[warp][e] + in_warp;
+    if (pos < idx_stride) pair_idx[(size_t)e * idx_stride + pos] = p;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Permutation tables: one CTA per expert walks all pairs in order and compacts
 // the ones routed to it (ascending pair id, the order the CPU path's
 // ex_tokens_ lists have), then pads its row with -1.
@@ -808,6 +891,39 @@ int knj_router_topk_launch(const void *x, int x_dtype, int64_t ldx, const uint16
   if (rc) return rc;
   router_topk_kernel<<<(T + 3) / 4, 128, 0, as_stream(s)>>>(logits, T, E, k, pair_exp, pair_w);
   return launch_status("router_topk_kernel");
+}
+
+// Large pair lists: the same tables from a three-step counting sort that is parallel over the pairs
+// (chunks of 256 pairs: per-chunk expert histogram -> per-expert scan over chunks -> ordered scatter).
+size_t knj_moe_permute_scratch_bytes(int P, int E) {
+  const size_t chunks = (size_t)(P > 0 ? (P + 255) / 256 : 1);
+  return chunks * (size_t)E * sizeof(int32_t);
+}
+
+int knj_moe_permute_ws_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,
+                              int32_t *exp_list, int32_t *n_active, void *scratch, size_t scratch_bytes, knj_stream_t s) {
+  KNJ_REQUIRE(pair_exp && pair_idx && pair_cnt && exp_list && n_active, "knj_moe_permute_ws: null pointer");
+  KNJ_REQUIRE(P >= 0 && E >= 1 && E <= 256 && idx_stride >= 1, "knj_moe_permute_ws: bad sizes (E <= 256)");
+  if (P < 8192 || !scratch) return knj_moe_permute_launch(pair_exp, P, E, idx_stride, pair_idx, pair_cnt, exp_list, n_active, s);
+  if (scratch_bytes < knj_moe_permute_scratch_bytes(P, E)) {
+    set_error("knj_moe_permute_ws: scratch of %zu bytes needed, %zu given", knj_moe_permute_scratch_bytes(P, E), scratch_bytes);
+    return KNJ_E_WORKSPACE;
+  }
+  cudaStream_t st = as_stream(s);
+  const int chunks = (P + 255) / 256;
+  int32_t *counts = static_cast<int32_t *>(scratch);
+  KNJ_CUDA(cudaMemsetAsync(pair_idx, 0xff, (size_t)E * idx_stride * sizeof(int32_t), st));  // -1 padding
+  permute_count_kernel<<<chunks, 256, 0, st>>>(pair_exp, P, E, counts);
+  int rc = launch_status("permute_count_kernel");
+  if (rc) return rc;
+  permute_scan_kernel<<<E, 256, 0, st>>>(counts, chunks, E, idx_stride, pair_cnt);
+  rc = launch_status("permute_scan_kernel");
+  if (rc) return rc;
+  permute_scatter_kernel<<<chunks, 256, 0, st>>>(pair_exp, P, E, counts, idx_stride, pair_idx);
+  rc = launch_status("permute_scatter_kernel");
+  if (rc) return rc;
+  active_list_kernel<<<1, 256, 0, st>>>(pair_cnt, E, exp_list, n_active);
+  return launch_status("active_list_kernel");
 }
 
 int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride, int32_t *pair_idx, int32_t *pair_cnt,

@@ -111,12 +111,18 @@ def router_topk(x: torch.Tensor, Wr: torch.Tensor, k: int, bias: torch.Tensor | 
 def moe_permute(pair_exp: torch.Tensor, E: int, idx_stride: int):
     _need(pair_exp, torch.int32)
     P = pair_exp.numel()
-    pair_idx = torch.full((E, idx_stride), -7, dtype=torch.int32, device="cuda")
-    pair_cnt = torch.full((E,), -7, dtype=torch.int32, device="cuda")
-    exp_list = torch.full((E,), -7, dtype=torch.int32, device="cuda")
-    n_active = torch.full((4,), -7, dtype=torch.int32, device="cuda")
-    check(lib().knj_moe_permute_launch(_p(pair_exp), P, E, idx_stride, _p(pair_idx), _p(pair_cnt), _p(exp_list),
-                                       _p(n_active), _stream()))
+    pair_idx = torch.empty((E, idx_stride), dtype=torch.int32, device="cuda")
+    pair_cnt = torch.empty((E,), dtype=torch.int32, device="cuda")
+    exp_list = torch.empty((E,), dtype=torch.int32, device="cuda")
+    n_active = torch.empty((4,), dtype=torch.int32, device="cuda")
+    if P >= 8192 and E <= 256:
+        nbytes = int(lib().knj_moe_permute_scratch_bytes(P, E))
+        scratch = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        check(lib().knj_moe_permute_ws_launch(_p(pair_exp), P, E, idx_stride, _p(pair_idx), _p(pair_cnt), _p(exp_list),
+                                              _p(n_active), _p(scratch), nbytes, _stream()))
+    else:
+        check(lib().knj_moe_permute_launch(_p(pair_exp), P, E, idx_stride, _p(pair_idx), _p(pair_cnt), _p(exp_list),
+                                           _p(n_active), _stream()))
     return pair_idx, pair_cnt, exp_list, n_active
 
 
