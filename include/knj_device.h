@@ -215,6 +215,9 @@ int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t
                          const uint16_t *Wr_bf16, const float *bias, int T, int H, int E, int k, float *logits,
                          int32_t *pair_exp, float *pair_w, int32_t *pair_idx, int idx_stride, int32_t *pair_cnt,
                          int32_t *exp_list, int32_t *n_active, void *xpanel, uint32_t *counter, knj_stream_t s);
+/* `counter` above is a block of 192 uint32: the launch zeroes the words it uses
+ * itself and its last CTA zeroes words 64..191, the slice counters of a
+ * knj_q4k_down_combine_launch that follows. */
 
 /* Measurement hook (no reference counterpart): a device buffer of 16 uint64 that
  * receives global-timer stamps (ns) of the front kernel's phases -- start,
@@ -269,6 +272,19 @@ int knj_q4k_gateup_launch(const void *Xpanel, const uint8_t *Wg, const uint8_t *
 int knj_q4k_proj_launch(const void *Apanel, const uint8_t *W, const int32_t *pair_idx, const int32_t *pair_cnt,
                         const int32_t *pair_row, const int32_t *exp_list, const int32_t *n_active, float *Y, int N,
                         int K, int rowBytes, int64_t idxStride, int n_experts, int max_tokens, knj_stream_t s);
+
+/* Down projection and the weighted combine of a decode batch (T <= 64) in one
+ * launch: knj_q4k_proj_launch followed by knj_moe_combine_launch
+ * (src/model/model.cpp:455-463 and the residual add at :652), with the combine of
+ * each 16*tg-column slice done by the CTA that finishes that slice last, in
+ * ascending expert order (same arithmetic and order as the separate kernel).
+ * Y f32 [T*k][N] still receives the per-pair rows. counters: at least N/16
+ * uint32, ZERO before the first launch; every launch leaves them zero. */
+int knj_q4k_down_combine_launch(const void *Apanel, const uint8_t *W, const int32_t *pair_idx, const int32_t *pair_cnt,
+                                const int32_t *exp_list, const int32_t *n_active, float *Y, int N, int K, int rowBytes,
+                                int64_t idxStride, int n_experts, const int32_t *pair_exp, const float *pair_w,
+                                const void *resid, int resid_dtype, int64_t ld_resid, void *out, int out_dtype,
+                                int64_t ldo, int T, int k, uint32_t *counters, knj_stream_t s);
 #define knj_q4k_down_launch knj_q4k_proj_launch
 
 /* A[i] = silu(G[i]) * U[i], n elements (tools/bench/q4k_stream_ffn.hip:1021-1031

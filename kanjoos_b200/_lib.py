@@ -106,6 +106,8 @@ SIGNATURES = {
     "knj_q4k_gateup_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i,
                                    _i, _vp]),
     "knj_q4k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp]),
+    "knj_q4k_down_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _vp, _vp, _i, _i64,
+                                         _vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_tc_trace": (None, [_vp, _i]),
     "knj_tc_tuning": (None, [_i]),
     "knj_chain_overlap": (None, [_i]),

@@ -44,7 +44,7 @@ DecodeWs carve_decode(void *base, int T, int H, int F, int E, int k) {
   w.pair_cnt = c.take<int32_t>((size_t)E * 4);
   w.exp_list = c.take<int32_t>((size_t)E * 4);
   w.n_active = c.take<int32_t>(16);
-  w.counter = c.take<uint32_t>(64);
+  w.counter = c.take<uint32_t>((64 + 128) * 4);  // front kernel: 64 words; fused combine: one per column slice
   w.xpanel = c.take<void>(knj_panel_bytes(T, H));
   w.A = c.take<float>(P * F * 4);
   w.apanel = c.take<void>(knj_panel_bytes((int)P, F));
@@ -150,6 +150,7 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
     // 4. prepared activation vectors
     rc = knj_act_prep_launch(src, src_dt, src_ld, T, H, w.xpanel, s);
     if (rc) return rc;
+    if (T <= 64) KNJ_CUDA(cudaMemsetAsync(w.counter + 64, 0, 128 * sizeof(uint32_t), as_stream(s)));  // slice counters
   }
   // gate, up, silu(g)*u
   rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
@@ -158,6 +159,13 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   // 5. down
   rc = knj_act_prep_launch(w.A, KNJ_DT_F32, F, P, F, w.apanel, s);
   if (rc) return rc;
+  if (T <= 64 && H / 16 <= 128) {
+    // down + weighted combine (+ residual) in one launch; the slice counters sit behind the front kernel's
+    // counters and were zeroed with them (they are left zero)
+    return knj_q4k_down_combine_launch(w.apanel, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F,
+                                       F / 256 * KNJ_Q4K_BYTES, T, E, pair_exp, pair_w, a->residual ? a->x : nullptr,
+                                       a->x_dtype, a->ldx, a->out, a->out_dtype, a->ldo, T, k, w.counter + 64, s);
+  }
   rc = knj_q4k_proj_launch(w.apanel, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active, w.Y, H, F,
                            F / 256 * KNJ_Q4K_BYTES, T, E, T, s);
   if (rc) return rc;

@@ -75,6 +75,15 @@ struct ProjParams {
   int64_t idxStride;
   int *status;    // optional: set to 1 when a bounded wait gave up
   CUtensorMap map0, map1;  // TMA descriptors of W0 / W1: box = this launch's row part x tile rows
+  // optional fused weighted combine (single-matrix form only; cmb_out == null: off). The CTA that finishes a
+  // column slice last (all active experts done) sums the slice for every token in ascending expert order.
+  const int32_t *cmb_pair_exp;
+  const float *cmb_pair_w;
+  const void *cmb_resid;
+  void *cmb_out;
+  unsigned int *cmb_counter;  // one word per column slice, zero before the launch, left zero
+  int64_t cmb_ld_resid, cmb_ldo;
+  int cmb_resid_dtype, cmb_out_dtype, cmb_T, cmb_k;
 };
 
 struct ProjSmem {
@@ -343,6 +352,51 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
       }
     }
     __syncwarp();
+
+    if (!DUAL && p.cmb_out) {
+      // ---- fused combine: did this CTA finish the column slice [grp * tg * 16, +tg * 16) as the last one?
+      __shared__ int s_last;
+      __shared__ unsigned char s_ord[64][8];
+      __shared__ unsigned char s_cnt[64];
+      __threadfence();
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        const unsigned old = atomicAdd(&p.cmb_counter[grp], 1u);
+        s_last = old == (unsigned)n_act - 1u;
+        if (s_last) p.cmb_counter[grp] = 0u;  // ready for the next launch
+      }
+      __syncthreads();
+      if (s_last) {
+        __threadfence();
+        const int T = p.cmb_T, k = p.cmb_k;
+        for (int t = threadIdx.x; t < T; t += blockDim.x) {  // the token's slots in ascending expert order
+          int ex[8], ord[8];
+          for (int sl = 0; sl < k; ++sl) { ex[sl] = p.cmb_pair_exp[t * k + sl]; ord[sl] = sl; }
+          for (int a2 = 1; a2 < k; ++a2) {
+            const int o = ord[a2], eo = ex[a2];
+            int b2 = a2 - 1;
+            while (b2 >= 0 && ex[b2] > eo) { ord[b2 + 1] = ord[b2]; ex[b2 + 1] = ex[b2]; --b2; }
+            ord[b2 + 1] = o;
+            ex[b2 + 1] = eo;
+          }
+          for (int sl = 0; sl < k; ++sl) s_ord[t][sl] = (unsigned char)ord[sl];
+          s_cnt[t] = (unsigned char)k;
+        }
+        __syncthreads();
+        const int width = p.tg * 16, c0 = grp * width;
+        for (int idx = threadIdx.x; idx < T * width; idx += blockDim.x) {
+          const int t = idx / width, c = c0 + idx - t * width;
+          float acc = 0.f;
+          for (int sl = 0; sl < k; ++sl) {
+            const int pp = t * k + s_ord[t][sl];
+            acc = __fadd_rn(acc, __fmul_rn(p.cmb_pair_w[pp], __ldcg(p.out0 + (size_t)pp * p.N + c)));
+          }
+          if (p.cmb_resid) acc = __fadd_rn(load_as_f32(p.cmb_resid, p.cmb_resid_dtype, (int64_t)t * p.cmb_ld_resid + c), acc);
+          store_from_f32(p.cmb_out, p.cmb_out_dtype, (int64_t)t * p.cmb_ldo + c, acc);
+        }
+      }
+      __syncthreads();
+    }
   }
   if (!ok && threadIdx.x == 0 && p.status) atomicExch(p.status, 1);
 }
@@ -508,6 +562,32 @@ int knj_q4k_proj_launch(const void *Apanel, const uint8_t *W, const int32_t *pai
   p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
   p.tiles_per_expert = N / 16; p.idxStride = idxStride; p.status = nullptr;
   return launch_proj_nt<false>(p, n_experts, max_tokens, as_stream(s));
+}
+
+int knj_q4k_down_combine_launch(const void *Apanel, const uint8_t *W, const int32_t *pair_idx, const int32_t *pair_cnt,
+                                const int32_t *exp_list, const int32_t *n_active, float *Y, int N, int K, int rowBytes,
+                                int64_t idxStride, int n_experts, const int32_t *pair_exp, const float *pair_w,
+                                const void *resid, int resid_dtype, int64_t ld_resid, void *out, int out_dtype,
+                                int64_t ldo, int T, int k, uint32_t *counters, knj_stream_t s) {
+  KNJ_REQUIRE(Apanel && W && pair_idx && pair_cnt && exp_list && n_active && Y && pair_exp && pair_w && out && counters,
+              "knj_q4k_down_combine: null pointer");
+  KNJ_REQUIRE(K > 0 && K % 256 == 0 && rowBytes == K / 256 * KNJ_Q4K_BYTES,
+              "knj_q4k_down_combine: rowBytes=%d does not match K=%d", rowBytes, K);
+  KNJ_REQUIRE(N > 0 && N % 16 == 0 && N / 16 <= 128 * 16, "knj_q4k_down_combine: N=%d must be a multiple of 16", N);
+  KNJ_REQUIRE(aligned16(W) && aligned16(Apanel), "knj_q4k_down_combine: weights/panel must be 16-byte aligned");
+  KNJ_REQUIRE(n_experts > 0 && T >= 1 && T <= 64 && k >= 1 && k <= 8, "knj_q4k_down_combine: at most 64 tokens, top-k of at most 8");
+  KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_q4k_down_combine: out must be f32 or bf16");
+  KNJ_REQUIRE(!resid || (resid_dtype >= KNJ_DT_F32 && resid_dtype <= KNJ_DT_F16), "knj_q4k_down_combine: unknown residual dtype");
+  ProjParams p{};
+  p.W0 = W; p.W1 = nullptr; p.panel = static_cast<const uint8_t *>(Apanel);
+  p.pair_idx = pair_idx; p.pair_cnt = pair_cnt; p.row_map = nullptr; p.exp_list = exp_list; p.n_active = n_active;
+  p.out0 = Y; p.out1 = nullptr; p.out2 = nullptr;
+  p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
+  p.tiles_per_expert = N / 16; p.idxStride = idxStride; p.status = nullptr;
+  p.cmb_pair_exp = pair_exp; p.cmb_pair_w = pair_w; p.cmb_resid = resid; p.cmb_out = out; p.cmb_counter = counters;
+  p.cmb_ld_resid = ld_resid; p.cmb_ldo = ldo; p.cmb_resid_dtype = resid_dtype; p.cmb_out_dtype = out_dtype;
+  p.cmb_T = T; p.cmb_k = k;
+  return launch_proj_nt<false>(p, n_experts, T, as_stream(s));
 }
 
 size_t knj_q4k_matmul_workspace_bytes(int m, int n_in) {

@@ -595,7 +595,7 @@ struct FrontParams {
   float *pair_w;
   int32_t *pair_idx, *pair_cnt, *exp_list, *n_active;
   uint8_t *xpanel;
-  unsigned int *counter;  // [1 + token groups] words, zero before the launch
+  unsigned int *counter;  // 192 words: [0, 1 + token groups) zero before the launch; [64, 192) are zeroed here
   unsigned long long *trace;  // optional [8]: global-timer stamps of the phases of the CTA that finishes last
 };
 
@@ -776,6 +776,10 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   if (!s_flag) return;
   __threadfence();
   stamp[5] = gtime_ns();
+
+  // the slice counters of the fused down + combine launch that follows in a decode layer (words 64..191 of the
+  // counter block) start from zero
+  if (threadIdx.x < 128) p.counter[64 + threadIdx.x] = 0u;
 
   // ---- permutation tables. Pairs are taken in chunks of 32 (one per warp pass):
   // count per (chunk, expert), scan over chunks, then every pair knows its rank.
