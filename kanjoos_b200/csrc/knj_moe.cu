@@ -159,7 +159,7 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   // 5. down
   rc = knj_act_prep_launch(w.A, KNJ_DT_F32, F, P, F, w.apanel, s);
   if (rc) return rc;
-  if (T <= 64 && H / 16 <= 128) {
+  if (T <= 4 && H / 16 <= 128) {  // larger batches: the one CTA per slice that combines becomes the tail
     // down + weighted combine (+ residual) in one launch; the slice counters sit behind the front kernel's
     // counters and were zeroed with them (they are left zero)
     return knj_q4k_down_combine_launch(w.apanel, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F,

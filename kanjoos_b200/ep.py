@@ -262,9 +262,33 @@ class EpMoeLayer:
     def forward(self, x: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
         if self.exchange == "dispatch":
             return self._forward_dispatch(x, out_dtype)
-        if (self.exchange == "peer" and self.world > 1 and x.is_cuda and (x.shape[0] * self.top_k) % 4 == 0):
+        if (self.exchange == "peer" and self.world > 1 and x.is_cuda and (x.shape[0] * self.top_k) % 4 == 0
+                and self._peer_ready(x)):
             return self._forward_peer(x, out_dtype)
         return self._forward_gather(x, out_dtype)
+
+    def _peer_ready(self, x: torch.Tensor) -> bool:
+        """The peer mappings are set up once per shape, and the ranks agree on the outcome: if any rank cannot
+        map its peers' buffers (no peer access, symmetric memory unavailable), all of them use the collectives."""
+        T_loc, H = x.shape
+        cp = self.compute
+        tc = (x.dtype == torch.bfloat16 and
+              T_loc * self.top_k >= getattr(cp, "tc_rows_per_expert", 1 << 30) * self.e_loc)
+        keys = [(T_loc, H, self.top_k, torch.float16 if tc else x.dtype)]  # the dtype rows_for_gather will return
+        verdict = self.__dict__.setdefault("_peer_verdict", {})
+        if keys[0] in verdict:
+            return verdict[keys[0]]
+        ok = 1
+        try:
+            for (_, _, _, d) in keys:
+                peer_buffers(self.group, self.world, self.rank, T_loc, H, self.top_k, d, x.device)
+        except Exception as ex:  # noqa: BLE001 - any failure means "use the collectives"
+            self.last_stats["peer_setup_error"] = repr(ex)
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=x.device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        verdict[keys[0]] = bool(int(flag.item()))
+        return verdict[keys[0]]
 
     def _forward_peer(self, x: torch.Tensor, out_dtype) -> torch.Tensor:
         """The gather exchange with this library's own kernels moving the rows over NVLink peer mappings:
