@@ -165,10 +165,23 @@ __global__ void __launch_bounds__(256) ep_reduce_kernel(const float *__restrict_
 __global__ void __launch_bounds__(256) ep_peer_gather_kernel(const uint4 *const *__restrict__ src, int n_ranks,
                                                              int64_t u4_per_rank, uint4 *__restrict__ dst) {
   const int64_t total = (int64_t)n_ranks * u4_per_rank;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int r = (int)(i / u4_per_rank);
-    const int64_t j = i - (int64_t)r * u4_per_rank;
-    dst[i] = src[r][j];
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  // four independent peer loads in flight per thread: NVLink latency is a few microseconds
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t idx = i + u * stride;
+      if (idx < total) {
+        const int r = (int)(idx / u4_per_rank);
+        v[u] = src[r][idx - (int64_t)r * u4_per_rank];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t idx = i + u * stride;
+      if (idx < total) dst[idx] = v[u];
+    }
   }
 }
 
@@ -179,43 +192,46 @@ __global__ void __launch_bounds__(256) ep_combine_partial_peer_kernel(const floa
                                                                       const int32_t *__restrict__ pair_exp,
                                                                       const float *__restrict__ pair_w, int exp_lo,
                                                                       int exp_hi, float *const *__restrict__ parts,
-                                                                      int my_rank, int T_loc, int H, int k) {
-  const int t = blockIdx.x;
-  __shared__ int s_row[8];
-  __shared__ float s_w[8];
-  __shared__ int s_n;
-  if (threadIdx.x == 0) {
-    int ex[8], ord[8], n = 0;
-    for (int s = 0; s < k; ++s) {
-      const int e = pair_exp[t * k + s];
-      if (e >= exp_lo && e < exp_hi) { ex[n] = e; ord[n] = s; ++n; }
-    }
-    for (int a = 1; a < n; ++a) {
-      const int o = ord[a], eo = ex[a];
-      int b = a - 1;
-      while (b >= 0 && ex[b] > eo) { ord[b + 1] = ord[b]; ex[b + 1] = ex[b]; --b; }
-      ord[b + 1] = o;
-      ex[b + 1] = eo;
-    }
-    for (int s = 0; s < n; ++s) {
-      s_row[s] = t * k + ord[s];
-      s_w[s] = pair_w[t * k + ord[s]];
-    }
-    s_n = n;
-  }
-  __syncthreads();
-  const int n = s_n;
+                                                                      int my_rank, int T_loc, int T, int H, int k) {
+  // one warp per token: lanes 0..k-1 hold the token's slots, the local ones are ranked by expert id
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int e = lane < k ? pair_exp[t * k + lane] : -1;
+  const float w = lane < k ? pair_w[t * k + lane] : 0.f;
+  const bool mine = lane < k && e >= exp_lo && e < exp_hi;
+  const unsigned m = __ballot_sync(0xffffffffu, mine);
+  const int n = __popc(m);
   if (n == 0) return;
+  int rank = 0;
+  for (int j = 0; j < k; ++j) {
+    const int ej = __shfl_sync(0xffffffffu, e, j);
+    if (((m >> j) & 1u) && ej < e) ++rank;
+  }
+  int row[8];
+  float ws[8];
+#pragma unroll
+  for (int sl = 0; sl < 8; ++sl) {
+    const unsigned b = __ballot_sync(0xffffffffu, mine && rank == sl);
+    const int src = b ? __ffs(b) - 1 : 0;
+    row[sl] = t * k + src;
+    ws[sl] = __shfl_sync(0xffffffffu, w, src);
+  }
   float *out = parts[t / T_loc] + ((size_t)my_rank * T_loc + (t % T_loc)) * H;
-  for (int h = threadIdx.x * 4; h < H; h += 1024) {
+  for (int h = lane * 4; h < H; h += 128) {
+    float4 y[8];
+#pragma unroll
+    for (int sl = 0; sl < 8; ++sl)
+      if (sl < n) y[sl] = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)row[sl] * H + h));
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int s = 0; s < n; ++s) {
-      const float4 y = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)s_row[s] * H + h));
-      const float w = s_w[s];
-      acc.x = __fadd_rn(acc.x, __fmul_rn(w, y.x));
-      acc.y = __fadd_rn(acc.y, __fmul_rn(w, y.y));
-      acc.z = __fadd_rn(acc.z, __fmul_rn(w, y.z));
-      acc.w = __fadd_rn(acc.w, __fmul_rn(w, y.w));
+#pragma unroll
+    for (int sl = 0; sl < 8; ++sl) {
+      if (sl < n) {
+        acc.x = __fadd_rn(acc.x, __fmul_rn(ws[sl], y[sl].x));
+        acc.y = __fadd_rn(acc.y, __fmul_rn(ws[sl], y[sl].y));
+        acc.z = __fadd_rn(acc.z, __fmul_rn(ws[sl], y[sl].z));
+        acc.w = __fadd_rn(acc.w, __fmul_rn(ws[sl], y[sl].w));
+      }
     }
     *reinterpret_cast<float4 *>(out + h) = acc;
   }
@@ -273,7 +289,7 @@ int knj_ep_combine_partial_peer_launch(const float *Y, const int32_t *pair_exp, 
   KNJ_REQUIRE(k >= 1 && k <= 8 && H > 0 && H % 4 == 0 && exp_lo <= exp_hi && T_loc >= 1 && my_rank >= 0,
               "knj_ep_combine_partial_peer: bad k / H / expert range / rank");
   if (T <= 0) return KNJ_OK;
-  ep_combine_partial_peer_kernel<<<T, 256, 0, as_stream(s)>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, H, k);
+  ep_combine_partial_peer_kernel<<<(T + 7) / 8, 256, 0, as_stream(s)>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, T, H, k);
   return launch_status("ep_combine_partial_peer_kernel");
 }
 
