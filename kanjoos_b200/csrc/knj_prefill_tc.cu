@@ -217,13 +217,44 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
 
   // ---- which (expert, token bucket) is this CTA's? scan the counts (E <= 256)
   const int m_tile = blockIdx.x % p.m_tiles;
-  int want = blockIdx.x / p.m_tiles;
+  // every warp finds it for itself: lane l holds the counts of experts 8l..8l+7, a warp scan over the bucket
+  // counts locates the expert (a serial walk over up to 128 counts cost the late CTAs 2-3 us)
+  const int want = blockIdx.x / p.m_tiles;
   int e = -1, tok0 = 0, cnt = 0;
-  for (int i = 0; i < p.n_experts; ++i) {
-    const int c = p.pair_cnt[i];
-    const int nt = (c + kMaxTok - 1) / kMaxTok;
-    if (want < nt) { e = i; tok0 = want * kMaxTok; cnt = c; break; }
-    want -= nt;
+  {
+    int cnts[8], nb = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int i = lane * 8 + j;
+      cnts[j] = i < p.n_experts ? p.pair_cnt[i] : 0;
+      nb += (cnts[j] + kMaxTok - 1) / kMaxTok;
+    }
+    int incl = nb;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int v = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += v;
+    }
+    const int excl = incl - nb;
+    int fe = -1, ft = 0, fc = 0;
+    if (want >= excl && want < incl) {
+      int w = want - excl;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int nt = (cnts[j] + kMaxTok - 1) / kMaxTok;
+        if (fe < 0) {
+          if (w < nt) { fe = lane * 8 + j; ft = w * kMaxTok; fc = cnts[j]; }
+          else w -= nt;
+        }
+      }
+    }
+    const unsigned owner = __ballot_sync(0xffffffffu, fe >= 0);
+    if (owner) {
+      const int src = __ffs(owner) - 1;
+      e = __shfl_sync(0xffffffffu, fe, src);
+      tok0 = __shfl_sync(0xffffffffu, ft, src);
+      cnt = __shfl_sync(0xffffffffu, fc, src);
+    }
   }
   if (e < 0) return;  // the same for both CTAs of a pair: nothing allocated yet, no barrier touched
   unsigned long long *cta_rec = (p.trace && (int)blockIdx.x < p.trace_ctas) ? p.trace + 256 + 4 * (size_t)blockIdx.x : nullptr;
@@ -466,7 +497,11 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   }
 
   // =========================== epilogue ===========================
-  if (warp < 8) {
+  if (warp != 8) {
+    // unpackers and loaders alike (12 warps); warp w may read the 32 TMEM lanes 32 * (w % 4)
+    constexpr int kEpiWarps = 12;
+    const int ew = warp < 8 ? warp : warp - 1;          // 0..11
+    const int slot = warp < 8 ? (warp >> 2) : 2;        // which of the three warps of a lane group
     if (ok && !mbar_wait(acc_full, 0, s_fail)) ok = false;
     tc_fence_after();
     if (cta_rec && tid == 0) cta_rec[1] = global_timer_ns();
@@ -483,7 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
 #pragma unroll 1
     for (int mat = 0; mat < kEpiMats; ++mat) {
       if (ok) {
-        for (int c = (warp >> 2); c * 16 < n_mma; c += 2) {
+        for (int c = slot; c * 16 < n_mma; c += 3) {
           float g[16];
           tmem_ld16(tmem_base + ((uint32_t)lane_base << 16) + mat * kMaxTok + c * 16, g);
           if (GATEUP) {
@@ -504,12 +539,12 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
         }
       }
       if (tr) p.trace[49 + 2 * mat] = clock64();
-      asm volatile("bar.sync 5, 256;" ::: "memory");
+      asm volatile("bar.sync 5, 384;" ::: "memory");
       if (ok) {
         constexpr int kLanesPerRow = kRowB / 16;            // 16 (fp16) or 32 (f32)
         constexpr int kRowsPerInstr = 32 / kLanesPerRow;    // 2 or 1
         const int sub = lane / kLanesPerRow, l16 = lane % kLanesPerRow;
-        for (int r = warp * kRowsPerInstr + sub; r < ntok; r += 8 * kRowsPerInstr) {
+        for (int r = ew * kRowsPerInstr + sub; r < ntok; r += kEpiWarps * kRowsPerInstr) {
           const int pr = s_pair[r];
           const uint4 v = *reinterpret_cast<const uint4 *>(stg + r * kRowB + l16 * 16);
           uint8_t *dst = GATEUP ? reinterpret_cast<uint8_t *>(static_cast<__half *>(p.out) + (size_t)pr * p.N + m0)
@@ -518,7 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
         }
       }
       if (tr) p.trace[50 + 2 * mat] = clock64();
-      if (mat + 1 < kEpiMats) asm volatile("bar.sync 5, 256;" ::: "memory");
+      if (mat + 1 < kEpiMats) asm volatile("bar.sync 5, 384;" ::: "memory");
     }
   }
   if (!ok && lane == 0 && p.status) atomicExch(p.status, 1);
