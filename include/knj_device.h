@@ -251,6 +251,12 @@ size_t knj_panel_bytes(int n_vec, int K);
  * K-split, tiles-per-CTA and 4-token tiles per pass (1, 2 or 4) of the decode
  * projections; 0 = automatic. */
 void knj_q4k_decode_tuning(int ks, int tg, int nt);
+
+/* Measurement hook (no reference counterpart): 16 uint64 receiving global-timer
+ * ns of CTA 0 / thread 0 of the decode projections: [0] start, [1] predecessor
+ * complete, [2] plan read, [3] first wait for weights, [4] weights landed,
+ * [5] first pass computed, [6] end; +8 for the single-matrix launch. NULL = off. */
+void knj_q4k_proj_trace(void *dev_buf);
 /* x [n_vec][K] (f32/bf16/f16, row stride ldx elements) -> panel. */
 int knj_act_prep_launch(const void *x, int x_dtype, int64_t ldx, int n_vec, int K, void *panel, knj_stream_t s);
 

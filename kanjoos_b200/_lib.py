@@ -101,6 +101,7 @@ SIGNATURES = {
     "knj_ep_reduce_sel_launch": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "knj_q4k_decode_tuning": (None, [_i, _i, _i]),
+    "knj_q4k_proj_trace": (None, [_vp]),
     "knj_panel_bytes": (_sz, [_i, _i]),
     "knj_act_prep_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i,

@@ -67,6 +67,8 @@ struct ProjParams {
   float *out1;  // dual: U
   float *out2;  // dual: A = silu(G)*U
   int N, K, rowBytes, row_div, tiles_per_expert;
+  int n_experts;  // length of exp_list / pair_cnt
+  unsigned long long *trace;  // optional: [0..7] gate+up launch, [8..15] single-matrix launch
   int ks;         // warps that split the K range of one tile
   int tg;         // tiles per CTA (blockDim = 32 * tg * ks)
   int pitch;      // padded bytes per staged row part
@@ -133,23 +135,36 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
     *s_fail = 0;
   }
   mbar_init_fence();
+  unsigned long long *tr = (p.trace && blockIdx.x == 0 && threadIdx.x == 0) ? p.trace + (DUAL ? 0 : 8) : nullptr;
+  if (tr) tr[0] = global_timer_ns();
   grid_dep_wait();  // the plan, the prepared vectors (and for the down projection the activations) come from earlier launches
   __syncthreads();
+  if (tr) tr[1] = global_timer_ns();
   uint32_t wphase = 0, bphase0 = 0, bphase1 = 0;
   bool ok = true;  // false: skip work and waits, but keep meeting the CTA barriers
   int staged_vec = -2;  // warp 0, lane i: the vector sitting in resident slot i
 
-  const int n_act = p.n_active[0];
+  // The plan is read with as few dependent round trips as possible (each costs most of a microsecond, and a
+  // small batch has nothing else to hide them behind): the first item's expert is fetched together with the
+  // number of active experts, later items' experts one item ahead, and an item's first pair ids together
+  // with its pair count.
   const int groups = p.tiles_per_expert / p.tg;
+  int e_next = 0;
+  if ((int)blockIdx.x / groups < p.n_experts) e_next = p.exp_list[blockIdx.x / groups];
+  const int n_act = p.n_active[0];
   const int total = n_act * groups;
   const size_t vec_bytes = panel_vec_bytes(p.K);
   const int rows_per_tile = DUAL ? 8 : 16;
+  const int first_lanes = min(min(TP, p.tp_alloc), (int)p.idxStride);
 
   for (int it = blockIdx.x; it < total; it += gridDim.x) {
     const int a = it / groups, grp = it - a * groups;
-    const int e = p.exp_list[a];
+    const int e = e_next;
+    if (it + (int)gridDim.x < total) e_next = p.exp_list[(it + gridDim.x) / groups];
+    const int pair_first = lane < first_lanes ? p.pair_idx[(size_t)e * p.idxStride + lane] : -1;
     const int cnt = p.pair_cnt[e];
     const int n0 = (grp * p.tg + tile_slot) * rows_per_tile;
+    if (tr && it == (int)blockIdx.x) tr[2] = global_timer_ns() + (cnt & 0);
 
     // ---- this warp's part of the 16 weight rows: one TMA box per matrix (rows x part bytes), dense in
     // shared memory
@@ -174,9 +189,11 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
       const int n_valid = min(min(TP, p.tp_alloc), cnt - tok0);
       // pair ids of this pass: lane i holds the pair of token tok0 + i
       int my_pair = -1, my_vec = -1;
+      float my_inv = 0.f;  // the vector's inverse scale, needed only at the very end: fetched now
       if (lane < n_valid) {
-        my_pair = p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
+        my_pair = tok0 == 0 ? pair_first : p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
         my_vec = p.row_map ? p.row_map[my_pair] : my_pair / p.row_div;
+        my_inv = __ldg(reinterpret_cast<const float *>(p.panel + (size_t)my_vec * vec_bytes + (size_t)nsb * kChunkBytes));
       }
       // staged activation chunks: buffer b, part pp, token i
       auto stage_chunks = [&](int j) {
@@ -236,9 +253,11 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
           have_b = true;
         }
         if (ok && !w_ready) {
+          if (tr && it == (int)blockIdx.x) tr[3] = global_timer_ns();
           if (!mbar_wait(wbar, wphase, s_fail)) ok = false;
           wphase ^= 1u;
           w_ready = true;
+          if (tr && it == (int)blockIdx.x) tr[4] = global_timer_ns();
         }
         if (!ok) continue;
 
@@ -317,6 +336,7 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
         else run(std::integral_constant<int, NT>{});
       }
 
+      if (tr && it == (int)blockIdx.x && tok0 == 0) tr[5] = global_timer_ns();
       // ---- combine the K parts (fixed order), undo the activation scale, store
       if (ks > 1) {
         float *mine = red + (size_t)(warp * 32 + lane) * 2 * NT;
@@ -335,9 +355,8 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const int pp = __shfl_sync(0xffffffffu, my_pair, nt * 4 + t);
-          const int vo = __shfl_sync(0xffffffffu, my_vec, nt * 4 + t);
+          const float inv = __shfl_sync(0xffffffffu, my_inv, nt * 4 + t);
           if (pp < 0) continue;
-          const float inv = __ldg(reinterpret_cast<const float *>(p.panel + (size_t)vo * vec_bytes + (size_t)nsb * kChunkBytes));
           const float v0 = acc0[nt] * inv, v1 = acc1[nt] * inv;
           if (DUAL) {
             const size_t o = (size_t)pp * p.N + n0 + g;
@@ -398,6 +417,7 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
       __syncthreads();
     }
   }
+  if (tr) tr[6] = global_timer_ns();
   if (!ok && threadIdx.x == 0 && p.status) atomicExch(p.status, 1);
 }
 
@@ -420,11 +440,14 @@ int pad_pitch(int rowBytes) {
 
 // Experiment hook: 0 = choose automatically.
 int g_force_ks = 0, g_force_tg = 0, g_force_nt = 0;
+unsigned long long *g_proj_trace = nullptr;  // measurement hook: 16 global-timer stamps of CTA 0, warp 0
 
 template <bool DUAL, int NT>
 int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st) {
   const int nsb = p.K / KNJ_QK_K;
   const int TP = 4 * NT;
+  p.n_experts = n_experts_max;
+  p.trace = g_proj_trace;
   // small batches: split K over the warps of a CTA so every SM has many warps in flight,
   // and keep the whole prepared vectors of a pass resident in shared memory
   p.tp_alloc = max_tokens < TP ? (max_tokens < 1 ? 1 : max_tokens) : TP;
@@ -503,6 +526,11 @@ extern "C" {
 
 // Experiment hook for tuning runs: force the K-split and tiles-per-CTA of the
 // decode projections (0 = automatic). Not part of the reference surface.
+// Measurement hook (no reference counterpart): 16 uint64 that receive global-timer ns of CTA 0 / thread 0 of the
+// decode projections -- [0] start, [1] predecessor complete, [2] plan read, [3] first wait for weights,
+// [4] weights landed, [5] first pass computed, [6] end; +8 for the single-matrix launch. NULL = off.
+void knj_q4k_proj_trace(void *dev_buf) { g_proj_trace = static_cast<unsigned long long *>(dev_buf); }
+
 void knj_q4k_decode_tuning(int ks, int tg, int nt) {
   g_force_ks = ks;
   g_force_tg = tg;

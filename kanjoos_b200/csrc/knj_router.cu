@@ -629,7 +629,6 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   unsigned long long stamp[9];
   stamp[6] = stamp[7] = stamp[8] = 0;
   stamp[0] = gtime_ns();
-  grid_dep_wait();  // the token rows are the previous layer's output
 
   // ---- logits (and the rows' scales)
   {
@@ -705,6 +704,9 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
       }
     };
     const int nt = min(kFrontTok, p.T - t0);
+    // the router and norm weights above do not depend on the previous launch and are already on their way;
+    // the token rows are the previous layer's output
+    grid_dep_wait();
     stamp[6] = gtime_ns();
     if (nt > 0) fetch(t0, ra);
     for (int i = 0; i < nt; i += 2) {
