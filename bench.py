@@ -363,8 +363,13 @@ def run_gpu(args):
 
     # dominant kernel alone (rank 0): gate+up grouped product on this rank's rows, CUDA events on its stream
     roof = None
+    imbalance = None
     if rank == 0:
         _, pe, _ = ops.router_topk(x, router, TOPK, bias)
+        # load imbalance of this rank's tokens: busiest expert / mean and busiest expert owner / mean
+        per_e = torch.bincount(pe.long(), minlength=E).double()
+        per_r = per_e.view(world, e_loc).sum(1)
+        imbalance = {"per_expert": float(per_e.max() / per_e.mean()), "per_rank": float(per_r.max() / per_r.mean())}
         own = (pe // e_loc) == 0 if world > 1 else torch.ones_like(pe, dtype=torch.bool)
         rows = int(own.sum().item()) if world > 1 else T_loc * TOPK
         # plan over this rank's experts only, tokens from the local shard stand in for received rows
@@ -440,7 +445,7 @@ def run_gpu(args):
     line = {"metric": "moe_ffn_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16 operands (Q4_K unpacked), f32 accumulate", "data": "synthetic",
-            "config": workload_config(args, world), "clocks": clocks,
+            "config": dict(workload_config(args, world), routing_imbalance=imbalance), "clocks": clocks,
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T_loc * H * 2 * world,
                     "d2h_bytes_per_step": T_loc * H * 2 * world, "ms_per_step": ms_e2e},
             "gpu_launches": launches * args.steps, "roofline": roof, "cpu_baseline": cb, "decode": dec,
