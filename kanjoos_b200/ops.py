@@ -155,6 +155,16 @@ def q4k_proj(apanel, W, pair_idx, pair_cnt, exp_list, n_active, P: int, max_toke
     return Y
 
 
+def q6k_proj(A: torch.Tensor, W6: torch.Tensor, pair_idx, pair_cnt, exp_list, n_active, P: int) -> torch.Tensor:
+    """A f32 [P][K], W6 uint8 [E][N][K/256][210] -> Y f32 [P][N] (rows of pairs of inactive experts stay poisoned)."""
+    _need(A, torch.float32), _need(W6, torch.uint8)
+    E, N, nblk, _ = W6.shape
+    Y = torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda")
+    check(lib().knj_q6k_proj_launch(_p(A), _p(W6), _p(pair_idx), _p(pair_cnt), _p(exp_list), _p(n_active), _p(Y), N,
+                                    nblk * 256, pair_idx.shape[1], E, _stream()))
+    return Y
+
+
 def fuse_gateup_silu(G: torch.Tensor, U: torch.Tensor, dtype=torch.float32) -> torch.Tensor:
     _need(G, torch.float32), _need(U, torch.float32)
     A = torch.empty(G.shape, dtype=dtype, device="cuda")

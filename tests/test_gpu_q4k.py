@@ -119,3 +119,26 @@ def test_refusals_do_not_launch():
     assert rc in (-1, -4)
     with pytest.raises(_lib.KnjError):
         ops.q4k_matmul(torch.zeros((16, 1, 144), dtype=torch.uint8, device="cuda")[1:], x)  # 15 rows: not a multiple of 16
+
+
+@pytest.mark.parametrize("E,N,K,counts", [(3, 80, 768, [5, 0, 11]), (2, 64, 256, [1, 9])])
+def test_q6k_projection(E, N, K, counts):
+    """Q6_K down projection of the mixed-format path against the CPU decoder + a double-precision product."""
+    from kanjoos_b200 import ops
+    rng = np.random.Generator(np.random.Philox([E, N, K]))
+    nblk = K // 256
+    W = rng.integers(0, 256, size=(E, N, nblk, 210), dtype=np.uint8)
+    W[..., 208:210] = (np.abs(rng.standard_normal((E, N, nblk, 1))) * 0.01).astype(np.float16).view(np.uint8)
+    Wf = np.empty((E * N * nblk, 256), np.float32)
+    ol.oracle().knj_or_dequant_q6k(ol.ptr(W, ol.u8p), ol.ptr(Wf, ol.f32p), Wf.size)
+    Wf = Wf.reshape(E, N, K)
+    P = int(sum(counts))
+    pe = np.concatenate([np.full(c, e, np.int32) for e, c in enumerate(counts)])
+    pe = pe[rng.permutation(P)]
+    A = rng.standard_normal((P, K)).astype(np.float32)
+    pair_idx, pair_cnt, exp_list, n_active = ops.moe_permute(dev(pe), E, P)
+    Y = ops.q6k_proj(dev(A), dev(W), pair_idx, pair_cnt, exp_list, n_active, P).cpu().numpy()
+    want = np.stack([(Wf[pe[p]].astype(np.float64) @ A[p].astype(np.float64)) for p in range(P)]).astype(np.float32)
+    st = ol.compare(Y, want)
+    print("[parity] q6k projection", st)
+    assert (Y == -12345.0).sum() == 0 and st["rel_rmse"] <= 1e-5
