@@ -401,6 +401,9 @@ typedef struct knj_moe_ffn_args {
   /* optional taps, may be NULL: the routing decision for inspection */
   int32_t *tap_pair_exp;     /* [T*k] */
   float *tap_pair_w;         /* [T*k] */
+  /* format of w_down: 0 = Q4_K as above, 1 = Q6_K [E][hidden][ffn/256][210] (the
+   * mixed-format layers of Q4_K_M checkpoints; decode launch only) */
+  int32_t down_format;
 } knj_moe_ffn_args;
 
 /* mode 0 = decode class (knj_moe_ffn_decode_launch), 1 = prefill class. */

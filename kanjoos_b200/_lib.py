@@ -36,7 +36,8 @@ class MoeFfnArgs(C.Structure):
                 ("w_router", C.c_void_p), ("router_bias", C.c_void_p), ("w_gate", C.c_void_p), ("w_up", C.c_void_p),
                 ("w_down", C.c_void_p), ("norm_w", C.c_void_p), ("rms_eps", C.c_float), ("residual", C.c_int32),
                 ("out", C.c_void_p), ("out_dtype", C.c_int32), ("ldo", C.c_int64), ("workspace", C.c_void_p),
-                ("workspace_bytes", C.c_size_t), ("tap_pair_exp", C.c_void_p), ("tap_pair_w", C.c_void_p)]
+                ("workspace_bytes", C.c_size_t), ("tap_pair_exp", C.c_void_p), ("tap_pair_w", C.c_void_p),
+                ("down_format", C.c_int32)]
 
 
 _vp, _i, _i64, _u32, _u64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint32, C.c_uint64, C.c_size_t, C.c_float

@@ -93,6 +93,7 @@ int check_args(const knj_moe_ffn_args *a, const char *who) {
   KNJ_REQUIRE(aligned16(a->w_gate) && aligned16(a->w_up) && aligned16(a->w_down) && aligned16(a->w_router),
               "%s: weight bases must be 16-byte aligned", who);
   KNJ_REQUIRE(a->ldx >= a->hidden && a->ldo >= a->hidden, "%s: row strides shorter than hidden", who);
+  KNJ_REQUIRE(a->down_format == 0 || a->down_format == 1, "%s: down_format must be 0 (Q4_K) or 1 (Q6_K)", who);
   return KNJ_OK;
 }
 
@@ -156,6 +157,13 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
                              nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, T, s);
   if (rc) return rc;
+  if (a->down_format == 1) {
+    // mixed-format layer: Q6_K down matrices (210-byte superblocks) through the plain f32 projection
+    rc = knj_q6k_proj_launch(w.A, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F, T, E, s);
+    if (rc) return rc;
+    return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
+                                  a->out, a->out_dtype, a->ldo, T, H, k, s);
+  }
   // 5. down
   rc = knj_act_prep_launch(w.A, KNJ_DT_F32, F, P, F, w.apanel, s);
   if (rc) return rc;
@@ -180,6 +188,7 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   if (rc) return rc;
   const int T = a->n_tokens, H = a->hidden, F = a->ffn, E = a->n_experts, k = a->top_k;
   KNJ_REQUIRE(H % 128 == 0 && F % 128 == 0, "knj_moe_ffn_prefill: hidden and ffn must be multiples of 128");
+  KNJ_REQUIRE(a->down_format == 0, "knj_moe_ffn_prefill: Q6_K down matrices have no tensor-core form yet; use knj_moe_ffn_decode_launch");
   const size_t need = knj_moe_ffn_workspace_bytes(T, H, F, E, k, 1);
   if (!a->workspace || a->workspace_bytes < need) {
     set_error("knj_moe_ffn_prefill: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);

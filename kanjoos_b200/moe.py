@@ -21,7 +21,7 @@ _DT = {torch.float32: DT_F32, torch.bfloat16: DT_BF16}
 class ExpertBank:
     """Weights of one MoE layer, all on one device.
 
-    gate, up: uint8 [E][F][H/256][144]; down: uint8 [E][H][F/256][144];
+    gate, up: uint8 [E][F][H/256][144]; down: uint8 [E][H][F/256][144] (Q4_K) or [...][210] (Q6_K);
     router: bf16 [E][H]; router_bias: f32 [E] or None; norm_w: bf16 [H] or None.
     """
     gate: torch.Tensor
@@ -103,6 +103,7 @@ class MoeFfnLayer:
         a.w_router = b.router.data_ptr()
         a.router_bias = b.router_bias.data_ptr() if b.router_bias is not None else None
         a.w_gate, a.w_up, a.w_down = b.gate.data_ptr(), b.up.data_ptr(), b.down.data_ptr()
+        a.down_format = 1 if b.down.shape[-1] == 210 else 0  # Q6_K down matrices of a mixed-format layer
         a.norm_w = b.norm_w.data_ptr() if self.use_norm else None
         a.rms_eps = b.rms_eps
         a.residual = 1 if self.residual else 0

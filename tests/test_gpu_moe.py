@@ -171,3 +171,37 @@ def test_prefill_t512_zipf(cfg2):
         want[rows] += wts[rows, slots][:, None] * y
     st = report(out.cpu().numpy(), want, "cfg3 prefill T=512 Zipf(1.1)")
     assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_PREFILL
+
+
+def test_mixed_format_layer_q6k_down():
+    """A layer whose down matrices are Q6_K (as half of them are in Q4_K_M files): decode launch against the CPU
+    pieces -- router, Q4_K gate/up and SiLU*up from the restatement, Q6_K decode + double-precision product for
+    down, weighted sum in ascending expert order."""
+    E, H, F, k, T = 8, 512, 256, 2, 6
+    bank = synth.expert_bank(105, n_experts=E, hidden=H, ffn=F)
+    wr, _ = synth.router_weight(105, n_experts=E, hidden=H)
+    rng = np.random.Generator(np.random.Philox(105))
+    nblk = F // 256
+    W6 = rng.integers(0, 256, size=(E, H, nblk, 210), dtype=np.uint8)
+    W6[..., 208:210] = (np.abs(rng.standard_normal((E, H, nblk, 1))) * 0.01).astype(np.float16).view(np.uint8)
+    Wd = np.empty((E * H * nblk, 256), np.float32)
+    ol.oracle().knj_or_dequant_q6k(ol.ptr(W6, ol.u8p), ol.ptr(Wd, ol.f32p), Wd.size)
+    Wd = Wd.reshape(E, H, F)
+    hx = synth.hidden_rows(105, T, H)
+    _, ch, wt = ol.route(wr, 1, hx, E, k)
+    want = np.zeros_like(hx)
+    for t in range(T):
+        for s_ in sorted(range(k), key=lambda s_: ch[t][s_]):
+            e = int(ch[t][s_])
+            g = ol.matmul_q4k(bank["gate"][e], hx[t:t + 1])
+            u = ol.matmul_q4k(bank["up"][e], hx[t:t + 1])
+            a = ol.silu_mul(g, u)[0]
+            y = (Wd[e].astype(np.float64) @ a.astype(np.float64)).astype(np.float32)
+            want[t] = want[t] + np.float32(wt[t][s_]) * y
+    mixed = dict(bank, down=W6)
+    layer = make_layer(mixed, wr, k, T)
+    out = layer.decode(dev(hx))
+    st = report(out.cpu().numpy(), want, "mixed-format layer (Q6_K down), decode launch")
+    assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_DECODE
+    with pytest.raises(Exception):
+        layer.prefill(dev(hx))
