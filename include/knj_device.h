@@ -417,6 +417,29 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s);
 int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
 
 /* ======================================================================== */
+/* Device-clock spans for a host profiler                                   */
+/* ======================================================================== */
+/* The event ring behind Profiler::device_span(name, start_ns, end_ns, stream)
+ * (src/profiler/profiler.h:98-137): spans are offsets from ONE epoch event on the
+ * stream, handed over at flush time, never inside the step loop; spans the ring
+ * could not hold are counted. While recording is on, knj_moe_ffn_decode_launch
+ * and knj_moe_ffn_prefill_launch bracket their stages with spans named as the
+ * CPU path's rows (src/model/model.cpp:408-500): moe-router, moe-gather,
+ * moe-gate (gate + up + activation, fused), moe-down, moe-scatter. Nothing is
+ * recorded on a stream that is being captured into a graph. One recorder per
+ * process; not thread-safe. */
+int knj_spans_enable(int capacity);            /* (re)starts recording with room for `capacity` spans */
+int knj_spans_disable(void);
+int knj_spans_active(void);                     /* 1 while recording is on */
+int knj_spans_epoch(knj_stream_t s);            /* marks time zero on `s`, empties the ring */
+int knj_span_begin(const char *name, knj_stream_t s);   /* handle >= 0, or -1: not recorded */
+int knj_span_end(int handle, knj_stream_t s);
+uint64_t knj_spans_dropped(void);               /* spans refused since the epoch because the ring was full */
+/* Waits for the recorded events, then calls cb(name, start_ns, end_ns, 0, user)
+ * for every closed span in recording order, and empties the ring. */
+int knj_spans_flush(void (*cb)(const char *name, uint64_t start_ns, uint64_t end_ns, int stream, void *user), void *user);
+
+/* ======================================================================== */
 /* Expert-parallel exchange helpers                                         */
 /* ======================================================================== */
 /* The reference keeps every expert on one device and has no counterpart for

@@ -94,6 +94,14 @@ SIGNATURES = {
                                   _vp, _vp, _vp, _vp]),
     "knj_moe_front_trace": (None, [_vp]),
     "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "knj_spans_enable": (_i, [_i]),
+    "knj_spans_disable": (_i, []),
+    "knj_spans_active": (_i, []),
+    "knj_spans_epoch": (_i, [_vp]),
+    "knj_span_begin": (_i, [C.c_char_p, _vp]),
+    "knj_span_end": (_i, [_i, _vp]),
+    "knj_spans_dropped": (_u64, []),
+    "knj_spans_flush": (_i, [_vp, _vp]),
     "knj_ep_pack_launch": (_i, [_vp, _i, _i, _vp, _i, _vp, _i, _vp, _vp, _vp, _vp]),
     "knj_ep_plan_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "knj_ep_combine_partial_launch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp]),

@@ -80,6 +80,14 @@ PrefillWs carve_prefill(void *base, int T, int H, int F, int E, int k) {
   return w;
 }
 
+// Device-clock span around a stage of a layer launch while a span ring is recording (knj_spans.cu).
+struct StageSpan {
+  int h;
+  knj_stream_t s;
+  StageSpan(const char *name, knj_stream_t st) : h(knj_spans_active() ? knj_span_begin(name, st) : -1), s(st) {}
+  ~StageSpan() { if (h >= 0) knj_span_end(h, s); }
+};
+
 int check_args(const knj_moe_ffn_args *a, const char *who) {
   KNJ_REQUIRE(a, "%s: null argument block", who);
   KNJ_REQUIRE(a->x && a->w_router && a->w_gate && a->w_up && a->w_down && a->out, "%s: null tensor pointer", who);
@@ -126,6 +134,7 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
   if (T <= 64 && H <= 2048 && a->ldx % 8 == 0 && aligned16(a->x)) {
     // decode batch: norm statistics, routing, tables and prepared vectors in one launch
+    StageSpan sp("moe-router", s);  // norm statistics, router, top-k, plan and prepared vectors in one launch
     rc = knj_moe_front_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, a->w_router, a->router_bias, T, H, E, k,
                               w.logits, pair_exp, pair_w, w.pair_idx, T, w.pair_cnt, w.exp_list, w.n_active, w.xpanel,
                               w.counter, s);
@@ -154,9 +163,13 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
     if (T <= 64) KNJ_CUDA(cudaMemsetAsync(w.counter + 64, 0, 128 * sizeof(uint32_t), as_stream(s)));  // slice counters
   }
   // gate, up, silu(g)*u
-  rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
-                             nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, T, s);
-  if (rc) return rc;
+  {
+    StageSpan sp("moe-gate", s);  // gate + up + activation fused
+    rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
+                               nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, T, s);
+    if (rc) return rc;
+  }
+  StageSpan sp_down("moe-down", s);  // down projection and the weighted combine (to the end of the launch)
   if (a->down_format == 1) {
     // mixed-format layer: Q6_K down matrices (210-byte superblocks) through the plain f32 projection
     rc = knj_q6k_proj_launch(w.A, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F, T, E, s);
@@ -210,20 +223,33 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   }
   int32_t *pair_exp = a->tap_pair_exp ? a->tap_pair_exp : w.pair_exp;
   float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
-  rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
-  if (rc) return rc;
-  // long pair lists take the counting-sort form; its scratch is the activation buffer, which is written later
-  rc = knj_moe_permute_ws_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.ah,
-                                 (size_t)P * F * 2, s);
-  if (rc) return rc;
-  rc = knj_to_f16_launch(src, src_dt, src_ld, T, H, w.xh, s);
-  if (rc) return rc;
-  rc = knj_q4k_gateup_tc_launch(w.xh, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.ah, F, H,
-                                H / 256 * KNJ_Q4K_BYTES, T, E, k, P, w.status, s);
-  if (rc) return rc;
-  rc = knj_q4k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, E,
-                              P, w.status, s);
-  if (rc) return rc;
+  {
+    StageSpan sp("moe-router", s);
+    rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
+    if (rc) return rc;
+  }
+  {
+    StageSpan sp("moe-gather", s);  // permutation tables and fp16 rows (rows are gathered inside the GEMM)
+    // long pair lists take the counting-sort form; its scratch is the activation buffer, which is written later
+    rc = knj_moe_permute_ws_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.ah,
+                                   (size_t)P * F * 2, s);
+    if (rc) return rc;
+    rc = knj_to_f16_launch(src, src_dt, src_ld, T, H, w.xh, s);
+    if (rc) return rc;
+  }
+  {
+    StageSpan sp("moe-gate", s);  // gate + up + activation fused
+    rc = knj_q4k_gateup_tc_launch(w.xh, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.ah, F, H,
+                                  H / 256 * KNJ_Q4K_BYTES, T, E, k, P, w.status, s);
+    if (rc) return rc;
+  }
+  {
+    StageSpan sp("moe-down", s);
+    rc = knj_q4k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, E,
+                                P, w.status, s);
+    if (rc) return rc;
+  }
+  StageSpan sp("moe-scatter", s);
   return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
                                 a->out, a->out_dtype, a->ldo, T, H, k, s);
 }
