@@ -94,6 +94,30 @@ SIGNATURES = {
                                   _vp, _vp, _vp, _vp]),
     "knj_moe_front_trace": (None, [_vp]),
     "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "knj_res_arena_create": (_vp, []),
+    "knj_res_arena_alloc": (_vp, [_vp, _u64]),
+    "knj_res_arena_free": (None, [_vp, _vp]),
+    "knj_res_arena_destroy": (None, [_vp]),
+    "knj_res_slots_create": (_vp, [_i, _u64]),
+    "knj_res_slot_acquire": (_i, [_vp, _u32, _u32, _u64]),
+    "knj_res_slot_release": (None, [_vp, _i]),
+    "knj_res_slot_released": (_i, [_vp, _i]),
+    "knj_res_slot_pin": (None, [_vp, _i]),
+    "knj_res_slot_unpin": (None, [_vp, _i]),
+    "knj_res_slot_load_fired": (_i, [_vp, _i]),
+    "knj_res_slot_ptr": (_vp, [_vp, _i]),
+    "knj_res_slot_bytes": (_u64, [_vp, _i]),
+    "knj_res_slot_watch": (None, [_vp, _i, _vp, _u64]),
+    "knj_res_slots_destroy": (None, [_vp]),
+    "knj_res_engine_create": (_vp, [C.c_char_p]),
+    "knj_res_submit_nvme_read": (_u64, [_vp, _vp, _u64, _u64, _i]),
+    "knj_res_submit_nvme_write": (_u64, [_vp, _vp, _u64, _u64, _i]),
+    "knj_res_submit_h2d": (_u64, [_vp, _vp, _vp, _u64, _i]),
+    "knj_res_submit_d2h": (_u64, [_vp, _vp, _vp, _u64, _i]),
+    "knj_res_poll": (_i, [_vp, _u64]),
+    "knj_res_cancel": (_i, [_vp, _u64]),
+    "knj_res_wait_on_stream": (_i, [_vp, _u64, _vp]),
+    "knj_res_engine_destroy": (None, [_vp]),
     "knj_spans_enable": (_i, [_i]),
     "knj_spans_disable": (_i, []),
     "knj_spans_active": (_i, []),

@@ -1,5 +1,5 @@
 """CPU-only checks of the boundary: the shared library loads and exports every
-symbol include/knj_device.h declares, argument validation refuses bad calls
+symbol include/knj_device.h and include/knj_residency.h declare, argument validation refuses bad calls
 before any device work, and the host-side device layer (arch guard, capability
 table, cap line, Backend gating) behaves like the reference's
 tests/unit/test_c2_device.cpp expects of its own."""
@@ -20,7 +20,7 @@ def L():
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "knj_device.h")).read()
+    text = "".join(open(os.path.join(ROOT, "include", h)).read() for h in ("knj_device.h", "knj_residency.h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     names = set(re.findall(r"\b(knj_[a-z0-9_]+)\s*\(", text))
     names -= {"knj_q4k_down_launch"}  # a #define alias of knj_q4k_proj_launch
@@ -33,7 +33,7 @@ def test_every_declared_symbol_is_exported_and_bound(L):
     assert len(names) >= 50
     handle = C.CDLL(_lib.LIB_PATH)
     for n in names:
-        assert hasattr(handle, n), f"{n} is declared in include/knj_device.h but not exported"
+        assert hasattr(handle, n), f"{n} is declared in include/ but not exported"
         assert n in _lib.SIGNATURES, f"{n} has no ctypes signature"
 
 
@@ -233,3 +233,28 @@ int t_stride(void) { return KNJ_GROUP_STRIDE_BYTES(4, KNJ_GROUP_EXPERT); }
     t.t_unpack(0xA1B2C3D4, C.byref(lo), C.byref(hi))
     assert lo.value == 0x01020304 and hi.value == 0x0A0B0C0D
     assert t.t_stride() == 68
+
+
+def test_residency_objects_without_a_device(L, tmp_path):
+    """The gates refuse cleanly where there is no device: no slot, no device copy; the file tier still works."""
+    n = C.c_int(-1)
+    if L.knj_dev_count(C.byref(n)) == 0 and n.value > 0:
+        pytest.skip("a GPU is present")
+    slots = L.knj_res_slots_create(2, 1024)
+    assert L.knj_res_slot_acquire(slots, 0, 0, 16) == -1 and L.knj_res_slot_ptr(slots, 0) is None
+    L.knj_res_slots_destroy(slots)
+    path = tmp_path / "tier.bin"
+    path.write_bytes(bytes(range(256)) * 4)
+    eng = L.knj_res_engine_create(str(path).encode())
+    buf = C.create_string_buffer(256)
+    assert L.knj_res_submit_h2d(eng, buf, buf, 16, 0) == 0
+    t = L.knj_res_submit_nvme_read(eng, buf, 256, 256, 1)
+    assert t != 0
+    while L.knj_res_poll(eng, t) == 0:
+        pass
+    assert L.knj_res_poll(eng, t) == 1 and buf.raw == bytes(range(256))
+    bad = L.knj_res_submit_nvme_read(eng, buf, 1 << 20, 256, 0)   # past the end of the file: fails, does not hang
+    while L.knj_res_poll(eng, bad) == 0:
+        pass
+    assert L.knj_res_poll(eng, bad) == 2
+    L.knj_res_engine_destroy(eng)
