@@ -416,6 +416,21 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s);
  * tcgen05.mma with f32 TMEM accumulators (<= 1e-3 rel-RMSE vs the CPU path). */
 int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
 
+/* The resident decode stack for batches of 1..4 tokens in ONE cooperative launch:
+ * n_layers layer descriptions (layer l's out is normally layer l+1's x; out must
+ * not alias x within a layer), all of one shape, Q4_K down matrices. The loop the
+ * reference runs on the host per layer (src/model/model.cpp:399-510) becomes grid
+ * barriers inside one kernel. Same arithmetic class as knj_moe_ffn_decode_launch
+ * (f32, <= 1e-5 rel-RMSE vs the CPU path; routing decisions identical to it).
+ * create validates, copies the layer table to the device and allocates scratch;
+ * the workspace fields of the layer descriptions are not used. status() waits for
+ * the stream and reports whether a grid barrier gave up (bounded waits). */
+typedef struct knj_moe_stack knj_moe_stack;
+int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_stack **out);
+int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s);
+int knj_moe_stack_status(knj_moe_stack *st, knj_stream_t s);
+void knj_moe_stack_destroy(knj_moe_stack *st);
+
 /* ======================================================================== */
 /* Device-clock spans for a host profiler                                   */
 /* ======================================================================== */

@@ -94,6 +94,10 @@ SIGNATURES = {
                                   _vp, _vp, _vp, _vp]),
     "knj_moe_front_trace": (None, [_vp]),
     "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
+    "knj_moe_stack_create": (_i, [_vp, _i, C.POINTER(_vp)]),
+    "knj_moe_stack_decode_launch": (_i, [_vp, _vp]),
+    "knj_moe_stack_status": (_i, [_vp, _vp]),
+    "knj_moe_stack_destroy": (None, [_vp]),
     "knj_res_arena_create": (_vp, []),
     "knj_res_arena_alloc": (_vp, [_vp, _u64]),
     "knj_res_arena_free": (None, [_vp, _vp]),

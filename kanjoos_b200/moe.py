@@ -168,3 +168,56 @@ class MoeStack:
         with torch.cuda.graph(g):
             out = self.step(x)
         return g, out
+
+
+class FusedMoeStack:
+    """The resident stack for 1..4 tokens as ONE cooperative launch (knj_moe_stack_*): the per-layer loop,
+    its routing and its hand-offs run inside a single kernel with grid barriers between the stages. Buffers are
+    static: write the step's rows into `self.x` (or pass them to step) and read `self.out` after the launch."""
+
+    def __init__(self, banks: list[ExpertBank], top_k: int = synth.TOP_K, n_tokens: int = 1, dtype=torch.bfloat16,
+                 residual: bool = True, use_norm: bool = True, taps: bool = False):
+        dev = banks[0].gate.device
+        H = banks[0].hidden
+        self.x = torch.zeros((n_tokens, H), dtype=dtype, device=dev)
+        self._buf = (torch.zeros_like(self.x), torch.zeros_like(self.x))
+        ws = torch.empty(256, dtype=torch.uint8, device=dev)
+        self._layers = [MoeFfnLayer.__new__(MoeFfnLayer) for _ in banks]
+        P = n_tokens * top_k
+        self.taps = [(torch.empty(P, dtype=torch.int32, device=dev), torch.empty(P, dtype=torch.float32, device=dev))
+                     for _ in banks] if taps else None
+        arr = (MoeFfnArgs * len(banks))()
+        cur = self.x
+        for l, (layer, b) in enumerate(zip(self._layers, banks)):
+            layer.bank, layer.top_k, layer.max_tokens, layer.residual = b, top_k, n_tokens, residual
+            layer.use_norm = use_norm and b.norm_w is not None
+            layer.workspace = ws
+            nxt = self._buf[l & 1]
+            arr[l] = layer._args(cur, nxt, self.taps[l] if taps else None)
+            cur = nxt
+        self.out = cur
+        self._banks = banks  # keep the weights alive
+        h = C.c_void_p()
+        check(lib().knj_moe_stack_create(arr, len(banks), C.byref(h)))
+        self._h = h
+
+    def step(self, x: torch.Tensor | None = None) -> torch.Tensor:
+        if x is not None:
+            self.x.copy_(x)
+        check(lib().knj_moe_stack_decode_launch(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return self.out
+
+    def status(self) -> None:
+        """Waits for the stream; raises if a grid barrier of the last launches gave up."""
+        check(lib().knj_moe_stack_status(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def close(self):
+        if self._h:
+            lib().knj_moe_stack_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
