@@ -97,6 +97,7 @@ SIGNATURES = {
     "knj_moe_stack_create": (_i, [_vp, _i, C.POINTER(_vp)]),
     "knj_moe_stack_decode_launch": (_i, [_vp, _vp]),
     "knj_moe_stack_status": (_i, [_vp, _vp]),
+    "knj_moe_stack_trace": (_i, [_vp, _vp]),
     "knj_moe_stack_destroy": (None, [_vp]),
     "knj_res_arena_create": (_vp, []),
     "knj_res_arena_alloc": (_vp, [_vp, _u64]),

@@ -62,6 +62,8 @@ struct StackParams {
   float *logits;       // [T][E]
   float *act;          // [T*k][F]
   unsigned int *sync;  // [0] arrivals, [1] error word; both zero before the launch
+  int slots;           // gate/up row pairs a warp stages at a time (1..3, by the shared memory left)
+  unsigned long long *trace;  // optional [16]: global-timer stamps of CTA 0's stages in layer 1 (or 0 if alone)
 };
 
 __device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
@@ -73,13 +75,19 @@ __device__ __forceinline__ void red_release(unsigned *p, unsigned v) {
   asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// All CTAs of the grid have arrived `target` times in total. False: a wait ran out (here or elsewhere).
-__device__ __forceinline__ bool grid_barrier(unsigned *sync, unsigned target) {
+// Grid barrier in two halves, so that work that does not depend on the other CTAs can sit between them.
+// arrive: everything this CTA wrote so far is published. wait: all CTAs of the grid have arrived `target`
+// times in total; false: a wait ran out (here or elsewhere).
+__device__ __forceinline__ void grid_arrive(unsigned *sync) {
   __syncthreads();
-  int ok = 1;
   if (threadIdx.x == 0) {
     __threadfence();
     red_release(sync, 1u);
+  }
+}
+__device__ __forceinline__ bool grid_wait(unsigned *sync, unsigned target) {
+  int ok = 1;
+  if (threadIdx.x == 0) {
     const long long t0 = clock64();
     unsigned polls = 0;
     while (ld_acquire(sync) < target) {
@@ -90,6 +98,10 @@ __device__ __forceinline__ bool grid_barrier(unsigned *sync, unsigned target) {
     }
   }
   return __syncthreads_and(ok) != 0;
+}
+__device__ __forceinline__ bool grid_barrier(unsigned *sync, unsigned target) {
+  grid_arrive(sync);
+  return grid_wait(sync, target);
 }
 
 __device__ __forceinline__ uint4 ldcg16(const void *p) { return __ldcg(reinterpret_cast<const uint4 *>(p)); }
@@ -140,54 +152,58 @@ __device__ __forceinline__ float byte_f32(unsigned v) {
 
 // sum over the quarter's 64 weights of q * x: S0 for the low nibbles (sub-block 2G), S1 for the high ones.
 // xq points at this quarter's first float4 of a transposed vector, consecutive float4s are `stride4` apart.
+// The loops below are deliberately NOT unrolled (two code words per step, the rest of the words rotate down):
+// the straight-line form of 64 or 128 weights needs more registers than a 512-thread CTA has and spills.
+__device__ __forceinline__ void word_fma(unsigned w, const float4 &xl, const float4 &xh, float &s0, float &s1) {
+  const unsigned lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
+  s0 = fmaf(byte_f32<0>(lo), xl.x, s0);
+  s0 = fmaf(byte_f32<1>(lo), xl.y, s0);
+  s0 = fmaf(byte_f32<2>(lo), xl.z, s0);
+  s0 = fmaf(byte_f32<3>(lo), xl.w, s0);
+  s1 = fmaf(byte_f32<0>(hi), xh.x, s1);
+  s1 = fmaf(byte_f32<1>(hi), xh.y, s1);
+  s1 = fmaf(byte_f32<2>(hi), xh.z, s1);
+  s1 = fmaf(byte_f32<3>(hi), xh.w, s1);
+}
 __device__ __forceinline__ void quarter_dot(const Quarter &w, const float4 *xq, int stride4, float &S0, float &S1) {
-  const unsigned words[8] = {w.q0.x, w.q0.y, w.q0.z, w.q0.w, w.q1.x, w.q1.y, w.q1.z, w.q1.w};
-  float s0 = 0.f, s1 = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float4 xl = xq[i * stride4], xh = xq[(8 + i) * stride4];
-    const unsigned lo = words[i] & 0x0f0f0f0fu, hi = (words[i] >> 4) & 0x0f0f0f0fu;
-    s0 = fmaf(byte_f32<0>(lo), xl.x, s0);
-    s0 = fmaf(byte_f32<1>(lo), xl.y, s0);
-    s0 = fmaf(byte_f32<2>(lo), xl.z, s0);
-    s0 = fmaf(byte_f32<3>(lo), xl.w, s0);
-    s1 = fmaf(byte_f32<0>(hi), xh.x, s1);
-    s1 = fmaf(byte_f32<1>(hi), xh.y, s1);
-    s1 = fmaf(byte_f32<2>(hi), xh.z, s1);
-    s1 = fmaf(byte_f32<3>(hi), xh.w, s1);
+  unsigned a0 = w.q0.x, a1 = w.q0.y, a2 = w.q0.z, a3 = w.q0.w, a4 = w.q1.x, a5 = w.q1.y, a6 = w.q1.z, a7 = w.q1.w;
+  float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
+  const float4 *xl = xq, *xh = xq + 8 * stride4;
+#pragma unroll 1
+  for (int it = 0; it < 4; ++it) {
+    const float4 l0 = xl[0], h0 = xh[0], l1 = xl[stride4], h1 = xh[stride4];
+    word_fma(a0, l0, h0, s0, s1);
+    word_fma(a1, l1, h1, t0, t1);
+    a0 = a2; a1 = a3; a2 = a4; a3 = a5; a4 = a6; a5 = a7;
+    xl += 2 * stride4;
+    xh += 2 * stride4;
   }
-  S0 = s0;
-  S1 = s1;
+  S0 = s0 + t0;
+  S1 = s1 + t1;
 }
 // the same for two rows that share the vector (gate and up)
 __device__ __forceinline__ void quarter_dot2(const Quarter &wa, const Quarter &wb, const float4 *xq, int stride4,
                                              float &A0, float &A1, float &B0, float &B1) {
-  const unsigned wa8[8] = {wa.q0.x, wa.q0.y, wa.q0.z, wa.q0.w, wa.q1.x, wa.q1.y, wa.q1.z, wa.q1.w};
-  const unsigned wb8[8] = {wb.q0.x, wb.q0.y, wb.q0.z, wb.q0.w, wb.q1.x, wb.q1.y, wb.q1.z, wb.q1.w};
-  float a0 = 0.f, a1 = 0.f, b0 = 0.f, b1 = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const float4 xl = xq[i * stride4], xh = xq[(8 + i) * stride4];
-    const unsigned la = wa8[i] & 0x0f0f0f0fu, ha = (wa8[i] >> 4) & 0x0f0f0f0fu;
-    const unsigned lb = wb8[i] & 0x0f0f0f0fu, hb = (wb8[i] >> 4) & 0x0f0f0f0fu;
-    a0 = fmaf(byte_f32<0>(la), xl.x, a0);
-    a0 = fmaf(byte_f32<1>(la), xl.y, a0);
-    a0 = fmaf(byte_f32<2>(la), xl.z, a0);
-    a0 = fmaf(byte_f32<3>(la), xl.w, a0);
-    a1 = fmaf(byte_f32<0>(ha), xh.x, a1);
-    a1 = fmaf(byte_f32<1>(ha), xh.y, a1);
-    a1 = fmaf(byte_f32<2>(ha), xh.z, a1);
-    a1 = fmaf(byte_f32<3>(ha), xh.w, a1);
-    b0 = fmaf(byte_f32<0>(lb), xl.x, b0);
-    b0 = fmaf(byte_f32<1>(lb), xl.y, b0);
-    b0 = fmaf(byte_f32<2>(lb), xl.z, b0);
-    b0 = fmaf(byte_f32<3>(lb), xl.w, b0);
-    b1 = fmaf(byte_f32<0>(hb), xh.x, b1);
-    b1 = fmaf(byte_f32<1>(hb), xh.y, b1);
-    b1 = fmaf(byte_f32<2>(hb), xh.z, b1);
-    b1 = fmaf(byte_f32<3>(hb), xh.w, b1);
+  unsigned a0 = wa.q0.x, a1 = wa.q0.y, a2 = wa.q0.z, a3 = wa.q0.w, a4 = wa.q1.x, a5 = wa.q1.y, a6 = wa.q1.z, a7 = wa.q1.w;
+  unsigned b0 = wb.q0.x, b1 = wb.q0.y, b2 = wb.q0.z, b3 = wb.q0.w, b4 = wb.q1.x, b5 = wb.q1.y, b6 = wb.q1.z, b7 = wb.q1.w;
+  float sa0 = 0.f, sa1 = 0.f, ta0 = 0.f, ta1 = 0.f, sb0 = 0.f, sb1 = 0.f, tb0 = 0.f, tb1 = 0.f;
+  const float4 *xl = xq, *xh = xq + 8 * stride4;
+#pragma unroll 1
+  for (int it = 0; it < 4; ++it) {
+    const float4 l0 = xl[0], h0 = xh[0], l1 = xl[stride4], h1 = xh[stride4];
+    word_fma(a0, l0, h0, sa0, sa1);
+    word_fma(b0, l0, h0, sb0, sb1);
+    word_fma(a1, l1, h1, ta0, ta1);
+    word_fma(b1, l1, h1, tb0, tb1);
+    a0 = a2; a1 = a3; a2 = a4; a3 = a5; a4 = a6; a5 = a7;
+    b0 = b2; b1 = b3; b2 = b4; b3 = b5; b4 = b6; b5 = b7;
+    xl += 2 * stride4;
+    xh += 2 * stride4;
   }
-  A0 = a0; A1 = a1; B0 = b0; B1 = b1;
+  A0 = sa0 + ta0;
+  A1 = sa1 + ta1;
+  B0 = sb0 + tb0;
+  B1 = sb1 + tb1;
 }
 
 // position of element k of a vector with Q quarters in its transposed shared-memory form:
@@ -197,132 +213,209 @@ __device__ __forceinline__ int tpos(int k, int Q) {
   return (((r >> 2) * Q + q) << 2) + (r & 3);
 }
 
-struct Smem {
-  float *xs, *xsum, *av, *asum, *ypart;
-  int *sel_e, *pair_d, *list, *ord;
-  unsigned *dmask;
-  float *sel_w, *scale;
-  int *n_distinct;
-};
-__host__ __device__ inline size_t smem_floats(int T, int H, int F, int k) {
-  const int P = T * k;
-  return (size_t)T * H + (size_t)T * H / 32 + (size_t)P * F + (size_t)P * F / 32 + (size_t)kWarps * P * (F / 64 + 1) +
-         (size_t)6 * kMaxPairs + 16;
+__device__ __forceinline__ void cp_async16(void *dst_smem, const void *src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src) : "memory");
 }
-__device__ __forceinline__ Smem carve(float *base, int T, int H, int F, int k) {
-  const int P = T * k;
-  Smem s;
-  s.xs = base;
-  s.av = s.xs + (size_t)T * H;
-  s.xsum = s.av + (size_t)P * F;
-  s.asum = s.xsum + (size_t)T * H / 32;
-  s.ypart = s.asum + (size_t)P * F / 32;
-  float *r = s.ypart + (size_t)kWarps * P * (F / 64 + 1);
-  s.sel_e = reinterpret_cast<int *>(r);
-  s.pair_d = s.sel_e + kMaxPairs;
-  s.list = s.pair_d + kMaxPairs;
-  s.ord = s.list + kMaxPairs;
-  s.dmask = reinterpret_cast<unsigned *>(s.ord + kMaxPairs);
-  s.sel_w = reinterpret_cast<float *>(s.dmask + kMaxPairs);
-  s.scale = s.sel_w + kMaxPairs;
-  s.n_distinct = reinterpret_cast<int *>(s.scale + 8);
-  return s;
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Shared-memory plan (byte offsets). `slots` gate/up row pairs are staged per warp at a time.
+struct Plan {
+  uint32_t xs, xsum, wr, nw, small, ypart, asum, av, wstage, total;
+};
+__host__ __device__ inline Plan make_plan(int T, int H, int F, int k, int slots) {
+  const uint32_t P = (uint32_t)(T * k);
+  Plan pl;
+  uint32_t o = 0;
+  auto take = [&](uint32_t bytes) { const uint32_t at = o; o += (bytes + 15u) & ~15u; return at; };
+  pl.xs = take((uint32_t)T * H * 4);
+  pl.xsum = take((uint32_t)T * (H / 32) * 4);
+  pl.wr = take((uint32_t)H * 2);
+  pl.nw = take((uint32_t)H * 2);
+  pl.small = take(1024);
+  pl.ypart = take((uint32_t)kWarps * P * (F / 64 + 1) * 4);
+  pl.asum = take(P * (F / 32) * 4);
+  pl.av = take(P * F * 4);
+  pl.wstage = take((uint32_t)kWarps * slots * 2 * (H / 256) * KNJ_Q4K_BYTES);
+  pl.total = o;
+  return pl;
 }
 
 __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParams p) {
-  extern __shared__ __align__(16) float smem_f[];
-  const Smem sm = carve(smem_f, p.T, p.H, p.F, p.k);
+  extern __shared__ __align__(16) uint8_t smem_b[];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int T = p.T, H = p.H, F = p.F, E = p.E, k = p.k, P = T * k;
   const int QH = H / 64, QF = F / 64;  // quarters per row of gate/up and of down
   const int nslice = H / 256;
   const int G = gridDim.x, c = blockIdx.x;
+  const Plan pl = make_plan(T, H, F, k, p.slots);
+  float *xs = reinterpret_cast<float *>(smem_b + pl.xs), *xsum = reinterpret_cast<float *>(smem_b + pl.xsum);
+  const uint8_t *wr_s = smem_b + pl.wr, *nw_s = smem_b + pl.nw;
+  int *sel_e = reinterpret_cast<int *>(smem_b + pl.small);
+  int *pair_d = sel_e + 32, *list = sel_e + 64, *ord = sel_e + 96;
+  unsigned *dmask = reinterpret_cast<unsigned *>(sel_e + 128), *bitmap = dmask + 32;
+  float *sel_w = reinterpret_cast<float *>(sel_e + 176), *scale_s = sel_w + 32;
+  int *n_distinct = sel_e + 220;
+  float *ypart = reinterpret_cast<float *>(smem_b + pl.ypart), *asum = reinterpret_cast<float *>(smem_b + pl.asum);
+  float *av = reinterpret_cast<float *>(smem_b + pl.av);
+  uint8_t *wstage = smem_b + pl.wstage;
   unsigned arrivals = 0;
+  const int trace_layer = p.n_layers > 1 ? 1 : 0;
 
+  // this CTA's router row and the norm weights of a layer, copied to shared memory ahead of their use
+  auto prefetch_router = [&](const StackLayer &Ln) {
+    const int chunks = H / 8;  // 16-byte pieces of a bf16 row
+    for (int i = threadIdx.x; i < 2 * chunks; i += kThreads) {
+      if (i < chunks) {
+        if (c < E) cp_async16(smem_b + pl.wr + 16 * i, reinterpret_cast<const uint8_t *>(Ln.Wr) + ((size_t)c * H) * 2 + 16 * i);
+      } else if (Ln.norm_w) {
+        cp_async16(smem_b + pl.nw + 16 * (i - chunks), reinterpret_cast<const uint8_t *>(Ln.norm_w) + 16 * (i - chunks));
+      }
+    }
+    cp_async_commit();
+  };
+  prefetch_router(p.layers[0]);
+
+  __shared__ StackLayer s_layer;  // the layer's description: read where needed instead of held in registers
+  static_assert(sizeof(StackLayer) % 4 == 0, "copied by words");
   for (int l = 0; l < p.n_layers; ++l) {
-    const StackLayer L = p.layers[l];
+    if (threadIdx.x < sizeof(StackLayer) / 4)
+      reinterpret_cast<uint32_t *>(&s_layer)[threadIdx.x] = reinterpret_cast<const uint32_t *>(p.layers + l)[threadIdx.x];
+    __syncthreads();
+    const StackLayer &L = s_layer;
+    unsigned long long *tr = (p.trace && c == 0 && threadIdx.x == 0 && l == trace_layer) ? p.trace : nullptr;
+    if (tr) tr[0] = global_timer_ns();
     const bool xf32 = L.x_dtype == KNJ_DT_F32;
+    const bool has_norm = L.norm_w != nullptr;
+
+    // ---- every thread fetches its share of the rows for the transposed copy (4 elements per group)
+    const int groups = T * (H / 4);
+    float4 xv[kMaxT];
+#pragma unroll
+    for (int r = 0; r < kMaxT; ++r) {
+      const int g = threadIdx.x + kThreads * r;
+      xv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (g < groups) {
+        const int t = g / (H / 4), k4 = g - t * (H / 4);
+        const int64_t at = (int64_t)t * L.ldx + 4 * k4;
+        if (xf32) {
+          const uint4 r0 = ldcg16(static_cast<const float *>(L.x) + at);
+          xv[r] = make_float4(__uint_as_float(r0.x), __uint_as_float(r0.y), __uint_as_float(r0.z), __uint_as_float(r0.w));
+        } else {
+          const uint2 r0 = __ldcg(reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(L.x) + at));
+          xv[r] = make_float4(__uint_as_float(r0.x << 16), __uint_as_float(r0.x & 0xffff0000u), __uint_as_float(r0.y << 16),
+                              __uint_as_float(r0.y & 0xffff0000u));
+        }
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // the router row and the norm weights are in shared memory
 
     // ---- row statistics of every token (each CTA for itself) and, in CTA e < E, expert e's logits.
     // Operation order of moe_front_kernel: lane owns elements 256*sl + 8*lane + j, even/odd chains, warp_sum.
     if (warp < T) {
       const int t = warp;
       const bool mine = c < E;
+      uint4 xr[8];  // a bf16 row is fetched whole before it is used; f32 rows (first layer at most) load in place
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl)
+        if (sl < nslice && !xf32) xr[sl] = ldcg16(static_cast<const unsigned short *>(L.x) + (int64_t)t * L.ldx + 256 * sl + 8 * lane);
       float d0 = 0.f, d1 = 0.f, s0 = 0.f, s1 = 0.f;
-      for (int sl = 0; sl < nslice; ++sl) {
-        const int64_t at = (int64_t)t * L.ldx + 256 * sl + 8 * lane;
-        float v[8];
-        if (xf32) {
-          const uint4 r0 = ldcg16(static_cast<const float *>(L.x) + at), r1 = ldcg16(static_cast<const float *>(L.x) + at + 4);
-          v[0] = __uint_as_float(r0.x); v[1] = __uint_as_float(r0.y); v[2] = __uint_as_float(r0.z); v[3] = __uint_as_float(r0.w);
-          v[4] = __uint_as_float(r1.x); v[5] = __uint_as_float(r1.y); v[6] = __uint_as_float(r1.z); v[7] = __uint_as_float(r1.w);
-        } else {
-          const uint4 r = ldcg16(static_cast<const unsigned short *>(L.x) + at);
-          const unsigned u[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            v[2 * j] = __uint_as_float(u[j] << 16);
-            v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-          }
-        }
-        float wr[8];
-        if (mine) {
-          const uint4 r = ldnc16(L.Wr + (size_t)c * H + 256 * sl + 8 * lane);
-          const unsigned u[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            wr[2 * j] = __uint_as_float(u[j] << 16);
-            wr[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-          }
-          if (L.norm_w) {
-            const uint4 rn = ldnc16(L.norm_w + 256 * sl + 8 * lane);
-            const unsigned un[4] = {rn.x, rn.y, rn.z, rn.w};
+      for (int sl = 0; sl < 8; ++sl) {
+        if (sl < nslice) {
+          float v[8], wr[8];
+          if (xf32) {
+            const float *xp = static_cast<const float *>(L.x) + (int64_t)t * L.ldx + 256 * sl + 8 * lane;
+            const uint4 r0 = ldcg16(xp), r1 = ldcg16(xp + 4);
+            v[0] = __uint_as_float(r0.x); v[1] = __uint_as_float(r0.y); v[2] = __uint_as_float(r0.z); v[3] = __uint_as_float(r0.w);
+            v[4] = __uint_as_float(r1.x); v[5] = __uint_as_float(r1.y); v[6] = __uint_as_float(r1.z); v[7] = __uint_as_float(r1.w);
+          } else {
+            const unsigned u[4] = {xr[sl].x, xr[sl].y, xr[sl].z, xr[sl].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              wr[2 * j] *= __uint_as_float(un[j] << 16);
-              wr[2 * j + 1] *= __uint_as_float(un[j] & 0xffff0000u);
+              v[2 * j] = __uint_as_float(u[j] << 16);
+              v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
             }
           }
-        } else {
+          if (mine) {
+            const uint4 r = *reinterpret_cast<const uint4 *>(wr_s + (256 * sl + 8 * lane) * 2);
+            const unsigned u[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-          for (int j = 0; j < 8; ++j) wr[j] = 0.f;
-        }
+            for (int j = 0; j < 4; ++j) {
+              wr[2 * j] = __uint_as_float(u[j] << 16);
+              wr[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
+            }
+            if (has_norm) {
+              const uint4 rn = *reinterpret_cast<const uint4 *>(nw_s + (256 * sl + 8 * lane) * 2);
+              const unsigned un[4] = {rn.x, rn.y, rn.z, rn.w};
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          d0 = fmaf(wr[j], v[j], d0);
-          d1 = fmaf(wr[j + 1], v[j + 1], d1);
-          s0 = fmaf(v[j], v[j], s0);
-          s1 = fmaf(v[j + 1], v[j + 1], s1);
+              for (int j = 0; j < 4; ++j) {
+                wr[2 * j] *= __uint_as_float(un[j] << 16);
+                wr[2 * j + 1] *= __uint_as_float(un[j] & 0xffff0000u);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) wr[j] = 0.f;
+          }
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            d0 = fmaf(wr[j], v[j], d0);
+            d1 = fmaf(wr[j + 1], v[j + 1], d1);
+            s0 = fmaf(v[j], v[j], s0);
+            s1 = fmaf(v[j + 1], v[j + 1], s1);
+          }
         }
       }
       const float dot = warp_sum(d0 + d1), ss = warp_sum(s0 + s1);
       if (lane == 0) {
-        const float scale = L.norm_w ? 1.0f / sqrtf(ss / (float)H + L.eps) : 1.0f;
-        sm.scale[t] = scale;
+        const float scale = has_norm ? 1.0f / sqrtf(ss / (float)H + L.eps) : 1.0f;
+        scale_s[t] = scale;
         if (mine) {
           const float bias = L.bias ? L.bias[c] : 0.f;
           p.logits[(size_t)t * E + c] = dot * scale + bias;
         }
       }
     }
-    __syncthreads();
-    // ---- the rows the experts see, transposed in shared memory, and their 32-element sums
-    for (int i = threadIdx.x; i < T * H; i += kThreads) {
-      const int t = i / H, kx = i - t * H;
-      float v = ldcg_as_f32(L.x, L.x_dtype, (int64_t)t * L.ldx + kx);
-      if (L.norm_w) v = __fmul_rn(__fmul_rn(v, sm.scale[t]), __bfloat162float(L.norm_w[kx]));
-      sm.xs[(size_t)t * H + tpos(kx, QH)] = v;
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < T * H / 32; i += kThreads) {
-      const int t = i / (H / 32), b = i - t * (H / 32);
-      float s = 0.f;
-      for (int j = 0; j < 32; ++j) s += sm.xs[(size_t)t * H + tpos(32 * b + j, QH)];
-      sm.xsum[i] = s;
-    }
-
+    if (tr) tr[1] = global_timer_ns();
     arrivals += G;
-    if (!grid_barrier(p.sync, arrivals)) return;
+    // this CTA's logits are out: the other CTAs need nothing else from it before the top-k
+    grid_arrive(p.sync);
+    // ---- the rows the experts see, transposed in shared memory, and their 32-element sums
+    // (scale_s was written before the barrier's first CTA-wide synchronisation)
+#pragma unroll
+    for (int r = 0; r < kMaxT; ++r) {
+      const int g = threadIdx.x + kThreads * r;
+      if (r * kThreads < groups) {  // whole warps take part in the shuffles
+        float4 v = xv[r];
+        int t = 0, k4 = 0;
+        if (g < groups) {
+          t = g / (H / 4);
+          k4 = g - t * (H / 4);
+          if (has_norm) {
+            const float sc = scale_s[t];
+            const uint2 nw = *reinterpret_cast<const uint2 *>(nw_s + 8 * k4);
+            v.x = __fmul_rn(__fmul_rn(v.x, sc), __uint_as_float(nw.x << 16));
+            v.y = __fmul_rn(__fmul_rn(v.y, sc), __uint_as_float(nw.x & 0xffff0000u));
+            v.z = __fmul_rn(__fmul_rn(v.z, sc), __uint_as_float(nw.y << 16));
+            v.w = __fmul_rn(__fmul_rn(v.w, sc), __uint_as_float(nw.y & 0xffff0000u));
+          }
+          *reinterpret_cast<float4 *>(xs + (size_t)t * H + tpos(4 * k4, QH)) = v;
+        }
+        float s = (v.x + v.y) + (v.z + v.w);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (g < groups && (lane & 7) == 0) xsum[t * (H / 32) + (k4 >> 3)] = s;
+      }
+    }
+    if (tr) tr[2] = global_timer_ns();
+    if (!grid_wait(p.sync, arrivals)) return;
+    if (tr) tr[3] = global_timer_ns();
 
     // ---- top-k per token (every CTA for itself), then the distinct experts in ascending order
     if (warp < T) {
@@ -333,157 +426,186 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
           if (s >= k) break;
-          sm.sel_e[warp * k + s] = se[s];
-          sm.sel_w[warp * k + s] = sw[s];
+          sel_e[warp * k + s] = se[s];
+          sel_w[warp * k + s] = sw[s];
           if (c == 0 && L.tap_exp) L.tap_exp[warp * k + s] = se[s];
           if (c == 0 && L.tap_w) L.tap_w[warp * k + s] = sw[s];
         }
       }
     }
+    if (warp == kWarps - 1 && lane < 8) bitmap[lane] = 0u;
     __syncthreads();
     if (warp == 0) {
-      const int e = lane < P ? sm.sel_e[lane] : -1 - lane;  // distinct dummies so that they match nobody
+      const int e = lane < P ? sel_e[lane] : -1 - lane;  // distinct dummies so that they match nobody
+      if (lane < P) atomicOr(&bitmap[e >> 5], 1u << (e & 31));
+      __syncwarp();
       const unsigned peers = __match_any_sync(0xffffffffu, e);
       const bool first = lane < P && (peers & ((1u << lane) - 1u)) == 0u;
-      int d = 0;
-      for (int j = 0; j < kMaxPairs; ++j) {
-        const int ej = __shfl_sync(0xffffffffu, e, j);
-        const int fj = __shfl_sync(0xffffffffu, (int)first, j);
-        if (fj && ej < e) ++d;
-      }
-      if (lane < P) sm.pair_d[lane] = d;
-      if (first) {
-        sm.list[d] = e;
-        sm.dmask[d] = peers;
-      }
-      const unsigned fm = __ballot_sync(0xffffffffu, first);
-      if (lane == 0) *sm.n_distinct = __popc(fm);
-      // a token's slots in ascending expert order (the order of the weighted sum)
-      if (lane < T) {
-        int ex[8], od[8];
-        for (int s = 0; s < k; ++s) { ex[s] = sm.sel_e[lane * k + s]; od[s] = s; }
-        for (int a = 1; a < k; ++a) {
-          const int o = od[a], eo = ex[a];
-          int b = a - 1;
-          while (b >= 0 && ex[b] > eo) { od[b + 1] = od[b]; ex[b + 1] = ex[b]; --b; }
-          od[b + 1] = o;
-          ex[b + 1] = eo;
+      if (lane < P) {
+        int d = 0, tot = 0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+          const unsigned m = bitmap[w];
+          tot += __popc(m);
+          if (w < (e >> 5)) d += __popc(m);
+          else if (w == (e >> 5)) d += __popc(m & ((1u << (e & 31)) - 1u));
         }
-        for (int s = 0; s < k; ++s) sm.ord[lane * k + s] = lane * k + od[s];
+        pair_d[lane] = d;
+        if (first) {
+          list[d] = e;
+          dmask[d] = peers;
+        }
+        if (lane == 0) *n_distinct = tot;
+        // a token's slots in ascending expert order (the order of the weighted sum)
+        const int t = lane / k;
+        int r = 0;
+        for (int j = 0; j < k; ++j) r += sel_e[t * k + j] < e ? 1 : 0;
+        ord[t * k + r] = lane;
       }
     }
     __syncthreads();
-    const int D = *sm.n_distinct;
+    const int D = *n_distinct;
+    if (tr) tr[4] = global_timer_ns();
 
-    // ---- gate/up + SiLU*up: row pairs [u0, u1) of this CTA, one per warp at a time
+    // ---- gate/up + SiLU*up: row pairs [u0, u1) of this CTA; a warp stages up to `slots` pairs at a time
     {
       const long long U = (long long)D * F;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
       const bool live = lane < QH;
-      const size_t row_bytes = (size_t)nslice * KNJ_Q4K_BYTES;
-      Quarter g0, up0, g1, up1;
-      auto fetch = [&](int u, Quarter &wg, Quarter &wu) {
-        const int d = u / F, n = u - d * F;
-        const size_t row = ((size_t)sm.list[d] * F + n) * row_bytes;
-        if (live) {
-          load_quarter(L.Wg + row, lane, wg);
-          load_quarter(L.Wu + row, lane, wu);
-        }
-      };
-      int u = u0 + warp;
-      if (u < u1) fetch(u, g0, up0);
-      for (; u < u1; u += kWarps) {
-        if (u + kWarps < u1) fetch(u + kWarps, g1, up1);
-        const int d = u / F, n = u - d * F;
-        float ga0 = 0.f, gb0 = 0.f, ga1 = 0.f, gb1 = 0.f, ua0 = 0.f, ub0 = 0.f, ua1 = 0.f, ub1 = 0.f;
-        if (live) {
-          quarter_scales(g0.hdr, lane & 3, ga0, gb0, ga1, gb1);
-          quarter_scales(up0.hdr, lane & 3, ua0, ub0, ua1, ub1);
-        }
-        unsigned todo = sm.dmask[d];
-        while (todo) {
-          const int pr = __ffs(todo) - 1;
-          todo &= todo - 1u;
-          const int t = pr / k;
-          float vg = 0.f, vu = 0.f;
-          if (live) {
-            float A0, A1, B0, B1;
-            quarter_dot2(g0, up0, reinterpret_cast<const float4 *>(sm.xs + (size_t)t * H) + lane, QH, A0, A1, B0, B1);
-            const float x0 = sm.xsum[t * (H / 32) + 2 * lane], x1 = sm.xsum[t * (H / 32) + 2 * lane + 1];
-            vg = (ga0 * A0 + ga1 * A1) - (gb0 * x0 + gb1 * x1);
-            vu = (ua0 * B0 + ua1 * B1) - (ub0 * x0 + ub1 * x1);
+      const int row_bytes = nslice * KNJ_Q4K_BYTES, pair_bytes = 2 * row_bytes, chunks = row_bytes / 16;
+      const int S = p.slots;
+      uint8_t *wbuf = wstage + (size_t)warp * S * pair_bytes;
+      for (int ub = u0 + warp; ub < u1; ub += kWarps * S) {
+#pragma unroll
+        for (int s = 0; s < 3; ++s) {
+          const int u = ub + s * kWarps;
+          if (s < S && u < u1) {
+            const int d = u / F, n = u - d * F;
+            const size_t row = ((size_t)list[d] * F + n) * row_bytes;
+            uint8_t *dst = wbuf + s * pair_bytes;
+            for (int ch = lane; ch < chunks; ch += 32) {
+              cp_async16(dst + 16 * ch, L.Wg + row + 16 * ch);
+              cp_async16(dst + row_bytes + 16 * ch, L.Wu + row + 16 * ch);
+            }
           }
-          vg = warp_sum(vg);
-          vu = warp_sum(vu);
-          if (lane == 0) p.act[(size_t)pr * F + n] = (vg / (1.0f + expf(-vg))) * vu;
+          cp_async_commit();
         }
-        g0 = g1;
-        up0 = up1;
+        if (tr) tr[11] = global_timer_ns();
+        for (int s = 0; s < 3; ++s) {
+          const int u = ub + s * kWarps;
+          if (s == 0) cp_async_wait<2>();
+          else if (s == 1) cp_async_wait<1>();
+          else cp_async_wait<0>();
+          __syncwarp();
+          if (tr) tr[12 + s] = global_timer_ns();
+          if (s < S && u < u1) {
+            const int d = u / F, n = u - d * F;
+            const uint8_t *slot = wbuf + s * pair_bytes;
+            Quarter wg, wu;
+            float ga0 = 0.f, gb0 = 0.f, ga1 = 0.f, gb1 = 0.f, ua0 = 0.f, ub0 = 0.f, ua1 = 0.f, ub1 = 0.f;
+            if (live) {
+              const uint8_t *sb = slot + (lane >> 2) * KNJ_Q4K_BYTES;
+              wg.hdr = *reinterpret_cast<const uint4 *>(sb);
+              wg.q0 = *reinterpret_cast<const uint4 *>(sb + KNJ_Q4K_OFF_QS + 32 * (lane & 3));
+              wg.q1 = *reinterpret_cast<const uint4 *>(sb + KNJ_Q4K_OFF_QS + 32 * (lane & 3) + 16);
+              wu.hdr = *reinterpret_cast<const uint4 *>(sb + row_bytes);
+              wu.q0 = *reinterpret_cast<const uint4 *>(sb + row_bytes + KNJ_Q4K_OFF_QS + 32 * (lane & 3));
+              wu.q1 = *reinterpret_cast<const uint4 *>(sb + row_bytes + KNJ_Q4K_OFF_QS + 32 * (lane & 3) + 16);
+              quarter_scales(wg.hdr, lane & 3, ga0, gb0, ga1, gb1);
+              quarter_scales(wu.hdr, lane & 3, ua0, ub0, ua1, ub1);
+            }
+            unsigned todo = dmask[d];
+            while (todo) {
+              const int pr = __ffs(todo) - 1;
+              todo &= todo - 1u;
+              const int t = (pr >= k) + (pr >= 2 * k) + (pr >= 3 * k);  // pr / k for at most four tokens
+              float vg = 0.f, vu = 0.f;
+              if (live) {
+                float A0, A1, B0, B1;
+                quarter_dot2(wg, wu, reinterpret_cast<const float4 *>(xs + (size_t)t * H) + lane, QH, A0, A1, B0, B1);
+                const float x0 = xsum[t * (H / 32) + 2 * lane], x1 = xsum[t * (H / 32) + 2 * lane + 1];
+                vg = (ga0 * A0 + ga1 * A1) - (gb0 * x0 + gb1 * x1);
+                vu = (ua0 * B0 + ua1 * B1) - (ub0 * x0 + ub1 * x1);
+              }
+              vg = warp_sum(vg);
+              vu = warp_sum(vu);
+              if (lane == 0) p.act[(size_t)pr * F + n] = (vg / (1.0f + expf(-vg))) * vu;
+            }
+          }
+        }
+        if (tr) tr[15] = global_timer_ns();
+        __syncwarp();  // the slots are free again
       }
     }
+    if (tr) tr[5] = global_timer_ns();
+    arrivals += G;
+    grid_arrive(p.sync);
 
     // ---- the down rows this warp will need are known already: fetch them before waiting for the activations
     const int n_lo = (int)((long long)H * c / G), n_hi = (int)((long long)H * (c + 1) / G);
-    const int tasks = D * QF;              // (distinct expert, quarter) pairs of one output column
-    constexpr int kRounds = 3;             // rounds of 32 tasks fetched ahead (8 experts x 12 quarters); later rounds load in place
+    const int tasks = D * QF;  // (distinct expert, quarter) pairs of one output column
     const size_t drow_bytes = (size_t)(F / 256) * KNJ_Q4K_BYTES;
-    const bool fast = (n_hi - n_lo) <= kWarps;
-    Quarter dq[kRounds];
     const int my_col = n_lo + warp;
-    if (fast && my_col < n_hi) {
-#pragma unroll
-      for (int r = 0; r < kRounds; ++r) {
-        const int j = lane + 32 * r;
-        if (j < tasks) {
-          const int d = j / QF, q = j - d * QF;
-          load_quarter(L.Wd + ((size_t)sm.list[d] * H + my_col) * drow_bytes, q, dq[r]);
-        }
-      }
+    const bool ahead = my_col < n_hi;
+    Quarter dq0, dq1, dq2;  // tasks lane, lane + 32, lane + 64 of the warp's first column
+    auto down_row = [&](int j, int n) {
+      const int d = j / QF;
+      return L.Wd + ((size_t)list[d] * H + n) * drow_bytes;
+    };
+    if (ahead) {
+      if (lane < tasks) load_quarter(down_row(lane, my_col), lane % QF, dq0);
+      if (lane + 32 < tasks) load_quarter(down_row(lane + 32, my_col), (lane + 32) % QF, dq1);
+      if (lane + 64 < tasks) load_quarter(down_row(lane + 64, my_col), (lane + 64) % QF, dq2);
     }
 
-    arrivals += G;
-    if (!grid_barrier(p.sync, arrivals)) return;
+    if (tr) tr[6] = global_timer_ns();
+    if (!grid_wait(p.sync, arrivals)) return;
+    if (tr) tr[7] = global_timer_ns();
+    if (l + 1 < p.n_layers) prefetch_router(p.layers[l + 1]);
 
     // ---- activations of all pairs, transposed, and their 32-element sums
-    for (int i = threadIdx.x; i < P * F; i += kThreads) {
-      const int pr = i / F, kx = i - pr * F;
-      sm.av[(size_t)pr * F + tpos(kx, QF)] = __ldcg(p.act + i);
+    {
+      const int agroups = P * (F / 4);
+      for (int g0 = 0; g0 < agroups; g0 += kThreads) {
+        const int g = g0 + threadIdx.x;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        int pr = 0, k4 = 0;
+        if (g < agroups) {
+          pr = g / (F / 4);
+          k4 = g - pr * (F / 4);
+          const uint4 r0 = ldcg16(p.act + (size_t)pr * F + 4 * k4);
+          v = make_float4(__uint_as_float(r0.x), __uint_as_float(r0.y), __uint_as_float(r0.z), __uint_as_float(r0.w));
+          *reinterpret_cast<float4 *>(av + (size_t)pr * F + tpos(4 * k4, QF)) = v;
+        }
+        float s = (v.x + v.y) + (v.z + v.w);
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (g < agroups && (lane & 7) == 0) asum[pr * (F / 32) + (k4 >> 3)] = s;
+      }
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < P * F / 32; i += kThreads) {
-      const int pr = i / (F / 32), b = i - pr * (F / 32);
-      float s = 0.f;
-      for (int j = 0; j < 32; ++j) s += sm.av[(size_t)pr * F + tpos(32 * b + j, QF)];
-      sm.asum[i] = s;
-    }
-    __syncthreads();
+    if (tr) tr[8] = global_timer_ns();
 
     // ---- down + ordered combine + residual: one output column per warp
-    float *yp = sm.ypart + (size_t)warp * P * (QF + 1);
-    for (int n = n_lo + warp; n < n_hi; n += kWarps) {
+    float *yp = ypart + (size_t)warp * P * (QF + 1);
+    for (int n = my_col; n < n_hi; n += kWarps) {
       for (int r = 0; r * 32 < tasks; ++r) {
         const int j = lane + 32 * r;
         if (j < tasks) {
           const int d = j / QF, q = j - d * QF;
           Quarter w;
-          if (fast && n == my_col && r < kRounds) {
-            // static indexing keeps dq in registers
-            w = dq[0];
-#pragma unroll
-            for (int rr = 1; rr < kRounds; ++rr)
-              if (rr == r) w = dq[rr];
-          } else {
-            load_quarter(L.Wd + ((size_t)sm.list[d] * H + n) * drow_bytes, q, w);
-          }
+          if (n == my_col && r < 3) w = r == 0 ? dq0 : (r == 1 ? dq1 : dq2);
+          else load_quarter(down_row(j, n), q, w);
           float a0, b0, a1, b1;
           quarter_scales(w.hdr, q & 3, a0, b0, a1, b1);
-          unsigned todo = sm.dmask[d];
+          unsigned todo = dmask[d];
           while (todo) {
             const int pr = __ffs(todo) - 1;
             todo &= todo - 1u;
             float S0, S1;
-            quarter_dot(w, reinterpret_cast<const float4 *>(sm.av + (size_t)pr * F) + q, QF, S0, S1);
-            const float x0 = sm.asum[pr * (F / 32) + 2 * q], x1 = sm.asum[pr * (F / 32) + 2 * q + 1];
+            quarter_dot(w, reinterpret_cast<const float4 *>(av + (size_t)pr * F) + q, QF, S0, S1);
+            const float x0 = asum[pr * (F / 32) + 2 * q], x1 = asum[pr * (F / 32) + 2 * q + 1];
             yp[pr * (QF + 1) + q] = (a0 * S0 + a1 * S1) - (b0 * x0 + b1 * x1);
           }
         }
@@ -498,8 +620,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       if (lane < T) {
         float acc = 0.f;
         for (int s = 0; s < k; ++s) {
-          const int pr = sm.ord[lane * k + s];
-          acc = __fadd_rn(acc, __fmul_rn(sm.sel_w[pr], yp[pr * (QF + 1) + QF]));
+          const int pr = ord[lane * k + s];
+          acc = __fadd_rn(acc, __fmul_rn(sel_w[pr], yp[pr * (QF + 1) + QF]));
         }
         if (L.residual) acc = __fadd_rn(ldcg_as_f32(L.x, L.x_dtype, (int64_t)lane * L.ldx + n), acc);
         store_from_f32(L.out, L.out_dtype, (int64_t)lane * L.ldo + n, acc);
@@ -507,9 +629,12 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       __syncwarp();
     }
 
+    if (tr) tr[9] = global_timer_ns();
     arrivals += G;
     if (l + 1 < p.n_layers && !grid_barrier(p.sync, arrivals)) return;
+    if (tr) tr[10] = global_timer_ns();
   }
+  cp_async_wait<0>();
 }
 
 }  // namespace
@@ -567,9 +692,12 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   }
   knj_moe_stack *st = new knj_moe_stack();
   KNJ_CUDA(cudaGetDevice(&st->device));
-  st->smem = smem_floats(T, H, F, k) * sizeof(float);
   cudaDeviceProp prop;
   KNJ_CUDA(cudaGetDeviceProperties(&prop, st->device));
+  st->p.slots = 1;
+  for (int sl = 3; sl >= 1; --sl)
+    if (make_plan(T, H, F, k, sl).total <= (size_t)prop.sharedMemPerBlockOptin) { st->p.slots = sl; break; }
+  st->smem = make_plan(T, H, F, k, st->p.slots).total;
   if (!prop.cooperativeLaunch || st->smem > (size_t)prop.sharedMemPerBlockOptin) {
     set_error("knj_moe_stack_create: the device lacks cooperative launch or %zu bytes of shared memory per block", st->smem);
     delete st;
@@ -615,6 +743,13 @@ int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s) {
   KNJ_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(moe_stack_kernel), dim3(st->grid), dim3(kThreads), args,
                                        st->smem, as_stream(s)));
   return launch_status("moe_stack_kernel");
+}
+
+/* debug hook: 16 global-timer stamps of CTA 0 (stages of the second layer); null switches it off */
+int knj_moe_stack_trace(knj_moe_stack *st, unsigned long long *buf16) {
+  KNJ_REQUIRE(st, "knj_moe_stack_trace: null stack");
+  st->p.trace = buf16;
+  return KNJ_OK;
 }
 
 int knj_moe_stack_status(knj_moe_stack *st, knj_stream_t s) {
