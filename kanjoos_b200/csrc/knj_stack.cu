@@ -279,13 +279,18 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
   };
   prefetch_router(p.layers[0]);
 
-  __shared__ StackLayer s_layer;  // the layer's description: read where needed instead of held in registers
+  // the layers' descriptions: read from shared memory where needed instead of held in registers; the next
+  // layer's arrives while the current one computes
+  __shared__ StackLayer s_layer[2];
   static_assert(sizeof(StackLayer) % 4 == 0, "copied by words");
-  for (int l = 0; l < p.n_layers; ++l) {
+  auto stage_layer = [&](int l) {
     if (threadIdx.x < sizeof(StackLayer) / 4)
-      reinterpret_cast<uint32_t *>(&s_layer)[threadIdx.x] = reinterpret_cast<const uint32_t *>(p.layers + l)[threadIdx.x];
-    __syncthreads();
-    const StackLayer &L = s_layer;
+      reinterpret_cast<uint32_t *>(&s_layer[l & 1])[threadIdx.x] = reinterpret_cast<const uint32_t *>(p.layers + l)[threadIdx.x];
+  };
+  stage_layer(0);
+  __syncthreads();
+  for (int l = 0; l < p.n_layers; ++l) {
+    const StackLayer &L = s_layer[l & 1];
     unsigned long long *tr = (p.trace && c == 0 && threadIdx.x == 0 && l == trace_layer) ? p.trace : nullptr;
     if (tr) tr[0] = global_timer_ns();
     const bool xf32 = L.x_dtype == KNJ_DT_F32;
@@ -311,6 +316,12 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
         }
       }
     }
+    uint4 xr[8];  // warps < T: a bf16 row is fetched whole before it is used; f32 rows (first layer at most) load in place
+    if (warp < T && !xf32) {
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl)
+        if (sl < nslice) xr[sl] = ldcg16(static_cast<const unsigned short *>(L.x) + (int64_t)warp * L.ldx + 256 * sl + 8 * lane);
+    }
     cp_async_wait<0>();
     __syncthreads();  // the router row and the norm weights are in shared memory
 
@@ -319,10 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     if (warp < T) {
       const int t = warp;
       const bool mine = c < E;
-      uint4 xr[8];  // a bf16 row is fetched whole before it is used; f32 rows (first layer at most) load in place
-#pragma unroll
-      for (int sl = 0; sl < 8; ++sl)
-        if (sl < nslice && !xf32) xr[sl] = ldcg16(static_cast<const unsigned short *>(L.x) + (int64_t)t * L.ldx + 256 * sl + 8 * lane);
+
       float d0 = 0.f, d1 = 0.f, s0 = 0.f, s1 = 0.f;
 #pragma unroll
       for (int sl = 0; sl < 8; ++sl) {
@@ -421,7 +429,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     if (warp < T) {
       int se[8];
       float sw[8];
-      warp_topk(p.logits + (size_t)warp * E, E, k, lane, se, sw);
+      if (E <= 128) warp_topk<4>(p.logits + (size_t)warp * E, E, k, lane, se, sw);
+      else warp_topk(p.logits + (size_t)warp * E, E, k, lane, se, sw);
       if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < 8; ++s) {
@@ -561,27 +570,41 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     if (tr) tr[6] = global_timer_ns();
     if (!grid_wait(p.sync, arrivals)) return;
     if (tr) tr[7] = global_timer_ns();
-    if (l + 1 < p.n_layers) prefetch_router(p.layers[l + 1]);
+    if (l + 1 < p.n_layers) {
+      prefetch_router(p.layers[l + 1]);
+      stage_layer(l + 1);  // published by the CTA-wide synchronisations below
+    }
 
     // ---- activations of all pairs, transposed, and their 32-element sums
     {
       const int agroups = P * (F / 4);
-      for (int g0 = 0; g0 < agroups; g0 += kThreads) {
-        const int g = g0 + threadIdx.x;
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        int pr = 0, k4 = 0;
-        if (g < agroups) {
-          pr = g / (F / 4);
-          k4 = g - pr * (F / 4);
-          const uint4 r0 = ldcg16(p.act + (size_t)pr * F + 4 * k4);
-          v = make_float4(__uint_as_float(r0.x), __uint_as_float(r0.y), __uint_as_float(r0.z), __uint_as_float(r0.w));
-          *reinterpret_cast<float4 *>(av + (size_t)pr * F + tpos(4 * k4, QF)) = v;
+      constexpr int kAhead = 3;  // loads in flight per thread
+      for (int g0 = 0; g0 < agroups; g0 += kThreads * kAhead) {
+        uint4 r0[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+          const int g = g0 + a * kThreads + threadIdx.x;
+          r0[a] = make_uint4(0u, 0u, 0u, 0u);
+          if (g < agroups) r0[a] = ldcg16(p.act + (size_t)4 * g);  // pair rows are contiguous: group g is floats 4g..4g+3
         }
-        float s = (v.x + v.y) + (v.z + v.w);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        if (g < agroups && (lane & 7) == 0) asum[pr * (F / 32) + (k4 >> 3)] = s;
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+          const int g = g0 + a * kThreads + threadIdx.x;
+          if (g0 + a * kThreads < agroups) {  // whole warps take part in the shuffles
+            const float4 v = make_float4(__uint_as_float(r0[a].x), __uint_as_float(r0[a].y), __uint_as_float(r0[a].z), __uint_as_float(r0[a].w));
+            int pr = 0, k4 = 0;
+            if (g < agroups) {
+              pr = g / (F / 4);
+              k4 = g - pr * (F / 4);
+              *reinterpret_cast<float4 *>(av + (size_t)pr * F + tpos(4 * k4, QF)) = v;
+            }
+            float s = (v.x + v.y) + (v.z + v.w);
+            s += __shfl_xor_sync(0xffffffffu, s, 1);
+            s += __shfl_xor_sync(0xffffffffu, s, 2);
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            if (g < agroups && (lane & 7) == 0) asum[pr * (F / 32) + (k4 >> 3)] = s;
+          }
+        }
       }
     }
     __syncthreads();
