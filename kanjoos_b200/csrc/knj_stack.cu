@@ -40,6 +40,7 @@ constexpr int kMaxT = 4;                 // tokens per step
 constexpr int kMaxPairs = kMaxT * 8;     // <= one warp's lanes
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
+constexpr float kUnscale = 0x1p85f;  // undoes the staging scale of the vectors, see word_fma
 constexpr long long kSpinLimit = 2000000000ll;  // clock cycles, about a second
 
 struct StackLayer {
@@ -138,33 +139,38 @@ __device__ __forceinline__ void quarter_scales(const uint4 &hdr, int G, float &a
     sc = (hi & 0x0f0fu) | ((((hdr.y >> sh) & 0xffffu) >> 2) & 0x3030u);
     mn = ((hi >> 4) & 0x0f0fu) | ((((hdr.z >> sh) & 0xffffu) >> 2) & 0x3030u);
   }
-  a0 = d * (float)(sc & 0xffu);
-  a1 = d * (float)(sc >> 8);
+  a0 = d * (float)(sc & 0xffu) * kUnscale;
+  a1 = d * (float)(sc >> 8) * kUnscale;
   b0 = dmin * (float)(mn & 0xffu);
   b1 = dmin * (float)(mn >> 8);
 }
 
-// byte j of v as an exact float: 0x4B0000vv is 8388608 + vv
-template <int J>
-__device__ __forceinline__ float byte_f32(unsigned v) {
-  return __uint_as_float(__byte_perm(v, 0x4B000000u, 0x7540u + J)) - 8388608.0f;
+// A code nibble enters the multiply-add WITHOUT a conversion: masked in place at bit p it is the bit pattern of
+// the denormal float q * 2^(p-149), which the FMA unit multiplies exactly. The vector element that meets it was
+// scaled by 2^(64-p) when it was staged (every element always meets the same nibble position), so each product
+// is q * x * 2^-85 and the sums are ordinary normal floats; the factor 2^85 is folded into the block scales.
+// Nibbles at bits 20..31 are shifted down by 12 first so that the pattern stays below the exponent field.
+// 2^(64-p) for the four elements of a staged float4: low nibbles sit at p = 0, 8, 16, 12 (byte 3 after the
+// shift), high nibbles at p = 4, 12, 8, 16 (bytes 2 and 3 after the shift)
+__device__ __forceinline__ float4 stage_scale(const float4 &v, bool high) {
+  return high ? make_float4(v.x * 0x1p60f, v.y * 0x1p52f, v.z * 0x1p56f, v.w * 0x1p48f)
+              : make_float4(v.x * 0x1p64f, v.y * 0x1p56f, v.z * 0x1p48f, v.w * 0x1p52f);
 }
-
+__device__ __forceinline__ void word_fma(unsigned w, const float4 &xl, const float4 &xh, float &s0, float &s1) {
+  const unsigned v = w >> 12;
+  s0 = fmaf(__uint_as_float(w & 0x0000000fu), xl.x, s0);
+  s0 = fmaf(__uint_as_float(w & 0x00000f00u), xl.y, s0);
+  s0 = fmaf(__uint_as_float(w & 0x000f0000u), xl.z, s0);
+  s0 = fmaf(__uint_as_float(v & 0x0000f000u), xl.w, s0);
+  s1 = fmaf(__uint_as_float(w & 0x000000f0u), xh.x, s1);
+  s1 = fmaf(__uint_as_float(w & 0x0000f000u), xh.y, s1);
+  s1 = fmaf(__uint_as_float(v & 0x00000f00u), xh.z, s1);
+  s1 = fmaf(__uint_as_float(v & 0x000f0000u), xh.w, s1);
+}
 // sum over the quarter's 64 weights of q * x: S0 for the low nibbles (sub-block 2G), S1 for the high ones.
 // xq points at this quarter's first float4 of a transposed vector, consecutive float4s are `stride4` apart.
 // The loops below are deliberately NOT unrolled (two code words per step, the rest of the words rotate down):
 // the straight-line form of 64 or 128 weights needs more registers than a 512-thread CTA has and spills.
-__device__ __forceinline__ void word_fma(unsigned w, const float4 &xl, const float4 &xh, float &s0, float &s1) {
-  const unsigned lo = w & 0x0f0f0f0fu, hi = (w >> 4) & 0x0f0f0f0fu;
-  s0 = fmaf(byte_f32<0>(lo), xl.x, s0);
-  s0 = fmaf(byte_f32<1>(lo), xl.y, s0);
-  s0 = fmaf(byte_f32<2>(lo), xl.z, s0);
-  s0 = fmaf(byte_f32<3>(lo), xl.w, s0);
-  s1 = fmaf(byte_f32<0>(hi), xh.x, s1);
-  s1 = fmaf(byte_f32<1>(hi), xh.y, s1);
-  s1 = fmaf(byte_f32<2>(hi), xh.z, s1);
-  s1 = fmaf(byte_f32<3>(hi), xh.w, s1);
-}
 __device__ __forceinline__ void quarter_dot(const Quarter &w, const float4 *xq, int stride4, float &S0, float &S1) {
   unsigned a0 = w.q0.x, a1 = w.q0.y, a2 = w.q0.z, a3 = w.q0.w, a4 = w.q1.x, a5 = w.q1.y, a6 = w.q1.z, a7 = w.q1.w;
   float s0 = 0.f, s1 = 0.f, t0 = 0.f, t1 = 0.f;
@@ -412,7 +418,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
             v.z = __fmul_rn(__fmul_rn(v.z, sc), __uint_as_float(nw.y << 16));
             v.w = __fmul_rn(__fmul_rn(v.w, sc), __uint_as_float(nw.y & 0xffff0000u));
           }
-          *reinterpret_cast<float4 *>(xs + (size_t)t * H + tpos(4 * k4, QH)) = v;
+          *reinterpret_cast<float4 *>(xs + (size_t)t * H + tpos(4 * k4, QH)) = stage_scale(v, (k4 & 8) != 0);
         }
         float s = (v.x + v.y) + (v.z + v.w);
         s += __shfl_xor_sync(0xffffffffu, s, 1);
@@ -596,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
             if (g < agroups) {
               pr = g / (F / 4);
               k4 = g - pr * (F / 4);
-              *reinterpret_cast<float4 *>(av + (size_t)pr * F + tpos(4 * k4, QF)) = v;
+              *reinterpret_cast<float4 *>(av + (size_t)pr * F + tpos(4 * k4, QF)) = stage_scale(v, (k4 & 8) != 0);
             }
             float s = (v.x + v.y) + (v.z + v.w);
             s += __shfl_xor_sync(0xffffffffu, s, 1);
