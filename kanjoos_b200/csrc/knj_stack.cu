@@ -105,6 +105,10 @@ __device__ __forceinline__ bool grid_barrier(unsigned *sync, unsigned target) {
   return grid_wait(sync, target);
 }
 
+// n / dv for the small operands of this kernel (n * dv < 2^32) as one multiply: magic = ceil(2^32 / dv), dv >= 2
+__device__ __forceinline__ unsigned div_magic(unsigned dv) { return 0xffffffffu / dv + 1u; }
+__device__ __forceinline__ int fast_div(int n, unsigned magic) { return (int)__umulhi((unsigned)n, magic); }
+
 __device__ __forceinline__ uint4 ldcg16(const void *p) { return __ldcg(reinterpret_cast<const uint4 *>(p)); }
 __device__ __forceinline__ uint4 ldnc16(const void *p) { return __ldg(reinterpret_cast<const uint4 *>(p)); }
 
@@ -269,6 +273,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
   float *av = reinterpret_cast<float *>(smem_b + pl.av);
   uint8_t *wstage = smem_b + pl.wstage;
   unsigned arrivals = 0;
+  const unsigned mF = div_magic(F), mQF = div_magic(QF), mF4 = div_magic(F / 4), mH4 = div_magic(H / 4);
   const int trace_layer = p.n_layers > 1 ? 1 : 0;
 
   // this CTA's router row and the norm weights of a layer, copied to shared memory ahead of their use
@@ -310,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       const int g = threadIdx.x + kThreads * r;
       xv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (g < groups) {
-        const int t = g / (H / 4), k4 = g - t * (H / 4);
+        const int t = fast_div(g, mH4), k4 = g - t * (H / 4);
         const int64_t at = (int64_t)t * L.ldx + 4 * k4;
         if (xf32) {
           const uint4 r0 = ldcg16(static_cast<const float *>(L.x) + at);
@@ -408,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
         float4 v = xv[r];
         int t = 0, k4 = 0;
         if (g < groups) {
-          t = g / (H / 4);
+          t = fast_div(g, mH4);
           k4 = g - t * (H / 4);
           if (has_norm) {
             const float sc = scale_s[t];
@@ -495,7 +500,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
         for (int s = 0; s < 3; ++s) {
           const int u = ub + s * kWarps;
           if (s < S && u < u1) {
-            const int d = u / F, n = u - d * F;
+            const int d = fast_div(u, mF), n = u - d * F;
             const size_t row = ((size_t)list[d] * F + n) * row_bytes;
             uint8_t *dst = wbuf + s * pair_bytes;
             for (int ch = lane; ch < chunks; ch += 32) {
@@ -514,7 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
           __syncwarp();
           if (tr) tr[12 + s] = global_timer_ns();
           if (s < S && u < u1) {
-            const int d = u / F, n = u - d * F;
+            const int d = fast_div(u, mF), n = u - d * F;
             const uint8_t *slot = wbuf + s * pair_bytes;
             Quarter wg, wu;
             float ga0 = 0.f, gb0 = 0.f, ga1 = 0.f, gb1 = 0.f, ua0 = 0.f, ub0 = 0.f, ua1 = 0.f, ub1 = 0.f;
@@ -564,13 +569,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     const bool ahead = my_col < n_hi;
     Quarter dq0, dq1, dq2;  // tasks lane, lane + 32, lane + 64 of the warp's first column
     auto down_row = [&](int j, int n) {
-      const int d = j / QF;
+      const int d = fast_div(j, mQF);
       return L.Wd + ((size_t)list[d] * H + n) * drow_bytes;
     };
     if (ahead) {
-      if (lane < tasks) load_quarter(down_row(lane, my_col), lane % QF, dq0);
-      if (lane + 32 < tasks) load_quarter(down_row(lane + 32, my_col), (lane + 32) % QF, dq1);
-      if (lane + 64 < tasks) load_quarter(down_row(lane + 64, my_col), (lane + 64) % QF, dq2);
+      if (lane < tasks) load_quarter(down_row(lane, my_col), lane - fast_div(lane, mQF) * QF, dq0);
+      if (lane + 32 < tasks) load_quarter(down_row(lane + 32, my_col), lane + 32 - fast_div(lane + 32, mQF) * QF, dq1);
+      if (lane + 64 < tasks) load_quarter(down_row(lane + 64, my_col), lane + 64 - fast_div(lane + 64, mQF) * QF, dq2);
     }
 
     if (tr) tr[6] = global_timer_ns();
@@ -600,7 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
             const float4 v = make_float4(__uint_as_float(r0[a].x), __uint_as_float(r0[a].y), __uint_as_float(r0[a].z), __uint_as_float(r0[a].w));
             int pr = 0, k4 = 0;
             if (g < agroups) {
-              pr = g / (F / 4);
+              pr = fast_div(g, mF4);
               k4 = g - pr * (F / 4);
               *reinterpret_cast<float4 *>(av + (size_t)pr * F + tpos(4 * k4, QF)) = stage_scale(v, (k4 & 8) != 0);
             }
@@ -622,7 +627,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       for (int r = 0; r * 32 < tasks; ++r) {
         const int j = lane + 32 * r;
         if (j < tasks) {
-          const int d = j / QF, q = j - d * QF;
+          const int d = fast_div(j, mQF), q = j - d * QF;
           Quarter w;
           if (n == my_col && r < 3) w = r == 0 ? dq0 : (r == 1 ? dq1 : dq2);
           else load_quarter(down_row(j, n), q, w);
