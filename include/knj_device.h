@@ -429,8 +429,8 @@ typedef struct knj_moe_stack knj_moe_stack;
 int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_stack **out);
 int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s);
 int knj_moe_stack_status(knj_moe_stack *st, knj_stream_t s);
-/* debug hook: device buffer of 16 u64 that receives global-timer stamps of one CTA's stages; NULL = off */
-int knj_moe_stack_trace(knj_moe_stack *st, unsigned long long *buf16);
+/* debug hook: device buffer of 32 u64 that receives global-timer stamps of one CTA's stages; NULL = off */
+int knj_moe_stack_trace(knj_moe_stack *st, unsigned long long *buf32);
 void knj_moe_stack_destroy(knj_moe_stack *st);
 
 /* ======================================================================== */

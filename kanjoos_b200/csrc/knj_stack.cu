@@ -64,7 +64,7 @@ struct StackParams {
   float *act;          // [T*k][F]
   unsigned int *sync;  // [0] arrivals, [1] error word; both zero before the launch
   int slots;           // gate/up row pairs a warp stages at a time (1..3, by the shared memory left)
-  unsigned long long *trace;  // optional [16]: global-timer stamps of CTA 0's stages in layer 1 (or 0 if alone)
+  unsigned long long *trace;  // optional [32]: global-timer stamps of CTA 0's stages in layer 1 (or 0 if alone)
 };
 
 __device__ __forceinline__ unsigned ld_acquire(const unsigned *p) {
@@ -307,34 +307,37 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     const bool xf32 = L.x_dtype == KNJ_DT_F32;
     const bool has_norm = L.norm_w != nullptr;
 
-    // ---- every thread fetches its share of the rows for the transposed copy (4 elements per group)
-    const int groups = T * (H / 4);
-    float4 xv[kMaxT];
-#pragma unroll
-    for (int r = 0; r < kMaxT; ++r) {
-      const int g = threadIdx.x + kThreads * r;
-      xv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (g < groups) {
-        const int t = fast_div(g, mH4), k4 = g - t * (H / 4);
-        const int64_t at = (int64_t)t * L.ldx + 4 * k4;
-        if (xf32) {
-          const uint4 r0 = ldcg16(static_cast<const float *>(L.x) + at);
-          xv[r] = make_float4(__uint_as_float(r0.x), __uint_as_float(r0.y), __uint_as_float(r0.z), __uint_as_float(r0.w));
-        } else {
-          const uint2 r0 = __ldcg(reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(L.x) + at));
-          xv[r] = make_float4(__uint_as_float(r0.x << 16), __uint_as_float(r0.x & 0xffff0000u), __uint_as_float(r0.y << 16),
-                              __uint_as_float(r0.y & 0xffff0000u));
-        }
-      }
-    }
+    // ---- loads first, conversions later: the rows come from L2 (another SM wrote them) and a use right after
+    // the load would serialise the round trips
     uint4 xr[8];  // warps < T: a bf16 row is fetched whole before it is used; f32 rows (first layer at most) load in place
     if (warp < T && !xf32) {
 #pragma unroll
       for (int sl = 0; sl < 8; ++sl)
         if (sl < nslice) xr[sl] = ldcg16(static_cast<const unsigned short *>(L.x) + (int64_t)warp * L.ldx + 256 * sl + 8 * lane);
     }
+    // every thread's share of the rows for the transposed copy (4 elements per group), still as loaded
+    const int groups = T * (H / 4);
+    uint4 xraw[kMaxT];
+#pragma unroll
+    for (int r = 0; r < kMaxT; ++r) {
+      const int g = threadIdx.x + kThreads * r;
+      xraw[r] = make_uint4(0u, 0u, 0u, 0u);
+      if (g < groups) {
+        const int t = fast_div(g, mH4), k4 = g - t * (H / 4);
+        const int64_t at = (int64_t)t * L.ldx + 4 * k4;
+        if (xf32) {
+          xraw[r] = ldcg16(static_cast<const float *>(L.x) + at);
+        } else {
+          const uint2 r0 = __ldcg(reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(L.x) + at));
+          xraw[r].x = r0.x;
+          xraw[r].y = r0.y;
+        }
+      }
+    }
+    if (tr) tr[16] = global_timer_ns();
     cp_async_wait<0>();
     __syncthreads();  // the router row and the norm weights are in shared memory
+    if (tr) tr[17] = global_timer_ns();
 
     // ---- row statistics of every token (each CTA for itself) and, in CTA e < E, expert e's logits.
     // Operation order of moe_front_kernel: lane owns elements 256*sl + 8*lane + j, even/odd chains, warp_sum.
@@ -390,6 +393,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
           }
         }
       }
+      if (tr) tr[18] = global_timer_ns();
       const float dot = warp_sum(d0 + d1), ss = warp_sum(s0 + s1);
       if (lane == 0) {
         const float scale = has_norm ? 1.0f / sqrtf(ss / (float)H + L.eps) : 1.0f;
@@ -410,7 +414,10 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     for (int r = 0; r < kMaxT; ++r) {
       const int g = threadIdx.x + kThreads * r;
       if (r * kThreads < groups) {  // whole warps take part in the shuffles
-        float4 v = xv[r];
+        float4 v;
+        if (xf32) v = make_float4(__uint_as_float(xraw[r].x), __uint_as_float(xraw[r].y), __uint_as_float(xraw[r].z), __uint_as_float(xraw[r].w));
+        else v = make_float4(__uint_as_float(xraw[r].x << 16), __uint_as_float(xraw[r].x & 0xffff0000u), __uint_as_float(xraw[r].y << 16),
+                             __uint_as_float(xraw[r].y & 0xffff0000u));
         int t = 0, k4 = 0;
         if (g < groups) {
           t = fast_div(g, mH4);
@@ -454,7 +461,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       }
     }
     if (warp == kWarps - 1 && lane < 8) bitmap[lane] = 0u;
+    if (tr) tr[19] = global_timer_ns();
     __syncthreads();
+    if (tr) tr[20] = global_timer_ns();
     if (warp == 0) {
       const int e = lane < P ? sel_e[lane] : -1 - lane;  // distinct dummies so that they match nobody
       if (lane < P) atomicOr(&bitmap[e >> 5], 1u << (e & 31));
@@ -483,6 +492,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
         ord[t * k + r] = lane;
       }
     }
+    if (tr) tr[21] = global_timer_ns();
     __syncthreads();
     const int D = *n_distinct;
     if (tr) tr[4] = global_timer_ns();
@@ -779,10 +789,10 @@ int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s) {
   return launch_status("moe_stack_kernel");
 }
 
-/* debug hook: 16 global-timer stamps of CTA 0 (stages of the second layer); null switches it off */
-int knj_moe_stack_trace(knj_moe_stack *st, unsigned long long *buf16) {
+/* debug hook: 32 global-timer stamps of CTA 0 (stages of the second layer); null switches it off */
+int knj_moe_stack_trace(knj_moe_stack *st, unsigned long long *buf32) {
   KNJ_REQUIRE(st, "knj_moe_stack_trace: null stack");
-  st->p.trace = buf16;
+  st->p.trace = buf32;
   return KNJ_OK;
 }
 
