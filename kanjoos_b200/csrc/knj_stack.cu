@@ -216,6 +216,37 @@ __device__ __forceinline__ void quarter_dot2(const Quarter &wa, const Quarter &w
   B1 = sb1 + tb1;
 }
 
+// four rows (two gate/up pairs) over one pass of the vector: the shared-memory reads of the vector are the
+// larger part of a row pair's traffic, so sharing them between pairs pays
+__device__ __forceinline__ void quarter_dot4(const Quarter &wa, const Quarter &wb, const Quarter &wc, const Quarter &wd,
+                                             const float4 *xq, int stride4, float (&S)[8]) {
+  unsigned a0 = wa.q0.x, a1 = wa.q0.y, a2 = wa.q0.z, a3 = wa.q0.w, a4 = wa.q1.x, a5 = wa.q1.y, a6 = wa.q1.z, a7 = wa.q1.w;
+  unsigned b0 = wb.q0.x, b1 = wb.q0.y, b2 = wb.q0.z, b3 = wb.q0.w, b4 = wb.q1.x, b5 = wb.q1.y, b6 = wb.q1.z, b7 = wb.q1.w;
+  unsigned c0 = wc.q0.x, c1 = wc.q0.y, c2 = wc.q0.z, c3 = wc.q0.w, c4 = wc.q1.x, c5 = wc.q1.y, c6 = wc.q1.z, c7 = wc.q1.w;
+  unsigned d0 = wd.q0.x, d1 = wd.q0.y, d2 = wd.q0.z, d3 = wd.q0.w, d4 = wd.q1.x, d5 = wd.q1.y, d6 = wd.q1.z, d7 = wd.q1.w;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) S[i] = 0.f;
+  const float4 *xl = xq, *xh = xq + 8 * stride4;
+#pragma unroll 1
+  for (int it = 0; it < 4; ++it) {
+    const float4 l0 = xl[0], h0 = xh[0], l1 = xl[stride4], h1 = xh[stride4];
+    word_fma(a0, l0, h0, S[0], S[1]);
+    word_fma(b0, l0, h0, S[2], S[3]);
+    word_fma(c0, l0, h0, S[4], S[5]);
+    word_fma(d0, l0, h0, S[6], S[7]);
+    word_fma(a1, l1, h1, S[0], S[1]);
+    word_fma(b1, l1, h1, S[2], S[3]);
+    word_fma(c1, l1, h1, S[4], S[5]);
+    word_fma(d1, l1, h1, S[6], S[7]);
+    a0 = a2; a1 = a3; a2 = a4; a3 = a5; a4 = a6; a5 = a7;
+    b0 = b2; b1 = b3; b2 = b4; b3 = b5; b4 = b6; b5 = b7;
+    c0 = c2; c1 = c3; c2 = c4; c3 = c5; c4 = c6; c5 = c7;
+    d0 = d2; d1 = d3; d2 = d4; d3 = d5; d4 = d6; d5 = d7;
+    xl += 2 * stride4;
+    xh += 2 * stride4;
+  }
+}
+
 // position of element k of a vector with Q quarters in its transposed shared-memory form:
 // float4 number (i*Q + q) holds elements 64q + 4i .. 64q + 4i + 3
 __device__ __forceinline__ int tpos(int k, int Q) {
@@ -528,6 +559,47 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
           else cp_async_wait<0>();
           __syncwarp();
           if (tr) tr[12 + s] = global_timer_ns();
+          if (T == 1 && s == 0 && S > 1 && u + kWarps < u1) {
+            // one token: slots 0 and 1 go over the vector together
+            cp_async_wait<1>();
+            __syncwarp();
+            const int e0 = fast_div(u, mF), e1 = fast_div(u + kWarps, mF);
+            const int n0 = u - e0 * F, n1 = u + kWarps - e1 * F;
+            const int pr0 = __ffs(dmask[e0]) - 1, pr1 = __ffs(dmask[e1]) - 1;  // the token's slot that chose the expert
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (live) {
+              const uint8_t *sb = wbuf + (lane >> 2) * KNJ_Q4K_BYTES;
+              const int qo = KNJ_Q4K_OFF_QS + 32 * (lane & 3);
+              Quarter w[4];
+#pragma unroll
+              for (int r = 0; r < 4; ++r) {
+                const uint8_t *rp = sb + r * row_bytes;  // gate 0, up 0, gate 1, up 1
+                w[r].hdr = *reinterpret_cast<const uint4 *>(rp);
+                w[r].q0 = *reinterpret_cast<const uint4 *>(rp + qo);
+                w[r].q1 = *reinterpret_cast<const uint4 *>(rp + qo + 16);
+              }
+              float S8[8];
+              quarter_dot4(w[0], w[1], w[2], w[3], reinterpret_cast<const float4 *>(xs) + lane, QH, S8);
+              const float x0 = xsum[2 * lane], x1 = xsum[2 * lane + 1];
+#pragma unroll
+              for (int r = 0; r < 4; ++r) {
+                float a0, b0, a1, b1;
+                quarter_scales(w[r].hdr, lane & 3, a0, b0, a1, b1);
+                v[r] = (a0 * S8[2 * r] + a1 * S8[2 * r + 1]) - (b0 * x0 + b1 * x1);
+              }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+              for (int r = 0; r < 4; ++r) v[r] += __shfl_xor_sync(0xffffffffu, v[r], o);
+            }
+            if (lane == 0) {
+              p.act[(size_t)pr0 * F + n0] = (v[0] / (1.0f + expf(-v[0]))) * v[1];
+              p.act[(size_t)pr1 * F + n1] = (v[2] / (1.0f + expf(-v[2]))) * v[3];
+            }
+            s = 1;  // slot 1 is done too
+            continue;
+          }
           if (s < S && u < u1) {
             const int d = fast_div(u, mF), n = u - d * F;
             const uint8_t *slot = wbuf + s * pair_bytes;
