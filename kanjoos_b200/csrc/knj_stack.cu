@@ -706,6 +706,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     // ---- down + ordered combine + residual: one output column per warp
     float *yp = ypart + (size_t)warp * P * (QF + 1);
     for (int n = my_col; n < n_hi; n += kWarps) {
+      // the residual element comes from L2: asked for now, used after the products
+      float resid = 0.f;
+      if (L.residual && lane < T) resid = ldcg_as_f32(L.x, L.x_dtype, (int64_t)lane * L.ldx + n);
       for (int r = 0; r * 32 < tasks; ++r) {
         const int j = lane + 32 * r;
         if (j < tasks) {
@@ -739,7 +742,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
           const int pr = ord[lane * k + s];
           acc = __fadd_rn(acc, __fmul_rn(sel_w[pr], yp[pr * (QF + 1) + QF]));
         }
-        if (L.residual) acc = __fadd_rn(ldcg_as_f32(L.x, L.x_dtype, (int64_t)lane * L.ldx + n), acc);
+        if (L.residual) acc = __fadd_rn(resid, acc);
         store_from_f32(L.out, L.out_dtype, (int64_t)lane * L.ldo + n, acc);
       }
       __syncwarp();
