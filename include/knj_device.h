@@ -424,7 +424,9 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
  * (f32, <= 1e-5 rel-RMSE vs the CPU path; routing decisions identical to it).
  * create validates, copies the layer table to the device and allocates scratch;
  * the workspace fields of the layer descriptions are not used. status() waits for
- * the stream and reports whether a grid barrier gave up (bounded waits). */
+ * the stream and reports whether a grid barrier gave up (bounded waits). One launch
+ * of a stack may be in flight at a time (its barrier words are per stack), and the
+ * launch needs every SM of the device (cooperative launch, one CTA per SM). */
 typedef struct knj_moe_stack knj_moe_stack;
 int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_stack **out);
 int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s);

@@ -809,10 +809,17 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
     s.x_dtype = a.x_dtype;
     s.out_dtype = a.out_dtype;
   }
+  int device = 0;
+  KNJ_CUDA(cudaGetDevice(&device));
   knj_moe_stack *st = new knj_moe_stack();
-  KNJ_CUDA(cudaGetDevice(&st->device));
+  st->device = device;
   cudaDeviceProp prop;
-  KNJ_CUDA(cudaGetDeviceProperties(&prop, st->device));
+  if (cudaGetDeviceProperties(&prop, st->device) != cudaSuccess) {
+    cudaGetLastError();
+    delete st;
+    set_error("knj_moe_stack_create: the device's properties cannot be read");
+    return KNJ_E_RUNTIME;
+  }
   st->p.slots = 1;
   for (int sl = 3; sl >= 1; --sl)
     if (make_plan(T, H, F, k, sl).total <= (size_t)prop.sharedMemPerBlockOptin) { st->p.slots = sl; break; }
