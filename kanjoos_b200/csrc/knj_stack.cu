@@ -37,7 +37,7 @@ using namespace knj;
 namespace {
 
 constexpr int kMaxT = 4;                 // tokens per step
-constexpr int kMaxPairs = kMaxT * 8;     // <= one warp's lanes
+static_assert(kMaxT * 8 <= 32, "the pairs of a step fit one warp's lanes");
 constexpr int kThreads = 512;
 constexpr int kWarps = kThreads / 32;
 constexpr float kUnscale = 0x1p85f;  // undoes the staging scale of the vectors, see word_fma
