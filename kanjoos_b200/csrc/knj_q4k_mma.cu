@@ -73,6 +73,7 @@ struct ProjParams {
   int tg;         // tiles per CTA (blockDim = 32 * tg * ks)
   int pitch;      // padded bytes per staged row part
   int tp_alloc;   // token slots per staged activation buffer
+  int by_pass;    // 1: the work unit is (expert, tile group, token pass) instead of (expert, tile group)
   int resident;   // 1: whole panel vectors of a pass are staged at once (small batch); 0: one superblock chunk per step
   int64_t idxStride;
   int *status;    // optional: set to 1 when a bounded wait gave up
@@ -149,20 +150,78 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
   // number of active experts, later items' experts one item ahead, and an item's first pair ids together
   // with its pair count.
   const int groups = p.tiles_per_expert / p.tg;
+  const int TPe = min(TP, p.tp_alloc);  // tokens per pass
   int e_next = 0;
-  if ((int)blockIdx.x / groups < p.n_experts) e_next = p.exp_list[blockIdx.x / groups];
+  if (!p.by_pass && (int)blockIdx.x / groups < p.n_experts) e_next = p.exp_list[blockIdx.x / groups];
   const int n_act = p.n_active[0];
-  const int total = n_act * groups;
+  int total = n_act * groups;
   const size_t vec_bytes = panel_vec_bytes(p.K);
   const int rows_per_tile = DUAL ? 8 : 16;
-  const int first_lanes = min(min(TP, p.tp_alloc), (int)p.idxStride);
+  const int first_lanes = min(TPe, (int)p.idxStride);
+
+  // Batches whose experts can hold more tokens than one pass takes: the unit of work is one PASS of one tile
+  // group, so that an expert with many tokens spreads over more CTAs instead of keeping a few of them busy
+  // several times longer than the rest (its weight tile is then fetched once per pass, from L2 after the
+  // first). Each CTA derives the same table: passes per active expert, exclusive prefix.
+  __shared__ int s_ubase[257];
+  __shared__ int s_uexp[256], s_ucnt[256];
+  if (p.by_pass) {
+    for (int a = threadIdx.x; a < 256; a += blockDim.x) {
+      int c = 0, ex = -1;
+      if (a < n_act) {
+        ex = p.exp_list[a];
+        c = p.pair_cnt[ex];
+      }
+      s_uexp[a] = ex;
+      s_ucnt[a] = c;
+      s_ubase[a] = (c + TPe - 1) / TPe;
+    }
+    __syncthreads();
+    if (warp == 0) {
+      int v[8], sum = 0;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { v[i] = s_ubase[lane * 8 + i]; sum += v[i]; }
+      int incl = sum;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      int base = incl - sum;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { s_ubase[lane * 8 + i] = base; base += v[i]; }
+      if (lane == 31) s_ubase[256] = incl;
+    }
+    __syncthreads();
+    total = s_ubase[256] * groups;
+  }
 
   for (int it = blockIdx.x; it < total; it += gridDim.x) {
-    const int a = it / groups, grp = it - a * groups;
-    const int e = e_next;
-    if (it + (int)gridDim.x < total) e_next = p.exp_list[(it + gridDim.x) / groups];
-    const int pair_first = lane < first_lanes ? p.pair_idx[(size_t)e * p.idxStride + lane] : -1;
-    const int cnt = p.pair_cnt[e];
+    int a, grp, e, cnt, tok_lo, tok_hi, pair_first = -1;
+    if (p.by_pass) {
+      const int pu = it / groups;
+      grp = it - pu * groups;
+      int lo = 0, hi = 255;  // the last a whose first pass is not beyond pu (inactive entries all hold the total)
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (s_ubase[mid] <= pu) lo = mid;
+        else hi = mid - 1;
+      }
+      a = lo;
+      e = s_uexp[a];
+      cnt = s_ucnt[a];
+      tok_lo = (pu - s_ubase[a]) * TPe;
+      tok_hi = min(cnt, tok_lo + TPe);
+    } else {
+      a = it / groups;
+      grp = it - a * groups;
+      e = e_next;
+      if (it + (int)gridDim.x < total) e_next = p.exp_list[(it + gridDim.x) / groups];
+      pair_first = lane < first_lanes ? p.pair_idx[(size_t)e * p.idxStride + lane] : -1;
+      cnt = p.pair_cnt[e];
+      tok_lo = 0;
+      tok_hi = cnt;
+    }
     const int n0 = (grp * p.tg + tile_slot) * rows_per_tile;
     if (tr && it == (int)blockIdx.x) tr[2] = global_timer_ns() + (cnt & 0);
 
@@ -185,13 +244,13 @@ __global__ void __launch_bounds__(512) q4k_proj_kernel(const __grid_constant__ P
     const uint8_t *rowA = wbase + (size_t)g * p.pitch;
     const uint8_t *rowB = wbase + (size_t)(g + 8) * p.pitch;
 
-    for (int tok0 = 0; tok0 < cnt; tok0 += min(TP, p.tp_alloc)) {
-      const int n_valid = min(min(TP, p.tp_alloc), cnt - tok0);
+    for (int tok0 = tok_lo; tok0 < tok_hi; tok0 += TPe) {
+      const int n_valid = min(TPe, cnt - tok0);
       // pair ids of this pass: lane i holds the pair of token tok0 + i
       int my_pair = -1, my_vec = -1;
       float my_inv = 0.f;  // the vector's inverse scale, needed only at the very end: fetched now
       if (lane < n_valid) {
-        my_pair = tok0 == 0 ? pair_first : p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
+        my_pair = (tok0 == 0 && !p.by_pass) ? pair_first : p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
         my_vec = p.row_map ? p.row_map[my_pair] : my_pair / p.row_div;
         my_inv = __ldg(reinterpret_cast<const float *>(p.panel + (size_t)my_vec * vec_bytes + (size_t)nsb * kChunkBytes));
       }
@@ -452,6 +511,7 @@ int launch_proj(ProjParams p, int n_experts_max, int max_tokens, cudaStream_t st
   // and keep the whole prepared vectors of a pass resident in shared memory
   p.tp_alloc = max_tokens < TP ? (max_tokens < 1 ? 1 : max_tokens) : TP;
   p.resident = (size_t)p.tp_alloc * panel_vec_bytes(p.K) <= 40 * 1024 ? 1 : 0;
+  p.by_pass = (max_tokens > TP && !p.cmb_out && n_experts_max <= 256) ? 1 : 0;
   // K-split: every part must fit one TMA box (at most 7 superblocks = 1008 bytes per row). Defaults measured
   // on B200 (48-layer resident stack, batch 1/8/64).
   auto fits = [&](int c) { return c >= 1 && nsb % c == 0 && nsb / c <= 7 && (p.resident || p.tp_alloc * c <= 32); };
