@@ -533,6 +533,7 @@ struct FrontParams {
   uint8_t *xpanel;
   unsigned int *counter;  // 192 words: [0, 1 + token groups) zero before the launch; [64, 192) are zeroed here
   unsigned long long *trace;  // optional [8]: global-timer stamps of the phases of the CTA that finishes last
+  int tpc;  // tokens per CTA: 4 up to batch 32 (the logits are a serial walk over a CTA's tokens), 8 above (fewer groups to close)
 };
 
 __device__ __forceinline__ unsigned long long gtime_ns() {
@@ -543,7 +544,7 @@ __device__ __forceinline__ unsigned long long gtime_ns() {
 
 constexpr int kFrontMaxT = 64;
 constexpr int kFrontMaxSlices = 8;  // H <= 2048
-constexpr int kFrontTok = 8;        // tokens per CTA
+constexpr int kFrontTok = 8;        // tokens per CTA, at most (FrontParams::tpc is the number in use)
 
 // Grid (ceil(E/8), ceil(T/8)): CTA (eg, tg) computes the logits of experts
 // 8eg..8eg+7 (one per warp) for tokens 8tg..8tg+7 and prepares the vectors of
@@ -561,7 +562,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   const int eg = blockIdx.x, tg = blockIdx.y, n_eg = gridDim.x, n_tg = gridDim.y;
   const int nslice = p.H / 256;
   const int e = eg * 8 + warp;
-  const int t0 = tg * kFrontTok;
+  const int t0 = tg * p.tpc;
   unsigned long long stamp[9];
   stamp[6] = stamp[7] = stamp[8] = 0;
   stamp[0] = gtime_ns();
@@ -639,7 +640,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
         if (e < p.E) p.logits[(size_t)(t0 + i) * p.E + e] = dot * scale + bias;
       }
     };
-    const int nt = min(kFrontTok, p.T - t0);
+    const int nt = min(p.tpc, p.T - t0);
     // the router and norm weights above do not depend on the previous launch and are already on their way;
     // the token rows are the previous layer's output
     grid_dep_wait();
@@ -660,7 +661,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   stamp[1] = gtime_ns();
 
   // ---- prepared vectors: CTA (eg, tg) takes tokens t0 + eg, t0 + eg + n_eg, ...
-  for (int i = eg; i < kFrontTok; i += n_eg) {
+  for (int i = eg; i < p.tpc; i += n_eg) {
     const int t = t0 + i;
     if (t >= p.T) break;
     const float scale = s_scale[i];
@@ -690,7 +691,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   // ---- top-k of the group's tokens, one warp each
   {
     const int t = t0 + warp;
-    if (t < p.T) {
+    if (warp < p.tpc && t < p.T) {
       int sel_e[8];
       float sel_w[8];
       warp_topk(p.logits + (size_t)t * p.E, p.E, p.k, lane, sel_e, sel_w);
@@ -903,7 +904,8 @@ int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t
   p.pair_cnt = pair_cnt; p.exp_list = exp_list; p.n_active = n_active; p.xpanel = static_cast<uint8_t *>(xpanel);
   p.counter = counter;
   p.trace = g_front_trace;
-  const int n_tg = (T + kFrontTok - 1) / kFrontTok;
+  p.tpc = T <= 32 ? 4 : kFrontTok;
+  const int n_tg = (T + p.tpc - 1) / p.tpc;
   KNJ_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t) * (1 + n_tg), as_stream(s)));
   dim3 grid((E + 7) / 8, n_tg);
   cudaError_t le;
