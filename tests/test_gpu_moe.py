@@ -173,6 +173,32 @@ def test_prefill_t512_zipf(cfg2):
     assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_PREFILL
 
 
+def test_decode_b64_zipf_unbalanced_experts(cfg2):
+    """Batch 64 with a Zipf(1.1) router: a few experts hold far more tokens than one pass of the projection
+    kernels takes, the case in which their work is split by token pass. Combine order on the CPU side is
+    ascending expert id, as in the CPU path."""
+    bank, _ = cfg2
+    wr, bias = synth.router_weight(3, zipf_s=1.1)
+    hx = synth.hidden_rows(3, 64, layer=64)
+    layer = make_layer(bank, wr, 8, 64, bias=bias)
+    out, pe, pw = layer.decode(dev(hx), return_routing=True)
+    ch = pe.cpu().numpy().reshape(64, 8)
+    cnt = np.bincount(ch.ravel(), minlength=128)
+    print("zipf bucket sizes at batch 64: max", cnt.max(), "experts above 8 tokens", int((cnt > 8).sum()))
+    assert cnt.max() > 8
+    wts = pw.cpu().numpy().reshape(64, 8)
+    want = np.zeros_like(hx)
+    for e in np.nonzero(cnt)[0]:
+        rows, slots = np.nonzero(ch == e)
+        g = ol.matmul_q4k(bank["gate"][e], hx[rows])
+        u = ol.matmul_q4k(bank["up"][e], hx[rows])
+        a = ((g / (1.0 + np.exp(-g))) * u).astype(np.float32)
+        y = ol.matmul_q4k(bank["down"][e], a)
+        want[rows] += wts[rows, slots][:, None] * y
+    st = report(out.cpu().numpy(), want, "decode batch 64 Zipf(1.1)")
+    assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_DECODE
+
+
 def test_mixed_format_layer_q6k_down():
     """A layer whose down matrices are Q6_K (as half of them are in Q4_K_M files): decode launch against the CPU
     pieces -- router, Q4_K gate/up and SiLU*up from the restatement, Q6_K decode + double-precision product for
