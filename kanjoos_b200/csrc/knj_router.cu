@@ -533,7 +533,7 @@ struct FrontParams {
   uint8_t *xpanel;
   unsigned int *counter;  // 192 words: [0, 1 + token groups) zero before the launch; [64, 192) are zeroed here
   unsigned long long *trace;  // optional [8]: global-timer stamps of the phases of the CTA that finishes last
-  int tpc;  // tokens per CTA: 4 up to batch 32 (the logits are a serial walk over a CTA's tokens), 8 above (fewer groups to close)
+  int tpc;  // tokens per CTA: ceil(T / 8), the logits being a serial walk over a CTA's tokens
 };
 
 __device__ __forceinline__ unsigned long long gtime_ns() {
@@ -904,7 +904,7 @@ int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t
   p.pair_cnt = pair_cnt; p.exp_list = exp_list; p.n_active = n_active; p.xpanel = static_cast<uint8_t *>(xpanel);
   p.counter = counter;
   p.trace = g_front_trace;
-  p.tpc = T <= 32 ? 4 : kFrontTok;
+  p.tpc = (T + 7) / 8;  // eight token groups at most: ~128 CTAs at every batch, and the serial walk over a CTA's tokens stays short
   const int n_tg = (T + p.tpc - 1) / p.tpc;
   KNJ_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t) * (1 + n_tg), as_stream(s)));
   dim3 grid((E + 7) / 8, n_tg);
