@@ -28,7 +28,8 @@ constexpr TransferId kNoTransfer = 0;
 enum class TransferState : uint8_t { PENDING = 0, DONE, FAILED, CANCELLED };
 enum class IoClass : uint8_t { DEMAND = 0, PREFETCH = 1 };
 
-/* Asynchronous copies only; every call returns a handle to poll. Demand traffic
+/* Asynchronous copies only; every call returns a handle to poll (the CUDA engine keeps the state of the most
+ * recent 65536 transfers; older finished ones poll as FAILED, like an unknown id). Demand traffic
  * runs on a higher-priority stream / ahead of queued prefetch work. */
 class TransferEngine {
  public:

@@ -16,6 +16,7 @@
 #include <atomic>
 #include <condition_variable>
 #include <deque>
+#include <iterator>
 #include <mutex>
 #include <thread>
 #include <unordered_map>
@@ -228,11 +229,30 @@ class CopyEngine final : public TransferEngine {
     std::lock_guard<std::mutex> g(m_);
     const TransferId id = next_++;
     dev_[id] = ev;
+    forget_old(id);
     return id;
+  }
+  // States are kept for the most recent kKept transfers: finished ones older than that are forgotten (a poll of
+  // them answers FAILED, as for an id never handed out), so a long run does not grow the tables. Called locked.
+  static constexpr TransferId kKept = 1u << 16;
+  void forget_old(TransferId newest) {
+    if ((newest & 0xfffu) != 0 || newest <= kKept) return;
+    const TransferId limit = newest - kKept;
+    for (auto it = file_.begin(); it != file_.end();)
+      it = (it->first < limit && it->second != TransferState::PENDING) ? file_.erase(it) : std::next(it);
+    for (auto it = dev_.begin(); it != dev_.end();) {
+      if (it->first < limit && cudaEventQuery(it->second) == cudaSuccess) {
+        cudaEventDestroy(it->second);
+        it = dev_.erase(it);
+      } else {
+        ++it;
+      }
+    }
   }
   TransferId enqueue_file(FileOp op, IoClass io) {
     std::lock_guard<std::mutex> g(m_);
     const TransferId id = next_++;
+    forget_old(id);
     file_[id] = TransferState::PENDING;
     (io == IoClass::DEMAND ? q_demand_ : q_prefetch_).push_back({id, op});
     cv_.notify_one();
