@@ -216,18 +216,15 @@ int knj_moe_permute_ws_launch(const int32_t *pair_exp, int P, int E, int idx_str
 /* Decode front end in one launch (T <= 64): per-row RMSNorm scale (norm_w NULL =
  * none), router logits + softmax + exact top-k (as knj_router_topk_launch over
  * the normalised rows), the permutation tables (as knj_moe_permute_launch) and
- * the prepared activation vector of every token (as knj_act_prep_launch over
- * the normalised rows). Replaces, for the decode step, rmsnorm_rows + the router
- * part of Model::moe (src/model/model.cpp:631, :419-460) and the host plan of the
- * benches. counter: 16 device words of scratch. H <= 2048, rows of x 16-byte
- * aligned. */
+ * the normalised rows xn f32 [T][H] the experts see (as knj_rmsnorm_launch).
+ * Replaces, for the decode step, rmsnorm_rows + the router part of Model::moe
+ * (src/model/model.cpp:631, :419-460) and the host plan of the benches. counter:
+ * 64 device words of scratch (the launch zeroes what it uses). H <= 2048, rows of
+ * x 16-byte aligned. */
 int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *norm_w, float eps,
                          const uint16_t *Wr_bf16, const float *bias, int T, int H, int E, int k, float *logits,
                          int32_t *pair_exp, float *pair_w, int32_t *pair_idx, int idx_stride, int32_t *pair_cnt,
-                         int32_t *exp_list, int32_t *n_active, void *xpanel, uint32_t *counter, knj_stream_t s);
-/* `counter` above is a block of 192 uint32: the launch zeroes the words it uses
- * itself and its last CTA zeroes words 64..191, the slice counters of a
- * knj_q4k_down_combine_launch that follows. */
+                         int32_t *exp_list, int32_t *n_active, float *xn, uint32_t *counter, knj_stream_t s);
 
 /* Measurement hook (no reference counterpart): a device buffer of 16 uint64 that
  * receives global-timer stamps (ns) of the front kernel's phases -- start,
@@ -251,57 +248,43 @@ int knj_moe_combine_launch(const float *Y, const int32_t *pair_row, const int32_
 /* Expert projections, decode class (f32-accurate, HBM-bound)               */
 /* ======================================================================== */
 
-/* The decode kernels multiply Q4_K codes as exact small integers on the
- * fp16 tensor cores and apply the per-32 scale/min in f32, so activations are
- * first split into a "panel": per vector a power-of-two scale, a high and a
- * low fp16 plane (together ~22 significant bits) and the per-32 sums the min
- * term needs. One panel vector = (K/256) * 1120 + 16 bytes. */
-size_t knj_panel_bytes(int n_vec, int K);
-/* Tuning hook for measurement runs (no reference counterpart): force the
- * K-split, tiles-per-CTA and 4-token tiles per pass (1, 2 or 4) of the decode
- * projections; 0 = automatic. */
-void knj_q4k_decode_tuning(int ks, int tg, int nt);
-
-/* Measurement hook (no reference counterpart): 16 uint64 receiving global-timer
- * ns of CTA 0 / thread 0 of the decode projections: [0] start, [1] predecessor
- * complete, [2] plan read, [3] first wait for weights, [4] weights landed,
- * [5] first pass computed, [6] end; +8 for the single-matrix launch. NULL = off. */
-void knj_q4k_proj_trace(void *dev_buf);
-/* x [n_vec][K] (f32/bf16/f16, row stride ldx elements) -> panel. */
-int knj_act_prep_launch(const void *x, int x_dtype, int64_t ldx, int n_vec, int K, void *panel, knj_stream_t s);
+/* The decode kernels multiply Q4_K codes as exact small integers on the fp16
+ * tensor cores: a 4-bit code left in place in an fp16 word is an exact subnormal,
+ * one packed fp16 multiply folds the 6-bit sub-block scale in, and the activations
+ * are split on the fly into a high and a low fp16 plane under a power-of-two scale
+ * per (token, 256-wide superblock), ~22 significant bits together. Results agree
+ * with the f32 CPU path to <= 1e-5 relative RMSE. Rows of at most 4096 weights.
+ * Activation rows (f32, bf16 or f16) must be 16-byte aligned.
+ * status (optional device int, zeroed by the caller) is set to 1 if a bounded
+ * wait inside the kernel gave up; the outputs are then incomplete. */
 
 /* Gate and up in one pass (tools/bench/q4k_moe_ffn.hip:164-241 knj_q4k_gateup):
  * for every pair p routed to expert e and every n < N
  *   G[p][n] = x[tok(p)] . Wg[e][n],  U[p][n] = x[tok(p)] . Wu[e][n],
  *   A[p][n] = silu(G) * U                       (tools/bench/q4k_stream_ffn.hip:1005-1031)
- * Xpanel holds one prepared vector per TOKEN; tok(p) = pair_tok[p] when given,
- * else p / top_k. G, U, A are f32 [P][N]; any of them may be NULL (not stored).
- * Experts are taken from exp_list[0 .. n_active[0]). */
-int knj_q4k_gateup_launch(const void *Xpanel, const uint8_t *Wg, const uint8_t *Wu, const int32_t *pair_idx,
-                          const int32_t *pair_cnt, const int32_t *pair_tok, const int32_t *exp_list,
-                          const int32_t *n_active, float *G, float *U, float *A, int N, int K, int rowBytes,
-                          int64_t idxStride, int n_experts, int top_k, int max_tokens, knj_stream_t s);
+ * X holds one activation row per TOKEN (row stride ldx elements); tok(p) =
+ * pair_tok[p] when given, else p / top_k. G, U, A are f32 [P][N]; any of them may
+ * be NULL (not stored). Experts are taken from exp_list[0 .. n_active[0]). */
+int knj_q4k_gateup_launch(const void *X, int x_dtype, int64_t ldx, const uint8_t *Wg, const uint8_t *Wu,
+                          const int32_t *pair_idx, const int32_t *pair_cnt, const int32_t *pair_tok,
+                          const int32_t *exp_list, const int32_t *n_active, float *G, float *U, float *A, int N, int K,
+                          int rowBytes, int64_t idxStride, int n_experts, int top_k, int *status, knj_stream_t s);
 
 /* One projection per pair (tools/bench/q4k_stream_ffn.hip:834-882 knj_q4k_proj;
- * :780-829 knj_q6k_down with dq4 = 1): Y[p][n] = a[p] . W[e][n]. Apanel holds
- * one prepared vector per PAIR (row_of as for the combine). Y f32 [P][N]. */
-int knj_q4k_proj_launch(const void *Apanel, const uint8_t *W, const int32_t *pair_idx, const int32_t *pair_cnt,
-                        const int32_t *pair_row, const int32_t *exp_list, const int32_t *n_active, float *Y, int N,
-                        int K, int rowBytes, int64_t idxStride, int n_experts, int max_tokens, knj_stream_t s);
-
-/* Down projection and the weighted combine of a decode batch (T <= 64) in one
- * launch: knj_q4k_proj_launch followed by knj_moe_combine_launch
- * (src/model/model.cpp:455-463 and the residual add at :652), with the combine of
- * each 16*tg-column slice done by the CTA that finishes that slice last, in
- * ascending expert order (same arithmetic and order as the separate kernel).
- * Y f32 [T*k][N] still receives the per-pair rows. counters: at least N/16
- * uint32, ZERO before the first launch; every launch leaves them zero. */
-int knj_q4k_down_combine_launch(const void *Apanel, const uint8_t *W, const int32_t *pair_idx, const int32_t *pair_cnt,
-                                const int32_t *exp_list, const int32_t *n_active, float *Y, int N, int K, int rowBytes,
-                                int64_t idxStride, int n_experts, const int32_t *pair_exp, const float *pair_w,
-                                const void *resid, int resid_dtype, int64_t ld_resid, void *out, int out_dtype,
-                                int64_t ldo, int T, int k, uint32_t *counters, knj_stream_t s);
+ * :780-829 knj_q6k_down with dq4 = 1): Y[p][n] = a[row(p)] . W[e][n]. A holds
+ * one activation row per PAIR (row(p) = pair_row[p] when given, else p; row
+ * stride lda elements). Y f32 [P][N]. */
+int knj_q4k_proj_launch(const void *A, int a_dtype, int64_t lda, const uint8_t *W, const int32_t *pair_idx,
+                        const int32_t *pair_cnt, const int32_t *pair_row, const int32_t *exp_list, const int32_t *n_active,
+                        float *Y, int N, int K, int rowBytes, int64_t idxStride, int n_experts, int *status,
+                        knj_stream_t s);
 #define knj_q4k_down_launch knj_q4k_proj_launch
+
+/* Limit, in SM clock cycles, of every bounded wait of the decode-class kernels
+ * (no reference counterpart; default about one second, <= 0 restores it). A wait
+ * that runs out makes the kernel skip the rest of its work and raise its status
+ * word; nothing traps and the context stays usable. */
+void knj_decode_wait_limit(long long cycles);
 
 /* A[i] = silu(G[i]) * U[i], n elements (tools/bench/q4k_stream_ffn.hip:1021-1031
  * knj_fuse_gateup_silu); out dtype f32, bf16 or f16. Uses expf, not the fast
@@ -415,6 +398,11 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s);
 /* Prefill: tokens bucketed per expert, Q4_K unpacked to fp16 operands for
  * tcgen05.mma with f32 TMEM accumulators (<= 1e-3 rel-RMSE vs the CPU path). */
 int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
+/* Outcome of the last layer launch over this argument block (same workspace):
+ * waits for the stream, then KNJ_OK, or KNJ_E_TIMEOUT when a bounded wait inside
+ * one of its kernels gave up (docs/BUILD-OUTLINE.md:588-598: RETRY). mode as for
+ * knj_moe_ffn_workspace_bytes. */
+int knj_moe_ffn_status(const knj_moe_ffn_args *a, int mode, knj_stream_t s);
 
 /* The resident decode stack for batches of 1..4 tokens in ONE cooperative launch:
  * n_layers layer descriptions (layer l's out is normally layer l+1's x; out must

@@ -139,15 +139,10 @@ SIGNATURES = {
     "knj_ep_combine_partial_peer_launch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "knj_ep_reduce_sel_launch": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
-    "knj_q4k_decode_tuning": (None, [_i, _i, _i]),
-    "knj_q4k_proj_trace": (None, [_vp]),
-    "knj_panel_bytes": (_sz, [_i, _i]),
-    "knj_act_prep_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
-    "knj_q4k_gateup_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i,
-                                   _i, _vp]),
-    "knj_q4k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp]),
-    "knj_q4k_down_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _vp, _vp, _i, _i64,
-                                         _vp, _i, _i64, _i, _i, _vp, _vp]),
+    "knj_q4k_gateup_launch": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64,
+                                   _i, _i, _vp, _vp]),
+    "knj_q4k_proj_launch": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _vp]),
+    "knj_decode_wait_limit": (None, [C.c_longlong]),
     "knj_tc_trace": (None, [_vp, _i]),
     "knj_tc_tuning": (None, [_i]),
     "knj_chain_overlap": (None, [_i]),
@@ -162,6 +157,7 @@ SIGNATURES = {
     "knj_moe_ffn_workspace_bytes": (_sz, [_i, _i, _i, _i, _i, _i]),
     "knj_moe_ffn_decode_launch": (_i, [C.POINTER(MoeFfnArgs), _vp]),
     "knj_moe_ffn_prefill_launch": (_i, [C.POINTER(MoeFfnArgs), _vp]),
+    "knj_moe_ffn_status": (_i, [C.POINTER(MoeFfnArgs), _i, _vp]),
     # flat C cover of the C++ Backend (include/backend.h)
     "knj_backend_create": (_vp, []),
     "knj_backend_from_caps": (_vp, [C.c_char_p, _i, _i, _i, _i]),

@@ -124,6 +124,22 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   }
 }
 
+// The same wait with the limit given at run time (clock cycles).
+__device__ __forceinline__ bool mbar_wait_for(uint64_t *bar, uint32_t parity, long long limit_cycles, volatile int *abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (abort_flag && *abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      if (abort_flag) *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
 // Same contract, but polls with the non-suspending test_wait: lowest wake-up latency,
 // for pipelines whose stage hand-offs sit on the critical path.
 __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {

@@ -28,7 +28,7 @@ struct DecodeWs {
   float *xn, *logits, *pair_w, *A, *Y;
   int32_t *pair_exp, *pair_idx, *pair_cnt, *exp_list, *n_active;
   uint32_t *counter;
-  void *xpanel, *apanel;
+  int32_t *status;
   size_t bytes;
 };
 
@@ -44,10 +44,9 @@ DecodeWs carve_decode(void *base, int T, int H, int F, int E, int k) {
   w.pair_cnt = c.take<int32_t>((size_t)E * 4);
   w.exp_list = c.take<int32_t>((size_t)E * 4);
   w.n_active = c.take<int32_t>(16);
-  w.counter = c.take<uint32_t>((64 + 128) * 4);  // front kernel: 64 words; fused combine: one per column slice
-  w.xpanel = c.take<void>(knj_panel_bytes(T, H));
+  w.counter = c.take<uint32_t>(64 * 4);  // front kernel's completion counters
+  w.status = c.take<int32_t>(16);        // [0] gate+up, [1] down: set when a bounded wait gave up
   w.A = c.take<float>(P * F * 4);
-  w.apanel = c.take<void>(knj_panel_bytes((int)P, F));
   w.Y = c.take<float>(P * H * 4);
   w.bytes = c.used;
   return w;
@@ -132,24 +131,28 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
 
   int32_t *pair_exp = a->tap_pair_exp ? a->tap_pair_exp : w.pair_exp;
   float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
+  KNJ_CUDA(cudaMemsetAsync(w.status, 0, 16, as_stream(s)));  // the projections raise it when a bounded wait gives up
+  const void *src = w.xn;  // the rows the experts see
+  int src_dt = KNJ_DT_F32;
+  int64_t src_ld = H;
   if (T <= 64 && H <= 2048 && a->ldx % 8 == 0 && aligned16(a->x)) {
-    // decode batch: norm statistics, routing, tables and prepared vectors in one launch
-    StageSpan sp("moe-router", s);  // norm statistics, router, top-k, plan and prepared vectors in one launch
+    // decode batch: norm statistics, routing, tables and the normalised rows in one launch
+    StageSpan sp("moe-router", s);
     rc = knj_moe_front_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, a->w_router, a->router_bias, T, H, E, k,
-                              w.logits, pair_exp, pair_w, w.pair_idx, T, w.pair_cnt, w.exp_list, w.n_active, w.xpanel,
+                              w.logits, pair_exp, pair_w, w.pair_idx, T, w.pair_cnt, w.exp_list, w.n_active, w.xn,
                               w.counter, s);
     if (rc) return rc;
   } else {
     // 1. ffn RMSNorm (optional) -> the rows the router and the experts see
-    const void *src = a->x;
-    int src_dt = a->x_dtype;
-    int64_t src_ld = a->ldx;
     if (a->norm_w) {
       rc = knj_rmsnorm_launch(a->x, a->x_dtype, a->ldx, a->norm_w, a->rms_eps, T, H, w.xn, s);
       if (rc) return rc;
-      src = w.xn;
-      src_dt = KNJ_DT_F32;
-      src_ld = H;
+    } else {
+      src = a->x;
+      src_dt = a->x_dtype;
+      src_ld = a->ldx;
+      const int64_t esz = src_dt == KNJ_DT_F32 ? 4 : 2;
+      KNJ_REQUIRE(aligned16(src) && (src_ld * esz) % 16 == 0, "knj_moe_ffn_decode: rows of x must be 16-byte aligned");
     }
     // 2. route
     rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
@@ -157,16 +160,12 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
     // 3. permutation tables
     rc = knj_moe_permute_launch(pair_exp, P, E, T, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, s);
     if (rc) return rc;
-    // 4. prepared activation vectors
-    rc = knj_act_prep_launch(src, src_dt, src_ld, T, H, w.xpanel, s);
-    if (rc) return rc;
-    if (T <= 64) KNJ_CUDA(cudaMemsetAsync(w.counter + 64, 0, 128 * sizeof(uint32_t), as_stream(s)));  // slice counters
   }
   // gate, up, silu(g)*u
   {
     StageSpan sp("moe-gate", s);  // gate + up + activation fused
-    rc = knj_q4k_gateup_launch(w.xpanel, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active,
-                               nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, T, s);
+    rc = knj_q4k_gateup_launch(src, src_dt, src_ld, a->w_gate, a->w_up, w.pair_idx, w.pair_cnt, nullptr, w.exp_list,
+                               w.n_active, nullptr, nullptr, w.A, F, H, H / 256 * KNJ_Q4K_BYTES, T, E, k, w.status, s);
     if (rc) return rc;
   }
   StageSpan sp_down("moe-down", s);  // down projection and the weighted combine (to the end of the launch)
@@ -174,23 +173,12 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
     // mixed-format layer: Q6_K down matrices (210-byte superblocks) through the plain f32 projection
     rc = knj_q6k_proj_launch(w.A, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F, T, E, s);
     if (rc) return rc;
-    return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
-                                  a->out, a->out_dtype, a->ldo, T, H, k, s);
+  } else {
+    rc = knj_q4k_proj_launch(w.A, KNJ_DT_F32, F, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active, w.Y, H,
+                             F, F / 256 * KNJ_Q4K_BYTES, T, E, w.status + 1, s);
+    if (rc) return rc;
   }
-  // 5. down
-  rc = knj_act_prep_launch(w.A, KNJ_DT_F32, F, P, F, w.apanel, s);
-  if (rc) return rc;
-  if (T <= 4 && H / 16 <= 128) {  // larger batches: the one CTA per slice that combines becomes the tail
-    // down + weighted combine (+ residual) in one launch; the slice counters sit behind the front kernel's
-    // counters and were zeroed with them (they are left zero)
-    return knj_q4k_down_combine_launch(w.apanel, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F,
-                                       F / 256 * KNJ_Q4K_BYTES, T, E, pair_exp, pair_w, a->residual ? a->x : nullptr,
-                                       a->x_dtype, a->ldx, a->out, a->out_dtype, a->ldo, T, k, w.counter + 64, s);
-  }
-  rc = knj_q4k_proj_launch(w.apanel, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active, w.Y, H, F,
-                           F / 256 * KNJ_Q4K_BYTES, T, E, T, s);
-  if (rc) return rc;
-  // 6. weighted combine (+ residual)
+  // weighted combine (+ residual)
   return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
                                 a->out, a->out_dtype, a->ldo, T, H, k, s);
 }
@@ -223,6 +211,7 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   }
   int32_t *pair_exp = a->tap_pair_exp ? a->tap_pair_exp : w.pair_exp;
   float *pair_w = a->tap_pair_w ? a->tap_pair_w : w.pair_w;
+  KNJ_CUDA(cudaMemsetAsync(w.status, 0, 16, as_stream(s)));  // the GEMMs raise it when a bounded wait gives up
   {
     StageSpan sp("moe-router", s);
     rc = knj_router_topk_launch(src, src_dt, src_ld, a->w_router, a->router_bias, T, H, E, k, w.logits, pair_exp, pair_w, s);
@@ -252,6 +241,24 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   StageSpan sp("moe-scatter", s);
   return knj_moe_combine_launch(w.Y, nullptr, pair_exp, pair_w, a->residual ? a->x : nullptr, a->x_dtype, a->ldx,
                                 a->out, a->out_dtype, a->ldo, T, H, k, s);
+}
+
+int knj_moe_ffn_status(const knj_moe_ffn_args *a, int mode, knj_stream_t s) {
+  int rc = check_args(a, "knj_moe_ffn_status");
+  if (rc) return rc;
+  if (a->n_tokens == 0) return KNJ_OK;
+  KNJ_REQUIRE(a->workspace && (mode == 0 || mode == 1), "knj_moe_ffn_status: no workspace or unknown mode %d", mode);
+  const int T = a->n_tokens, H = a->hidden, F = a->ffn, E = a->n_experts, k = a->top_k;
+  const int32_t *dev_words = mode == 1 ? carve_prefill(a->workspace, T, H, F, E, k).status : carve_decode(a->workspace, T, H, F, E, k).status;
+  int32_t words[4] = {0, 0, 0, 0};
+  KNJ_CUDA(cudaMemcpyAsync(words, dev_words, sizeof(words), cudaMemcpyDeviceToHost, as_stream(s)));
+  KNJ_CUDA(cudaStreamSynchronize(as_stream(s)));
+  if (words[0] != 0 || words[1] != 0) {
+    set_error("knj_moe_ffn: a bounded device wait gave up in the %s launch (gate+up %d, down %d)", mode == 1 ? "prefill" : "decode",
+              words[0], words[1]);
+    return KNJ_E_TIMEOUT;
+  }
+  return KNJ_OK;
 }
 
 }  // extern "C"

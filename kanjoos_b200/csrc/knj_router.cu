@@ -6,7 +6,6 @@
 // kernels of the benches).
 #include "knj_common.cuh"
 #include "knj_topk.cuh"
-#include "knj_panel.cuh"
 
 using namespace knj;
 
@@ -530,8 +529,8 @@ struct FrontParams {
   int32_t *pair_exp;
   float *pair_w;
   int32_t *pair_idx, *pair_cnt, *exp_list, *n_active;
-  uint8_t *xpanel;
-  unsigned int *counter;  // 192 words: [0, 1 + token groups) zero before the launch; [64, 192) are zeroed here
+  float *xn;  // [T][H]: the rows the experts see (normalised where norm_w is given)
+  unsigned int *counter;  // [0, 1 + token groups) zero before the launch
   unsigned long long *trace;  // optional [8]: global-timer stamps of the phases of the CTA that finishes last
   int tpc;  // tokens per CTA: ceil(T / 8), the logits being a serial walk over a CTA's tokens
 };
@@ -554,7 +553,6 @@ constexpr int kFrontTok = 8;        // tokens per CTA, at most (FrontParams::tpc
 template <int DT>
 __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   __shared__ float s_scale[kFrontTok];
-  __shared__ float s_red[16];
   __shared__ int s_flag;
   __shared__ int32_t s_pe[kFrontMaxT * 8];
   __shared__ int32_t s_cc[16][256];  // per 32-pair chunk and expert: count, then exclusive base
@@ -660,21 +658,15 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   __syncthreads();
   stamp[1] = gtime_ns();
 
-  // ---- prepared vectors: CTA (eg, tg) takes tokens t0 + eg, t0 + eg + n_eg, ...
+  // ---- the rows the experts see: CTA (eg, tg) writes tokens t0 + eg, t0 + eg + n_eg, ...
   for (int i = eg; i < p.tpc; i += n_eg) {
     const int t = t0 + i;
     if (t >= p.T) break;
     const float scale = s_scale[i];
-    if (p.norm_w) {
-      panel_prep_vector(
-          [&](int k) {
-            return __fmul_rn(__fmul_rn(load_as_f32(p.x, DT, (int64_t)t * p.ldx + k), scale),
-                             __bfloat162float(p.norm_w[k]));
-          },
-          p.H, p.xpanel + (size_t)t * panel_vec_bytes(p.H), s_red);
-    } else {
-      panel_prep_vector([&](int k) { return load_as_f32(p.x, DT, (int64_t)t * p.ldx + k); }, p.H,
-                        p.xpanel + (size_t)t * panel_vec_bytes(p.H), s_red);
+    for (int k = threadIdx.x; k < p.H; k += 256) {
+      float v = load_as_f32(p.x, DT, (int64_t)t * p.ldx + k);
+      if (p.norm_w) v = __fmul_rn(__fmul_rn(v, scale), __bfloat162float(p.norm_w[k]));
+      p.xn[(size_t)t * p.H + k] = v;
     }
   }
 
@@ -715,10 +707,6 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   if (!s_flag) return;
   __threadfence();
   stamp[5] = gtime_ns();
-
-  // the slice counters of the fused down + combine launch that follows in a decode layer (words 64..191 of the
-  // counter block) start from zero
-  if (threadIdx.x < 128) p.counter[64 + threadIdx.x] = 0u;
 
   // ---- permutation tables. Pairs are taken in chunks of 32 (one per warp pass):
   // count per (chunk, expert), scan over chunks, then every pair knows its rank.
@@ -888,20 +876,20 @@ void knj_moe_front_trace(void *dev_buf) { g_front_trace = static_cast<unsigned l
 int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *norm_w, float eps,
                          const uint16_t *Wr_bf16, const float *bias, int T, int H, int E, int k, float *logits,
                          int32_t *pair_exp, float *pair_w, int32_t *pair_idx, int idx_stride, int32_t *pair_cnt,
-                         int32_t *exp_list, int32_t *n_active, void *xpanel, uint32_t *counter, knj_stream_t s) {
-  KNJ_REQUIRE(x && Wr_bf16 && logits && pair_exp && pair_w && pair_idx && pair_cnt && exp_list && n_active && xpanel && counter,
+                         int32_t *exp_list, int32_t *n_active, float *xn, uint32_t *counter, knj_stream_t s) {
+  KNJ_REQUIRE(x && Wr_bf16 && logits && pair_exp && pair_w && pair_idx && pair_cnt && exp_list && n_active && xn && counter,
               "knj_moe_front: null pointer");
   KNJ_REQUIRE(T >= 1 && T <= kFrontMaxT, "knj_moe_front: T=%d out of range (1..%d)", T, kFrontMaxT);
   KNJ_REQUIRE(H % 256 == 0 && H <= 256 * kFrontMaxSlices, "knj_moe_front: H=%d must be a multiple of 256, <= %d", H,
               256 * kFrontMaxSlices);
   KNJ_REQUIRE(E >= 1 && E <= 256 && k >= 1 && k <= 8 && k <= E && idx_stride >= T, "knj_moe_front: bad E / k / stride");
-  KNJ_REQUIRE(aligned16(Wr_bf16) && aligned16(xpanel) && (!norm_w || aligned16(norm_w)) && aligned16(x) && ldx % 8 == 0,
-              "knj_moe_front: 16-byte alignment of x rows, weights and panel");
+  KNJ_REQUIRE(aligned16(Wr_bf16) && aligned16(xn) && (!norm_w || aligned16(norm_w)) && aligned16(x) && ldx % 8 == 0,
+              "knj_moe_front: 16-byte alignment of x rows, weights and normalised rows");
   FrontParams p{};
   p.x = x; p.x_dtype = x_dtype; p.ldx = ldx; p.norm_w = reinterpret_cast<const __nv_bfloat16 *>(norm_w); p.eps = eps;
   p.Wr = reinterpret_cast<const __nv_bfloat16 *>(Wr_bf16); p.bias = bias; p.T = T; p.H = H; p.E = E; p.k = k;
   p.idx_stride = idx_stride; p.logits = logits; p.pair_exp = pair_exp; p.pair_w = pair_w; p.pair_idx = pair_idx;
-  p.pair_cnt = pair_cnt; p.exp_list = exp_list; p.n_active = n_active; p.xpanel = static_cast<uint8_t *>(xpanel);
+  p.pair_cnt = pair_cnt; p.exp_list = exp_list; p.n_active = n_active; p.xn = xn;
   p.counter = counter;
   p.trace = g_front_trace;
   p.tpc = (T + 7) / 8;  // eight token groups at most: ~128 CTAs at every batch, and the serial walk over a CTA's tokens stays short

@@ -122,11 +122,9 @@ class CudaCompute:
             Y, st2 = ops.q4k_down_tc(A, bank.down, pair_idx, pair_cnt, n_rows, poison=False)
             self.last_status = (st, st2)  # device flags: non-zero if a bounded wait inside the kernels gave up
             return Y
-        xp = ops.act_prep(rows)
-        A = ops.q4k_gateup(xp, bank.gate, bank.up, pair_idx, pair_cnt, exp_list, n_active, n_rows, 1, max_tokens,
+        A = ops.q4k_gateup(rows, bank.gate, bank.up, pair_idx, pair_cnt, exp_list, n_active, n_rows, 1,
                            want=("A",))["A"]
-        ap = ops.act_prep(A)
-        return ops.q4k_proj(ap, bank.down, pair_idx, pair_cnt, exp_list, n_active, n_rows, max_tokens)
+        return ops.q4k_proj(A, bank.down, pair_idx, pair_cnt, exp_list, n_active, n_rows)
 
     def combine(self, Yback, pair_row, pair_exp, pair_w, T, out_dtype):
         return self.ops.moe_combine(Yback, pair_exp, pair_w, T, self.top_k, out_dtype=out_dtype, pair_row=pair_row)
@@ -152,11 +150,8 @@ class CudaCompute:
             Y, st2 = ops.q4k_down_tc(A, bank.down, pair_idx, pair_cnt, P, poison=False)
             self.last_status = (st, st2)
             return Y
-        xp = ops.act_prep(x_all)
-        T = x_all.shape[0]
-        A = ops.q4k_gateup(xp, bank.gate, bank.up, pair_idx, pair_cnt, exp_list, n_active, P, k, T, want=("A",))["A"]
-        ap = ops.act_prep(A)  # rows of foreign pairs are unwritten and never read back
-        return ops.q4k_proj(ap, bank.down, pair_idx, pair_cnt, exp_list, n_active, P, T)
+        A = ops.q4k_gateup(x_all, bank.gate, bank.up, pair_idx, pair_cnt, exp_list, n_active, P, k, want=("A",))["A"]
+        return ops.q4k_proj(A, bank.down, pair_idx, pair_cnt, exp_list, n_active, P)  # rows of foreign pairs stay unwritten
 
     def combine_partial(self, Y, pair_exp_all, pair_w_all, T, exp_lo, exp_hi):
         from ._lib import check, lib

@@ -126,32 +126,29 @@ def moe_permute(pair_exp: torch.Tensor, E: int, idx_stride: int):
     return pair_idx, pair_cnt, exp_list, n_active
 
 
-def act_prep(x: torch.Tensor) -> torch.Tensor:
+def q4k_gateup(x, Wg, Wu, pair_idx, pair_cnt, exp_list, n_active, P: int, top_k: int, want=("G", "U", "A"),
+               pair_tok=None):
+    """x [T][K] activation rows (f32/bf16/f16) -> dict of f32 [P][N] outputs (G, U, A = silu(G)*U)."""
     _need(x)
-    n, K = x.shape
-    panel = torch.empty(lib().knj_panel_bytes(n, K), dtype=torch.uint8, device="cuda")
-    check(lib().knj_act_prep_launch(_p(x), _DT[x.dtype], K, n, K, _p(panel), _stream()))
-    return panel
-
-
-def q4k_gateup(xpanel, Wg, Wu, pair_idx, pair_cnt, exp_list, n_active, P: int, top_k: int, max_tokens: int,
-               want=("G", "U", "A"), pair_tok=None):
     E, N, nsb, _ = Wg.shape
     K = nsb * 256
     outs = {n: (torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda") if n in want else None)
             for n in ("G", "U", "A")}
-    check(lib().knj_q4k_gateup_launch(_p(xpanel), _p(Wg), _p(Wu), _p(pair_idx), _p(pair_cnt), _p(pair_tok), _p(exp_list),
-                                      _p(n_active), _p(outs["G"]), _p(outs["U"]), _p(outs["A"]), N, K, nsb * 144,
-                                      pair_idx.shape[1], E, top_k, max_tokens, _stream()))
+    check(lib().knj_q4k_gateup_launch(_p(x), _DT[x.dtype], x.shape[1], _p(Wg), _p(Wu), _p(pair_idx), _p(pair_cnt),
+                                      _p(pair_tok), _p(exp_list), _p(n_active), _p(outs["G"]), _p(outs["U"]),
+                                      _p(outs["A"]), N, K, nsb * 144, pair_idx.shape[1], E, top_k, None, _stream()))
     return outs
 
 
-def q4k_proj(apanel, W, pair_idx, pair_cnt, exp_list, n_active, P: int, max_tokens: int, pair_row=None):
+def q4k_proj(a, W, pair_idx, pair_cnt, exp_list, n_active, P: int, pair_row=None):
+    """a [rows][K] activation rows (one per pair unless pair_row maps them) -> Y f32 [P][N]."""
+    _need(a)
     E, N, nsb, _ = W.shape
     K = nsb * 256
     Y = torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda")
-    check(lib().knj_q4k_proj_launch(_p(apanel), _p(W), _p(pair_idx), _p(pair_cnt), _p(pair_row), _p(exp_list),
-                                    _p(n_active), _p(Y), N, K, nsb * 144, pair_idx.shape[1], E, max_tokens, _stream()))
+    check(lib().knj_q4k_proj_launch(_p(a), _DT[a.dtype], a.shape[1], _p(W), _p(pair_idx), _p(pair_cnt), _p(pair_row),
+                                    _p(exp_list), _p(n_active), _p(Y), N, K, nsb * 144, pair_idx.shape[1], E, None,
+                                    _stream()))
     return Y
 
 

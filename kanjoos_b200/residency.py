@@ -140,7 +140,6 @@ class StreamedMoeLayer:
             ids, n_units = pe, self.E
             gate, up, down = resident_bank
         pair_idx, pair_cnt, exp_list, n_active = ops.moe_permute(ids, n_units, T)
-        xp = ops.act_prep(x)
-        A = ops.q4k_gateup(xp, gate, up, pair_idx, pair_cnt, exp_list, n_active, P, k, T, want=("A",))["A"]
-        Y = ops.q4k_proj(ops.act_prep(A), down, pair_idx, pair_cnt, exp_list, n_active, P, T)
+        A = ops.q4k_gateup(x, gate, up, pair_idx, pair_cnt, exp_list, n_active, P, k, want=("A",))["A"]
+        Y = ops.q4k_proj(A, down, pair_idx, pair_cnt, exp_list, n_active, P)
         return ops.moe_combine(Y, pe, pw, T, k)

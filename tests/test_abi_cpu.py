@@ -81,9 +81,9 @@ def test_null_and_geometry_refusals(L):
     del one
 
 
-def test_workspace_and_panel_sizes(L):
-    assert L.knj_panel_bytes(1, 2048) == 8 * 1120 + 16  # one 1120-byte chunk per superblock + the scale slot
-    assert L.knj_panel_bytes(3, 768) == 3 * (3 * 1120 + 16)
+def test_workspace_sizes(L):
+    assert L.knj_q4k_matmul_workspace_bytes(1, 2048) == 512   # identity pair list + the one-expert plan
+    assert L.knj_q4k_matmul_workspace_bytes(0, 2048) == 0
     small = L.knj_moe_ffn_workspace_bytes(1, 2048, 768, 128, 8, 0)
     big = L.knj_moe_ffn_workspace_bytes(64, 2048, 768, 128, 8, 0)
     assert 0 < small < big and big % 256 == 0
