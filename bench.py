@@ -164,14 +164,23 @@ def cpu_layer_tokens_per_s(sample_tokens: int, steps: int, warmup: int, routing:
 
 
 def run_reference(args):
+    """The reference arm: the reference's own CPU layer on the host cores. One of its steps is a bounded SAMPLE
+    of the workload's step (cpu_sample tokens of the T), and the line says so: `steps` / `warmup` are the steps
+    actually run, `ms_per_step` is the time of one sample step, and `config` carries both token counts."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cb, dt = cpu_layer_tokens_per_s(args.cpu_sample, max(1, min(args.steps, 5)), min(args.warmup, 1), args.routing)
+    steps, warm = max(1, min(args.steps, 5)), min(args.warmup, 1)
+    cb, dt = cpu_layer_tokens_per_s(args.cpu_sample, steps, warm, args.routing)
+    cfg = workload_config(args, args.gpus)
+    cfg["sample_tokens_per_step"] = args.cpu_sample
+    cfg["sample_note"] = (f"each timed step runs {args.cpu_sample} of the workload's {args.tokens} tokens on the host "
+                          "(per-token cost of the CPU path does not depend on T); value = sample tokens / sample time")
     line = {"impl": "reference", "metric": "moe_ffn_tokens_per_s", "value": cb["value"], "unit": "tokens/s",
-            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+            "n_gpus": args.gpus, "steps": steps, "warmup": warm, "steps_requested": args.steps,
+            "ms_per_step": dt * 1e3, "ms_per_full_step_extrapolated": dt * 1e3 * args.tokens / args.cpu_sample,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": workload_config(args, 1), "cpu_baseline": cb,
+            "config": cfg, "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line))

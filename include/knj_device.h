@@ -22,9 +22,13 @@
  *   - Every function returns int: 0 = ok, negative = error (codes below). No
  *     exception crosses this boundary. knj_last_error_string() describes the
  *     last error on the calling thread.
- *   - All buffers are owned by the caller. The library allocates no device
- *     memory; kernels that need scratch take an explicit workspace whose size a
- *     *_workspace_bytes function reports.
+ *   - All buffers are owned by the caller. The kernel launches allocate no
+ *     device memory: those that need scratch take an explicit workspace whose
+ *     size a *_workspace_bytes function reports. Three object constructors do
+ *     allocate and say so where they are declared: knj_moe_stack_create (the
+ *     stack launch's scratch), the residency slot pool and the pinned arena
+ *     (knj_residency.h). The library image also carries a 64 KiB device array
+ *     per GPU, the scratch of knj_q4k_matmul_noalloc_launch.
  *   - Quantized weights are borrowed and immutable: Q4_K superblocks of 144
  *     bytes, row-major [expert][row][K/256][144], base address 16-byte aligned
  *     (KNJ_E_REFUSE otherwise).
@@ -158,6 +162,12 @@ int knj_build_asum_launch(const uint32_t *Act, int32_t *Asum, uint32_t M, uint32
  * (sum_k u_k a_k - 8 * Asum[m][g]); Bq is [N][K/128][68]. */
 int knj_gemm_w4_i8_launch(const uint8_t *Bq, const uint32_t *Act, const int32_t *Asum, float *C, uint32_t M,
                           uint32_t N, uint32_t K, uint32_t n_threads, uint32_t n_blocks, knj_stream_t s);
+
+/* The dot helpers of include/knj_dot.h on the device (kernels/knj_dot.h:117-174;
+ * device mirrors tools/bench/gemm_w4.hip:345-397): out4/out8/out2[i] =
+ * knj_dot4_i32_i8 / knj_dot8_i32_i4 / knj_dot2_i32_i16 (a[i], b[i], acc[i]). */
+int knj_dot_helpers_launch(const int32_t *a, const int32_t *b, const int32_t *acc, int32_t *out4, int32_t *out8,
+                           int32_t *out2, int n, knj_stream_t s);
 
 /* ======================================================================== */
 /* Q4_K decode (kernels/knj_q4k.h, src/loader/dequant.cpp)                  */
@@ -303,7 +313,8 @@ int knj_q4k_matmul_launch(const uint8_t *W, int n_in, int n_out, const void *x, 
  * they call and have no workspace to lend (a serving loop whose pool is fully
  * committed to resident experts, a plug-in host that only receives input and
  * output buffers, start-up-only allocation policies). Scratch is a fixed array
- * inside the library image, knj_q4k_matmul_noalloc_max_scratch() bytes (1 MiB),
+ * inside the library image, knj_q4k_matmul_noalloc_max_scratch() bytes (64 KiB,
+ * enough for 16,256 activation rows),
  * held by every GPU that loads the library until the process exits. Returns
  * KNJ_E_WORKSPACE when knj_q4k_matmul_workspace_bytes(m, n_in) exceeds it. All
  * calls on a device share the array: calls that overlap on the GPU race and must
@@ -404,23 +415,30 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s);
  * knj_moe_ffn_workspace_bytes. */
 int knj_moe_ffn_status(const knj_moe_ffn_args *a, int mode, knj_stream_t s);
 
-/* The resident decode stack for batches of 1..4 tokens in ONE cooperative launch:
- * n_layers layer descriptions (layer l's out is normally layer l+1's x; out must
- * not alias x within a layer), all of one shape, Q4_K down matrices. The loop the
- * reference runs on the host per layer (src/model/model.cpp:399-510) becomes grid
- * barriers inside one kernel. Same arithmetic class as knj_moe_ffn_decode_launch
- * (f32, <= 1e-5 rel-RMSE vs the CPU path; routing decisions identical to it).
- * create validates, copies the layer table to the device and allocates scratch;
- * the workspace fields of the layer descriptions are not used. status() waits for
- * the stream and reports whether a grid barrier gave up (bounded waits). One launch
- * of a stack may be in flight at a time (its barrier words are per stack), and the
- * launch needs every SM of the device (cooperative launch, one CTA per SM). */
+/* The resident decode stack for a decode batch of 1..64 tokens in ONE cooperative
+ * launch: n_layers layer descriptions (layer l's out is normally layer l+1's x; out
+ * must not alias x within a layer), all of one shape, Q4_K down matrices. The loop
+ * the reference runs on the host per layer (src/model/model.cpp:399-510) becomes
+ * grid barriers inside one kernel. Same arithmetic class as
+ * knj_moe_ffn_decode_launch (f32, <= 1e-5 rel-RMSE vs the CPU path; routing
+ * decisions identical to it). create validates, builds the layer table on the
+ * device and ALLOCATES the launch's scratch (cudaMalloc; freed by destroy); the
+ * workspace fields of the layer descriptions are not used. status() waits for the
+ * stream and returns KNJ_E_TIMEOUT when a bounded wait inside the kernel (a grid
+ * barrier or a weight copy) gave up. One launch of a stack may be in flight at a
+ * time (its barrier words are per stack), and the launch needs every SM of the
+ * device (cooperative launch, one CTA per SM). */
 typedef struct knj_moe_stack knj_moe_stack;
 int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_stack **out);
 int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s);
 int knj_moe_stack_status(knj_moe_stack *st, knj_stream_t s);
-/* debug hook: device buffer of 32 u64 that receives global-timer stamps of one CTA's stages; NULL = off */
-int knj_moe_stack_trace(knj_moe_stack *st, unsigned long long *buf32);
+/* Limit of the kernel's bounded waits in SM clock cycles (<= 0: the default, about
+ * a second), and a fault-injection hook for tests of the RETRY path
+ * (docs/BUILD-OUTLINE.md:588-598): stall_first_barrier > 0 raises the first grid
+ * barrier's target by that many arrivals, so the wait runs out, every CTA returns
+ * and status() reports KNJ_E_TIMEOUT; 0 restores normal operation. Nothing traps
+ * and the context stays usable. */
+int knj_moe_stack_set_wait(knj_moe_stack *st, long long wait_cycles, int stall_first_barrier);
 void knj_moe_stack_destroy(knj_moe_stack *st);
 
 /* ======================================================================== */

@@ -10,7 +10,8 @@ import ctypes as C
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libknj_device.so")
+# KNJ_DEVICE_LIB points at another build of the same library (e.g. a measurement build); default: the in-tree one
+LIB_PATH = os.environ.get("KNJ_DEVICE_LIB") or os.path.join(PKG, "libknj_device.so")
 
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
 
@@ -82,6 +83,7 @@ SIGNATURES = {
     "knj_probe_caps_launch": (_i, [_vp, _vp, _vp]),
     "knj_build_asum_launch": (_i, [_vp, _vp, _u32, _u32, _u32, _u32, _vp]),
     "knj_gemm_w4_i8_launch": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _u32, _vp]),
+    "knj_dot_helpers_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "knj_q4k_dequant_launch": (_i, [_vp, _vp, _u64, _vp]),
     "knj_q6k_dequant_launch": (_i, [_vp, _vp, _u64, _vp]),
     "knj_q6k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
@@ -97,7 +99,7 @@ SIGNATURES = {
     "knj_moe_stack_create": (_i, [_vp, _i, C.POINTER(_vp)]),
     "knj_moe_stack_decode_launch": (_i, [_vp, _vp]),
     "knj_moe_stack_status": (_i, [_vp, _vp]),
-    "knj_moe_stack_trace": (_i, [_vp, _vp]),
+    "knj_moe_stack_set_wait": (_i, [_vp, C.c_longlong, _i]),
     "knj_moe_stack_destroy": (None, [_vp]),
     "knj_res_arena_create": (_vp, []),
     "knj_res_arena_alloc": (_vp, [_vp, _u64]),

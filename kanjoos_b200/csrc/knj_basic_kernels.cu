@@ -197,6 +197,17 @@ __global__ void q6k_dequant_kernel(const uint8_t *__restrict__ blocks, float *__
   }
 }
 
+// The three dot helpers of knj_dot.h executed on the device, one (a, b, acc) triple per thread: lets a test pin
+// the device result to the host definition (the reference's device mirrors: tools/bench/gemm_w4.hip:345-397).
+__global__ void dot_helpers_kernel(const int32_t *__restrict__ a, const int32_t *__restrict__ b, const int32_t *__restrict__ acc,
+                                   int32_t *__restrict__ out4, int32_t *__restrict__ out8, int32_t *__restrict__ out2, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  out4[i] = knj_dot4_i32_i8(a[i], b[i], acc[i]);
+  out8[i] = knj_dot8_i32_i4(a[i], b[i], acc[i]);
+  out2[i] = knj_dot2_i32_i16(a[i], b[i], acc[i]);
+}
+
 extern "C" {
 
 int knj_control_launch(uint32_t *out, uint32_t seed, uint32_t n_threads, uint32_t n_blocks, knj_stream_t s) {
@@ -254,6 +265,14 @@ int knj_q6k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks,
                                                                                  : (uint64_t)sm_count() * 16);
   q6k_dequant_kernel<<<grid, 256, 0, as_stream(s)>>>(blocks, out, n);
   return launch_status("knj_q6k_dequant");
+}
+
+int knj_dot_helpers_launch(const int32_t *a, const int32_t *b, const int32_t *acc, int32_t *out4, int32_t *out8,
+                           int32_t *out2, int n, knj_stream_t s) {
+  KNJ_REQUIRE(a && b && acc && out4 && out8 && out2 && n >= 0, "knj_dot_helpers: null pointer");
+  if (n == 0) return KNJ_OK;
+  dot_helpers_kernel<<<(n + 255) / 256, 256, 0, as_stream(s)>>>(a, b, acc, out4, out8, out2, n);
+  return launch_status("dot_helpers_kernel");
 }
 
 }  // extern "C"

@@ -92,6 +92,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Arrival without release ordering: for hand-offs whose data was written to shared memory by the arriving
+// warp itself (the same in-order path the arrival takes) and ordered across its lanes by __syncwarp(). A
+// releasing arrival would first wait for every asynchronous copy the thread still has in flight.
+__device__ __forceinline__ void mbar_arrive_relaxed(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -153,6 +159,21 @@ __device__ __forceinline__ bool mbar_test(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Polling wait with the limit given at run time (clock cycles).
+__device__ __forceinline__ bool mbar_spin_for(uint64_t *bar, uint32_t parity, long long limit_cycles, volatile int *abort_flag) {
+  if (mbar_test(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 64; ++i)
+      if (mbar_test(bar, parity)) return true;
+    if (abort_flag && *abort_flag) return false;
+    if (clock64() - t0 > limit_cycles) {
+      if (abort_flag) *abort_flag = 1;
+      return false;
+    }
+  }
+}
 __device__ __forceinline__ bool mbar_spin(uint64_t *bar, uint32_t parity, volatile int *abort_flag = nullptr) {
   if (mbar_test(bar, parity)) return true;
   const long long t0 = clock64();
@@ -201,7 +222,7 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 // D(16x8,f32) += A(16x16,f16,row) * B(16x8,f16,col)
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                               uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -211,7 +232,7 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
 // instead of clearing four registers first)
 __device__ __forceinline__ void mma_f16_16816_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                    uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));

@@ -12,17 +12,20 @@
 //     the tensor core and d is applied once per superblock and row in f32;
 //   * activations are split into a high and a low fp16 plane under a power-of-two
 //     scale per (token, superblock) -- together ~22 significant bits -- so the
-//     products and the f32 accumulation of mma.sync are exact to f32 level;
+//     products and the f32 accumulation of mma.sync are exact to f32 level; the
+//     two planes of a token sit in adjacent MMA columns, so one m16n8k16 covers
+//     four tokens and the planes are summed in-thread;
 //   * the min term is one more MMA per superblock: A = the eight 6-bit m_sb,
 //     B = the per-32 sums of the token's planes.
 //
-// Work split. A TEAM of `ks` warps owns a 16-row tile (8 gate + 8 up rows of the
-// same output indices, or 16 rows of one matrix); warp `part` of the team owns
-// superblock `part` of every row, i.e. the K range [256 part, 256 part + 256).
-// The activations of that K range for up to 8 tokens live in the warp's REGISTERS
-// as ready-made B fragments for as long as the team stays with one expert, so the
-// inner loop reads nothing but weights. Per tile the warps' partial sums meet in
-// shared memory (fixed order, one named barrier per tile).
+// Work split. A JOB is one expert with up to four of its tokens; its activations
+// are converted once per CTA into a PANEL in shared memory, laid out so that a
+// warp's fragment loads are 128 contiguous bytes per quarter-warp. A warp owns a
+// 16-row tile (8 gate + 8 up rows of the same output indices, or 16 rows of one
+// matrix) for the whole K: it walks the superblocks, each arriving as one TMA box
+// (16 rows x 144 bytes) in the warp's own ring, and keeps the running sums in
+// registers. Warps never exchange anything; gate and up of an output meet in one
+// thread, so SiLU*up is applied there.
 //
 // Fragment bookkeeping (m16n8k16, lane = 4 g + t). Lane t of a row owns code
 // group t of the superblock: bytes 32t..32t+31 of qs = sub-block 2t in the low
@@ -30,7 +33,7 @@
 // Word i (bytes 4i..4i+3) feeds one MMA step per nibble kind: bytes 0 and 2 are
 // the k pair (2t, 2t+1), bytes 1 and 3 the pair (2t+8, 2t+9). The activation
 // planes keep every aligned group of four k in the order (0,2,1,3), so the B
-// fragments of step i are 8 consecutive bytes.
+// fragments of a step are 8 consecutive bytes. MMA column n = 2 * token + plane.
 #pragma once
 #include "knj_common.cuh"
 #include "knj_q4k.h"
@@ -40,8 +43,12 @@ namespace q4e {
 
 constexpr int kTileRows = 16;
 constexpr int kStageBytes = kTileRows * KNJ_Q4K_BYTES;  // 2304: one superblock column of a 16-row tile
-constexpr int kScratchBytes = 1088;                     // per warp: hi plane 512 | lo plane 512 | 8 sums | pad
-constexpr int kMaxTok = 8;                              // tokens of one job (the n dimension of the MMA)
+constexpr int kJobTok = 4;                              // tokens of one job (x 2 planes = the n dimension of the MMA)
+// Panel of one (token, superblock): eight 128-byte units u = 4 * (sub-block & 1) + (16-byte piece of the
+// sub-block's plane); inside a unit, 16 bytes per (plane, t) at 16 * (4 * plane + t): the eight lanes of a
+// quarter-warp (planes 0/1 of one token, t = 0..3) read one unit without bank conflicts. Then the per-32
+// sums / 64 as fp16 pairs (sub-blocks 2t, 2t+1): high plane at 1024 + 4t, low plane at 1040 + 4t.
+constexpr int kPanelBytes = 1088;
 
 __device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
   uint32_t d;
@@ -62,79 +69,9 @@ __device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi) {
   return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
 }
 
-// The activations of one job as B fragments: lane (g, t) holds token g, sub-blocks 2t and 2t+1 of the warp's
-// superblock. h/l[2i], h/l[2i+1]: step i of sub-block 2t; [16 + 2i], [17 + 2i]: sub-block 2t+1.
-struct BFrag {
-  uint32_t h[32], l[32];
-  uint32_t sxh, sxl;  // (sum of sub-block 2t, sum of 2t+1) / 64, high and low fp16 plane
-  float inv0, inv1;   // 1 / plane scale of tokens 2t and 2t+1 (the columns this lane's accumulators hold)
-};
-
-__device__ __forceinline__ void bfrag_clear(BFrag &b) {
-#pragma unroll
-  for (int i = 0; i < 32; ++i) b.h[i] = b.l[i] = 0u;
-  b.sxh = b.sxl = 0u;
-  b.inv0 = b.inv1 = 0.f;
-}
-
-// One token's 256 values of this warp's superblock -> fp16 planes in the warp's scratch (all lanes take part,
-// lane l converts values 8l..8l+7), then the lanes of MMA column `j` (g == j) pick up their fragments.
-// Returns nothing; b.inv0 / b.inv1 are set when j is one of this lane's accumulator columns.
-__device__ __forceinline__ void bfrag_take_token(BFrag &b, const float (&v)[8], int j, uint8_t *scratch, int lane) {
-  const int g = lane >> 2, t = lane & 3;
-  float amax = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  amax = warp_max(amax);
-  // power-of-two scale that puts the largest magnitude in [2^13, 2^14)
-  const int be = (int)(__float_as_uint(amax) >> 23);
-  int e = 0;
-  if (amax > 0.f && be != 0xff) e = max(-120, min(120, 140 - be));
-  const float s = __uint_as_float((uint32_t)(127 + e) << 23);
-  const float inv = __uint_as_float((uint32_t)(127 - e) << 23);
-  uint32_t hw[4], lw[4];
-  float part = 0.f;
-#pragma unroll
-  for (int q = 0; q < 2; ++q) {
-    __half hh[4], ll[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float f = v[4 * q + i] * s;
-      hh[i] = __float2half_rn(f);
-      const float hf = __half2float(hh[i]);
-      ll[i] = __float2half_rn(f - hf);
-      part += hf + __half2float(ll[i]);
-    }
-    hw[2 * q] = pack_h2(hh[0], hh[2]);
-    hw[2 * q + 1] = pack_h2(hh[1], hh[3]);
-    lw[2 * q] = pack_h2(ll[0], ll[2]);
-    lw[2 * q + 1] = pack_h2(ll[1], ll[3]);
-  }
-  __syncwarp();  // the previous token's fragments have been read
-  *reinterpret_cast<uint4 *>(scratch + 16 * lane) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-  *reinterpret_cast<uint4 *>(scratch + 512 + 16 * lane) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
-  part += __shfl_xor_sync(0xffffffffu, part, 1);
-  part += __shfl_xor_sync(0xffffffffu, part, 2);
-  if ((lane & 3) == 0) reinterpret_cast<float *>(scratch + 1024)[lane >> 2] = part;
-  __syncwarp();
-  if (g == j) {
-    const uint4 *ph = reinterpret_cast<const uint4 *>(scratch + 128 * t);
-    const uint4 *pl = reinterpret_cast<const uint4 *>(scratch + 512 + 128 * t);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint4 a = ph[i], c = pl[i];
-      b.h[4 * i] = a.x; b.h[4 * i + 1] = a.y; b.h[4 * i + 2] = a.z; b.h[4 * i + 3] = a.w;
-      b.l[4 * i] = c.x; b.l[4 * i + 1] = c.y; b.l[4 * i + 2] = c.z; b.l[4 * i + 3] = c.w;
-    }
-    const float2 sx = *reinterpret_cast<const float2 *>(scratch + 1024 + 8 * t);
-    const float s0 = sx.x * 0.015625f, s1 = sx.y * 0.015625f;  // |sum| < 32 * 2^14: / 64 keeps it inside fp16
-    const __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
-    b.sxh = pack_h2(h0, h1);
-    b.sxl = pack_h2(__float2half_rn(s0 - __half2float(h0)), __float2half_rn(s1 - __half2float(h1)));
-  }
-  if (j == 2 * t) b.inv0 = inv;
-  if (j == 2 * t + 1) b.inv1 = inv;
-}
+// x * sigmoid(x). The plain division would take its slow path whenever exp(-x) overflows; the fast one is
+// within 2 ulp for divisors below 2^126 and returns 0 beyond, which is the limit value here.
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.0f + expf(-x)); }
 
 // Eight consecutive activations as f32 (16-byte aligned source).
 __device__ __forceinline__ void load8_f32(const void *base, int dtype, int64_t elem, float (&v)[8]) {
@@ -159,6 +96,59 @@ __device__ __forceinline__ void load8_f32(const void *base, int dtype, int64_t e
   }
 }
 
+// One warp converts the 256 values of one (token, superblock) -- lane l holds values 8l..8l+7 -- into the panel
+// at `dst`; returns 1 / scale (the same in every lane).
+__device__ __forceinline__ float panel_convert(const float (&v)[8], uint8_t *dst, int lane) {
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = warp_max(amax);
+  // power-of-two scale that puts the largest magnitude in [2^13, 2^14)
+  const int be = (int)(__float_as_uint(amax) >> 23);
+  int e = 0;
+  if (amax > 0.f && be != 0xff) e = max(-120, min(120, 140 - be));
+  const float s = __uint_as_float((uint32_t)(127 + e) << 23);
+  uint32_t hw[4], lw[4];
+  float part = 0.f;
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {
+    __half hh[4], ll[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float f = v[4 * q + i] * s;
+      hh[i] = __float2half_rn(f);
+      const float hf = __half2float(hh[i]);
+      ll[i] = __float2half_rn(f - hf);
+      part += hf + __half2float(ll[i]);
+    }
+    hw[2 * q] = pack_h2(hh[0], hh[2]);
+    hw[2 * q + 1] = pack_h2(hh[1], hh[3]);
+    lw[2 * q] = pack_h2(ll[0], ll[2]);
+    lw[2 * q + 1] = pack_h2(ll[1], ll[3]);
+  }
+  const int sb = lane >> 2, t = sb >> 1, u = 4 * (sb & 1) + (lane & 3);
+  *reinterpret_cast<uint4 *>(dst + 128 * u + 16 * t) = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+  *reinterpret_cast<uint4 *>(dst + 128 * u + 16 * (4 + t)) = make_uint4(lw[0], lw[1], lw[2], lw[3]);
+  part += __shfl_xor_sync(0xffffffffu, part, 1);
+  part += __shfl_xor_sync(0xffffffffu, part, 2);              // the sub-block's sum, in its four lanes
+  const float next = __shfl_down_sync(0xffffffffu, part, 4);  // the following sub-block's
+  if ((lane & 7) == 0) {
+    const float s0 = part * 0.015625f, s1 = next * 0.015625f;  // |sum| < 32 * 2^14: / 64 keeps it inside fp16
+    const __half h0 = __float2half_rn(s0), h1 = __float2half_rn(s1);
+    *reinterpret_cast<uint32_t *>(dst + 1024 + 4 * t) = pack_h2(h0, h1);
+    *reinterpret_cast<uint32_t *>(dst + 1040 + 4 * t) =
+        pack_h2(__float2half_rn(s0 - __half2float(h0)), __float2half_rn(s1 - __half2float(h1)));
+  }
+  return __uint_as_float((uint32_t)(127 - e) << 23);
+}
+
+// Weight row (0..7) that fragment row g of a lane stands for. A quarter-warp reads two rows at a time (g = 2j,
+// 2j + 1), 64 bytes of each; they fall on disjoint shared-memory banks when the rows are 16 or 64 bytes apart
+// modulo 128: adjacent rows for the 144-byte pitch, rows two apart for the 288-byte pitch.
+__device__ __forceinline__ int tile_row(int g, int pitch) {
+  return pitch == KNJ_Q4K_BYTES ? g : ((g & 4) | ((g & 1) << 1) | ((g >> 1) & 1));
+}
+
 // (sc[2t], sc[2t+1]) and (m[2t], m[2t+1]) of a superblock header as two bytes each (get_scale_min_k4,
 // src/loader/dequant.cpp:64-77). sel16 picks halfword (t & 1) of a word, hi_var = (t >= 2).
 __device__ __forceinline__ void header_pairs(const uint4 &hd, uint32_t sel16, bool hi_var, uint32_t &sc2, uint32_t &m2) {
@@ -170,19 +160,32 @@ __device__ __forceinline__ void header_pairs(const uint4 &hd, uint32_t sel16, bo
   m2 = hi_var ? m_hi : m_lo;
 }
 
-// One tile part: the warp's superblock column of a 16-row tile (dense rows of 144 bytes at `stage`) times the
-// job's activations. Returns, for this lane's accumulator positions -- (row g, tokens 2t, 2t+1) and
-// (row g+8, tokens 2t, 2t+1) -- the superblock's contribution in activation units.
-__device__ __forceinline__ float4 tile_part(const uint8_t *stage, const BFrag &b, int lane) {
+// One tile part: a superblock column of a 16-row tile (rows `pitch` bytes apart, the superblock at `stage` in
+// each) times the panel `pan` of the job's four tokens for that superblock (token stride `tok_stride` bytes).
+// Lane (g, t) works on weight rows wrow and wrow + 8 of the tile (see tile_row) and receives the superblock's
+// contribution to (row wrow, token t) in rg and to (row wrow + 8, token t) in rh, in the units of the token's
+// scaled planes; the caller multiplies by 1 / scale.
+__device__ __forceinline__ void tile_part(const uint8_t *stage, int pitch, int wrow, const uint8_t *pan, int tok_stride,
+                                          int lane, float &rg, float &rh) {
   const int g = lane >> 2, t = lane & 3;
-  const uint8_t *rg = stage + g * KNJ_Q4K_BYTES, *rh = stage + (g + 8) * KNJ_Q4K_BYTES;
-  const uint4 hg = *reinterpret_cast<const uint4 *>(rg), hh = *reinterpret_cast<const uint4 *>(rh);
-  const uint4 wg0 = *reinterpret_cast<const uint4 *>(rg + KNJ_Q4K_OFF_QS + 32 * t);
-  const uint4 wh0 = *reinterpret_cast<const uint4 *>(rh + KNJ_Q4K_OFF_QS + 32 * t);
-  const uint4 wg1 = *reinterpret_cast<const uint4 *>(rg + KNJ_Q4K_OFF_QS + 32 * t + 16);
-  const uint4 wh1 = *reinterpret_cast<const uint4 *>(rh + KNJ_Q4K_OFF_QS + 32 * t + 16);
+  const uint8_t *wg_row = stage + wrow * pitch, *wh_row = stage + (wrow + 8) * pitch;
+  const uint4 hg = *reinterpret_cast<const uint4 *>(wg_row), hh = *reinterpret_cast<const uint4 *>(wh_row);
+  const uint4 wg0 = *reinterpret_cast<const uint4 *>(wg_row + KNJ_Q4K_OFF_QS + 32 * t);
+  const uint4 wh0 = *reinterpret_cast<const uint4 *>(wh_row + KNJ_Q4K_OFF_QS + 32 * t);
+  const uint4 wg1 = *reinterpret_cast<const uint4 *>(wg_row + KNJ_Q4K_OFF_QS + 32 * t + 16);
+  const uint4 wh1 = *reinterpret_cast<const uint4 *>(wh_row + KNJ_Q4K_OFF_QS + 32 * t + 16);
   const uint32_t wg[8] = {wg0.x, wg0.y, wg0.z, wg0.w, wg1.x, wg1.y, wg1.z, wg1.w};
   const uint32_t wh[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
+  // this lane's column: token g / 2, plane g & 1
+  const uint8_t *col = pan + (size_t)(g >> 1) * tok_stride;
+  const uint8_t *bsrc = col + 16 * (4 * (g & 1) + t);
+  uint32_t bp[32];
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const uint4 q = *reinterpret_cast<const uint4 *>(bsrc + 128 * u);
+    bp[4 * u] = q.x; bp[4 * u + 1] = q.y; bp[4 * u + 2] = q.z; bp[4 * u + 3] = q.w;
+  }
+  const uint32_t sx = *reinterpret_cast<const uint32_t *>(col + 1024 + 16 * (g & 1) + 4 * t);
 
   const uint32_t sel16 = (t & 1) ? 0x4432u : 0x4410u;
   uint32_t scg, mg, sch, mh;
@@ -198,41 +201,209 @@ __device__ __forceinline__ float4 tile_part(const uint8_t *stage, const BFrag &b
   const uint32_t mmg = sub_f16x2(__byte_perm(mg, 0x64646464u, 0x4140u), k1024);
   const uint32_t mmh = sub_f16x2(__byte_perm(mh, 0x64646464u, 0x4140u), k1024);
 
-  float cm[4], ch[4], cl[4];
-  mma_f16_16816_zero(cm, mmg, mmh, mmg, mmh, b.sxh, b.sxl);
+  // four independent accumulator chains (nibble kind x step parity): the MMAs of one chain depend on each other
+  float cm[4], c0[4], c1[4], c2[4], c3[4];
+  mma_f16_16816_zero(cm, mmg, mmh, 0u, 0u, sx, 0u);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) ch[i] = cl[i] = 0.f;
+  for (int i = 0; i < 4; ++i) c0[i] = c1[i] = c2[i] = c3[i] = 0.f;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const uint32_t xg = wg[i], xh = wh[i], yg = xg >> 8, yh = xh >> 8;
     {
       const uint32_t a0 = mul_f16x2(xg & 0x000f000fu, sEg), a1 = mul_f16x2(xh & 0x000f000fu, sEh);
       const uint32_t a2 = mul_f16x2(yg & 0x000f000fu, sEg), a3 = mul_f16x2(yh & 0x000f000fu, sEh);
-      mma_f16_16816(ch, a0, a1, a2, a3, b.h[2 * i], b.h[2 * i + 1]);
-      mma_f16_16816(cl, a0, a1, a2, a3, b.l[2 * i], b.l[2 * i + 1]);
+      if (i & 1) mma_f16_16816(c1, a0, a1, a2, a3, bp[2 * i], bp[2 * i + 1]);
+      else mma_f16_16816(c0, a0, a1, a2, a3, bp[2 * i], bp[2 * i + 1]);
     }
     {
       const uint32_t a0 = mul_f16x2(xg & 0x00f000f0u, sOg), a1 = mul_f16x2(xh & 0x00f000f0u, sOh);
       const uint32_t a2 = mul_f16x2(yg & 0x00f000f0u, sOg), a3 = mul_f16x2(yh & 0x00f000f0u, sOh);
-      mma_f16_16816(ch, a0, a1, a2, a3, b.h[16 + 2 * i], b.h[17 + 2 * i]);
-      mma_f16_16816(cl, a0, a1, a2, a3, b.l[16 + 2 * i], b.l[17 + 2 * i]);
+      if (i & 1) mma_f16_16816(c3, a0, a1, a2, a3, bp[16 + 2 * i], bp[17 + 2 * i]);
+      else mma_f16_16816(c2, a0, a1, a2, a3, bp[16 + 2 * i], bp[17 + 2 * i]);
     }
   }
-  // codes carried 2^-24, the sums 1/64
+  // codes carried 2^-24, the sums 1/64; columns 2t and 2t+1 are the two planes of token t
   const float dg = __half2float(__ushort_as_half((unsigned short)(hg.x & 0xffffu))) * 16777216.0f;
   const float ng = __half2float(__ushort_as_half((unsigned short)(hg.x >> 16))) * 64.0f;
   const float dh = __half2float(__ushort_as_half((unsigned short)(hh.x & 0xffffu))) * 16777216.0f;
   const float nh = __half2float(__ushort_as_half((unsigned short)(hh.x >> 16))) * 64.0f;
-  float4 r;
-  r.x = (dg * (ch[0] + cl[0]) - ng * cm[0]) * b.inv0;
-  r.y = (dg * (ch[1] + cl[1]) - ng * cm[1]) * b.inv1;
-  r.z = (dh * (ch[2] + cl[2]) - nh * cm[2]) * b.inv0;
-  r.w = (dh * (ch[3] + cl[3]) - nh * cm[3]) * b.inv1;
-  return r;
+  const float sg = ((c0[0] + c1[0]) + (c2[0] + c3[0])) + ((c0[1] + c1[1]) + (c2[1] + c3[1]));
+  const float sh = ((c0[2] + c1[2]) + (c2[2] + c3[2])) + ((c0[3] + c1[3]) + (c2[3] + c3[3]));
+  rg = dg * sg - ng * (cm[0] + cm[1]);
+  rh = dh * sh - nh * (cm[2] + cm[3]);
 }
 
-__device__ __forceinline__ void team_sync(int team, int threads) {
-  asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(threads) : "memory");
+// ---------------------------------------------------------------------------
+// One projection phase of a CTA: its run [u0, u1) of the flat (job, tile) list.
+// ---------------------------------------------------------------------------
+constexpr int kWarps = 16;      // warps of a CTA that runs a phase
+constexpr int kMaxStages = 4;   // TMA boxes in flight per warp, at most
+
+struct JobTable {        // in shared memory, the same in every CTA
+  int *jbase;            // [257] first job of active expert a; entries past the active ones hold the total
+  int *uexp;             // [256] expert id of active expert a
+};
+
+struct PhaseShape {
+  int N;                 // output rows per expert
+  int nsb, sbs, stages;  // superblocks per row, per TMA box, boxes in flight per warp
+  int tiles;             // tiles per expert: N / 8 (gate+up) or N / 16
+};
+
+struct PhaseSmem {       // per CTA
+  uint8_t *ring;         // kWarps * stages * sbs * kStageBytes
+  uint8_t *panels;       // 2 jobs * kJobTok * nsb * kPanelBytes
+  uint64_t *bars;        // kWarps * kMaxStages, initialised with count 1
+  float *inv;            // [2][kJobTok][16]
+  int *pair;             // [2][kJobTok]
+  volatile int *fail;    // raised by the first wait that gives up
+};
+
+__host__ __device__ inline size_t phase_ring_bytes(int sbs, int stages) { return (size_t)kWarps * stages * sbs * kStageBytes; }
+__host__ __device__ inline size_t phase_panel_bytes(int nsb) { return (size_t)2 * kJobTok * nsb * kPanelBytes; }
+
+// active expert of a job: the last a whose first job is not beyond it
+__device__ __forceinline__ int job_locate(const int *jbase, int job) {
+  int lo = 0, hi = 255;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (jbase[mid] <= job) lo = mid;
+    else hi = mid - 1;
+  }
+  return lo;
+}
+
+// Runs tiles [u0, u1) of the flat list, two jobs at a time. All kWarps * 32 threads of the CTA call it together
+// (it contains CTA barriers). job_token(job, a, tk, pair, row) -> bool says whether token slot tk of the job
+// exists and names its output row (pair) and its activation row; load_row(row, sb, lane, v) fetches values
+// 256 sb + 8 lane .. + 7 of that activation row. out0/out1/out2 as for the launches: DUAL -> G, U, silu(G) * U;
+// otherwise out0 = Y. Bit s of `parity` is the phase the warp's next wait on its barrier s expects (0 after
+// initialisation); `ok` turns false when a wait gave up (the rest of the phase is then skipped, the CTA barriers
+// are still met).
+template <bool DUAL, class JobToken, class LoadRow>
+__device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem &sm, const JobTable &jt, int u0, int u1,
+                                          const CUtensorMap *map0, const CUtensorMap *map1, float *out0, float *out1,
+                                          float *out2, long long wait_cycles, unsigned &parity, bool &ok, JobToken job_token,
+                                          LoadRow load_row, int trace_mode = 0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int nsb = sh.nsb, S = sh.stages, sbs = sh.sbs, nbox = nsb / sbs, tiles = sh.tiles;
+  const int stage_bytes = sbs * kStageBytes, pitch = sbs * KNJ_Q4K_BYTES;
+  const int wrow = tile_row(g, pitch);
+  const int rows_per_tile = DUAL ? 8 : 16;
+  const int job_stride = kJobTok * nsb * kPanelBytes, tok_stride = nsb * kPanelBytes;
+  uint8_t *ring = sm.ring + (size_t)warp * S * stage_bytes;
+  uint64_t *bars = sm.bars + warp * kMaxStages;
+  if (u0 >= u1) return;
+  const int jfirst = u0 / tiles, jlast = (u1 - 1) / tiles;
+  for (int jb = jfirst; jb <= jlast; jb += 2) {
+    const int njr = min(2, jlast - jb + 1);
+    __syncthreads();  // the previous round's tiles are done with the panels
+    // ---- panels of the round's jobs: one warp per (job, token, superblock)
+    for (int item = warp; item < njr * kJobTok * nsb; item += kWarps) {
+      const int sb = item % nsb, jtk = item / nsb, tk = jtk % kJobTok, jr = jtk / kJobTok;
+      const int job = jb + jr, a = job_locate(jt.jbase, job);
+      int pair = -1, row = 0;
+      if (job_token(job, a, tk, pair, row)) {
+        float v[8];
+        load_row(row, sb, lane, v);
+        if (trace_mode != 3) {
+          const float inv = panel_convert(v, sm.panels + (size_t)jr * job_stride + (size_t)tk * tok_stride + (size_t)sb * kPanelBytes, lane);
+          if (lane == 0) sm.inv[(jr * kJobTok + tk) * 16 + sb] = inv;
+        }
+      } else {
+        pair = -1;
+      }
+      if (sb == 0 && lane == 0) sm.pair[jr * kJobTok + tk] = pair;
+    }
+    __syncthreads();
+
+    // ---- this warp's tiles of the round: r0 + warp, r0 + warp + 16, ...
+    const int r0 = max(u0, jb * tiles), r1 = min(u1, (jb + 2) * tiles);
+    const int n_mine = r0 + warp < r1 ? (r1 - r0 - warp + kWarps - 1) / kWarps : 0;
+    const int n_items = n_mine * nbox;
+    int p_row = 0;  // first weight row of the tile the producer cursor is in (boxes are issued in order)
+    auto issue = [&](int i) {  // box i of the round: box i % nbox of this warp's tile i / nbox
+      const int bx = i % nbox;
+      if (bx == 0) {
+        const int u = r0 + warp + kWarps * (i / nbox), job = u / tiles;
+        p_row = jt.uexp[job_locate(jt.jbase, job)] * sh.N + (u - job * tiles) * rows_per_tile;
+      }
+      if (lane == 0) {
+        const int stage = i % S;
+        uint8_t *dst = ring + (size_t)stage * stage_bytes;
+        fence_proxy_async();
+        mbar_expect_tx(&bars[stage], (uint32_t)stage_bytes);
+        tma_load_rows(dst, map0, bx * (pitch / 4), p_row, &bars[stage]);
+        if (DUAL) tma_load_rows(dst + 8 * pitch, map1, bx * (pitch / 4), p_row, &bars[stage]);
+      }
+    };
+    if (ok && trace_mode != 2)
+      for (int i = 0; i < S && i < n_items; ++i) issue(i);
+
+    float rg = 0.f, rh = 0.f;
+    int jr = 0, n0 = 0;
+    for (int i = 0; i < n_items; ++i) {
+      const int bx = i % nbox;
+      if (bx == 0) {
+        const int u = r0 + warp + kWarps * (i / nbox), job = u / tiles;
+        jr = job - jb;
+        n0 = (u - job * tiles) * rows_per_tile;
+        rg = rh = 0.f;
+      }
+      const int stage = i % S;
+      if (ok && trace_mode != 2) {
+        if (!mbar_wait_for(&bars[stage], (parity >> stage) & 1u, wait_cycles, sm.fail)) ok = false;
+        parity ^= 1u << stage;
+      }
+      if (ok) {
+        if (trace_mode != 1)
+          for (int k = 0; k < sbs; ++k) {
+            const int sb = bx * sbs + k;
+            float pg, ph;
+            tile_part(ring + (size_t)stage * stage_bytes + k * KNJ_Q4K_BYTES, pitch, wrow,
+                      sm.panels + (size_t)jr * job_stride + (size_t)sb * kPanelBytes, tok_stride, lane, pg, ph);
+            const float inv = sm.inv[(jr * kJobTok + t) * 16 + sb];
+            rg = fmaf(pg, inv, rg);
+            rh = fmaf(ph, inv, rh);
+          }
+        __syncwarp();  // every lane is done with the stage
+        if (trace_mode != 2 && i + S < n_items) issue(i + S);
+      }
+      if (bx == nbox - 1 && ok) {
+        const int pair = sm.pair[jr * kJobTok + t];
+        if (pair >= 0) {
+          if (DUAL) {
+            const size_t o = (size_t)pair * sh.N + n0 + wrow;
+            if (out0) out0[o] = rg;
+            if (out1) out1[o] = rh;
+            if (out2) out2[o] = silu(rg) * rh;
+          } else {
+            out0[(size_t)pair * sh.N + n0 + wrow] = rg;
+            out0[(size_t)pair * sh.N + n0 + wrow + 8] = rh;
+          }
+        }
+      }
+    }
+  }
+}
+
+// Jobs per active expert -> exclusive prefix in jbase[0..256] (jbase[a] holds the job count of active expert a on
+// entry, 0 past the active ones). Called by warp 0 after a CTA barrier; a CTA barrier must follow.
+__device__ __forceinline__ void job_prefix(int *jbase, int lane) {
+  int v[8], sum = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { v[i] = jbase[lane * 8 + i]; sum += v[i]; }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int up = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += up;
+  }
+  int base = incl - sum;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { jbase[lane * 8 + i] = base; base += v[i]; }
+  if (lane == 31) jbase[256] = incl;
 }
 
 }  // namespace q4e

@@ -4,15 +4,15 @@
 // (tools/bench/q4k_stream_ffn.hip:834-882 knj_q4k_proj) and Model::matmul
 // (src/model/model.cpp:326-380), all on the tile engine of knj_q4k_engine.cuh.
 //
-// One persistent CTA per SM, 16 warps in teams of `ks` = K / 256 warps. The work
-// of a launch is the flat list (job, tile): a JOB is one active expert with up to
-// 8 of its tokens (an expert with more tokens yields several jobs; its weights
-// then come from L2 after the first), a tile is 16 weight rows. Every team takes
-// an equal contiguous run of that list. Each warp runs its own ring of TMA boxes
-// (16 rows x 144 bytes: its superblock column of a tile), filled `stages` tiles
-// ahead and across job boundaries, so the weight stream never waits for the
-// arithmetic; the only other memory traffic is the job's activation rows, read
-// once per job into registers, and the 16 x 8 results per tile.
+// One persistent CTA per SM, 16 independent warps. The work of a launch is the
+// flat list (job, tile): a JOB is one active expert with up to 4 of its tokens (an
+// expert with more tokens yields several jobs; its weights then come from L2 after
+// the first), a tile is 16 weight rows. Every CTA takes an equal contiguous run of
+// that list, two jobs at a time: the CTA converts the two jobs' activation rows
+// into shared-memory panels once, then warp w takes every 16th tile of the run,
+// walks its superblocks through its own ring of TMA boxes (filled `stages` boxes
+// ahead, across tile boundaries) and stores the 16 x 4 results itself. No partial
+// sums cross warps and nothing but weights is read in the inner loop.
 #include "knj_common.cuh"
 #include "knj_q4k.h"
 #include "knj_q4k_engine.cuh"
@@ -21,9 +21,7 @@ using namespace knj;
 
 namespace {
 
-constexpr int kThreads = 512;
-constexpr int kWarps = kThreads / 32;
-constexpr int kStages = 4;
+constexpr int kThreads = q4e::kWarps * 32;
 
 struct ProjParams {
   const uint8_t *W0;  // gate (dual) or the single matrix
@@ -39,46 +37,51 @@ struct ProjParams {
   float *out0;  // dual: G        single: Y
   float *out1;  // dual: U
   float *out2;  // dual: A = silu(G)*U
-  int N, K, row_div, tiles_per_expert;
+  int K, row_div;
   int n_experts;  // length of exp_list / pair_cnt
-  int ks;         // warps per team = superblocks per row
-  int teams;      // teams per CTA
+  q4e::PhaseShape shape;
   int64_t idxStride;
   int *status;    // optional: set to 1 when a bounded wait gave up
-  long long wait_cycles;  // limit of every wait inside the kernel
-  CUtensorMap map0, map1;  // TMA descriptors of W0 / W1: box = one superblock x 8 (dual) or 16 rows
+  long long wait_cycles;   // limit of every wait inside the kernel
+  CUtensorMap map0, map1;  // TMA descriptors of W0 / W1: box = sbs superblocks x 8 (dual) or 16 rows
 };
 
 struct ProjSmem {
-  size_t ring, scratch, red, bars, total;
+  size_t ring, panels, bars, total;
 };
-__host__ __device__ inline ProjSmem proj_smem() {
+__host__ __device__ inline ProjSmem proj_smem(int nsb, int sbs, int stages) {
   ProjSmem m;
   m.ring = 0;
-  m.scratch = m.ring + (size_t)kWarps * kStages * q4e::kStageBytes;
-  m.red = m.scratch + (size_t)kWarps * q4e::kScratchBytes;
-  m.bars = m.red + (size_t)2 * kWarps * 32 * sizeof(float4);
-  m.total = m.bars + (size_t)kWarps * kStages * 8;
+  m.panels = m.ring + q4e::phase_ring_bytes(sbs, stages);
+  m.bars = m.panels + q4e::phase_panel_bytes(nsb);
+  m.total = m.bars + (size_t)q4e::kWarps * q4e::kMaxStages * 8;
   return m;
 }
+
+#ifdef KNJ_TRACE
+// Measurement build only: experiment modes (1: no arithmetic; 2: no weight copies; 3: no activation panels).
+__device__ int g_trace_mode = 0;
+#endif
 
 template <bool DUAL>
 __global__ void __launch_bounds__(kThreads, 1) q4k_proj_kernel(const __grid_constant__ ProjParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
-  __shared__ int s_jbase[257];  // first job of active expert a (entries past the active ones hold the total)
+  __shared__ int s_jbase[257];
   __shared__ int s_uexp[256], s_ucnt[256];
+  __shared__ float s_inv[2 * q4e::kJobTok * 16];
+  __shared__ int s_pair[2 * q4e::kJobTok];
   __shared__ int s_fail;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const int ks = p.ks, team = warp / ks, part = warp - team * ks;
-  const ProjSmem lay = proj_smem();
-  uint8_t *ring = smem + lay.ring + (size_t)warp * kStages * q4e::kStageBytes;
-  uint8_t *scratch = smem + lay.scratch + (size_t)warp * q4e::kScratchBytes;
-  float4 *red = reinterpret_cast<float4 *>(smem + lay.red);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + lay.bars) + warp * kStages;
-
+  const ProjSmem lay = proj_smem(p.shape.nsb, p.shape.sbs, p.shape.stages);
+  q4e::PhaseSmem sm;
+  sm.ring = smem + lay.ring;
+  sm.panels = smem + lay.panels;
+  sm.bars = reinterpret_cast<uint64_t *>(smem + lay.bars);
+  sm.inv = s_inv;
+  sm.pair = s_pair;
+  sm.fail = &s_fail;
   if (lane == 0)
-    for (int s = 0; s < kStages; ++s) mbar_init(&bars[s], 1);
+    for (int s = 0; s < q4e::kMaxStages; ++s) mbar_init(&sm.bars[warp * q4e::kMaxStages + s], 1);
   if (threadIdx.x == 0) s_fail = 0;
   mbar_init_fence();
   grid_dep_wait();  // the plan and the activation rows come from earlier launches
@@ -93,164 +96,32 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_proj_kernel(const __grid_cons
     }
     s_uexp[a] = ex;
     s_ucnt[a] = c;
-    s_jbase[a] = (c + q4e::kMaxTok - 1) / q4e::kMaxTok;
+    s_jbase[a] = (c + q4e::kJobTok - 1) / q4e::kJobTok;
   }
   __syncthreads();
-  if (warp == 0) {
-    int v[8], sum = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { v[i] = s_jbase[lane * 8 + i]; sum += v[i]; }
-    int incl = sum;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
-    }
-    int base = incl - sum;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { s_jbase[lane * 8 + i] = base; base += v[i]; }
-    if (lane == 31) s_jbase[256] = incl;
-  }
+  if (warp == 0) q4e::job_prefix(s_jbase, lane);
   __syncthreads();
-  if (team >= p.teams) return;  // warps beyond the last whole team (no CTA-wide barrier follows)
 
-  const int tiles = p.tiles_per_expert;
-  const long long U = (long long)s_jbase[256] * tiles;  // < 2^31 (checked by the launcher)
-  const long long gteam = (long long)blockIdx.x * p.teams + team, nteams = (long long)gridDim.x * p.teams;
-  const int u0 = (int)(U * gteam / nteams), u1 = (int)(U * (gteam + 1) / nteams);
-  if (u0 >= u1) return;
-  const int rows_per_tile = DUAL ? 8 : 16;
-  volatile int *fail = &s_fail;
-
-  // active expert of a job: the last a whose first job is not beyond it
-  auto locate = [&](int job) {
-    int lo = 0, hi = 255;
-    while (lo < hi) {
-      const int mid = (lo + hi + 1) >> 1;
-      if (s_jbase[mid] <= job) lo = mid;
-      else hi = mid - 1;
-    }
-    return lo;
-  };
-
-  // ---- producer cursor (lane 0 issues; every lane keeps the same counters)
-  int p_job = u0 / tiles, p_tile = u0 - p_job * tiles;
-  int p_a = locate(p_job);
-  int pu = u0;
-  auto issue = [&]() {
-    const int stage = (pu - u0) % kStages;
-    if (lane == 0) {
-      const int row = s_uexp[p_a] * p.N + p_tile * rows_per_tile;
-      uint8_t *dst = ring + (size_t)stage * q4e::kStageBytes;
-      fence_proxy_async();
-      mbar_expect_tx(&bars[stage], (uint32_t)q4e::kStageBytes);
-      tma_load_rows(dst, &p.map0, part * (KNJ_Q4K_BYTES / 4), row, &bars[stage]);
-      if (DUAL) tma_load_rows(dst + 8 * KNJ_Q4K_BYTES, &p.map1, part * (KNJ_Q4K_BYTES / 4), row, &bars[stage]);
-    }
-    ++pu;
-    if (++p_tile == tiles) {
-      p_tile = 0;
-      ++p_job;
-      while (p_a < 255 && s_jbase[p_a + 1] <= p_job) ++p_a;
-    }
-  };
-  for (int s = 0; s < kStages && pu < u1; ++s) issue();
-
-  // ---- consumer
-  q4e::BFrag b;
-  q4e::bfrag_clear(b);
-  int c_job = u0 / tiles, c_tile = u0 - c_job * tiles;
-  int my_pair = -1;
-  bool new_job = true, ok = true;
-  uint32_t phases = 0;  // bit s: parity the next wait on stage s expects
-  int rbuf = 0, rturn = 0;
-  for (int u = u0; u < u1; ++u) {
-    if (new_job) {
-      const int a = locate(c_job);
-      const int e = s_uexp[a], cnt = s_ucnt[a];
-      const int tok0 = (c_job - s_jbase[a]) * q4e::kMaxTok;
-      const int n_tok = min(q4e::kMaxTok, cnt - tok0);
-      my_pair = -1;
-      int my_row = 0;
-      if (lane < n_tok) {
-        my_pair = p.pair_idx[(size_t)e * p.idxStride + tok0 + lane];
-        my_row = p.row_map ? p.row_map[my_pair] : my_pair / p.row_div;
-      }
-      // activation rows of the job, four tokens in flight at a time
-      for (int j0 = 0; j0 < n_tok; j0 += 4) {
-        float v[4][8];
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const int row = __shfl_sync(0xffffffffu, my_row, min(j0 + jj, n_tok - 1));
-          q4e::load8_f32(p.X, p.x_dtype, (int64_t)row * p.ldx + 256 * part + 8 * lane, v[jj]);
-        }
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-          if (j0 + jj < n_tok) q4e::bfrag_take_token(b, v[jj], j0 + jj, scratch, lane);
-      }
-      new_job = false;
-    }
-    const int stage = (u - u0) % kStages;
-    float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (ok) {
-      if (!mbar_wait_for(&bars[stage], (phases >> stage) & 1u, p.wait_cycles, fail)) ok = false;
-      phases ^= 1u << stage;
-    }
-    if (ok) r = q4e::tile_part(ring + (size_t)stage * q4e::kStageBytes, b, lane);
-    __syncwarp();  // every lane is done with the stage
-    if (ok && pu < u1) issue();
-
-    // ---- the K parts meet (fixed order); the warps of a team take turns as the one that sums and stores
-    const int n0 = c_tile * rows_per_tile;
-    bool mine = true;
-    if (ks > 1) {
-      red[(size_t)(rbuf * kWarps + warp) * 32 + lane] = r;
-      q4e::team_sync(team, ks * 32);
-      mine = part == rturn;
-      if (mine) {
-        const float4 *src = red + (size_t)(rbuf * kWarps + team * ks) * 32 + lane;
-        r = src[0];
-        for (int pp = 1; pp < ks; ++pp) {
-          const float4 o = src[(size_t)pp * 32];
-          r.x += o.x; r.y += o.y; r.z += o.z; r.w += o.w;
-        }
-      }
-      rbuf ^= 1;
-      if (++rturn == ks) rturn = 0;
-    }
-    const int pa = __shfl_sync(0xffffffffu, my_pair, 2 * t), pb = __shfl_sync(0xffffffffu, my_pair, 2 * t + 1);
-    if (mine && ok) {
-      if (DUAL) {
-        const int n = n0 + g;
-        if (pa >= 0) {
-          const size_t o = (size_t)pa * p.N + n;
-          if (p.out0) p.out0[o] = r.x;
-          if (p.out1) p.out1[o] = r.z;
-          if (p.out2) p.out2[o] = (r.x / (1.0f + expf(-r.x))) * r.z;
-        }
-        if (pb >= 0) {
-          const size_t o = (size_t)pb * p.N + n;
-          if (p.out0) p.out0[o] = r.y;
-          if (p.out1) p.out1[o] = r.w;
-          if (p.out2) p.out2[o] = (r.y / (1.0f + expf(-r.y))) * r.w;
-        }
-      } else {
-        if (pa >= 0) {
-          p.out0[(size_t)pa * p.N + n0 + g] = r.x;
-          p.out0[(size_t)pa * p.N + n0 + g + 8] = r.z;
-        }
-        if (pb >= 0) {
-          p.out0[(size_t)pb * p.N + n0 + g] = r.y;
-          p.out0[(size_t)pb * p.N + n0 + g + 8] = r.w;
-        }
-      }
-    }
-    if (++c_tile == tiles) {
-      c_tile = 0;
-      ++c_job;
-      new_job = true;
-    }
-  }
+  const long long U = (long long)s_jbase[256] * p.shape.tiles;  // < 2^31 (checked by the launcher)
+  const int u0 = (int)(U * blockIdx.x / gridDim.x), u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
+  q4e::JobTable jt{s_jbase, s_uexp};
+  unsigned parity = 0;
+  bool ok = true;
+  int tmode = 0;
+#ifdef KNJ_TRACE
+  tmode = g_trace_mode;
+#endif
+  q4e::run_phase<DUAL>(
+      p.shape, sm, jt, u0, u1, &p.map0, &p.map1, p.out0, p.out1, p.out2, p.wait_cycles, parity, ok,
+      [&](int job, int a, int tk, int &pair, int &row) {
+        const int tok = (job - s_jbase[a]) * q4e::kJobTok + tk;
+        if (tok >= s_ucnt[a]) return false;
+        pair = p.pair_idx[(size_t)s_uexp[a] * p.idxStride + tok];
+        row = p.row_map ? p.row_map[pair] : pair / p.row_div;
+        return true;
+      },
+      [&](int row, int sb, int ln, float (&v)[8]) { q4e::load8_f32(p.X, p.x_dtype, (int64_t)row * p.ldx + 256 * sb + 8 * ln, v); },
+      tmode);
   if (!ok && lane == 0 && p.status) atomicExch(p.status, 1);
 }
 
@@ -270,33 +141,39 @@ long long g_decode_wait_cycles = kMaxWaitCycles;
 template <bool DUAL>
 int launch_proj(ProjParams p, int n_experts_max, cudaStream_t st) {
   const int nsb = p.K / KNJ_QK_K;
-  KNJ_REQUIRE(nsb >= 1 && nsb <= kWarps, "q4k projection: rows of %d weights (at most %d are taken)", p.K, kWarps * KNJ_QK_K);
-  KNJ_REQUIRE((long long)n_experts_max * (p.idxStride / q4e::kMaxTok + 1) * p.tiles_per_expert < (1ll << 31),
-              "q4k projection: %d experts x %d tiles exceed the work index", n_experts_max, p.tiles_per_expert);
+  KNJ_REQUIRE(nsb >= 1 && nsb <= 16, "q4k projection: rows of %d weights (at most 4096 are taken)", p.K);
+  KNJ_REQUIRE((long long)n_experts_max * (p.idxStride / q4e::kJobTok + 1) * p.shape.tiles < (1ll << 31),
+              "q4k projection: %d experts x %d tiles exceed the work index", n_experts_max, p.shape.tiles);
   p.n_experts = n_experts_max;
-  p.ks = nsb;
-  p.teams = kWarps / nsb;
+  p.shape.nsb = nsb;
+  p.shape.sbs = (nsb % 2 == 0) ? 2 : 1;
   p.wait_cycles = g_decode_wait_cycles;
   {
-    const uint64_t rows = (uint64_t)n_experts_max * p.N;
-    const uint32_t row_bytes = (uint32_t)nsb * KNJ_Q4K_BYTES;
-    int rc = make_row_tensor_map(&p.map0, p.W0, rows, row_bytes, KNJ_Q4K_BYTES, DUAL ? 8 : 16);
+    const uint64_t rows = (uint64_t)n_experts_max * p.shape.N;
+    const uint32_t box = (uint32_t)p.shape.sbs * KNJ_Q4K_BYTES;
+    int rc = make_row_tensor_map(&p.map0, p.W0, rows, (uint32_t)nsb * KNJ_Q4K_BYTES, box, DUAL ? 8 : 16);
     if (rc) return rc;
     if (DUAL) {
-      rc = make_row_tensor_map(&p.map1, p.W1, rows, row_bytes, KNJ_Q4K_BYTES, 8);
+      rc = make_row_tensor_map(&p.map1, p.W1, rows, (uint32_t)nsb * KNJ_Q4K_BYTES, box, 8);
       if (rc) return rc;
     }
   }
   int dev = 0;
   KNJ_CUDA(cudaGetDevice(&dev));
-  const size_t smem = proj_smem().total;
+  int smem_max = 0;
+  KNJ_CUDA(cudaDeviceGetAttribute(&smem_max, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+  const size_t reserve = 6 * 1024;  // the kernel's static shared memory
+  p.shape.stages = p.shape.sbs == 2 ? 2 : q4e::kMaxStages;  // four superblocks in flight per warp either way
+  while (p.shape.stages > 2 && proj_smem(nsb, p.shape.sbs, p.shape.stages).total + reserve > (size_t)smem_max) --p.shape.stages;
+  const size_t smem = proj_smem(nsb, p.shape.sbs, p.shape.stages).total;
+  KNJ_REQUIRE(smem + reserve <= (size_t)smem_max, "q4k projection: rows of %d weights do not fit the shared memory", p.K);
   auto kern = q4k_proj_kernel<DUAL>;
   // opt in to the large dynamic shared memory once per device and instantiation
   // (kept out of later launches so they are plain stream work, capturable in a graph)
-  static bool opted[64] = {false};
-  if (dev >= 0 && dev < 64 && !opted[dev]) {
+  static size_t opted[64] = {0};
+  if (dev >= 0 && dev < 64 && opted[dev] < smem) {
     KNJ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    opted[dev] = true;
+    opted[dev] = smem;
   }
   KNJ_CUDA(launch_chain(kern, dim3((unsigned)sm_count()), dim3(kThreads), smem, st, p));
   return launch_status("q4k_proj_kernel");
@@ -313,6 +190,14 @@ int check_rows(const void *X, int dtype, int64_t ld, int K, const char *who) {
 }  // namespace
 
 extern "C" {
+
+#ifdef KNJ_TRACE
+int knj_trace_proj(long long *, int mode) {  // measurement build only
+  KNJ_CUDA(cudaMemcpyToSymbol(g_trace_mode, &mode, sizeof(mode)));
+  return KNJ_OK;
+}
+int knj_trace_feed(int) { return 0; }
+#endif
 
 void knj_decode_wait_limit(long long cycles) { g_decode_wait_cycles = cycles > 0 ? cycles : kMaxWaitCycles; }
 
@@ -333,8 +218,8 @@ int knj_q4k_gateup_launch(const void *X, int x_dtype, int64_t ldx, const uint8_t
   p.W0 = Wg; p.W1 = Wu; p.X = X; p.x_dtype = x_dtype; p.ldx = ldx;
   p.pair_idx = pair_idx; p.pair_cnt = pair_cnt; p.row_map = pair_tok; p.exp_list = exp_list; p.n_active = n_active;
   p.out0 = G; p.out1 = U; p.out2 = A;
-  p.N = N; p.K = K; p.row_div = top_k > 0 ? top_k : 1;
-  p.tiles_per_expert = N / 8; p.idxStride = idxStride; p.status = status;
+  p.shape.N = N; p.K = K; p.row_div = top_k > 0 ? top_k : 1;
+  p.shape.tiles = N / 8; p.idxStride = idxStride; p.status = status;
   return launch_proj<true>(p, n_experts, as_stream(s));
 }
 
@@ -354,8 +239,8 @@ int knj_q4k_proj_launch(const void *A, int a_dtype, int64_t lda, const uint8_t *
   p.W0 = W; p.W1 = nullptr; p.X = A; p.x_dtype = a_dtype; p.ldx = lda;
   p.pair_idx = pair_idx; p.pair_cnt = pair_cnt; p.row_map = pair_row; p.exp_list = exp_list; p.n_active = n_active;
   p.out0 = Y; p.out1 = nullptr; p.out2 = nullptr;
-  p.N = N; p.K = K; p.row_div = 1;
-  p.tiles_per_expert = N / 16; p.idxStride = idxStride; p.status = status;
+  p.shape.N = N; p.K = K; p.row_div = 1;
+  p.shape.tiles = N / 16; p.idxStride = idxStride; p.status = status;
   return launch_proj<false>(p, n_experts, as_stream(s));
 }
 
@@ -411,7 +296,7 @@ int knj_q4k_matmul_launch(const uint8_t *W, int n_in, int n_out, const void *x, 
 // starting any stream capture.
 // ---------------------------------------------------------------------------
 namespace {
-constexpr size_t kNoAllocScratchBytes = (size_t)1 << 20;  // 1 MiB
+constexpr size_t kNoAllocScratchBytes = (size_t)64 << 10;  // 64 KiB: the pair list of up to 16,256 activation rows
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
 
 int noalloc_scratch_ptr(void **out) {

@@ -171,12 +171,15 @@ class MoeStack:
 
 
 class FusedMoeStack:
-    """The resident stack for 1..4 tokens as ONE cooperative launch (knj_moe_stack_*): the per-layer loop,
+    """The resident stack for a decode batch of 1..64 tokens as ONE cooperative launch (knj_moe_stack_*): the per-layer loop,
     its routing and its hand-offs run inside a single kernel with grid barriers between the stages. Buffers are
     static: write the step's rows into `self.x` (or pass them to step) and read `self.out` after the launch."""
 
     def __init__(self, banks: list[ExpertBank], top_k: int = synth.TOP_K, n_tokens: int = 1, dtype=torch.bfloat16,
-                 residual: bool = True, use_norm: bool = True, taps: bool = False):
+                 residual: bool = True, use_norm: bool = True, taps: bool = False,
+                 layer_inputs: list[torch.Tensor] | None = None):
+        """layer_inputs: one [n_tokens][H] tensor per layer that the layer reads INSTEAD of its predecessor's output
+        (independent layers, e.g. to drive every layer with fresh rows); default: the layers form a chain."""
         dev = banks[0].gate.device
         H = banks[0].hidden
         self.x = torch.zeros((n_tokens, H), dtype=dtype, device=dev)
@@ -193,10 +196,12 @@ class FusedMoeStack:
             layer.use_norm = use_norm and b.norm_w is not None
             layer.workspace = ws
             nxt = self._buf[l & 1]
+            if layer_inputs is not None:
+                cur = layer_inputs[l]
             arr[l] = layer._args(cur, nxt, self.taps[l] if taps else None)
             cur = nxt
         self.out = cur
-        self._banks = banks  # keep the weights alive
+        self._banks, self._inputs = banks, layer_inputs  # keep the weights and the rows alive
         h = C.c_void_p()
         check(lib().knj_moe_stack_create(arr, len(banks), C.byref(h)))
         self._h = h
@@ -210,6 +215,11 @@ class FusedMoeStack:
     def status(self) -> None:
         """Waits for the stream; raises if a grid barrier of the last launches gave up."""
         check(lib().knj_moe_stack_status(self._h, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def set_wait(self, wait_cycles: int = 0, stall_first_barrier: int = 0) -> None:
+        """Limit of the kernel's bounded waits (SM cycles; 0 = default) and the test hook that makes the first
+        grid barrier unreachable."""
+        check(lib().knj_moe_stack_set_wait(self._h, wait_cycles, stall_first_barrier))
 
     def close(self):
         if self._h:

@@ -68,6 +68,14 @@ def gemm_w4_i8(Bq: torch.Tensor, act: torch.Tensor, asum: torch.Tensor, M: int, 
     return Cm
 
 
+def dot_helpers(a: torch.Tensor, b: torch.Tensor, acc: torch.Tensor):
+    """int32 [n] x 3 -> (dot4_i8, dot8_i4, dot2_i16) computed by include/knj_dot.h on the device."""
+    _need(a, torch.int32), _need(b, torch.int32), _need(acc, torch.int32)
+    outs = [torch.full_like(a, 0x5A5A5A5A) for _ in range(3)]
+    check(lib().knj_dot_helpers_launch(_p(a), _p(b), _p(acc), _p(outs[0]), _p(outs[1]), _p(outs[2]), a.numel(), _stream()))
+    return outs
+
+
 def q4k_dequant(blocks: torch.Tensor) -> torch.Tensor:
     """uint8 [..., 144] -> f32 [..., 256]."""
     _need(blocks, torch.uint8)

@@ -2,7 +2,8 @@
 sources (oracle/_ref/libknj_ref.so, built by `make -C oracle ref`) and from
 gguf-py. Run in a container where the reference tree is mounted:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py        (golden.npz and golden_q6k.npz)
+    python tests/golden/make_golden.py q6k    (golden_q6k.npz only)
 
 The inputs are regenerated from seeds by kanjoos_b200.synth; each fixture stores
 a sha256 of the input bytes so a drift in the generator is caught, plus the
@@ -43,6 +44,42 @@ def crafted_blocks() -> np.ndarray:
     for i in range(8):
         blocks[i, 0:4] = (np.abs(rng.standard_normal(2)) * 0.01).astype(np.float16).view(np.uint8)
     return blocks
+
+
+def crafted_q6k_blocks() -> np.ndarray:
+    """Q6_K superblocks (210 bytes: ql[128], qh[64], int8 scales[16], fp16 d): random ones plus all-0x00,
+    all-0xFF codes, extreme int8 scales (-128 / 127) and fp16 corner values of d."""
+    rng = np.random.Generator(np.random.Philox(20261126))
+    blocks = rng.integers(0, 256, size=(12, 210), dtype=np.uint8)
+    for i in range(12):
+        blocks[i, 208:210] = (np.abs(rng.standard_normal(1)) * 0.01).astype(np.float16).view(np.uint8)
+    blocks[6, :208] = 0x00
+    blocks[7, :208] = 0xFF
+    blocks[8, 192:208] = np.array([-128, 127] * 8, dtype=np.int8).view(np.uint8)
+    blocks[9, 208:210] = np.array([0x0001], dtype=np.uint16).view(np.uint8)   # subnormal d
+    blocks[10, 208:210] = np.array([0x7BFF], dtype=np.uint16).view(np.uint8)  # largest finite d
+    blocks[11, 208:210] = np.array([0x8000], dtype=np.uint16).view(np.uint8)  # -0
+    return blocks
+
+
+def q6k_golden() -> None:
+    """Q6_K decode of the reference (src/loader/dequant.cpp:164-191 through dequant_row_f32, and the per-element
+    twin kernels/knj_q4k.h knj_q6k_weight), cross-checked against gguf-py."""
+    r = ol.ref()
+    assert r is not None, "reference library not built: make -C oracle ref"
+    import gguf
+    from gguf import quants
+    blocks = crafted_q6k_blocks()
+    deq = np.empty((blocks.shape[0], 256), dtype=np.float32)
+    r.ref_dequant_row_q6k(ol.ptr(blocks, ol.u8p), ol.ptr(deq, ol.f32p), deq.size)
+    per_elem = np.array([[r.ref_q6k_weight(ol.ptr(blocks[b], ol.u8p), i) for i in range(256)]
+                         for b in range(blocks.shape[0])], dtype=np.float32)
+    assert np.array_equal(deq.view(np.uint32), per_elem.view(np.uint32)), "the reference's two Q6_K decoders disagree"
+    gg = quants.dequantize(blocks, gguf.GGMLQuantizationType.Q6_K).astype(np.float32)
+    assert np.array_equal(deq.view(np.uint32), gg.view(np.uint32)), "gguf-py disagrees"
+    path = os.path.join(HERE, "golden_q6k.npz")
+    np.savez_compressed(path, q6k_blocks=blocks, q6k_blocks_f32=deq)
+    print("wrote", path, os.path.getsize(path), "bytes")
 
 
 def main() -> None:
@@ -139,4 +176,8 @@ def main() -> None:
 
 
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "q6k":
+        q6k_golden()      # only the Q6_K fixture
+    else:
+        main()
+        q6k_golden()

@@ -17,6 +17,15 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORACLE_DIR = os.path.join(ROOT, "oracle")
 
+
+def reference_root() -> str | None:
+    """Root of the reference project's source tree: $KNJ_REFERENCE_ROOT, else a directory named `reference` beside
+    this repository; None when neither holds the loader sources."""
+    for cand in (os.environ.get("KNJ_REFERENCE_ROOT"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "src", "loader")):
+            return cand
+    return None
+
 u8p = C.POINTER(C.c_uint8)
 i8p = C.POINTER(C.c_int8)
 f32p = C.POINTER(C.c_float)
@@ -73,9 +82,10 @@ def oracle() -> C.CDLL:
 def ref():
     so = os.path.join(ORACLE_DIR, "_ref", "libknj_ref.so")
     if not os.path.exists(so):
-        if not os.path.isdir("/root/reference/src/loader"):
+        root = reference_root()
+        if root is None:
             return None
-        subprocess.check_call(["make", "-C", ORACLE_DIR, "ref"], stdout=subprocess.DEVNULL)
+        subprocess.check_call(["make", "-C", ORACLE_DIR, "ref", "REF=" + root], stdout=subprocess.DEVNULL)
     lib = C.CDLL(so)
     lib.ref_fp16_to_fp32.restype = C.c_float
     lib.ref_fp16_to_fp32.argtypes = [C.c_uint16]

@@ -265,7 +265,7 @@ def test_stack_create_refuses_bad_arguments(L):
     h = C.c_void_p()
     assert L.knj_moe_stack_create(None, 1, C.byref(h)) == -1 and not h.value
     a = (MoeFfnArgs * 1)()
-    a[0].n_tokens, a[0].hidden, a[0].ffn, a[0].n_experts, a[0].top_k = 5, 2048, 768, 128, 8
+    a[0].n_tokens, a[0].hidden, a[0].ffn, a[0].n_experts, a[0].top_k = 65, 2048, 768, 128, 8
     assert L.knj_moe_stack_create(a, 1, C.byref(h)) == -1 and b"n_tokens" in L.knj_last_error_string()
     a[0].n_tokens, a[0].hidden = 1, 4096
     assert L.knj_moe_stack_create(a, 1, C.byref(h)) == -1 and b"hidden" in L.knj_last_error_string()

@@ -121,3 +121,50 @@ def test_backend_create_is_arch_guarded(L, monkeypatch):
     assert L.knj_backend_arch(b) == b"sm_100"
     assert L.knj_backend_launch(b, 0, None, None) == 1 and L.knj_backend_launch(b, 1, None, None) == 1
     L.knj_backend_destroy(b)
+
+
+def test_dot_helpers_on_the_device_match_their_definition():
+    """knj_dot4_i32_i8 / knj_dot8_i32_i4 / knj_dot2_i32_i16 executed in a kernel against the plain-integer
+    definition (kernels/knj_dot.h:117-174), incl. the sign corners of every field width."""
+    from kanjoos_b200 import ops
+    rng = np.random.Generator(np.random.Philox(77))
+    n = 4096
+    a = rng.integers(-2**31, 2**31, size=n, dtype=np.int64).astype(np.int32)
+    b = rng.integers(-2**31, 2**31, size=n, dtype=np.int64).astype(np.int32)
+    acc = rng.integers(-2**20, 2**20, size=n, dtype=np.int64).astype(np.int32)
+    corners = np.array([0, -1, 0x7fffffff, -2**31, 0x88888888 - 2**32, 0x77777777, 0x80808080 - 2**32, 0x7f7f7f7f,
+                        0x80008000 - 2**32, 0x7fff7fff], dtype=np.int64).astype(np.int32)
+    a[:corners.size] = corners
+    b[:corners.size] = corners[::-1]
+
+    def fields(x, bits):
+        u = x.astype(np.int64) & 0xffffffff
+        out = []
+        for i in range(32 // bits):
+            f = (u >> (bits * i)) & ((1 << bits) - 1)
+            out.append(np.where(f >= (1 << (bits - 1)), f - (1 << bits), f))
+        return out
+    want = {}
+    for bits in (8, 4, 16):
+        s = acc.astype(np.int64)
+        for fa, fb in zip(fields(a, bits), fields(b, bits)):
+            s = s + fa * fb
+        want[bits] = ((s + 2**31) % 2**32 - 2**31).astype(np.int32)
+    d4, d8, d2 = (t.cpu().numpy() for t in ops.dot_helpers(torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda(),
+                                                          torch.from_numpy(acc).cuda()))
+    assert np.array_equal(d4, want[8]) and np.array_equal(d8, want[4]) and np.array_equal(d2, want[16])
+
+
+def test_fuse_gateup_silu_kernel():
+    """knj_fuse_gateup_silu_launch (tools/bench/q4k_stream_ffn.hip:1021-1031) against the CPU path's silu * up."""
+    import oracle_lib as ol
+    from kanjoos_b200 import ops
+    rng = np.random.Generator(np.random.Philox(78))
+    g = (rng.standard_normal((37, 768)) * 4).astype(np.float32)
+    u = rng.standard_normal((37, 768)).astype(np.float32)
+    g[0, :4] = [0.0, -100.0, 100.0, -1e-8]
+    want = ol.silu_mul(g, u)
+    got = ops.fuse_gateup_silu(torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda()).cpu().numpy()
+    assert ol.compare(got, want)["rel_rmse"] <= 1e-6
+    got16 = ops.fuse_gateup_silu(torch.from_numpy(g).cuda(), torch.from_numpy(u).cuda(), dtype=torch.bfloat16).float().cpu().numpy()
+    assert ol.compare(got16, want)["rel_rmse"] <= 5e-3

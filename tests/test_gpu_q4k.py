@@ -42,6 +42,11 @@ def test_dequant_empty_and_q6k():
     ol.oracle().knj_or_dequant_q6k(ol.ptr(blk, ol.u8p), ol.ptr(want, ol.f32p), want.size)
     got = ops.q6k_dequant(dev(blk)).cpu().numpy()
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    # and the reference's own decode of crafted blocks (all-0x00, all-0xFF, extreme scales, fp16 corners of d)
+    import os
+    g6 = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_q6k.npz"))
+    got = ops.q6k_dequant(dev(g6["q6k_blocks"])).cpu().numpy()
+    assert np.array_equal(got.view(np.uint32), g6["q6k_blocks_f32"].view(np.uint32))
 
 
 def test_cfg1_gemv(golden):

@@ -43,6 +43,27 @@ def test_crafted_blocks_bit_exact(golden):
             assert np.array_equal(bits(span), bits(want[b, r0:r0 + 16]))
 
 
+def test_q6k_crafted_blocks_bit_exact():
+    """The Q6_K restatement (row decoder and per-element form) against the reference's decode of crafted blocks:
+    random, all-0x00, all-0xFF, extreme int8 scales, fp16 corner values of d (tests/golden/golden_q6k.npz)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "golden_q6k.npz"))
+    blocks, want = g["q6k_blocks"], g["q6k_blocks_f32"]
+    o = ol.oracle()
+    got = np.empty_like(want)
+    o.knj_or_dequant_q6k(ol.ptr(np.ascontiguousarray(blocks), ol.u8p), ol.ptr(got, ol.f32p), got.size)
+    assert np.array_equal(bits(got), bits(want))
+    for b in range(blocks.shape[0]):
+        blk = np.ascontiguousarray(blocks[b])
+        pe = np.array([o.knj_or_q6k_weight(ol.ptr(blk, ol.u8p), r) for r in range(256)], np.float32)
+        assert np.array_equal(bits(pe), bits(want[b]))
+    r = ol.ref()
+    if r is not None:  # and directly against the compiled reference where it is present
+        again = np.empty_like(want)
+        r.ref_dequant_row_q6k(ol.ptr(np.ascontiguousarray(blocks), ol.u8p), ol.ptr(again, ol.f32p), again.size)
+        assert np.array_equal(bits(again), bits(want))
+
+
 def test_cfg1_dequant_and_gemv(golden):
     W = synth.q4k_rows(synth.stream(1, "gate"), synth.FFN, synth.HIDDEN)
     x = synth.stream(1, "x").standard_normal(synth.HIDDEN).astype(np.float32)
