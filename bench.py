@@ -196,63 +196,46 @@ def workload_config(args, world):
 # --------------------------------------------------------------------------- GPU arm
 
 def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64)):
-    """Resident stack (48 layers by default), batch 1/8/64: tokens/s and HBM roofline of the decode path."""
-    from kanjoos_b200.moe import ExpertBank, FusedMoeStack, MoeStack
+    """Resident stack (48 layers by default): tokens/s and HBM roofline of the decode path, one cooperative launch
+    per step (knj_moe_stack_*). Two inputs per batch: `chained` feeds each layer the previous layer's output (the
+    decode loop as it runs; with random-init weights the residual stream concentrates the routing on a third of
+    the experts after a few layers) and `fresh` gives every layer its own N(0,1) rows (the expert spread of a
+    trained router: ~126 of 128 experts at batch 64). Algorithmic bytes use the distinct experts actually routed."""
+    from kanjoos_b200.moe import ExpertBank, FusedMoeStack
     banks = [ExpertBank.random(seed=1000 + l) for l in range(layers)]
     out = {"layers": layers, "resident_weight_gib": round(layers * E * EXPERT_BYTES / 2**30, 2), "batches": {}}
     for B in batches:
-        stack = MoeStack(banks, top_k=TOPK, max_tokens=B)
         g = torch.Generator(device="cuda")
         g.manual_seed(B)
         x = torch.randn((B, H), device="cuda", generator=g).to(torch.bfloat16)
-        # distinct experts per layer for this input (untimed pass with routing taps)
-        distinct = 0
-        cur = x
-        bufs = (torch.empty_like(x), torch.empty_like(x))
-        for i, layer in enumerate(stack.layers):
-            o, pe, _ = layer.decode(cur, out=bufs[i & 1], return_routing=True)
-            distinct += int(torch.unique(pe).numel())
-            cur = o
-        graph, _ = stack.capture(x)
-        for _ in range(max(3, warmup)):
-            graph.replay()
-        torch.cuda.synchronize()
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
-        ev[0].record()
-        for _ in range(steps):
-            graph.replay()
-        ev[1].record()
-        torch.cuda.synchronize()
-        ms = ev[0].elapsed_time(ev[1]) / steps
-        path, other = "layer launches (CUDA graph)", None
-        if B == 1:
-            # batch 1 also runs as ONE cooperative launch over the whole stack; the faster of the two is reported
-            try:
-                fused = FusedMoeStack(banks, top_k=TOPK, n_tokens=B)
-                for _ in range(max(3, warmup)):
-                    fused.step(x)
-                fused.status()
-                ev[0].record()
-                for _ in range(steps):
-                    fused.step()
-                ev[1].record()
-                torch.cuda.synchronize()
-                fused.status()
-                fms = ev[0].elapsed_time(ev[1]) / steps
-                fused.close()
-                if fms < ms:
-                    ms, other, path = fms, ms, "fused stack (one cooperative launch)"
-                else:
-                    other = fms
-            except RuntimeError as e:  # e.g. a device that refuses cooperative launches: the layer launches stand
-                other = "fused stack unavailable: " + str(e)[:120]
-        alg = distinct * EXPERT_BYTES + layers * (E * H * 2 + H * 2 + B * H * 2 * 2)
-        out["batches"][str(B)] = {"tokens_per_s": B / (ms * 1e-3), "ms_per_step": ms,
-                                  "path": path, "other_path_ms_per_step": other,
-                                  "distinct_experts_per_layer": distinct / layers, "algorithmic_bytes": alg,
-                                  "hbm_gbs": alg / (ms * 1e-3) / 1e9,
-                                  "frac_of_" + pk["_source"]: alg / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
-        del stack, graph
+        for mode in ("chained", "fresh"):
+            if mode == "fresh" and B == 1:
+                continue  # one token routes to eight experts whatever its row is
+            ins = ([torch.randn((B, H), device="cuda", generator=g).to(torch.bfloat16) for _ in range(layers)]
+                   if mode == "fresh" else None)
+            stack = FusedMoeStack(banks, top_k=TOPK, n_tokens=B, taps=True, layer_inputs=ins)
+            for _ in range(max(3, warmup)):
+                stack.step(x)
+            stack.status()
+            distinct = sum(int(torch.unique(t[0]).numel()) for t in stack.taps)
+            ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+            reps = max(steps, int(0.3 / max(1e-4, layers * 150e-6)))  # at least ~0.3 s of timed launches
+            ev[0].record()
+            for _ in range(reps):
+                stack.step()
+            ev[1].record()
+            torch.cuda.synchronize()
+            stack.status()
+            ms = ev[0].elapsed_time(ev[1]) / reps
+            alg = distinct * EXPERT_BYTES + layers * (E * H * 2 + H * 2 + B * H * 2 * 2)
+            key = str(B) if mode == "chained" else f"{B}_fresh"
+            out["batches"][key] = {"tokens_per_s": B / (ms * 1e-3), "ms_per_step": ms, "timed_steps": reps,
+                                   "path": "one cooperative launch per step (knj_moe_stack_decode_launch)",
+                                   "inputs": mode, "distinct_experts_per_layer": distinct / layers,
+                                   "algorithmic_bytes": alg, "hbm_gbs": alg / (ms * 1e-3) / 1e9,
+                                   "frac_of_" + pk["_source"]: alg / (ms * 1e-3) / 1e9 / pk["hbm_gbs"]}
+            stack.close()
+            del stack
     del banks
     torch.cuda.empty_cache()
     return out

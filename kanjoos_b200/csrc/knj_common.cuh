@@ -66,6 +66,15 @@ inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, s
 int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t row_bytes, uint32_t box_bytes,
                         uint32_t box_rows);
 
+// The cooperative stack launch for the smallest batches (knj_stack_small.cu), behind knj_moe_stack_*.
+struct SmallStack;
+constexpr int kSmallStackMaxTokens = 2;  // measured: from 3 tokens on the tensor-core kernel is the faster one
+int small_stack_create(const knj_moe_ffn_args *layers, int n_layers, SmallStack **out);
+int small_stack_launch(SmallStack *st, knj_stream_t s);
+int small_stack_status(SmallStack *st, knj_stream_t s);
+void small_stack_set_wait(SmallStack *st, long long cycles, int stall);
+void small_stack_destroy(SmallStack *st);
+
 // ---- device helpers --------------------------------------------------------
 #if defined(__CUDACC__)
 

@@ -18,7 +18,8 @@
 //   * the min term is one more MMA per superblock: A = the eight 6-bit m_sb,
 //     B = the per-32 sums of the token's planes.
 //
-// Work split. A JOB is one expert with up to four of its tokens; its activations
+// Work split. A JOB is one expert with up to eight of its tokens (one or two MMA
+// column groups of four; the unpacked weights serve both groups); its activations
 // are converted once per CTA into a PANEL in shared memory, laid out so that a
 // warp's fragment loads are 128 contiguous bytes per quarter-warp. A warp owns a
 // 16-row tile (8 gate + 8 up rows of the same output indices, or 16 rows of one
@@ -43,7 +44,7 @@ namespace q4e {
 
 constexpr int kTileRows = 16;
 constexpr int kStageBytes = kTileRows * KNJ_Q4K_BYTES;  // 2304: one superblock column of a 16-row tile
-constexpr int kJobTok = 4;                              // tokens of one job (x 2 planes = the n dimension of the MMA)
+constexpr int kJobTok = 8;                              // tokens of one job: one or two groups of 4 (x 2 planes = the MMA's n)
 // Panel of one (token, superblock): eight 128-byte units u = 4 * (sub-block & 1) + (16-byte piece of the
 // sub-block's plane); inside a unit, 16 bytes per (plane, t) at 16 * (4 * plane + t): the eight lanes of a
 // quarter-warp (planes 0/1 of one token, t = 0..3) read one unit without bank conflicts. Then the per-32
@@ -161,12 +162,14 @@ __device__ __forceinline__ void header_pairs(const uint4 &hd, uint32_t sel16, bo
 }
 
 // One tile part: a superblock column of a 16-row tile (rows `pitch` bytes apart, the superblock at `stage` in
-// each) times the panel `pan` of the job's four tokens for that superblock (token stride `tok_stride` bytes).
-// Lane (g, t) works on weight rows wrow and wrow + 8 of the tile (see tile_row) and receives the superblock's
-// contribution to (row wrow, token t) in rg and to (row wrow + 8, token t) in rh, in the units of the token's
-// scaled planes; the caller multiplies by 1 / scale.
+// each) times the panels of the job's tokens for that superblock (`pan`: token 0, token stride `tok_stride`
+// bytes). NG = groups of four tokens (1 or 2). Lane (g, t) works on weight rows wrow and wrow + 8 of the tile
+// (see tile_row) and receives, per group q, the superblock's contribution to (row wrow, token 4q + t) in
+// rg[q] and to (row wrow + 8, token 4q + t) in rh[q], in the units of the token's scaled planes; the caller
+// multiplies by 1 / scale. after_loads() runs once the weights are in registers (the stage may be refilled).
+template <int NG, class AfterLoads>
 __device__ __forceinline__ void tile_part(const uint8_t *stage, int pitch, int wrow, const uint8_t *pan, int tok_stride,
-                                          int lane, float &rg, float &rh) {
+                                          int lane, float (&rg)[NG], float (&rh)[NG], AfterLoads after_loads) {
   const int g = lane >> 2, t = lane & 3;
   const uint8_t *wg_row = stage + wrow * pitch, *wh_row = stage + (wrow + 8) * pitch;
   const uint4 hg = *reinterpret_cast<const uint4 *>(wg_row), hh = *reinterpret_cast<const uint4 *>(wh_row);
@@ -174,18 +177,13 @@ __device__ __forceinline__ void tile_part(const uint8_t *stage, int pitch, int w
   const uint4 wh0 = *reinterpret_cast<const uint4 *>(wh_row + KNJ_Q4K_OFF_QS + 32 * t);
   const uint4 wg1 = *reinterpret_cast<const uint4 *>(wg_row + KNJ_Q4K_OFF_QS + 32 * t + 16);
   const uint4 wh1 = *reinterpret_cast<const uint4 *>(wh_row + KNJ_Q4K_OFF_QS + 32 * t + 16);
+  after_loads();
   const uint32_t wg[8] = {wg0.x, wg0.y, wg0.z, wg0.w, wg1.x, wg1.y, wg1.z, wg1.w};
   const uint32_t wh[8] = {wh0.x, wh0.y, wh0.z, wh0.w, wh1.x, wh1.y, wh1.z, wh1.w};
-  // this lane's column: token g / 2, plane g & 1
+  // this lane's column in group q: token 4q + g / 2, plane g & 1
   const uint8_t *col = pan + (size_t)(g >> 1) * tok_stride;
   const uint8_t *bsrc = col + 16 * (4 * (g & 1) + t);
-  uint32_t bp[32];
-#pragma unroll
-  for (int u = 0; u < 8; ++u) {
-    const uint4 q = *reinterpret_cast<const uint4 *>(bsrc + 128 * u);
-    bp[4 * u] = q.x; bp[4 * u + 1] = q.y; bp[4 * u + 2] = q.z; bp[4 * u + 3] = q.w;
-  }
-  const uint32_t sx = *reinterpret_cast<const uint32_t *>(col + 1024 + 16 * (g & 1) + 4 * t);
+  const int grp_stride = 4 * tok_stride;
 
   const uint32_t sel16 = (t & 1) ? 0x4432u : 0x4410u;
   uint32_t scg, mg, sch, mh;
@@ -201,36 +199,61 @@ __device__ __forceinline__ void tile_part(const uint8_t *stage, int pitch, int w
   const uint32_t mmg = sub_f16x2(__byte_perm(mg, 0x64646464u, 0x4140u), k1024);
   const uint32_t mmh = sub_f16x2(__byte_perm(mh, 0x64646464u, 0x4140u), k1024);
 
-  // four independent accumulator chains (nibble kind x step parity): the MMAs of one chain depend on each other
-  float cm[4], c0[4], c1[4], c2[4], c3[4];
-  mma_f16_16816_zero(cm, mmg, mmh, 0u, 0u, sx, 0u);
+  // independent accumulator chains (the MMAs of one chain depend on each other): with one group, nibble kind
+  // x step parity; with two groups, nibble kind x group
+  constexpr int NC = NG == 1 ? 2 : 1;  // chains per (group, nibble kind)
+  float cm[NG][4], ce[NG][NC][4], co[NG][NC][4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) c0[i] = c1[i] = c2[i] = c3[i] = 0.f;
+  for (int q = 0; q < NG; ++q) {
+    const uint32_t sx = *reinterpret_cast<const uint32_t *>(col + q * grp_stride + 1024 + 16 * (g & 1) + 4 * t);
+    mma_f16_16816_zero(cm[q], mmg, mmh, 0u, 0u, sx, 0u);
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const uint32_t xg = wg[i], xh = wh[i], yg = xg >> 8, yh = xh >> 8;
-    {
-      const uint32_t a0 = mul_f16x2(xg & 0x000f000fu, sEg), a1 = mul_f16x2(xh & 0x000f000fu, sEh);
-      const uint32_t a2 = mul_f16x2(yg & 0x000f000fu, sEg), a3 = mul_f16x2(yh & 0x000f000fu, sEh);
-      if (i & 1) mma_f16_16816(c1, a0, a1, a2, a3, bp[2 * i], bp[2 * i + 1]);
-      else mma_f16_16816(c0, a0, a1, a2, a3, bp[2 * i], bp[2 * i + 1]);
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) ce[q][c][i] = co[q][c][i] = 0.f;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {  // steps 2j and 2j + 1 share one 16-byte fragment load per sub-block and group
+    uint4 be[NG], bo[NG];
+#pragma unroll
+    for (int q = 0; q < NG; ++q) {
+      be[q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * j);
+      bo[q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * (4 + j));
     }
-    {
-      const uint32_t a0 = mul_f16x2(xg & 0x00f000f0u, sOg), a1 = mul_f16x2(xh & 0x00f000f0u, sOh);
-      const uint32_t a2 = mul_f16x2(yg & 0x00f000f0u, sOg), a3 = mul_f16x2(yh & 0x00f000f0u, sOh);
-      if (i & 1) mma_f16_16816(c3, a0, a1, a2, a3, bp[16 + 2 * i], bp[17 + 2 * i]);
-      else mma_f16_16816(c2, a0, a1, a2, a3, bp[16 + 2 * i], bp[17 + 2 * i]);
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int i = 2 * j + h;
+      const uint32_t xg = wg[i], xh = wh[i], yg = xg >> 8, yh = xh >> 8;
+      {
+        const uint32_t a0 = mul_f16x2(xg & 0x000f000fu, sEg), a1 = mul_f16x2(xh & 0x000f000fu, sEh);
+        const uint32_t a2 = mul_f16x2(yg & 0x000f000fu, sEg), a3 = mul_f16x2(yh & 0x000f000fu, sEh);
+#pragma unroll
+        for (int q = 0; q < NG; ++q) mma_f16_16816(ce[q][NC == 2 ? h : 0], a0, a1, a2, a3, h ? be[q].z : be[q].x, h ? be[q].w : be[q].y);
+      }
+      {
+        const uint32_t a0 = mul_f16x2(xg & 0x00f000f0u, sOg), a1 = mul_f16x2(xh & 0x00f000f0u, sOh);
+        const uint32_t a2 = mul_f16x2(yg & 0x00f000f0u, sOg), a3 = mul_f16x2(yh & 0x00f000f0u, sOh);
+#pragma unroll
+        for (int q = 0; q < NG; ++q) mma_f16_16816(co[q][NC == 2 ? h : 0], a0, a1, a2, a3, h ? bo[q].z : bo[q].x, h ? bo[q].w : bo[q].y);
+      }
     }
   }
-  // codes carried 2^-24, the sums 1/64; columns 2t and 2t+1 are the two planes of token t
+  // codes carried 2^-24, the sums 1/64; columns 2t and 2t+1 are the two planes of token t of the group
   const float dg = __half2float(__ushort_as_half((unsigned short)(hg.x & 0xffffu))) * 16777216.0f;
   const float ng = __half2float(__ushort_as_half((unsigned short)(hg.x >> 16))) * 64.0f;
   const float dh = __half2float(__ushort_as_half((unsigned short)(hh.x & 0xffffu))) * 16777216.0f;
   const float nh = __half2float(__ushort_as_half((unsigned short)(hh.x >> 16))) * 64.0f;
-  const float sg = ((c0[0] + c1[0]) + (c2[0] + c3[0])) + ((c0[1] + c1[1]) + (c2[1] + c3[1]));
-  const float sh = ((c0[2] + c1[2]) + (c2[2] + c3[2])) + ((c0[3] + c1[3]) + (c2[3] + c3[3]));
-  rg = dg * sg - ng * (cm[0] + cm[1]);
-  rh = dh * sh - nh * (cm[2] + cm[3]);
+#pragma unroll
+  for (int q = 0; q < NG; ++q) {
+    float sg = 0.f, sh = 0.f;
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+      sg += (ce[q][c][0] + ce[q][c][1]) + (co[q][c][0] + co[q][c][1]);
+      sh += (ce[q][c][2] + ce[q][c][3]) + (co[q][c][2] + co[q][c][3]);
+    }
+    rg[q] = dg * sg - ng * (cm[q][0] + cm[q][1]);
+    rh[q] = dh * sh - nh * (cm[q][2] + cm[q][3]);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -252,15 +275,15 @@ struct PhaseShape {
 
 struct PhaseSmem {       // per CTA
   uint8_t *ring;         // kWarps * stages * sbs * kStageBytes
-  uint8_t *panels;       // 2 jobs * kJobTok * nsb * kPanelBytes
+  uint8_t *panels;       // kJobTok * nsb * kPanelBytes: the panels of the job in progress
   uint64_t *bars;        // kWarps * kMaxStages, initialised with count 1
-  float *inv;            // [2][kJobTok][16]
-  int *pair;             // [2][kJobTok]
+  float *inv;            // [kJobTok][16]
+  int *pair;             // [kJobTok]: output rows of the job's tokens, -1: no token in the slot
   volatile int *fail;    // raised by the first wait that gives up
 };
 
 __host__ __device__ inline size_t phase_ring_bytes(int sbs, int stages) { return (size_t)kWarps * stages * sbs * kStageBytes; }
-__host__ __device__ inline size_t phase_panel_bytes(int nsb) { return (size_t)2 * kJobTok * nsb * kPanelBytes; }
+__host__ __device__ inline size_t phase_panel_bytes(int nsb) { return (size_t)kJobTok * nsb * kPanelBytes; }
 
 // active expert of a job: the last a whose first job is not beyond it
 __device__ __forceinline__ int job_locate(const int *jbase, int job) {
@@ -273,7 +296,7 @@ __device__ __forceinline__ int job_locate(const int *jbase, int job) {
   return lo;
 }
 
-// Runs tiles [u0, u1) of the flat list, two jobs at a time. All kWarps * 32 threads of the CTA call it together
+// Runs tiles [u0, u1) of the flat list, one job at a time. All kWarps * 32 threads of the CTA call it together
 // (it contains CTA barriers). job_token(job, a, tk, pair, row) -> bool says whether token slot tk of the job
 // exists and names its output row (pair) and its activation row; load_row(row, sb, lane, v) fetches values
 // 256 sb + 8 lane .. + 7 of that activation row. out0/out1/out2 as for the launches: DUAL -> G, U, silu(G) * U;
@@ -291,96 +314,107 @@ __device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem 
   const int stage_bytes = sbs * kStageBytes, pitch = sbs * KNJ_Q4K_BYTES;
   const int wrow = tile_row(g, pitch);
   const int rows_per_tile = DUAL ? 8 : 16;
-  const int job_stride = kJobTok * nsb * kPanelBytes, tok_stride = nsb * kPanelBytes;
+  const int tok_stride = nsb * kPanelBytes;
   uint8_t *ring = sm.ring + (size_t)warp * S * stage_bytes;
   uint64_t *bars = sm.bars + warp * kMaxStages;
   if (u0 >= u1) return;
   const int jfirst = u0 / tiles, jlast = (u1 - 1) / tiles;
-  for (int jb = jfirst; jb <= jlast; jb += 2) {
-    const int njr = min(2, jlast - jb + 1);
-    __syncthreads();  // the previous round's tiles are done with the panels
-    // ---- panels of the round's jobs: one warp per (job, token, superblock)
-    for (int item = warp; item < njr * kJobTok * nsb; item += kWarps) {
-      const int sb = item % nsb, jtk = item / nsb, tk = jtk % kJobTok, jr = jtk / kJobTok;
-      const int job = jb + jr, a = job_locate(jt.jbase, job);
-      int pair = -1, row = 0;
-      if (job_token(job, a, tk, pair, row)) {
-        float v[8];
-        load_row(row, sb, lane, v);
-        if (trace_mode != 3) {
-          const float inv = panel_convert(v, sm.panels + (size_t)jr * job_stride + (size_t)tk * tok_stride + (size_t)sb * kPanelBytes, lane);
-          if (lane == 0) sm.inv[(jr * kJobTok + tk) * 16 + sb] = inv;
-        }
-      } else {
-        pair = -1;
-      }
-      if (sb == 0 && lane == 0) sm.pair[jr * kJobTok + tk] = pair;
-    }
-    __syncthreads();
-
-    // ---- this warp's tiles of the round: r0 + warp, r0 + warp + 16, ...
-    const int r0 = max(u0, jb * tiles), r1 = min(u1, (jb + 2) * tiles);
+  for (int job = jfirst; job <= jlast; ++job) {
+    const int a = job_locate(jt.jbase, job);
+    // ---- this warp's tiles of the job: r0 + warp, r0 + warp + 16, ...; their first boxes leave before the
+    // panels are built (weights do not depend on the activations)
+    const int r0 = max(u0, job * tiles), r1 = min(u1, (job + 1) * tiles);
     const int n_mine = r0 + warp < r1 ? (r1 - r0 - warp + kWarps - 1) / kWarps : 0;
     const int n_items = n_mine * nbox;
-    int p_row = 0;  // first weight row of the tile the producer cursor is in (boxes are issued in order)
-    auto issue = [&](int i) {  // box i of the round: box i % nbox of this warp's tile i / nbox
-      const int bx = i % nbox;
-      if (bx == 0) {
-        const int u = r0 + warp + kWarps * (i / nbox), job = u / tiles;
-        p_row = jt.uexp[job_locate(jt.jbase, job)] * sh.N + (u - job * tiles) * rows_per_tile;
-      }
+    const int row_base = jt.uexp[a] * sh.N + (r0 + warp - job * tiles) * rows_per_tile;
+    auto issue = [&](int i) {  // box i of the job: box i % nbox of this warp's tile i / nbox
       if (lane == 0) {
-        const int stage = i % S;
+        const int bx = i % nbox, row = row_base + (i / nbox) * kWarps * rows_per_tile, stage = i % S;
         uint8_t *dst = ring + (size_t)stage * stage_bytes;
         fence_proxy_async();
         mbar_expect_tx(&bars[stage], (uint32_t)stage_bytes);
-        tma_load_rows(dst, map0, bx * (pitch / 4), p_row, &bars[stage]);
-        if (DUAL) tma_load_rows(dst + 8 * pitch, map1, bx * (pitch / 4), p_row, &bars[stage]);
+        tma_load_rows(dst, map0, bx * (pitch / 4), row, &bars[stage]);
+        if (DUAL) tma_load_rows(dst + 8 * pitch, map1, bx * (pitch / 4), row, &bars[stage]);
       }
     };
     if (ok && trace_mode != 2)
       for (int i = 0; i < S && i < n_items; ++i) issue(i);
 
-    float rg = 0.f, rh = 0.f;
-    int jr = 0, n0 = 0;
+    __syncthreads();  // the previous job's tiles are done with the panels
+    // ---- panels of the job: one warp per (token, superblock)
+    for (int item = warp; item < kJobTok * nsb; item += kWarps) {
+      const int sb = item % nsb, tk = item / nsb;
+      int pair = -1, row = 0;
+      const bool live = job_token(job, a, tk, pair, row);
+      if (live) {
+        float v[8];
+        load_row(row, sb, lane, v);
+        if (trace_mode != 3) {
+          const float inv = panel_convert(v, sm.panels + (size_t)tk * tok_stride + (size_t)sb * kPanelBytes, lane);
+          if (lane == 0) sm.inv[tk * 16 + sb] = inv;
+        }
+      }
+      if (sb == 0 && lane == 0) sm.pair[tk] = live ? pair : -1;
+    }
+    __syncthreads();
+    const bool two = sm.pair[4] >= 0;  // tokens fill the slots from 0 up: a fifth token means a second group
+
+    float rg[2] = {0.f, 0.f}, rh[2] = {0.f, 0.f};
     for (int i = 0; i < n_items; ++i) {
       const int bx = i % nbox;
-      if (bx == 0) {
-        const int u = r0 + warp + kWarps * (i / nbox), job = u / tiles;
-        jr = job - jb;
-        n0 = (u - job * tiles) * rows_per_tile;
-        rg = rh = 0.f;
-      }
+      if (bx == 0) rg[0] = rg[1] = rh[0] = rh[1] = 0.f;
       const int stage = i % S;
       if (ok && trace_mode != 2) {
         if (!mbar_wait_for(&bars[stage], (parity >> stage) & 1u, wait_cycles, sm.fail)) ok = false;
         parity ^= 1u << stage;
       }
       if (ok) {
-        if (trace_mode != 1)
+        if (trace_mode != 1) {
           for (int k = 0; k < sbs; ++k) {
             const int sb = bx * sbs + k;
-            float pg, ph;
-            tile_part(ring + (size_t)stage * stage_bytes + k * KNJ_Q4K_BYTES, pitch, wrow,
-                      sm.panels + (size_t)jr * job_stride + (size_t)sb * kPanelBytes, tok_stride, lane, pg, ph);
-            const float inv = sm.inv[(jr * kJobTok + t) * 16 + sb];
-            rg = fmaf(pg, inv, rg);
-            rh = fmaf(ph, inv, rh);
+            const uint8_t *src = ring + (size_t)stage * stage_bytes + k * KNJ_Q4K_BYTES;
+            const uint8_t *pan = sm.panels + (size_t)sb * kPanelBytes;
+            // the box is free again once the last superblock's weights are in registers
+            auto refill = [&]() {
+              if (k == sbs - 1) {
+                __syncwarp();
+                if (trace_mode != 2 && i + S < n_items) issue(i + S);
+              }
+            };
+            if (two) {
+              float pg[2], ph[2];
+              tile_part<2>(src, pitch, wrow, pan, tok_stride, lane, pg, ph, refill);
+              rg[0] = fmaf(pg[0], sm.inv[t * 16 + sb], rg[0]);
+              rh[0] = fmaf(ph[0], sm.inv[t * 16 + sb], rh[0]);
+              rg[1] = fmaf(pg[1], sm.inv[(4 + t) * 16 + sb], rg[1]);
+              rh[1] = fmaf(ph[1], sm.inv[(4 + t) * 16 + sb], rh[1]);
+            } else {
+              float pg[1], ph[1];
+              tile_part<1>(src, pitch, wrow, pan, tok_stride, lane, pg, ph, refill);
+              rg[0] = fmaf(pg[0], sm.inv[t * 16 + sb], rg[0]);
+              rh[0] = fmaf(ph[0], sm.inv[t * 16 + sb], rh[0]);
+            }
           }
-        __syncwarp();  // every lane is done with the stage
-        if (trace_mode != 2 && i + S < n_items) issue(i + S);
+        } else {
+          __syncwarp();
+          if (i + S < n_items) issue(i + S);
+        }
       }
       if (bx == nbox - 1 && ok) {
-        const int pair = sm.pair[jr * kJobTok + t];
-        if (pair >= 0) {
-          if (DUAL) {
-            const size_t o = (size_t)pair * sh.N + n0 + wrow;
-            if (out0) out0[o] = rg;
-            if (out1) out1[o] = rh;
-            if (out2) out2[o] = silu(rg) * rh;
-          } else {
-            out0[(size_t)pair * sh.N + n0 + wrow] = rg;
-            out0[(size_t)pair * sh.N + n0 + wrow + 8] = rh;
+        const int n0 = (r0 + warp - job * tiles + (i / nbox) * kWarps) * rows_per_tile;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const int pair = (q == 0 || two) ? sm.pair[4 * q + t] : -1;
+          if (pair >= 0) {
+            if (DUAL) {
+              const size_t o = (size_t)pair * sh.N + n0 + wrow;
+              if (out0) out0[o] = rg[q];
+              if (out1) out1[o] = rh[q];
+              if (out2) out2[o] = silu(rg[q]) * rh[q];
+            } else {
+              out0[(size_t)pair * sh.N + n0 + wrow] = rg[q];
+              out0[(size_t)pair * sh.N + n0 + wrow + 8] = rh[q];
+            }
           }
         }
       }

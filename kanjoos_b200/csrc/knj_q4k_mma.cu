@@ -5,14 +5,14 @@
 // (src/model/model.cpp:326-380), all on the tile engine of knj_q4k_engine.cuh.
 //
 // One persistent CTA per SM, 16 independent warps. The work of a launch is the
-// flat list (job, tile): a JOB is one active expert with up to 4 of its tokens (an
+// flat list (job, tile): a JOB is one active expert with up to 8 of its tokens (an
 // expert with more tokens yields several jobs; its weights then come from L2 after
 // the first), a tile is 16 weight rows. Every CTA takes an equal contiguous run of
-// that list, two jobs at a time: the CTA converts the two jobs' activation rows
-// into shared-memory panels once, then warp w takes every 16th tile of the run,
-// walks its superblocks through its own ring of TMA boxes (filled `stages` boxes
-// ahead, across tile boundaries) and stores the 16 x 4 results itself. No partial
-// sums cross warps and nothing but weights is read in the inner loop.
+// that list, one job at a time: the CTA converts the job's activation rows into a
+// shared-memory panel once, then warp w takes every 16th tile of the run, walks its
+// superblocks through its own ring of TMA boxes (filled `stages` boxes ahead, across
+// tile boundaries) and stores the 16 x 8 results itself. No partial sums cross warps
+// and nothing but weights and the panel is read in the inner loop.
 #include "knj_common.cuh"
 #include "knj_q4k.h"
 #include "knj_q4k_engine.cuh"
@@ -68,8 +68,8 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_proj_kernel(const __grid_cons
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ int s_jbase[257];
   __shared__ int s_uexp[256], s_ucnt[256];
-  __shared__ float s_inv[2 * q4e::kJobTok * 16];
-  __shared__ int s_pair[2 * q4e::kJobTok];
+  __shared__ float s_inv[q4e::kJobTok * 16];
+  __shared__ int s_pair[q4e::kJobTok];
   __shared__ int s_fail;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const ProjSmem lay = proj_smem(p.shape.nsb, p.shape.sbs, p.shape.stages);

@@ -36,8 +36,10 @@ constexpr int kMaxT = 64;  // tokens per step
 constexpr int kThreads = q4e::kWarps * 32;
 constexpr int kMaxSlices = 8;  // hidden <= 2048: the logits keep a router row in registers
 
-struct alignas(64) StackLayer {
+struct LayerMaps {  // stay in global memory: the TMA unit reads them there
   CUtensorMap mg, mu, md;  // gate, up, down weights as TMA boxes of the projection phases
+};
+struct LayerDesc {  // copied to shared memory one layer ahead
   const void *x;
   void *out;
   const __nv_bfloat16 *Wr;
@@ -49,9 +51,11 @@ struct alignas(64) StackLayer {
   float eps;
   int residual, x_dtype, out_dtype;
 };
+static_assert(sizeof(LayerDesc) % 4 == 0, "copied by words");
 
 struct StackParams {
-  const StackLayer *layers;
+  const LayerMaps *maps;
+  const LayerDesc *layers;
   int n_layers, T, H, F, E, k;
   float *logits;       // [T][E]
   float *scales;       // [T] RMSNorm scale of the layer's rows
@@ -99,7 +103,7 @@ __device__ __forceinline__ bool grid_wait(unsigned *sync, unsigned target, long 
 
 // Shared-memory plan (byte offsets into the dynamic block).
 struct Plan {
-  uint32_t ring, panels, bars, sel_e, sel_w, mask, jbase, uexp, inv, pair, scale, ord, fail, total;
+  uint32_t ring, panels, bars, sel_e, sel_w, mask, jbase, uexp, inv, pair, scale, ord, fail, desc, total;
 };
 __host__ __device__ inline Plan make_plan(const q4e::PhaseShape &gu, const q4e::PhaseShape &dn, int T, int k) {
   Plan pl;
@@ -115,11 +119,12 @@ __host__ __device__ inline Plan make_plan(const q4e::PhaseShape &gu, const q4e::
   pl.mask = take(256 * 8);
   pl.jbase = take(257 * 4);
   pl.uexp = take(256 * 4);
-  pl.inv = take(2 * q4e::kJobTok * 16 * 4);
-  pl.pair = take(2 * q4e::kJobTok * 4);
+  pl.inv = take(q4e::kJobTok * 16 * 4);
+  pl.pair = take(q4e::kJobTok * 4);
   pl.scale = take((size_t)T * 4);
   pl.ord = take((size_t)T * k);
   pl.fail = take(16);
+  pl.desc = take(2 * sizeof(LayerDesc));
   pl.total = o;
   return pl;
 }
@@ -134,125 +139,133 @@ __device__ __forceinline__ void load8_bf16(const __nv_bfloat16 *p, float (&v)[8]
   }
 }
 
+#ifdef KNJ_TRACE
+// Measurement build only: global-timer stamps of one CTA's stages in layer 1 (layer 0 of a one-layer stack).
+__device__ unsigned long long g_stack_trace[16 * 160];
+#define KNJ_STAMP(i) do { if (threadIdx.x == 0 && l == trace_layer) g_stack_trace[blockIdx.x * 16 + (i)] = global_timer_ns(); } while (0)
+#else
+#define KNJ_STAMP(i)
+#endif
+
 // Stage 1 of a layer for one CTA item: experts 8 eg .. 8 eg + 7 (one per warp, two warps per expert) times tokens
 // 8 tg .. 8 tg + 7 (four per warp). Row statistics and logits in moe_front_kernel's operation order (lane owns
-// elements 256 sl + 8 lane + j, even/odd chains, warp_sum). rows_s: at least 8 * H * 4 bytes of shared memory.
-__device__ __noinline__ void stage_logits(const StackParams &p, const StackLayer &L, int eg, int tg, uint8_t *rows_s) {
+// elements 256 sl + 8 lane + j, even/odd chains, warp_sum). The CTA first brings its eight router rows (times the
+// norm weights, f32) and its token rows (as they are) into shared memory with every load in flight at once;
+// scratch: 8 * H * 4 bytes for the router rows followed by 8 * H * 4 for the token rows.
+__device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc &L, int eg, int tg, uint8_t *scratch, int l,
+                                          int trace_layer) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int T = p.T, H = p.H, E = p.E, nslice = H / 256;
   const bool has_norm = L.norm_w != nullptr;
-  {
-      const int e = eg * 8 + (warp & 7), ee = min(e, E - 1);
-      const int t_first = tg * 8 + (warp >> 3) * 4, t_end = min(T, t_first + 4);
-      float wr[kMaxSlices][8];
+  float *wr_s = reinterpret_cast<float *>(scratch);
+  uint8_t *rows_s = scratch + (size_t)8 * H * 4;
+  const int esz = L.x_dtype == KNJ_DT_F32 ? 4 : 2, row_bytes = H * esz, cpr = row_bytes / 16;
+  const int nt = min(8, T - tg * 8);
+  // ---- loads first (router rows, norm weights, token rows), conversions after
+  const int wchunks = 8 * (H / 8);  // 16-byte pieces of the eight bf16 router rows
+  constexpr int kPer = (8 * 256 * kMaxSlices / 8 + kThreads - 1) / kThreads;  // 4 pieces per thread at H = 2048
+  uint4 wraw[kPer], nraw[kPer];
 #pragma unroll
-      for (int i = 0; i < kMaxSlices; ++i) {
-        if (i < nslice) {
-          load8_bf16(L.Wr + (size_t)ee * H + 256 * i + 8 * lane, wr[i]);
-          if (has_norm) {
-            float nw[8];
-            load8_bf16(L.norm_w + 256 * i + 8 * lane, nw);
+  for (int q = 0; q < kPer; ++q) {
+    const int i = threadIdx.x + q * kThreads;
+    if (i < wchunks) {
+      const int r = i / (H / 8), ch = i - r * (H / 8);
+      const int ee = min(eg * 8 + r, E - 1);
+      wraw[q] = __ldg(reinterpret_cast<const uint4 *>(L.Wr + (size_t)ee * H + 8 * ch));
+      if (has_norm) nraw[q] = __ldg(reinterpret_cast<const uint4 *>(L.norm_w + 8 * ch));
+    }
+  }
+  for (int i = threadIdx.x; i < nt * cpr; i += kThreads) {
+    const int r = i / cpr, ch = i - r * cpr;
+    *reinterpret_cast<uint4 *>(rows_s + (size_t)r * row_bytes + 16 * ch) =
+        __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(L.x) + (int64_t)(tg * 8 + r) * L.ldx * esz + 16 * ch));
+  }
 #pragma unroll
-            for (int j = 0; j < 8; ++j) wr[i][j] *= nw[j];
-          }
+  for (int q = 0; q < kPer; ++q) {
+    const int i = threadIdx.x + q * kThreads;
+    if (i < wchunks) {
+      const uint32_t w[4] = {wraw[q].x, wraw[q].y, wraw[q].z, wraw[q].w}, n[4] = {nraw[q].x, nraw[q].y, nraw[q].z, nraw[q].w};
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        v[2 * j] = __uint_as_float(w[j] << 16);
+        v[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+        if (has_norm) {
+          v[2 * j] *= __uint_as_float(n[j] << 16);
+          v[2 * j + 1] *= __uint_as_float(n[j] & 0xffff0000u);
         }
       }
-      const float bias = (L.bias && e < E) ? L.bias[e] : 0.f;
-      // the item's (at most eight) token rows, as they are, into the idle weight ring: one trip to L2 for the
-      // whole CTA instead of one per warp and token
-      const int esz = L.x_dtype == KNJ_DT_F32 ? 4 : 2, row_bytes = H * esz, cpr = row_bytes / 16;
-      const int nt = min(8, T - tg * 8);
-      for (int i = threadIdx.x; i < nt * cpr; i += kThreads) {
-        const int r = i / cpr, ch = i - r * cpr;
-        *reinterpret_cast<uint4 *>(rows_s + (size_t)r * row_bytes + 16 * ch) =
-            __ldcg(reinterpret_cast<const uint4 *>(static_cast<const uint8_t *>(L.x) + (int64_t)(tg * 8 + r) * L.ldx * esz + 16 * ch));
-      }
-      __syncthreads();
-      for (int t = t_first; t < t_end; ++t) {
-        float d0 = 0.f, d1 = 0.f, s0 = 0.f, s1 = 0.f;
-        const uint8_t *row = rows_s + (size_t)(t - tg * 8) * row_bytes;
+      *reinterpret_cast<float4 *>(wr_s + (size_t)8 * i) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4 *>(wr_s + (size_t)8 * i + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    }
+  }
+  __syncthreads();
+  KNJ_STAMP(11);
+  const int e = eg * 8 + (warp & 7);
+  const int t_first = tg * 8 + (warp >> 3) * 4, t_end = min(T, t_first + 4);
+  const float bias = (L.bias && e < E) ? L.bias[e] : 0.f;
+  const float *wrow = wr_s + (size_t)(warp & 7) * H;
+  // two tokens per pass over the router row: their chains are independent of each other
+  for (int t = t_first; t < t_end; t += 2) {
+    const bool second = t + 1 < t_end;
+    float d0[2] = {0.f, 0.f}, d1[2] = {0.f, 0.f}, s0[2] = {0.f, 0.f}, s1[2] = {0.f, 0.f};
 #pragma unroll
-        for (int sl = 0; sl < kMaxSlices; ++sl) {
-          if (sl < nslice) {
-            float v[8];
-            if (esz == 4) {
-              const float4 a = *reinterpret_cast<const float4 *>(row + (256 * sl + 8 * lane) * 4);
-              const float4 b = *reinterpret_cast<const float4 *>(row + (256 * sl + 8 * lane) * 4 + 16);
-              v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
-            } else {
-              const uint4 r = *reinterpret_cast<const uint4 *>(row + (256 * sl + 8 * lane) * 2);
-              const uint32_t u[4] = {r.x, r.y, r.z, r.w};
+    for (int sl = 0; sl < kMaxSlices; ++sl) {
+      if (sl < nslice) {
+        const float4 wa = *reinterpret_cast<const float4 *>(wrow + 256 * sl + 8 * lane);
+        const float4 wb = *reinterpret_cast<const float4 *>(wrow + 256 * sl + 8 * lane + 4);
+        const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                v[2 * j] = __uint_as_float(u[j] << 16);
-                v[2 * j + 1] = __uint_as_float(u[j] & 0xffff0000u);
-              }
-            }
+        for (int u = 0; u < 2; ++u) {
+          const uint8_t *row = rows_s + (size_t)(t + (second ? u : 0) - tg * 8) * row_bytes;
+          float v[8];
+          if (esz == 4) {
+            const float4 a = *reinterpret_cast<const float4 *>(row + (256 * sl + 8 * lane) * 4);
+            const float4 b = *reinterpret_cast<const float4 *>(row + (256 * sl + 8 * lane) * 4 + 16);
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+          } else {
+            const uint4 r = *reinterpret_cast<const uint4 *>(row + (256 * sl + 8 * lane) * 2);
+            const uint32_t x4[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-            for (int j = 0; j < 8; j += 2) {
-              d0 = fmaf(wr[sl][j], v[j], d0);
-              d1 = fmaf(wr[sl][j + 1], v[j + 1], d1);
-              s0 = fmaf(v[j], v[j], s0);
-              s1 = fmaf(v[j + 1], v[j + 1], s1);
+            for (int j = 0; j < 4; ++j) {
+              v[2 * j] = __uint_as_float(x4[j] << 16);
+              v[2 * j + 1] = __uint_as_float(x4[j] & 0xffff0000u);
             }
           }
-        }
-        const float dot = warp_sum(d0 + d1), ss = warp_sum(s0 + s1);
-        if (lane == 0) {
-          const float scale = has_norm ? 1.0f / sqrtf(ss / (float)H + L.eps) : 1.0f;
-          if (eg == 0 && (warp & 7) == 0) p.scales[t] = scale;
-          if (e < E) p.logits[(size_t)t * E + e] = dot * scale + bias;
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            d0[u] = fmaf(w[j], v[j], d0[u]);
+            d1[u] = fmaf(w[j + 1], v[j + 1], d1[u]);
+            s0[u] = fmaf(v[j], v[j], s0[u]);
+            s1[u] = fmaf(v[j + 1], v[j + 1], s1[u]);
+          }
         }
       }
     }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (u == 1 && !second) break;
+      const float dot = warp_sum(d0[u] + d1[u]), ss = warp_sum(s0[u] + s1[u]);
+      if (lane == 0) {
+        const float scale = has_norm ? 1.0f / sqrtf(ss / (float)H + L.eps) : 1.0f;
+        if (eg == 0 && (warp & 7) == 0) p.scales[t + u] = scale;
+        if (e < E) p.logits[(size_t)(t + u) * E + e] = dot * scale + bias;
+      }
+    }
+  }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParams p) {
-  extern __shared__ __align__(128) uint8_t smem[];
+// Stage 2 of a layer, by every CTA for itself: top-k of every token, the per-expert token sets (bit masks), the
+// order of a token's slots for the weighted sum, and the job table of the projection stages.
+__device__ __noinline__ void stage_plan(const StackParams &p, const LayerDesc &L, const Plan &pl, uint8_t *smem) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int T = p.T, H = p.H, F = p.F, E = p.E, k = p.k, P = T * k;
-  const int G = gridDim.x, c = blockIdx.x;
-  const Plan pl = make_plan(p.gu, p.dn, T, k);
+  const int T = p.T, E = p.E, k = p.k, P = T * k, c = blockIdx.x;
   int *sel_e = reinterpret_cast<int *>(smem + pl.sel_e);
   float *sel_w = reinterpret_cast<float *>(smem + pl.sel_w);
   unsigned long long *mask = reinterpret_cast<unsigned long long *>(smem + pl.mask);
   int *jbase = reinterpret_cast<int *>(smem + pl.jbase), *uexp = reinterpret_cast<int *>(smem + pl.uexp);
   float *scale_s = reinterpret_cast<float *>(smem + pl.scale);
   unsigned char *ord = smem + pl.ord;
-  int *s_fail = reinterpret_cast<int *>(smem + pl.fail);
-  q4e::PhaseSmem sm;
-  sm.ring = smem + pl.ring;
-  sm.panels = smem + pl.panels;
-  sm.bars = reinterpret_cast<uint64_t *>(smem + pl.bars);
-  sm.inv = reinterpret_cast<float *>(smem + pl.inv);
-  sm.pair = reinterpret_cast<int *>(smem + pl.pair);
-  sm.fail = s_fail;
-  const q4e::JobTable jt{jbase, uexp};
-
-  if (lane == 0)
-    for (int s = 0; s < q4e::kMaxStages; ++s) mbar_init(&sm.bars[warp * q4e::kMaxStages + s], 1);
-  if (threadIdx.x == 0) *s_fail = 0;
-  mbar_init_fence();
-  __syncthreads();
-
-  unsigned arrivals = 0, parity = 0;
-  bool ok = true;
-  // logits: CTA c < n_eg * n_tg takes experts 8 eg .. 8 eg + 7 (one per warp pair) for tokens 8 tg .. 8 tg + 7
-  const int n_eg = (E + 7) / 8, n_tg = (T + 7) / 8;
-  const bool has_item = c < n_eg * n_tg;
-  const int eg = c % n_eg, tg = c / n_eg;
-
-  for (int l = 0; l < p.n_layers; ++l) {
-    const StackLayer &L = p.layers[l];
-    const bool has_norm = L.norm_w != nullptr;
-
-    // ---- stage 1: row statistics and router logits
-    if (has_item) stage_logits(p, L, eg, tg, smem + pl.ring);
-    arrivals += G;
-    grid_arrive(p.sync);
-    if (!grid_wait(p.sync, arrivals + (l == 0 ? (unsigned)p.stall : 0u), p.wait_cycles)) return;
-
-    // ---- stage 2: top-k per token (every CTA for itself), the per-expert token sets, the job table
     for (int t = threadIdx.x; t < T; t += kThreads) scale_s[t] = __ldcg(p.scales + t);
     for (int a = threadIdx.x; a < 256; a += kThreads) mask[a] = 0ull;
     for (int t = warp; t < T; t += q4e::kWarps) {
@@ -312,6 +325,76 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     }
     __syncthreads();
 
+}
+
+__global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParams p) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int T = p.T, H = p.H, F = p.F, E = p.E, k = p.k;
+  const int G = gridDim.x, c = blockIdx.x;
+  const Plan pl = make_plan(p.gu, p.dn, T, k);
+  int *sel_e = reinterpret_cast<int *>(smem + pl.sel_e);
+  float *sel_w = reinterpret_cast<float *>(smem + pl.sel_w);
+  unsigned long long *mask = reinterpret_cast<unsigned long long *>(smem + pl.mask);
+  int *jbase = reinterpret_cast<int *>(smem + pl.jbase), *uexp = reinterpret_cast<int *>(smem + pl.uexp);
+  float *scale_s = reinterpret_cast<float *>(smem + pl.scale);
+  unsigned char *ord = smem + pl.ord;
+  int *s_fail = reinterpret_cast<int *>(smem + pl.fail);
+  q4e::PhaseSmem sm;
+  sm.ring = smem + pl.ring;
+  sm.panels = smem + pl.panels;
+  sm.bars = reinterpret_cast<uint64_t *>(smem + pl.bars);
+  sm.inv = reinterpret_cast<float *>(smem + pl.inv);
+  sm.pair = reinterpret_cast<int *>(smem + pl.pair);
+  sm.fail = s_fail;
+  const q4e::JobTable jt{jbase, uexp};
+
+  if (lane == 0)
+    for (int s = 0; s < q4e::kMaxStages; ++s) mbar_init(&sm.bars[warp * q4e::kMaxStages + s], 1);
+  if (threadIdx.x == 0) *s_fail = 0;
+  mbar_init_fence();
+  __syncthreads();
+
+  unsigned arrivals = 0, parity = 0;
+  bool ok = true;
+  // logits: CTA c < n_eg * n_tg takes experts 8 eg .. 8 eg + 7 (one per warp pair) for tokens 8 tg .. 8 tg + 7
+  const int n_eg = (E + 7) / 8, n_tg = (T + 7) / 8;
+  const bool has_item = c < n_eg * n_tg;
+  const int eg = c % n_eg, tg = c / n_eg;
+
+#ifdef KNJ_TRACE
+  const int trace_layer = p.n_layers > 1 ? 1 : 0;
+#endif
+  // the layers' descriptions are read from shared memory; the next layer's arrives while the current one computes
+  LayerDesc *descs = reinterpret_cast<LayerDesc *>(smem + pl.desc);
+  auto stage_desc = [&](int l) {
+    if (threadIdx.x < sizeof(LayerDesc) / 4)
+      reinterpret_cast<uint32_t *>(&descs[l & 1])[threadIdx.x] = reinterpret_cast<const uint32_t *>(p.layers + l)[threadIdx.x];
+  };
+  stage_desc(0);
+  __syncthreads();
+  for (int l = 0; l < p.n_layers; ++l) {
+    const LayerDesc &L = descs[l & 1];
+    const LayerMaps &M = p.maps[l];
+    const bool has_norm = L.norm_w != nullptr;
+    if (l + 1 < p.n_layers) stage_desc(l + 1);  // published by the CTA barriers of this layer
+    KNJ_STAMP(0);
+
+    // ---- stage 1: row statistics and router logits
+#ifdef KNJ_TRACE
+    if (has_item) stage_logits(p, L, eg, tg, smem + pl.ring, l, trace_layer);
+#else
+    if (has_item) stage_logits(p, L, eg, tg, smem + pl.ring, l, 0);
+#endif
+    KNJ_STAMP(1);
+    arrivals += G;
+    grid_arrive(p.sync);
+    if (!grid_wait(p.sync, arrivals + (l == 0 ? (unsigned)p.stall : 0u), p.wait_cycles)) return;
+    KNJ_STAMP(2);
+
+    // ---- stage 2: top-k per token (every CTA for itself), the per-expert token sets, the job table
+    stage_plan(p, L, pl, smem);
+
     // token slot tk of a job: the (4 (job - first job of the expert) + tk)-th token of the expert's set
     auto job_tok = [&](int job, int a, int tk, int &e_out) {
       const int e = uexp[a];
@@ -328,12 +411,13 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       return tok * k + s;
     };
 
+    KNJ_STAMP(3);
     // ---- stage 3: gate, up, SiLU*up -> act
     {
       const long long U = (long long)jbase[256] * p.gu.tiles;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
       q4e::run_phase<true>(
-          p.gu, sm, jt, u0, u1, &L.mg, &L.mu, nullptr, nullptr, p.act, p.wait_cycles, parity, ok,
+          p.gu, sm, jt, u0, u1, &M.mg, &M.mu, nullptr, nullptr, p.act, p.wait_cycles, parity, ok,
           [&](int job, int a, int tk, int &pair, int &row) {
             int e;
             const int tok = job_tok(job, a, tk, e);
@@ -353,16 +437,18 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
             }
           });
     }
+    KNJ_STAMP(4);
     arrivals += G;
     grid_arrive(p.sync);
     if (!grid_wait(p.sync, arrivals, p.wait_cycles)) return;
+    KNJ_STAMP(5);
 
     // ---- stage 4: down -> Y (one row per pair)
     {
       const long long U = (long long)jbase[256] * p.dn.tiles;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
       q4e::run_phase<false>(
-          p.dn, sm, jt, u0, u1, &L.md, &L.md, p.Y, nullptr, nullptr, p.wait_cycles, parity, ok,
+          p.dn, sm, jt, u0, u1, &M.md, &M.md, p.Y, nullptr, nullptr, p.wait_cycles, parity, ok,
           [&](int job, int a, int tk, int &pair, int &row) {
             int e;
             const int tok = job_tok(job, a, tk, e);
@@ -373,9 +459,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
           },
           [&](int row, int sb, int ln, float (&v)[8]) { q4e::load8_f32(p.act, KNJ_DT_F32, (int64_t)row * F + 256 * sb + 8 * ln, v); });
     }
+    KNJ_STAMP(6);
     arrivals += G;
     grid_arrive(p.sync);
     if (!grid_wait(p.sync, arrivals, p.wait_cycles)) return;
+    KNJ_STAMP(7);
 
     // ---- stage 5: ordered weighted sum of a token's k rows, residual last, four columns per thread
     {
@@ -414,18 +502,25 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
         }
       }
     }
+    KNJ_STAMP(8);
     if (l + 1 < p.n_layers) {
       arrivals += G;
       grid_arrive(p.sync);
       if (!grid_wait(p.sync, arrivals, p.wait_cycles)) return;
     }
+    KNJ_STAMP(9);
   }
   if (!ok && threadIdx.x == 0) atomicExch(p.sync + 1, 1u);
 }
 
 }  // namespace
 
+namespace {
+int g_force_big_stack = 0;  // measurement builds: run the tensor-core kernel for the smallest batches too
+}
+
 struct knj_moe_stack {
+  SmallStack *small = nullptr;  // batches of at most kSmallStackMaxTokens run the scalar-FMA kernel instead
   StackParams p{};
   void *dev_block = nullptr;  // layer table, logits, scales, activations, per-pair rows, sync words
   size_t smem = 0;
@@ -441,6 +536,15 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   const knj_moe_ffn_args &a0 = layers[0];
   const int T = a0.n_tokens, H = a0.hidden, F = a0.ffn, E = a0.n_experts, k = a0.top_k;
   KNJ_REQUIRE(T >= 1 && T <= kMaxT, "knj_moe_stack_create: n_tokens=%d, this launch takes 1..%d", T, kMaxT);
+  if (T <= kSmallStackMaxTokens && !g_force_big_stack) {
+    SmallStack *sm = nullptr;
+    const int rc = small_stack_create(layers, n_layers, &sm);
+    if (rc) return rc;
+    knj_moe_stack *st = new knj_moe_stack();
+    st->small = sm;
+    *out = st;
+    return KNJ_OK;
+  }
   KNJ_REQUIRE(H > 0 && H % 256 == 0 && H <= 256 * kMaxSlices, "knj_moe_stack_create: hidden=%d must be a multiple of 256, at most %d", H,
               256 * kMaxSlices);
   KNJ_REQUIRE(F > 0 && F % 256 == 0 && F <= 4096, "knj_moe_stack_create: ffn=%d must be a multiple of 256, at most 4096", F);
@@ -450,7 +554,8 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   sp.dn.N = H; sp.dn.nsb = F / 256; sp.dn.sbs = (sp.dn.nsb % 2 == 0) ? 2 : 1; sp.dn.tiles = H / 16;
   sp.gu.stages = sp.gu.sbs == 2 ? 2 : q4e::kMaxStages;
   sp.dn.stages = sp.dn.sbs == 2 ? 2 : q4e::kMaxStages;
-  std::vector<StackLayer> table(n_layers);
+  std::vector<LayerDesc> table(n_layers);
+  std::vector<LayerMaps> maps(n_layers);
   for (int l = 0; l < n_layers; ++l) {
     const knj_moe_ffn_args &a = layers[l];
     KNJ_REQUIRE(a.n_tokens == T && a.hidden == H && a.ffn == F && a.n_experts == E && a.top_k == k,
@@ -465,10 +570,11 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
                     (!a.norm_w || al16(a.norm_w)),
                 "knj_moe_stack_create: layer %d: x, out, router, norm and expert bases must be 16-byte aligned", l);
     KNJ_REQUIRE(a.x != a.out, "knj_moe_stack_create: layer %d: out must not alias x (other CTAs still read x)", l);
-    StackLayer &s = table[l];
-    int rc = make_row_tensor_map(&s.mg, a.w_gate, (uint64_t)E * F, (uint32_t)sp.gu.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.gu.sbs * KNJ_Q4K_BYTES, 8);
-    if (!rc) rc = make_row_tensor_map(&s.mu, a.w_up, (uint64_t)E * F, (uint32_t)sp.gu.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.gu.sbs * KNJ_Q4K_BYTES, 8);
-    if (!rc) rc = make_row_tensor_map(&s.md, a.w_down, (uint64_t)E * H, (uint32_t)sp.dn.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.dn.sbs * KNJ_Q4K_BYTES, 16);
+    LayerDesc &s = table[l];
+    LayerMaps &m = maps[l];
+    int rc = make_row_tensor_map(&m.mg, a.w_gate, (uint64_t)E * F, (uint32_t)sp.gu.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.gu.sbs * KNJ_Q4K_BYTES, 8);
+    if (!rc) rc = make_row_tensor_map(&m.mu, a.w_up, (uint64_t)E * F, (uint32_t)sp.gu.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.gu.sbs * KNJ_Q4K_BYTES, 8);
+    if (!rc) rc = make_row_tensor_map(&m.md, a.w_down, (uint64_t)E * H, (uint32_t)sp.dn.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.dn.sbs * KNJ_Q4K_BYTES, 16);
     if (rc) return rc;
     s.x = a.x;
     s.out = a.out;
@@ -518,13 +624,16 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   st->grid = sm_count();
   auto up256 = [](size_t n) { return (n + 255) & ~(size_t)255; };
   const size_t P = (size_t)T * k;
-  const size_t off_logits = up256((size_t)n_layers * sizeof(StackLayer));
+  const size_t off_desc = up256((size_t)n_layers * sizeof(LayerMaps));
+  const size_t off_logits = off_desc + up256((size_t)n_layers * sizeof(LayerDesc));
   const size_t off_scales = off_logits + up256((size_t)T * E * 4);
   const size_t off_act = off_scales + up256((size_t)T * 4);
   const size_t off_y = off_act + up256(P * F * 4);
   const size_t off_sync = off_y + up256(P * H * 4);
   e = cudaMalloc(&st->dev_block, off_sync + 256);
-  if (e == cudaSuccess) e = cudaMemcpy(st->dev_block, table.data(), (size_t)n_layers * sizeof(StackLayer), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(st->dev_block, maps.data(), (size_t)n_layers * sizeof(LayerMaps), cudaMemcpyHostToDevice);
+  if (e == cudaSuccess)
+    e = cudaMemcpy(static_cast<char *>(st->dev_block) + off_desc, table.data(), (size_t)n_layers * sizeof(LayerDesc), cudaMemcpyHostToDevice);
   if (e != cudaSuccess) {
     if (st->dev_block) cudaFree(st->dev_block);
     delete st;
@@ -534,7 +643,8 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   }
   char *base = static_cast<char *>(st->dev_block);
   st->p = sp;
-  st->p.layers = reinterpret_cast<const StackLayer *>(base);
+  st->p.maps = reinterpret_cast<const LayerMaps *>(base);
+  st->p.layers = reinterpret_cast<const LayerDesc *>(base + off_desc);
   st->p.n_layers = n_layers;
   st->p.T = T; st->p.H = H; st->p.F = F; st->p.E = E; st->p.k = k;
   st->p.logits = reinterpret_cast<float *>(base + off_logits);
@@ -549,7 +659,8 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
 }
 
 int knj_moe_stack_decode_launch(knj_moe_stack *st, knj_stream_t s) {
-  KNJ_REQUIRE(st && st->dev_block, "knj_moe_stack_decode_launch: null stack");
+  KNJ_REQUIRE(st && (st->small || st->dev_block), "knj_moe_stack_decode_launch: null stack");
+  if (st->small) return small_stack_launch(st->small, s);
   KNJ_CUDA(cudaMemsetAsync(st->p.sync, 0, 8, as_stream(s)));
   void *args[] = {&st->p};
   KNJ_CUDA(cudaLaunchCooperativeKernel(reinterpret_cast<const void *>(moe_stack_kernel), dim3(st->grid), dim3(kThreads), args,
@@ -561,11 +672,13 @@ int knj_moe_stack_set_wait(knj_moe_stack *st, long long wait_cycles, int stall_f
   KNJ_REQUIRE(st, "knj_moe_stack_set_wait: null stack");
   st->p.wait_cycles = wait_cycles > 0 ? wait_cycles : kMaxWaitCycles;
   st->p.stall = stall_first_barrier > 0 ? stall_first_barrier : 0;
+  if (st->small) small_stack_set_wait(st->small, st->p.wait_cycles, st->p.stall);
   return KNJ_OK;
 }
 
 int knj_moe_stack_status(knj_moe_stack *st, knj_stream_t s) {
-  KNJ_REQUIRE(st && st->dev_block, "knj_moe_stack_status: null stack");
+  KNJ_REQUIRE(st && (st->small || st->dev_block), "knj_moe_stack_status: null stack");
+  if (st->small) return small_stack_status(st->small, s);
   unsigned int words[2] = {0, 0};
   KNJ_CUDA(cudaMemcpyAsync(words, st->p.sync, 8, cudaMemcpyDeviceToHost, as_stream(s)));
   KNJ_CUDA(cudaStreamSynchronize(as_stream(s)));
@@ -576,8 +689,17 @@ int knj_moe_stack_status(knj_moe_stack *st, knj_stream_t s) {
   return KNJ_OK;
 }
 
+#ifdef KNJ_TRACE
+int knj_trace_force_big_stack(int on) { g_force_big_stack = on; return 0; }
+int knj_trace_stack(unsigned long long *host_out) {  // measurement build only: 160 CTAs x 16 stamps
+  KNJ_CUDA(cudaMemcpyFromSymbol(host_out, g_stack_trace, sizeof(unsigned long long) * 16 * 160));
+  return KNJ_OK;
+}
+#endif
+
 void knj_moe_stack_destroy(knj_moe_stack *st) {
   if (!st) return;
+  if (st->small) small_stack_destroy(st->small);
   if (st->dev_block) cudaFree(st->dev_block);
   delete st;
 }
