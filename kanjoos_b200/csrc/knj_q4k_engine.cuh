@@ -212,13 +212,26 @@ __device__ __forceinline__ void tile_part(const uint8_t *stage, int pitch, int w
 #pragma unroll
       for (int i = 0; i < 4; ++i) ce[q][c][i] = co[q][c][i] = 0.f;
   }
+  // B fragments: one 16-byte load per (group, sub-block, step pair). One group: all eight loads go out first;
+  // two groups: the loads of step pair j + 1 travel while pair j is multiplied.
+  constexpr int NB = NG == 1 ? 4 : 2;  // step pairs held in registers
+  uint4 be[NB][NG], bo[NB][NG];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {  // steps 2j and 2j + 1 share one 16-byte fragment load per sub-block and group
-    uint4 be[NG], bo[NG];
+  for (int j = 0; j < (NG == 1 ? 4 : 1); ++j)
 #pragma unroll
     for (int q = 0; q < NG; ++q) {
-      be[q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * j);
-      bo[q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * (4 + j));
+      be[j][q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * j);
+      bo[j][q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * (4 + j));
+    }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {  // steps 2j and 2j + 1
+    const int cur = NG == 1 ? j : (j & 1);
+    if (NG == 2 && j + 1 < 4) {
+#pragma unroll
+      for (int q = 0; q < NG; ++q) {
+        be[(j + 1) & 1][q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * (j + 1));
+        bo[(j + 1) & 1][q] = *reinterpret_cast<const uint4 *>(bsrc + q * grp_stride + 128 * (4 + j + 1));
+      }
     }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -228,13 +241,15 @@ __device__ __forceinline__ void tile_part(const uint8_t *stage, int pitch, int w
         const uint32_t a0 = mul_f16x2(xg & 0x000f000fu, sEg), a1 = mul_f16x2(xh & 0x000f000fu, sEh);
         const uint32_t a2 = mul_f16x2(yg & 0x000f000fu, sEg), a3 = mul_f16x2(yh & 0x000f000fu, sEh);
 #pragma unroll
-        for (int q = 0; q < NG; ++q) mma_f16_16816(ce[q][NC == 2 ? h : 0], a0, a1, a2, a3, h ? be[q].z : be[q].x, h ? be[q].w : be[q].y);
+        for (int q = 0; q < NG; ++q)
+          mma_f16_16816(ce[q][NC == 2 ? h : 0], a0, a1, a2, a3, h ? be[cur][q].z : be[cur][q].x, h ? be[cur][q].w : be[cur][q].y);
       }
       {
         const uint32_t a0 = mul_f16x2(xg & 0x00f000f0u, sOg), a1 = mul_f16x2(xh & 0x00f000f0u, sOh);
         const uint32_t a2 = mul_f16x2(yg & 0x00f000f0u, sOg), a3 = mul_f16x2(yh & 0x00f000f0u, sOh);
 #pragma unroll
-        for (int q = 0; q < NG; ++q) mma_f16_16816(co[q][NC == 2 ? h : 0], a0, a1, a2, a3, h ? bo[q].z : bo[q].x, h ? bo[q].w : bo[q].y);
+        for (int q = 0; q < NG; ++q)
+          mma_f16_16816(co[q][NC == 2 ? h : 0], a0, a1, a2, a3, h ? bo[cur][q].z : bo[cur][q].x, h ? bo[cur][q].w : bo[cur][q].y);
       }
     }
   }
@@ -279,6 +294,7 @@ struct PhaseSmem {       // per CTA
   uint64_t *bars;        // kWarps * kMaxStages, initialised with count 1
   float *inv;            // [kJobTok][16]
   int *pair;             // [kJobTok]: output rows of the job's tokens, -1: no token in the slot
+  float4 *red;           // [kWarps][32]: partial sums of the warps that share a tile (ksplit > 1 only)
   volatile int *fail;    // raised by the first wait that gives up
 };
 
@@ -303,11 +319,14 @@ __device__ __forceinline__ int job_locate(const int *jbase, int job) {
 // otherwise out0 = Y. Bit s of `parity` is the phase the warp's next wait on its barrier s expects (0 after
 // initialisation); `ok` turns false when a wait gave up (the rest of the phase is then skipped, the CTA barriers
 // are still met).
+// ksplit (1, 2 or 4, a divisor of the boxes per tile): that many adjacent warps share a tile, each taking a
+// contiguous part of its K range; their partial sums meet in sm.red (fixed order, two named barriers per tile).
+// For runs with few tiles per warp, where a warp walking the whole K alone would be the critical path.
 template <bool DUAL, class JobToken, class LoadRow>
 __device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem &sm, const JobTable &jt, int u0, int u1,
-                                          const CUtensorMap *map0, const CUtensorMap *map1, float *out0, float *out1,
-                                          float *out2, long long wait_cycles, unsigned &parity, bool &ok, JobToken job_token,
-                                          LoadRow load_row, int trace_mode = 0) {
+                                          int ksplit, const CUtensorMap *map0, const CUtensorMap *map1, float *out0,
+                                          float *out1, float *out2, long long wait_cycles, unsigned &parity, bool &ok,
+                                          JobToken job_token, LoadRow load_row, int trace_mode = 0) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int nsb = sh.nsb, S = sh.stages, sbs = sh.sbs, nbox = nsb / sbs, tiles = sh.tiles;
@@ -315,30 +334,42 @@ __device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem 
   const int wrow = tile_row(g, pitch);
   const int rows_per_tile = DUAL ? 8 : 16;
   const int tok_stride = nsb * kPanelBytes;
+  const int f = ksplit, nb = nbox / f;         // warps per tile, boxes per warp and tile
+  const int part = warp % f, slot = warp / f;  // this warp's K part; its group's place among the CTA's tiles
+  const int groups = kWarps / f;
   uint8_t *ring = sm.ring + (size_t)warp * S * stage_bytes;
   uint64_t *bars = sm.bars + warp * kMaxStages;
   if (u0 >= u1) return;
   const int jfirst = u0 / tiles, jlast = (u1 - 1) / tiles;
   for (int job = jfirst; job <= jlast; ++job) {
     const int a = job_locate(jt.jbase, job);
-    // ---- this warp's tiles of the job: r0 + warp, r0 + warp + 16, ...; their first boxes leave before the
+    // ---- this warp's tiles of the job: r0 + slot, r0 + slot + groups, ...; their first boxes leave before the
     // panels are built (weights do not depend on the activations)
     const int r0 = max(u0, job * tiles), r1 = min(u1, (job + 1) * tiles);
-    const int n_mine = r0 + warp < r1 ? (r1 - r0 - warp + kWarps - 1) / kWarps : 0;
-    const int n_items = n_mine * nbox;
-    const int row_base = jt.uexp[a] * sh.N + (r0 + warp - job * tiles) * rows_per_tile;
-    auto issue = [&](int i) {  // box i of the job: box i % nbox of this warp's tile i / nbox
+    const int n_mine = r0 + slot < r1 ? (r1 - r0 - slot + groups - 1) / groups : 0;
+    const int n_items = n_mine * nb;
+    const int row_base = jt.uexp[a] * sh.N + (r0 + slot - job * tiles) * rows_per_tile;
+    // producer cursor: boxes are issued in the order they are consumed, so its stage is always the one the
+    // consumer has just left once the ring is full. No divisions in the loops below: counters only.
+    int p_left = n_items, p_stage = 0, p_bl = 0, p_row = row_base;
+    auto issue_next = [&]() {
       if (lane == 0) {
-        const int bx = i % nbox, row = row_base + (i / nbox) * kWarps * rows_per_tile, stage = i % S;
-        uint8_t *dst = ring + (size_t)stage * stage_bytes;
+        uint8_t *dst = ring + (size_t)p_stage * stage_bytes;
+        const int x = (part * nb + p_bl) * (pitch / 4);
         fence_proxy_async();
-        mbar_expect_tx(&bars[stage], (uint32_t)stage_bytes);
-        tma_load_rows(dst, map0, bx * (pitch / 4), row, &bars[stage]);
-        if (DUAL) tma_load_rows(dst + 8 * pitch, map1, bx * (pitch / 4), row, &bars[stage]);
+        mbar_expect_tx(&bars[p_stage], (uint32_t)stage_bytes);
+        tma_load_rows(dst, map0, x, p_row, &bars[p_stage]);
+        if (DUAL) tma_load_rows(dst + 8 * pitch, map1, x, p_row, &bars[p_stage]);
       }
+      if (++p_stage == S) p_stage = 0;
+      if (++p_bl == nb) {
+        p_bl = 0;
+        p_row += groups * rows_per_tile;
+      }
+      --p_left;
     };
     if (ok && trace_mode != 2)
-      for (int i = 0; i < S && i < n_items; ++i) issue(i);
+      for (int i = 0; i < S && p_left > 0; ++i) issue_next();
 
     __syncthreads();  // the previous job's tiles are done with the panels
     // ---- panels of the job: one warp per (token, superblock)
@@ -359,49 +390,58 @@ __device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem 
     __syncthreads();
     const bool two = sm.pair[4] >= 0;  // tokens fill the slots from 0 up: a fifth token means a second group
 
-    float rg[2] = {0.f, 0.f}, rh[2] = {0.f, 0.f};
-    for (int i = 0; i < n_items; ++i) {
-      const int bx = i % nbox;
-      if (bx == 0) rg[0] = rg[1] = rh[0] = rh[1] = 0.f;
-      const int stage = i % S;
-      if (ok && trace_mode != 2) {
-        if (!mbar_wait_for(&bars[stage], (parity >> stage) & 1u, wait_cycles, sm.fail)) ok = false;
-        parity ^= 1u << stage;
-      }
-      if (ok) {
-        if (trace_mode != 1) {
-          for (int k = 0; k < sbs; ++k) {
-            const int sb = bx * sbs + k;
-            const uint8_t *src = ring + (size_t)stage * stage_bytes + k * KNJ_Q4K_BYTES;
-            const uint8_t *pan = sm.panels + (size_t)sb * kPanelBytes;
-            // the box is free again once the last superblock's weights are in registers
-            auto refill = [&]() {
-              if (k == sbs - 1) {
-                __syncwarp();
-                if (trace_mode != 2 && i + S < n_items) issue(i + S);
+    int stage = 0;
+    int n0 = (r0 + slot - job * tiles) * rows_per_tile;  // first output row of the tile in progress
+    const int sb_first = part * nb * sbs;
+    for (int ti = 0; ti < n_mine; ++ti, n0 += groups * rows_per_tile) {
+      float rg[2] = {0.f, 0.f}, rh[2] = {0.f, 0.f};
+      const uint8_t *pan = sm.panels + (size_t)sb_first * kPanelBytes;
+      const float *inv = sm.inv + t * 16 + sb_first;
+      for (int bl = 0; bl < nb; ++bl) {
+        if (ok && trace_mode != 2) {
+          if (!mbar_wait_for(&bars[stage], (parity >> stage) & 1u, wait_cycles, sm.fail)) ok = false;
+          parity ^= 1u << stage;
+        }
+        if (ok) {
+          if (trace_mode != 1) {
+            const uint8_t *src = ring + (size_t)stage * stage_bytes;
+            for (int k = 0; k < sbs; ++k, src += KNJ_Q4K_BYTES, pan += kPanelBytes, ++inv) {
+              auto nothing = [] {};
+              if (two) {
+                float pg[2], ph[2];
+                tile_part<2>(src, pitch, wrow, pan, tok_stride, lane, pg, ph, nothing);
+                rg[0] = fmaf(pg[0], inv[0], rg[0]);
+                rh[0] = fmaf(ph[0], inv[0], rh[0]);
+                rg[1] = fmaf(pg[1], inv[64], rg[1]);
+                rh[1] = fmaf(ph[1], inv[64], rh[1]);
+              } else {
+                float pg[1], ph[1];
+                tile_part<1>(src, pitch, wrow, pan, tok_stride, lane, pg, ph, nothing);
+                rg[0] = fmaf(pg[0], inv[0], rg[0]);
+                rh[0] = fmaf(ph[0], inv[0], rh[0]);
               }
-            };
-            if (two) {
-              float pg[2], ph[2];
-              tile_part<2>(src, pitch, wrow, pan, tok_stride, lane, pg, ph, refill);
-              rg[0] = fmaf(pg[0], sm.inv[t * 16 + sb], rg[0]);
-              rh[0] = fmaf(ph[0], sm.inv[t * 16 + sb], rh[0]);
-              rg[1] = fmaf(pg[1], sm.inv[(4 + t) * 16 + sb], rg[1]);
-              rh[1] = fmaf(ph[1], sm.inv[(4 + t) * 16 + sb], rh[1]);
-            } else {
-              float pg[1], ph[1];
-              tile_part<1>(src, pitch, wrow, pan, tok_stride, lane, pg, ph, refill);
-              rg[0] = fmaf(pg[0], sm.inv[t * 16 + sb], rg[0]);
-              rh[0] = fmaf(ph[0], sm.inv[t * 16 + sb], rh[0]);
             }
           }
-        } else {
-          __syncwarp();
-          if (i + S < n_items) issue(i + S);
+          __syncwarp();  // every lane is done with the box
+          if (trace_mode != 2 && p_left > 0) issue_next();
         }
+        if (++stage == S) stage = 0;
       }
-      if (bx == nbox - 1 && ok) {
-        const int n0 = (r0 + warp - job * tiles + (i / nbox) * kWarps) * rows_per_tile;
+      bool mine = true;
+      if (f > 1) {  // the K parts of the tile meet; the group's first warp sums them in order and stores
+        float4 *red = sm.red + (size_t)warp * 32 + lane;
+        *red = make_float4(rg[0], rh[0], rg[1], rh[1]);
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * f) : "memory");
+        mine = part == 0;
+        if (mine) {
+          for (int pp = 1; pp < f; ++pp) {
+            const float4 o = red[(size_t)pp * 32];
+            rg[0] += o.x; rh[0] += o.y; rg[1] += o.z; rh[1] += o.w;
+          }
+        }
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + slot), "r"(32 * f) : "memory");
+      }
+      if (mine && ok) {
 #pragma unroll
         for (int q = 0; q < 2; ++q) {
           const int pair = (q == 0 || two) ? sm.pair[4 * q + t] : -1;
@@ -420,6 +460,14 @@ __device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem 
       }
     }
   }
+}
+
+// How many warps should share a tile: more when the run has so few tiles per warp that one warp walking the
+// whole K range would be the critical path. total_tiles over all CTAs, nbox boxes per tile.
+__device__ __forceinline__ int choose_ksplit(long long total_tiles, int nbox, int n_ctas) {
+  int f = 1;
+  while (f < 4 && nbox % (2 * f) == 0 && total_tiles * f < 3ll * n_ctas * kWarps) f *= 2;
+  return f;
 }
 
 // Jobs per active expert -> exclusive prefix in jbase[0..256] (jbase[a] holds the job count of active expert a on

@@ -47,14 +47,15 @@ struct ProjParams {
 };
 
 struct ProjSmem {
-  size_t ring, panels, bars, total;
+  size_t ring, panels, bars, red, total;
 };
 __host__ __device__ inline ProjSmem proj_smem(int nsb, int sbs, int stages) {
   ProjSmem m;
   m.ring = 0;
   m.panels = m.ring + q4e::phase_ring_bytes(sbs, stages);
   m.bars = m.panels + q4e::phase_panel_bytes(nsb);
-  m.total = m.bars + (size_t)q4e::kWarps * q4e::kMaxStages * 8;
+  m.red = m.bars + (size_t)q4e::kWarps * q4e::kMaxStages * 8;
+  m.total = m.red + (size_t)q4e::kWarps * 32 * sizeof(float4);
   return m;
 }
 
@@ -77,6 +78,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_proj_kernel(const __grid_cons
   sm.ring = smem + lay.ring;
   sm.panels = smem + lay.panels;
   sm.bars = reinterpret_cast<uint64_t *>(smem + lay.bars);
+  sm.red = reinterpret_cast<float4 *>(smem + lay.red);
   sm.inv = s_inv;
   sm.pair = s_pair;
   sm.fail = &s_fail;
@@ -112,7 +114,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_proj_kernel(const __grid_cons
   tmode = g_trace_mode;
 #endif
   q4e::run_phase<DUAL>(
-      p.shape, sm, jt, u0, u1, &p.map0, &p.map1, p.out0, p.out1, p.out2, p.wait_cycles, parity, ok,
+      p.shape, sm, jt, u0, u1, q4e::choose_ksplit(U, p.shape.nsb / p.shape.sbs, gridDim.x), &p.map0, &p.map1, p.out0, p.out1, p.out2, p.wait_cycles, parity, ok,
       [&](int job, int a, int tk, int &pair, int &row) {
         const int tok = (job - s_jbase[a]) * q4e::kJobTok + tk;
         if (tok >= s_ucnt[a]) return false;

@@ -34,6 +34,7 @@ namespace {
 
 constexpr int kMaxT = 64;  // tokens per step
 constexpr int kThreads = q4e::kWarps * 32;
+constexpr int kSplitMaxT = 16;  // batches up to this size may split a tile's K range over several warps
 constexpr int kMaxSlices = 8;  // hidden <= 2048: the logits keep a router row in registers
 
 struct LayerMaps {  // stay in global memory: the TMA unit reads them there
@@ -103,7 +104,7 @@ __device__ __forceinline__ bool grid_wait(unsigned *sync, unsigned target, long 
 
 // Shared-memory plan (byte offsets into the dynamic block).
 struct Plan {
-  uint32_t ring, panels, bars, sel_e, sel_w, mask, jbase, uexp, inv, pair, scale, ord, fail, desc, total;
+  uint32_t ring, panels, bars, sel_e, sel_w, mask, jbase, uexp, inv, pair, scale, ord, fail, desc, red, total;
 };
 __host__ __device__ inline Plan make_plan(const q4e::PhaseShape &gu, const q4e::PhaseShape &dn, int T, int k) {
   Plan pl;
@@ -125,6 +126,8 @@ __host__ __device__ inline Plan make_plan(const q4e::PhaseShape &gu, const q4e::
   pl.ord = take((size_t)T * k);
   pl.fail = take(16);
   pl.desc = take(2 * sizeof(LayerDesc));
+  // partial sums of warps that share a tile: only small batches have so few tiles that they do
+  pl.red = T <= kSplitMaxT ? take((size_t)q4e::kWarps * 32 * sizeof(float4)) : 0;
   pl.total = o;
   return pl;
 }
@@ -147,13 +150,14 @@ __device__ unsigned long long g_stack_trace[16 * 160];
 #define KNJ_STAMP(i)
 #endif
 
-// Stage 1 of a layer for one CTA item: experts 8 eg .. 8 eg + 7 (one per warp, two warps per expert) times tokens
-// 8 tg .. 8 tg + 7 (four per warp). Row statistics and logits in moe_front_kernel's operation order (lane owns
+// Stage 1 of a layer for one CTA item: experts epi * eg .. + epi - 1 times tokens 8 tg .. 8 tg + 7; warp w takes
+// expert w % epi and the token slot w / epi (epi / 2 tokens, at least one). epi = 8, 4, 2 or 1: fewer experts per
+// item for smaller batches, so that the items still cover most of the grid. Row statistics and logits in moe_front_kernel's operation order (lane owns
 // elements 256 sl + 8 lane + j, even/odd chains, warp_sum). The CTA first brings its eight router rows (times the
 // norm weights, f32) and its token rows (as they are) into shared memory with every load in flight at once;
 // scratch: 8 * H * 4 bytes for the router rows followed by 8 * H * 4 for the token rows.
-__device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc &L, int eg, int tg, uint8_t *scratch, int l,
-                                          int trace_layer) {
+__device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc &L, int epi, int eg, int tg, uint8_t *scratch,
+                                          int l, int trace_layer) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int T = p.T, H = p.H, E = p.E, nslice = H / 256;
   const bool has_norm = L.norm_w != nullptr;
@@ -162,7 +166,7 @@ __device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc 
   const int esz = L.x_dtype == KNJ_DT_F32 ? 4 : 2, row_bytes = H * esz, cpr = row_bytes / 16;
   const int nt = min(8, T - tg * 8);
   // ---- loads first (router rows, norm weights, token rows), conversions after
-  const int wchunks = 8 * (H / 8);  // 16-byte pieces of the eight bf16 router rows
+  const int wchunks = epi * (H / 8);  // 16-byte pieces of the item's bf16 router rows
   constexpr int kPer = (8 * 256 * kMaxSlices / 8 + kThreads - 1) / kThreads;  // 4 pieces per thread at H = 2048
   uint4 wraw[kPer], nraw[kPer];
 #pragma unroll
@@ -170,7 +174,7 @@ __device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc 
     const int i = threadIdx.x + q * kThreads;
     if (i < wchunks) {
       const int r = i / (H / 8), ch = i - r * (H / 8);
-      const int ee = min(eg * 8 + r, E - 1);
+      const int ee = min(eg * epi + r, E - 1);
       wraw[q] = __ldg(reinterpret_cast<const uint4 *>(L.Wr + (size_t)ee * H + 8 * ch));
       if (has_norm) nraw[q] = __ldg(reinterpret_cast<const uint4 *>(L.norm_w + 8 * ch));
     }
@@ -201,10 +205,11 @@ __device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc 
   }
   __syncthreads();
   KNJ_STAMP(11);
-  const int e = eg * 8 + (warp & 7);
-  const int t_first = tg * 8 + (warp >> 3) * 4, t_end = min(T, t_first + 4);
+  const int es = warp % epi, tpw = max(1, epi / 2);
+  const int e = eg * epi + es;
+  const int t_first = tg * 8 + (warp / epi) * tpw, t_end = min(min(T, tg * 8 + 8), t_first + tpw);
   const float bias = (L.bias && e < E) ? L.bias[e] : 0.f;
-  const float *wrow = wr_s + (size_t)(warp & 7) * H;
+  const float *wrow = wr_s + (size_t)es * H;
   // two tokens per pass over the router row: their chains are independent of each other
   for (int t = t_first; t < t_end; t += 2) {
     const bool second = t + 1 < t_end;
@@ -248,7 +253,7 @@ __device__ __noinline__ void stage_logits(const StackParams &p, const LayerDesc 
       const float dot = warp_sum(d0[u] + d1[u]), ss = warp_sum(s0[u] + s1[u]);
       if (lane == 0) {
         const float scale = has_norm ? 1.0f / sqrtf(ss / (float)H + L.eps) : 1.0f;
-        if (eg == 0 && (warp & 7) == 0) p.scales[t + u] = scale;
+        if (eg == 0 && es == 0) p.scales[t + u] = scale;
         if (e < E) p.logits[(size_t)(t + u) * E + e] = dot * scale + bias;
       }
     }
@@ -347,6 +352,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
   sm.inv = reinterpret_cast<float *>(smem + pl.inv);
   sm.pair = reinterpret_cast<int *>(smem + pl.pair);
   sm.fail = s_fail;
+  sm.red = reinterpret_cast<float4 *>(smem + pl.red);
   const q4e::JobTable jt{jbase, uexp};
 
   if (lane == 0)
@@ -357,8 +363,11 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
 
   unsigned arrivals = 0, parity = 0;
   bool ok = true;
-  // logits: CTA c < n_eg * n_tg takes experts 8 eg .. 8 eg + 7 (one per warp pair) for tokens 8 tg .. 8 tg + 7
-  const int n_eg = (E + 7) / 8, n_tg = (T + 7) / 8;
+  // logits: CTA c < n_eg * n_tg takes experts epi * eg .. + epi - 1 for tokens 8 tg .. 8 tg + 7
+  const int n_tg = (T + 7) / 8;
+  int epi = 8;
+  while (epi > 1 && n_tg * ((E + epi / 2 - 1) / (epi / 2)) <= G) epi >>= 1;
+  const int n_eg = (E + epi - 1) / epi;
   const bool has_item = c < n_eg * n_tg;
   const int eg = c % n_eg, tg = c / n_eg;
 
@@ -382,9 +391,9 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
 
     // ---- stage 1: row statistics and router logits
 #ifdef KNJ_TRACE
-    if (has_item) stage_logits(p, L, eg, tg, smem + pl.ring, l, trace_layer);
+    if (has_item) stage_logits(p, L, epi, eg, tg, smem + pl.ring, l, trace_layer);
 #else
-    if (has_item) stage_logits(p, L, eg, tg, smem + pl.ring, l, 0);
+    if (has_item) stage_logits(p, L, epi, eg, tg, smem + pl.ring, l, 0);
 #endif
     KNJ_STAMP(1);
     arrivals += G;
@@ -417,7 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       const long long U = (long long)jbase[256] * p.gu.tiles;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
       q4e::run_phase<true>(
-          p.gu, sm, jt, u0, u1, &M.mg, &M.mu, nullptr, nullptr, p.act, p.wait_cycles, parity, ok,
+          p.gu, sm, jt, u0, u1, T <= kSplitMaxT ? q4e::choose_ksplit(U, p.gu.nsb / p.gu.sbs, G) : 1, &M.mg, &M.mu, nullptr, nullptr, p.act, p.wait_cycles, parity, ok,
           [&](int job, int a, int tk, int &pair, int &row) {
             int e;
             const int tok = job_tok(job, a, tk, e);
@@ -448,7 +457,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
       const long long U = (long long)jbase[256] * p.dn.tiles;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
       q4e::run_phase<false>(
-          p.dn, sm, jt, u0, u1, &M.md, &M.md, p.Y, nullptr, nullptr, p.wait_cycles, parity, ok,
+          p.dn, sm, jt, u0, u1, T <= kSplitMaxT ? q4e::choose_ksplit(U, p.dn.nsb / p.dn.sbs, G) : 1, &M.md, &M.md, p.Y, nullptr, nullptr, p.wait_cycles, parity, ok,
           [&](int job, int a, int tk, int &pair, int &row) {
             int e;
             const int tok = job_tok(job, a, tk, e);
