@@ -370,6 +370,19 @@ int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pai
                            const int32_t *pair_row, float *Y, int N, int K, int rowBytes, int64_t idxStride,
                            int n_experts, int max_pairs, int *status, knj_stream_t s);
 
+/* Grouped down GEMM with the weighted scatter-combine in its epilogue (the sum the
+ * reference does on the host, tools/bench/q4k_moe_ffn.hip:682-694, residual
+ * tools/bench/q4k_stream_ffn.hip:1305-1313): acc[p / top_k][n] += pair_w[p] * 2^6 *
+ * (A[row(p)] . Wd[e][n]) for every pair p, as f32 vector reductions in L2. acc f32
+ * [T][N] holds the start value (knj_moe_acc_init_launch: the residual rows or zero);
+ * knj_moe_acc_finish_launch converts it to the output's element type. No per-pair
+ * rows are written. The order of a token's k additions is not fixed. */
+int knj_q4k_down_combine_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pair_idx, const int32_t *pair_cnt,
+                                   const int32_t *pair_row, const float *pair_w, int top_k, float *acc, int N, int K,
+                                   int rowBytes, int64_t idxStride, int n_experts, int max_pairs, int *status, knj_stream_t s);
+int knj_moe_acc_init_launch(const void *x, int x_dtype, int64_t ldx, int residual, int T, int H, float *acc, knj_stream_t s);
+int knj_moe_acc_finish_launch(const float *acc, void *out, int out_dtype, int64_t ldo, int T, int H, knj_stream_t s);
+
 /* ======================================================================== */
 /* Whole MoE-FFN layer (src/model/model.cpp:399-510 Model::moe)             */
 /* ======================================================================== */
@@ -398,6 +411,10 @@ typedef struct knj_moe_ffn_args {
   /* format of w_down: 0 = Q4_K as above, 1 = Q6_K [E][hidden][ffn/256][210] (the
    * mixed-format layers of Q4_K_M checkpoints; decode launch only) */
   int32_t down_format;
+  /* prefill launch: 0 = the weighted combine is fused into the down GEMM's epilogue (f32 vector reductions in
+   * L2: the k rows of a token are added in no fixed order, results vary in the last bits between runs);
+   * 1 = per-pair rows + the ordered combine kernel (bit-reproducible, the CPU path's summation order) */
+  int32_t ordered_combine;
 } knj_moe_ffn_args;
 
 /* mode 0 = decode class (knj_moe_ffn_decode_launch), 1 = prefill class. */

@@ -38,7 +38,7 @@ class MoeFfnArgs(C.Structure):
                 ("w_down", C.c_void_p), ("norm_w", C.c_void_p), ("rms_eps", C.c_float), ("residual", C.c_int32),
                 ("out", C.c_void_p), ("out_dtype", C.c_int32), ("ldo", C.c_int64), ("workspace", C.c_void_p),
                 ("workspace_bytes", C.c_size_t), ("tap_pair_exp", C.c_void_p), ("tap_pair_w", C.c_void_p),
-                ("down_format", C.c_int32)]
+                ("down_format", C.c_int32), ("ordered_combine", C.c_int32)]
 
 
 _vp, _i, _i64, _u32, _u64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint32, C.c_uint64, C.c_size_t, C.c_float
@@ -151,6 +151,9 @@ SIGNATURES = {
     "knj_to_f16_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp]),
     "knj_q4k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),
+    "knj_q4k_down_combine_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),
+    "knj_moe_acc_init_launch": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp]),
+    "knj_moe_acc_finish_launch": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp]),
     "knj_fuse_gateup_silu_launch": (_i, [_vp, _vp, _vp, _i, _i64, _vp]),
     "knj_q4k_matmul_workspace_bytes": (_sz, [_i, _i]),
     "knj_q4k_matmul_launch": (_i, [_vp, _i, _i, _vp, _i, _i64, _i, _vp, _i64, _vp, _sz, _vp]),

@@ -232,6 +232,24 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
                                   H / 256 * KNJ_Q4K_BYTES, T, E, k, P, w.status, s);
     if (rc) return rc;
   }
+  if (!a->ordered_combine) {
+    // down GEMM with the weighted combine in its epilogue: the token's sum starts from the residual (or zero) in
+    // f32 and receives its k rows as vector reductions; no per-pair rows exist. The f32 sums sit where the
+    // per-pair rows would (or directly in a dense f32 output).
+    const bool direct = a->out_dtype == KNJ_DT_F32 && a->ldo == H;
+    float *acc = direct ? static_cast<float *>(a->out) : w.Y;
+    {
+      StageSpan sp("moe-down", s);
+      rc = knj_moe_acc_init_launch(a->x, a->x_dtype, a->ldx, a->residual, T, H, acc, s);
+      if (rc) return rc;
+      rc = knj_q4k_down_combine_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, pair_w, k, acc, H, F,
+                                          F / 256 * KNJ_Q4K_BYTES, T, E, P, w.status, s);
+      if (rc) return rc;
+    }
+    if (direct) return KNJ_OK;
+    StageSpan sp("moe-scatter", s);
+    return knj_moe_acc_finish_launch(acc, a->out, a->out_dtype, a->ldo, T, H, s);
+  }
   {
     StageSpan sp("moe-down", s);
     rc = knj_q4k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, E,

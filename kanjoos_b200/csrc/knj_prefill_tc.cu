@@ -56,6 +56,11 @@ struct TcParams {
   int64_t idxStride;
   float out_scale;
   int *status;
+  // fused weighted combine (single-matrix form only; cmb_acc == null: off): instead of storing the per-pair row,
+  // the epilogue adds cmb_w[pair] * row into cmb_acc[pair / cmb_div] with vector reductions in L2
+  const float *cmb_w;
+  float *cmb_acc;
+  int cmb_div;
   unsigned long long *trace;  // optional: SM-clock stamps of CTA 0's first slabs (measurement hook)
   int trace_ctas;             // per-CTA records that fit behind the 64 slab stamps
   CUtensorMap map0, map1;     // TMA descriptors of W0 / W1, box = one superblock (36 words) x 32 rows
@@ -547,6 +552,16 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
         for (int r = ew * kRowsPerInstr + sub; r < ntok; r += kEpiWarps * kRowsPerInstr) {
           const int pr = s_pair[r];
           const uint4 v = *reinterpret_cast<const uint4 *>(stg + r * kRowB + l16 * 16);
+          if (!GATEUP && p.cmb_acc) {
+            // the row's share of its token's weighted sum: one 16-byte reduction per lane (the k rows of a token
+            // arrive from different CTAs in no fixed order)
+            const float w = __ldg(p.cmb_w + pr);
+            float *dst = p.cmb_acc + (size_t)(pr / p.cmb_div) * p.N + m0 + mat * kRowsM + l16 * 4;
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(__uint_as_float(v.x) * w),
+                         "f"(__uint_as_float(v.y) * w), "f"(__uint_as_float(v.z) * w), "f"(__uint_as_float(v.w) * w)
+                         : "memory");
+            continue;
+          }
           uint8_t *dst = GATEUP ? reinterpret_cast<uint8_t *>(static_cast<__half *>(p.out) + (size_t)pr * p.N + m0)
                                 : reinterpret_cast<uint8_t *>(static_cast<float *>(p.out) + (size_t)pr * p.N + m0 + mat * kRowsM);
           *reinterpret_cast<uint4 *>(dst + l16 * 16) = v;
@@ -590,6 +605,36 @@ __global__ void __launch_bounds__(256) bf16_to_f16_kernel(const uint4 *__restric
       o[j] = *reinterpret_cast<const uint32_t *>(&h);
     }
     out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// acc[t][:] = residual ? x[t][:] : 0 (f32), the start value of the fused weighted combine; four columns per thread
+__global__ void __launch_bounds__(256) acc_init_kernel(const void *__restrict__ x, int dtype, int64_t ldx, int residual, int H,
+                                                       int64_t n4, float *__restrict__ acc) {
+  const int H4 = H / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (residual) {
+      const int64_t t = i / H4, c = 4 * (i - t * H4);
+      v.x = load_as_f32(x, dtype, t * ldx + c);
+      v.y = load_as_f32(x, dtype, t * ldx + c + 1);
+      v.z = load_as_f32(x, dtype, t * ldx + c + 2);
+      v.w = load_as_f32(x, dtype, t * ldx + c + 3);
+    }
+    reinterpret_cast<float4 *>(acc)[i] = v;
+  }
+}
+// out[t][:] = acc[t][:] in the output's element type
+__global__ void __launch_bounds__(256) acc_finish_kernel(const float *__restrict__ acc, void *__restrict__ out, int dtype, int64_t ldo,
+                                                         int H, int64_t n4) {
+  const int H4 = H / 4;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4 *>(acc)[i];
+    const int64_t t = i / H4, c = 4 * (i - t * H4);
+    store_from_f32(out, dtype, t * ldo + c, v.x);
+    store_from_f32(out, dtype, t * ldo + c + 1, v.y);
+    store_from_f32(out, dtype, t * ldo + c + 2, v.z);
+    store_from_f32(out, dtype, t * ldo + c + 3, v.w);
   }
 }
 
@@ -713,6 +758,45 @@ int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pai
   }
   p.m_tiles = N / kRowsM;
   return launch_tc<1, false>(p, max_pairs, as_stream(s));
+}
+
+int knj_q4k_down_combine_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pair_idx, const int32_t *pair_cnt,
+                                   const int32_t *pair_row, const float *pair_w, int top_k, float *acc, int N, int K,
+                                   int rowBytes, int64_t idxStride, int n_experts, int max_pairs, int *status, knj_stream_t s) {
+  KNJ_REQUIRE(Ah && Wd && pair_idx && pair_cnt && pair_w && acc, "knj_q4k_down_combine_tc: null pointer");
+  KNJ_REQUIRE(K > 0 && K % 256 == 0 && rowBytes == K / 256 * KNJ_Q4K_BYTES, "knj_q4k_down_combine_tc: rowBytes=%d does not match K=%d",
+              rowBytes, K);
+  KNJ_REQUIRE(N > 0 && N % kRowsM == 0, "knj_q4k_down_combine_tc: N=%d must be a multiple of 128", N);
+  KNJ_REQUIRE(aligned16(Wd) && aligned16(Ah) && aligned16(acc), "knj_q4k_down_combine_tc: bases must be 16-byte aligned");
+  KNJ_REQUIRE(n_experts >= 1 && n_experts <= 256 && max_pairs >= 0 && top_k >= 1, "knj_q4k_down_combine_tc: bad expert / pair counts");
+  if (max_pairs == 0) return KNJ_OK;
+  TcParams p{};
+  p.X = static_cast<const __half *>(Ah); p.W0 = Wd; p.W1 = nullptr; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
+  p.row_map = pair_row; p.out = nullptr; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
+  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; p.trace = g_tc_trace; p.trace_ctas = g_tc_trace_ctas;
+  p.cmb_w = pair_w; p.cmb_acc = acc; p.cmb_div = top_k;
+  if (N % (2 * kRowsM) == 0) {
+    p.m_tiles = N / (2 * kRowsM);
+    return launch_tc<2, false>(p, max_pairs, as_stream(s));
+  }
+  p.m_tiles = N / kRowsM;
+  return launch_tc<1, false>(p, max_pairs, as_stream(s));
+}
+
+int knj_moe_acc_init_launch(const void *x, int x_dtype, int64_t ldx, int residual, int T, int H, float *acc, knj_stream_t s) {
+  KNJ_REQUIRE(acc && (!residual || x) && T >= 0 && H > 0 && H % 4 == 0, "knj_moe_acc_init: bad arguments");
+  if (T == 0) return KNJ_OK;
+  const int64_t n4 = (int64_t)T * H / 4, blocks = (n4 + 255) / 256, cap = (int64_t)sm_count() * 16;
+  acc_init_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, as_stream(s)>>>(x, x_dtype, ldx, residual, H, n4, acc);
+  return launch_status("acc_init_kernel");
+}
+
+int knj_moe_acc_finish_launch(const float *acc, void *out, int out_dtype, int64_t ldo, int T, int H, knj_stream_t s) {
+  KNJ_REQUIRE(acc && out && T >= 0 && H > 0 && H % 4 == 0, "knj_moe_acc_finish: bad arguments");
+  if (T == 0) return KNJ_OK;
+  const int64_t n4 = (int64_t)T * H / 4, blocks = (n4 + 255) / 256, cap = (int64_t)sm_count() * 16;
+  acc_finish_kernel<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, as_stream(s)>>>(acc, out, out_dtype, ldo, H, n4);
+  return launch_status("acc_finish_kernel");
 }
 
 }  // extern "C"

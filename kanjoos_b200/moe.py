@@ -93,7 +93,7 @@ class MoeFfnLayer:
         self.workspace = workspace
         self._need = need
 
-    def _args(self, x: torch.Tensor, out: torch.Tensor, taps=None) -> MoeFfnArgs:
+    def _args(self, x: torch.Tensor, out: torch.Tensor, taps=None, ordered_combine: bool = False) -> MoeFfnArgs:
         b = self.bank
         T, H = x.shape
         assert H == b.hidden and T <= self.max_tokens and x.is_contiguous() and out.is_contiguous()
@@ -107,20 +107,21 @@ class MoeFfnLayer:
         a.norm_w = b.norm_w.data_ptr() if self.use_norm else None
         a.rms_eps = b.rms_eps
         a.residual = 1 if self.residual else 0
+        a.ordered_combine = 1 if ordered_combine else 0
         a.out, a.out_dtype, a.ldo = out.data_ptr(), _DT[out.dtype], H
         a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
         if taps is not None:
             a.tap_pair_exp, a.tap_pair_w = taps[0].data_ptr(), taps[1].data_ptr()
         return a
 
-    def _run(self, fn, x, out, out_dtype, return_routing):
+    def _run(self, fn, x, out, out_dtype, return_routing, ordered_combine=False):
         if out is None:
             out = torch.empty(x.shape, dtype=out_dtype or torch.float32, device=x.device)
         taps = None
         if return_routing:
             P = x.shape[0] * self.top_k
             taps = (torch.empty(P, dtype=torch.int32, device=x.device), torch.empty(P, dtype=torch.float32, device=x.device))
-        args = self._args(x, out, taps)
+        args = self._args(x, out, taps, ordered_combine)
         check(fn(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return (out, taps[0], taps[1]) if return_routing else out
 
@@ -128,9 +129,10 @@ class MoeFfnLayer:
         """f32-accurate path (batch <= 64 is the intended use)."""
         return self._run(lib().knj_moe_ffn_decode_launch, x, out, out_dtype, return_routing)
 
-    def prefill(self, x, out=None, out_dtype=None, return_routing=False):
-        """Grouped-GEMM path over per-expert token buckets."""
-        return self._run(lib().knj_moe_ffn_prefill_launch, x, out, out_dtype, return_routing)
+    def prefill(self, x, out=None, out_dtype=None, return_routing=False, ordered_combine=False):
+        """Grouped-GEMM path over per-expert token buckets. ordered_combine=False: the weighted sum is fused into
+        the down GEMM's epilogue (f32 reductions, unordered); True: per-pair rows + the ordered combine kernel."""
+        return self._run(lib().knj_moe_ffn_prefill_launch, x, out, out_dtype, return_routing, ordered_combine)
 
 
 class MoeStack:
@@ -177,13 +179,15 @@ class FusedMoeStack:
 
     def __init__(self, banks: list[ExpertBank], top_k: int = synth.TOP_K, n_tokens: int = 1, dtype=torch.bfloat16,
                  residual: bool = True, use_norm: bool = True, taps: bool = False,
-                 layer_inputs: list[torch.Tensor] | None = None):
+                 layer_inputs: list[torch.Tensor] | None = None, keep_outputs: bool = False):
         """layer_inputs: one [n_tokens][H] tensor per layer that the layer reads INSTEAD of its predecessor's output
-        (independent layers, e.g. to drive every layer with fresh rows); default: the layers form a chain."""
+        (independent layers, e.g. to drive every layer with fresh rows); default: the layers form a chain.
+        keep_outputs: every layer writes a buffer of its own (self.outs[l]) instead of two alternating ones."""
         dev = banks[0].gate.device
         H = banks[0].hidden
         self.x = torch.zeros((n_tokens, H), dtype=dtype, device=dev)
         self._buf = (torch.zeros_like(self.x), torch.zeros_like(self.x))
+        self.outs = [torch.zeros_like(self.x) for _ in banks] if keep_outputs else None
         ws = torch.empty(256, dtype=torch.uint8, device=dev)
         self._layers = [MoeFfnLayer.__new__(MoeFfnLayer) for _ in banks]
         P = n_tokens * top_k
@@ -195,7 +199,7 @@ class FusedMoeStack:
             layer.bank, layer.top_k, layer.max_tokens, layer.residual = b, top_k, n_tokens, residual
             layer.use_norm = use_norm and b.norm_w is not None
             layer.workspace = ws
-            nxt = self._buf[l & 1]
+            nxt = self.outs[l] if keep_outputs else self._buf[l & 1]
             if layer_inputs is not None:
                 cur = layer_inputs[l]
             arr[l] = layer._args(cur, nxt, self.taps[l] if taps else None)

@@ -231,3 +231,69 @@ def test_mixed_format_layer_q6k_down():
     assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_DECODE
     with pytest.raises(Exception):
         layer.prefill(dev(hx))
+
+
+def _sample_want(bank, hx, ch, wts, sample):
+    """CPU path on the device's routing decision for the sampled tokens (a token's output depends on its own
+    row only), experts in ascending order as the CPU path sums them."""
+    want = np.zeros((len(sample), hx.shape[1]), np.float32)
+    chs, ws = ch[sample], wts[sample]
+    for e in np.unique(chs):
+        rows, slots = np.nonzero(chs == e)
+        xs = hx[sample[rows]]
+        g = ol.matmul_q4k(bank["gate"][e], xs)
+        u = ol.matmul_q4k(bank["up"][e], xs)
+        y = ol.matmul_q4k(bank["down"][e], ol.silu_mul(g, u))
+        want[rows] += ws[rows, slots][:, None] * y
+    return want
+
+
+@pytest.fixture(scope="module")
+def cfg5():
+    return synth.expert_bank(5)
+
+
+@pytest.mark.parametrize("T,routing", [(4096, "uniform"), (4096, "zipf"), (16384, "uniform"), (16384, "zipf")])
+def test_config5_prefill_sampled_tokens(cfg5, T, routing):
+    """Config 5 on one GPU at the benchmark's sizes (every expert holds several full 256-token buckets): 256
+    seeded tokens of the layer's output against the CPU path, both combine forms; routing sets against the CPU
+    router for the unbiased case."""
+    bank = cfg5
+    wr, bias = synth.router_weight(5, zipf_s=1.1 if routing == "zipf" else None)
+    hx = synth.bf16_round(synth.hidden_rows(5, T))
+    layer = make_layer(bank, wr, 8, T, bias=bias)
+    x = dev(hx).to(torch.bfloat16)
+    out, pe, pw = layer.prefill(x, return_routing=True)
+    ch, wts = pe.cpu().numpy().reshape(T, 8), pw.cpu().numpy().reshape(T, 8)
+    cnt = np.bincount(ch.ravel(), minlength=128)
+    print(f"T={T} {routing}: bucket sizes max {cnt.max()} min {cnt.min()}")
+    sample = np.sort(np.random.Generator(np.random.Philox([T, len(routing)])).choice(T, 256, replace=False))
+    want = _sample_want(bank, hx, ch, wts, sample)
+    got = out.cpu().numpy()
+    st = report(got[sample], want, f"cfg5 prefill T={T} {routing}, fused combine, 256 sampled tokens")
+    assert (got == SENTINEL).sum() == 0 and st["rel_rmse"] <= TOL_PREFILL
+    ordered = layer.prefill(x, ordered_combine=True).cpu().numpy()
+    st = report(ordered[sample], want, f"cfg5 prefill T={T} {routing}, ordered combine")
+    assert st["rel_rmse"] <= TOL_PREFILL
+    # the two combine forms differ by the order of eight f32 additions per output only
+    assert report(got, ordered, "fused vs ordered combine, all tokens")["rel_rmse"] <= 1e-6
+    if routing == "uniform":
+        logits, ch_cpu, _ = ol.route(wr, 1, hx[sample], 128, 8)
+        checked, skipped = routing_sets_match(ch[sample], logits, ch_cpu, 8)
+        assert checked >= 200
+
+
+def test_prefill_combine_forms_with_residual_and_bf16_output(cfg2):
+    """The fused epilogue starts the token's sum from the residual row and ends in a bf16 store; the ordered form
+    is bit-reproducible from run to run."""
+    bank, wr = cfg2
+    hx = synth.bf16_round(synth.hidden_rows(2, 300, layer=7))
+    layer = make_layer(bank, wr, 8, 300, residual=True)
+    x = dev(hx).to(torch.bfloat16)
+    fused = layer.prefill(x, out_dtype=torch.bfloat16).float().cpu().numpy()
+    o1 = layer.prefill(x, out_dtype=torch.bfloat16, ordered_combine=True).float().cpu().numpy()
+    o2 = layer.prefill(x, out_dtype=torch.bfloat16, ordered_combine=True).float().cpu().numpy()
+    assert np.array_equal(o1, o2)
+    assert np.mean(fused != o1) < 0.01 and report(fused, o1, "fused vs ordered, bf16 out + residual")["rel_rmse"] <= 5e-3
+    want, _, _ = ol.moe(wr, bank, hx)
+    assert report(o1, synth.bf16_round(hx + want), "ordered, residual, bf16 out vs CPU path")["rel_rmse"] <= 5e-3

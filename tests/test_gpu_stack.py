@@ -85,6 +85,41 @@ def test_stack_follows_layer_by_layer_launches_larger_batches(T):
     st.close()
 
 
+@pytest.mark.parametrize("B", [1, 8, 64])
+def test_config4_full_size_stack_checked_layers(B):
+    """Config 4: the 48-layer resident stack at full size (about 15 GiB of random-init Q4_K experts), f32 residual
+    stream. Layers 0, 1, 23 and 47 are checked against the CPU path fed with the GPU's own layer input: tokens
+    whose routed expert sets agree (all but near-ties) within 1e-5, and nearly all tokens must agree."""
+    from kanjoos_b200.moe import ExpertBank, FusedMoeStack
+    L, k = 48, 8
+    free, _ = torch.cuda.mem_get_info()
+    if free < 20 * 2**30:
+        pytest.skip("needs 20 GiB of free device memory")
+    banks = [ExpertBank.random(seed=4000 + l) for l in range(L)]
+    g = torch.Generator(device="cuda")
+    g.manual_seed(B)
+    x = torch.randn((B, synth.HIDDEN), device="cuda", generator=g)
+    st = FusedMoeStack(banks, top_k=k, n_tokens=B, dtype=torch.float32, taps=True, keep_outputs=True)
+    st.step(x)
+    st.status()
+    for l in (0, 1, 23, 47):
+        b = banks[l]
+        bank = {"gate": b.gate.cpu().numpy(), "up": b.up.cpu().numpy(), "down": b.down.cpu().numpy()}
+        wr = b.router.view(torch.int16).cpu().numpy().view(np.uint16)
+        nw = b.norm_w.view(torch.int16).cpu().numpy().view(np.uint16)
+        xin = (x if l == 0 else st.outs[l - 1]).cpu().numpy()
+        xn = ol.rmsnorm(xin, synth.bf16_bits_to_f32(nw), b.rms_eps)
+        mo, ch_cpu, _ = ol.moe(wr, bank, xn, k)
+        want = xin + mo
+        got = st.outs[l].cpu().numpy()
+        ch_gpu = st.taps[l][0].cpu().numpy().reshape(B, k)
+        same = np.array([set(ch_gpu[t]) == set(ch_cpu[t]) for t in range(B)])
+        assert same.mean() >= 0.9, f"layer {l}: routed sets differ for {int((~same).sum())} of {B} tokens"
+        s = report(got[same], want[same], f"48-layer stack, batch {B}, layer {l} ({int(same.sum())} tokens)")
+        assert s["rel_rmse"] <= 1e-5
+    st.close()
+
+
 def test_bounded_wait_gives_up_and_the_stack_recovers():
     """A grid barrier whose target cannot be reached runs into its limit: the launch returns, status() reports
     KNJ_E_TIMEOUT (-5), nothing traps, and the next normal launch on the same stack is right again."""
