@@ -241,6 +241,44 @@ def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64)):
     return out
 
 
+def check_parity(torch, args, world, rank, e_loc, n_banks, banks, router, bias, x, step, out):
+    """Relative RMSE of the layer's output rows against an independent computation (never timed)."""
+    import numpy as np
+    from kanjoos_b200 import ops
+    from kanjoos_b200.moe import ExpertBank, MoeFfnLayer
+    got_all = out.float().cpu().numpy()   # the step over bank 0 that every rank has just run
+    if world == 1:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import oracle_lib as ol
+        n = 64
+        bk = banks[0]
+        bank = {k: getattr(bk, k).cpu().numpy() for k in ("gate", "up", "down")}
+        _, pe, pw = ops.router_topk(x[:n].contiguous(), router, TOPK, bias)
+        ch, wts = pe.cpu().numpy().reshape(n, TOPK), pw.cpu().numpy().reshape(n, TOPK)
+        hx = x[:n].float().cpu().numpy()
+        want = np.zeros((n, H), np.float32)
+        for e in np.unique(ch):
+            rows, slots = np.nonzero(ch == e)
+            g = ol.matmul_q4k(bank["gate"][e], hx[rows])
+            u = ol.matmul_q4k(bank["up"][e], hx[rows])
+            want[rows] += wts[rows, slots][:, None] * ol.matmul_q4k(bank["down"][e], ol.silu_mul(g, u))
+        ref_kind = "CPU path (oracle) on the device's routing decision"
+    else:
+        n = min(256, x.shape[0])
+        parts = [ExpertBank.random(n_experts=e_loc, seed=100 + 1000 * r, with_norm=False) for r in range(world)]
+        full = ExpertBank(gate=torch.cat([b.gate for b in parts]), up=torch.cat([b.up for b in parts]),
+                          down=torch.cat([b.down for b in parts]), router=router, router_bias=bias)
+        layer = MoeFfnLayer(full, top_k=TOPK, max_tokens=n, use_norm=False)
+        want = layer.prefill(x[:n].contiguous()).cpu().numpy()
+        del parts, full, layer
+        ref_kind = "single-GPU layer over all experts (ordered combine)"
+    got = got_all[:n]
+    d = (got.astype(np.float64) - want.astype(np.float64))
+    rms = float(np.sqrt((want.astype(np.float64) ** 2).mean()))
+    return {"rel_rmse": float(np.sqrt((d ** 2).mean()) / max(rms, 1e-30)), "max_abs": float(np.abs(d).max()),
+            "n_tokens": int(n), "against": ref_kind, "note": "the timed workload with f32 output rows"}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -301,7 +339,7 @@ def run_gpu(args):
         eps = [EpMoeLayer(bk, E, cp, None, TOPK, exchange=args.exchange) for bk in banks]
 
         def step(i, xin=x, dst=out):
-            dst.copy_(eps[i % n_banks].forward(xin, out_dtype=torch.bfloat16))
+            eps[i % n_banks].forward(xin, out=dst)
 
     def barrier():
         torch.cuda.synchronize()
@@ -317,13 +355,25 @@ def run_gpu(args):
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # a first pass of K steps sizes the timed region: the K-step loop is repeated until it lasts half a second
     barrier()
     e0.record()
     for i in range(args.steps):
         step(W + i)
     e1.record()
     barrier()
-    ms_step = e0.elapsed_time(e1) / args.steps
+    probe = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(probe, op=dist.ReduceOp.MAX)
+    repeats = max(1, int(math.ceil(500.0 / max(float(probe.item()), 1e-3))))
+    barrier()
+    e0.record()
+    for r in range(repeats):
+        for i in range(args.steps):
+            step(W + i)
+    e1.record()
+    barrier()
+    ms_step = e0.elapsed_time(e1) / (args.steps * repeats)
 
     # end to end: pinned host rows in, bf16 result rows out, every step's copies inside the timed region.
     # Three streams and two device buffers per direction: the copy-in of step i+1 and the copy-out of
@@ -365,10 +415,10 @@ def run_gpu(args):
     e2e_run(2, 0)
     barrier()
     e0.record()
-    e2e_run(args.steps, W)
+    e2e_run(args.steps * repeats, W)
     e1.record()
     barrier()
-    ms_e2e = e0.elapsed_time(e1) / args.steps
+    ms_e2e = e0.elapsed_time(e1) / (args.steps * repeats)
     clocks = sampler.stop() if rank == 0 else None
 
     t = torch.tensor([ms_step, ms_e2e], dtype=torch.float64, device="cuda")
@@ -430,6 +480,17 @@ def run_gpu(args):
                 "weight_bytes_per_launch": int((pair_cnt > 0).sum().item()) * 2 * F * (H // 256) * 144,
                 "t_tensor_ms": t_tensor * 1e3}
 
+    # parity, outside the timed regions: the first rows of rank 0's shard against the CPU path (N = 1: 64 tokens on
+    # the device's routing decision) or against the single-GPU layer over the same experts (N > 1: 256 tokens)
+    parity = None
+    out32 = torch.empty((T_loc, H), dtype=torch.float32, device="cuda")
+    step(0, x, out32)   # bank 0 with f32 output rows, every rank takes part
+    barrier()
+    if rank == 0:
+        parity = check_parity(torch, args, world, rank, e_loc, n_banks, banks, router, bias, x, step, out32)
+        if parity["rel_rmse"] > 1e-3:
+            raise SystemExit(f"parity check failed: {parity}")
+
     if rank != 0:
         if world > 1:
             dist.barrier()
@@ -458,12 +519,13 @@ def run_gpu(args):
     else:
         launches = 2 + n_perm + 2 + 2 + 1 + 2 + 1  # pack (2), plan (2)
     line = {"metric": "moe_ffn_tokens_per_s", "value": T / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
-            "steps": args.steps, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "steps": args.steps, "timed_repeats": repeats, "timed_steps": args.steps * repeats, "warmup": W,
+            "ms_per_step": ms_step, "parity": parity, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "fp16 operands (Q4_K unpacked), f32 accumulate", "data": "synthetic",
             "config": dict(workload_config(args, world), routing_imbalance=imbalance), "clocks": clocks,
             "e2e": {"value": T / (ms_e2e * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": T_loc * H * 2 * world,
                     "d2h_bytes_per_step": T_loc * H * 2 * world, "ms_per_step": ms_e2e},
-            "gpu_launches": launches * args.steps, "roofline": roof, "cpu_baseline": cb, "decode": dec,
+            "gpu_launches": launches * args.steps * repeats, "roofline": roof, "cpu_baseline": cb, "decode": dec,
             "flops_per_step": T * TOPK * 3 * 2 * H * F + 2 * T * H * E}
     print(json.dumps(line))
     if world > 1:

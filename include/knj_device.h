@@ -411,10 +411,11 @@ typedef struct knj_moe_ffn_args {
   /* format of w_down: 0 = Q4_K as above, 1 = Q6_K [E][hidden][ffn/256][210] (the
    * mixed-format layers of Q4_K_M checkpoints; decode launch only) */
   int32_t down_format;
-  /* prefill launch: 0 = the weighted combine is fused into the down GEMM's epilogue (f32 vector reductions in
-   * L2: the k rows of a token are added in no fixed order, results vary in the last bits between runs);
-   * 1 = per-pair rows + the ordered combine kernel (bit-reproducible, the CPU path's summation order) */
-  int32_t ordered_combine;
+  /* prefill launch: 0 = per-pair rows + the ordered combine kernel (bit-reproducible, the CPU path's summation
+   * order; the faster form on B200 at every measured size); 1 = the weighted combine fused into the down GEMM's
+   * epilogue as f32 vector reductions in L2 (no per-pair rows are written; the k rows of a token are added in
+   * no fixed order, so results vary in the last bits between runs) */
+  int32_t fused_combine;
 } knj_moe_ffn_args;
 
 /* mode 0 = decode class (knj_moe_ffn_decode_launch), 1 = prefill class. */
@@ -538,6 +539,54 @@ int knj_ep_combine_partial_peer_launch(const float *Y, const int32_t *pair_exp, 
 int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, const int32_t *pair_exp, int k,
                              int experts_per_rank, const void *resid, int resid_dtype, void *out, int out_dtype,
                              knj_stream_t s);
+
+/* ---------------------------------------------------------------------------
+ * The expert-parallel layer of one rank as one object (no reference counterpart;
+ * the per-rank arithmetic is src/model/model.cpp:399-510). One process per GPU;
+ * the five exchange buffers of EVERY rank are mapped into this process (CUDA IPC,
+ * symmetric memory or any other peer mapping made by the host) and passed as HOST
+ * arrays of `world` device pointers, entry r = rank r's buffer, entry `rank` =
+ * this rank's own:
+ *   xall_ptrs  fp16 [world*n_tokens_local][hidden]  every rank's rows, by global token
+ *   pe_ptrs    int32 [world*n_tokens_local*top_k]   every rank's expert ids
+ *   pw_ptrs    f32   [world*n_tokens_local*top_k]   every rank's routing weights
+ *   parts_ptrs f32   [world][n_tokens_local][hidden] partial sums of this rank's tokens, by contributing rank
+ *   flag_ptrs  uint32 [world]                       barrier words, zero before the first step
+ * knj_ep_create allocates the rank's private scratch (plan tables, the activation
+ * and per-pair output rows) once; knj_ep_forward_launch allocates nothing and calls
+ * no collective library: rows and routing tables are STORED into the peers'
+ * buffers, the ranks meet at a flag barrier in peer memory (bounded spin; a wait
+ * that gives up raises the status word read by knj_ep_status -> KNJ_E_TIMEOUT and
+ * the step's output is then undefined), each rank runs the grouped tensor-core
+ * GEMMs over its experts and stores its weighted partial sums into the token
+ * owners' buffers, a second barrier, and the rank-ordered sum (+ residual = x).
+ * All ranks must call knj_ep_forward_launch the same number of times.
+ * hidden, ffn multiples of 256; n_tokens_local*top_k a multiple of 4; experts
+ * split contiguously, n_experts / world <= 256.
+ * ------------------------------------------------------------------------- */
+typedef struct knj_ep_desc {
+  int32_t world, rank, n_tokens_local, hidden, ffn, n_experts, top_k, reserved;
+  void *const *xall_ptrs;
+  int32_t *const *pe_ptrs;
+  float *const *pw_ptrs;
+  float *const *parts_ptrs;
+  uint32_t *const *flag_ptrs;
+} knj_ep_desc;
+typedef struct knj_ep_ctx knj_ep_ctx;
+int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out);
+/* w_router bf16 [n_experts][hidden] (replicated), router_bias f32 [n_experts] or NULL;
+ * w_gate / w_up / w_down: this rank's experts, Q4_K, [n_experts/world][rows][row bytes].
+ * x [n_tokens_local][ldx] f32 / bf16 / fp16; out dense f32 or bf16 [n_tokens_local][hidden]. */
+int knj_ep_forward_launch(knj_ep_ctx *ctx, const void *x, int x_dtype, int64_t ldx, const uint16_t *w_router,
+                          const float *router_bias, const uint8_t *w_gate, const uint8_t *w_up, const uint8_t *w_down,
+                          int residual, void *out, int out_dtype, knj_stream_t s);
+/* the rank barrier alone (what knj_ep_forward_launch runs twice per step) */
+int knj_ep_barrier_launch(knj_ep_ctx *ctx, knj_stream_t s);
+/* limit of the barrier's spin in SM clock cycles (<= 0 restores the default, about a second) */
+int knj_ep_set_wait(knj_ep_ctx *ctx, long long wait_cycles);
+/* synchronises the stream; KNJ_E_TIMEOUT if a barrier or a GEMM pipeline wait gave up since the last step began */
+int knj_ep_status(knj_ep_ctx *ctx, knj_stream_t s);
+void knj_ep_destroy(knj_ep_ctx *ctx);
 
 #ifdef __cplusplus
 }

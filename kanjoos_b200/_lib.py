@@ -38,8 +38,16 @@ class MoeFfnArgs(C.Structure):
                 ("w_down", C.c_void_p), ("norm_w", C.c_void_p), ("rms_eps", C.c_float), ("residual", C.c_int32),
                 ("out", C.c_void_p), ("out_dtype", C.c_int32), ("ldo", C.c_int64), ("workspace", C.c_void_p),
                 ("workspace_bytes", C.c_size_t), ("tap_pair_exp", C.c_void_p), ("tap_pair_w", C.c_void_p),
-                ("down_format", C.c_int32), ("ordered_combine", C.c_int32)]
+                ("down_format", C.c_int32), ("fused_combine", C.c_int32)]
 
+
+
+class EpDescC(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("n_tokens_local", C.c_int32), ("hidden", C.c_int32),
+                ("ffn", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32), ("reserved", C.c_int32),
+                ("xall_ptrs", C.POINTER(C.c_void_p)), ("pe_ptrs", C.POINTER(C.c_void_p)),
+                ("pw_ptrs", C.POINTER(C.c_void_p)), ("parts_ptrs", C.POINTER(C.c_void_p)),
+                ("flag_ptrs", C.POINTER(C.c_void_p))]
 
 _vp, _i, _i64, _u32, _u64, _sz, _f = C.c_void_p, C.c_int, C.c_int64, C.c_uint32, C.c_uint64, C.c_size_t, C.c_float
 
@@ -140,6 +148,12 @@ SIGNATURES = {
     "knj_ep_peer_gather_launch": (_i, [_vp, _i, _i64, _vp, _vp]),
     "knj_ep_combine_partial_peer_launch": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _i, _vp]),
     "knj_ep_reduce_sel_launch": (_i, [_vp, _i, _i, _i, _vp, _i, _i, _vp, _i, _vp, _i, _vp]),
+    "knj_ep_create": (_i, [C.POINTER(EpDescC), C.POINTER(_vp)]),
+    "knj_ep_forward_launch": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
+    "knj_ep_barrier_launch": (_i, [_vp, _vp]),
+    "knj_ep_set_wait": (_i, [_vp, C.c_longlong]),
+    "knj_ep_status": (_i, [_vp, _vp]),
+    "knj_ep_destroy": (None, [_vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),
     "knj_q4k_gateup_launch": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64,
                                    _i, _i, _vp, _vp]),

@@ -232,7 +232,7 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
                                   H / 256 * KNJ_Q4K_BYTES, T, E, k, P, w.status, s);
     if (rc) return rc;
   }
-  if (!a->ordered_combine) {
+  if (a->fused_combine) {
     // down GEMM with the weighted combine in its epilogue: the token's sum starts from the residual (or zero) in
     // f32 and receives its k rows as vector reductions; no per-pair rows exist. The f32 sums sit where the
     // per-pair rows would (or directly in a dense f32 output).

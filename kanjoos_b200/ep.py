@@ -14,10 +14,14 @@ the step needs no host synchronisation.
 
 "peer": the gather exchange carried by this library's own kernels over NVLink
 peer mappings (torch symmetric memory gives every rank pointers to every other
-rank's exchange buffers): rows and routing tables are pulled with plain loads
-from the peers, partial rows are stored straight into the token owner's buffer
-and only for tokens that have an expert on the sending rank; two small
-all-reduces serve as barriers. CUDA only.
+rank's exchange buffers). Steps whose buckets are large enough for the
+tensor-core GEMMs run as ONE C-ABI call on the library's layer object
+(knj_ep_forward_launch): rows and routing tables are stored into the peers'
+buffers while the router runs, flag barriers in peer memory order the ranks,
+partial rows are stored straight into the token owner's buffer and only for
+tokens that have an expert on the sending rank; no allocation and no
+collective in the step. Smaller steps pull the rows with plain loads, run the
+f32-accurate kernels, and use two small all-reduces as barriers. CUDA only.
 
 "dispatch": route -> pack hidden rows in (destination, expert, pair) order ->
 all-to-all #1 (one row per routed pair) -> grouped expert FFN on the received
@@ -224,6 +228,82 @@ class PeerBuffers:
         dist.all_reduce(self._token, group=self.group)
 
 
+class EpPeerContext:
+    """The rank's expert-parallel layer object of the C-ABI (knj_ep_create): symmetric-memory exchange buffers
+    whose per-rank addresses are handed to the library once; a step is one knj_ep_forward_launch, which
+    allocates nothing and calls no collective."""
+
+    def __init__(self, group, world, rank, T_loc, H, F, E, k, device):
+        import torch.distributed._symmetric_memory as symm
+        g = group if group is not None else dist.group.WORLD
+        T = T_loc * world
+        self.x_all = symm.empty((T, H), dtype=torch.float16, device=device)
+        self.pe_all = symm.empty((T * k,), dtype=torch.int32, device=device)
+        self.pw_all = symm.empty((T * k,), dtype=torch.float32, device=device)
+        self.parts = symm.empty((world, T_loc, H), dtype=torch.float32, device=device)
+        self.flags = symm.empty((64,), dtype=torch.int32, device=device)
+        self.flags.zero_()
+        bufs = (self.x_all, self.pe_all, self.pw_all, self.parts, self.flags)
+        self._handles = [symm.rendezvous(t, g) for t in bufs]
+        torch.cuda.synchronize(device)
+        dist.barrier(group=group)  # every rank's flag words are zero before anyone's first step
+        self._bind(world, rank, T_loc, H, F, E, k, [[int(p) for p in h.buffer_ptrs] for h in self._handles])
+
+    def _bind(self, world, rank, T_loc, H, F, E, k, ptrs):
+        """ptrs: five lists (rows, expert ids, weights, partial sums, flags) of `world` device addresses."""
+        from ._lib import EpDescC, check, lib
+        self._tables = [C.cast((C.c_void_p * world)(*p), C.POINTER(C.c_void_p)) for p in ptrs]
+        d = EpDescC(world, rank, T_loc, H, F, E, k, 0, *self._tables)
+        self._ctx = C.c_void_p()
+        check(lib().knj_ep_create(C.byref(d), C.byref(self._ctx)))
+        self.shape = (T_loc, H)
+
+    @classmethod
+    def from_pointers(cls, world, rank, T_loc, H, F, E, k, ptrs, keep=None):
+        """A layer object over exchange buffers the caller mapped itself (any peer mapping; the tests emulate two
+        ranks inside one process this way). `keep` holds whatever owns the memory."""
+        self = cls.__new__(cls)
+        self._keep = keep
+        self._bind(world, rank, T_loc, H, F, E, k, ptrs)
+        return self
+
+    def forward(self, x, router, bias, bank, residual, out_dtype):
+        assert tuple(x.shape) == self.shape and x.stride(1) == 1
+        out = torch.empty(self.shape, dtype=out_dtype, device=x.device)
+        return self.forward_into(x, router, bias, bank, residual, out)
+
+    def forward_into(self, x, router, bias, bank, residual, out):
+        from ._lib import DT_BF16, DT_F16, DT_F32, check, lib
+        dt = {torch.float32: DT_F32, torch.bfloat16: DT_BF16, torch.float16: DT_F16}
+        check(lib().knj_ep_forward_launch(self._ctx, C.c_void_p(x.data_ptr()), dt[x.dtype], x.stride(0),
+                                          C.c_void_p(router.data_ptr()),
+                                          C.c_void_p(bias.data_ptr() if bias is not None else None),
+                                          C.c_void_p(bank.gate.data_ptr()), C.c_void_p(bank.up.data_ptr()),
+                                          C.c_void_p(bank.down.data_ptr()), int(bool(residual)),
+                                          C.c_void_p(out.data_ptr()), dt[out.dtype],
+                                          C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
+    def barrier(self):
+        from ._lib import check, lib
+        check(lib().knj_ep_barrier_launch(self._ctx, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def set_wait(self, cycles: int):
+        from ._lib import check, lib
+        check(lib().knj_ep_set_wait(self._ctx, int(cycles)))
+
+    def status(self):
+        """Synchronises; raises KnjError (KNJ_E_TIMEOUT) if a bounded device-side wait gave up in the last step."""
+        from ._lib import check, lib
+        check(lib().knj_ep_status(self._ctx, C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+
+    def close(self):
+        from ._lib import lib
+        if self._ctx:
+            lib().knj_ep_destroy(self._ctx)
+            self._ctx = C.c_void_p()
+
+
 _PEER_BUFFERS = {}
 
 
@@ -233,6 +313,18 @@ def peer_buffers(group, world, rank, T_loc, H, k, row_dtype, device) -> PeerBuff
     if key not in _PEER_BUFFERS:
         _PEER_BUFFERS[key] = PeerBuffers(group, world, rank, T_loc, H, k, row_dtype, device)
     return _PEER_BUFFERS[key]
+
+
+_EP_CONTEXTS = {}
+
+
+def ep_context(group, world, rank, T_loc, H, F, E, k, device) -> EpPeerContext:
+    """One layer object per (group, shape), shared by the layers of a stack (the weights are per-call arguments):
+    creation is a collective, so every rank asks in the same order."""
+    key = (id(group), world, T_loc, H, F, E, k, str(device))
+    if key not in _EP_CONTEXTS:
+        _EP_CONTEXTS[key] = EpPeerContext(group, world, rank, T_loc, H, F, E, k, device)
+    return _EP_CONTEXTS[key]
 
 
 class EpMoeLayer:
@@ -254,13 +346,40 @@ class EpMoeLayer:
         self.e_loc = n_experts // self.world
         self.last_stats = {}
 
-    def forward(self, x: torch.Tensor, out_dtype=torch.float32) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, out_dtype=torch.float32, out: torch.Tensor | None = None) -> torch.Tensor:
+        """out: optional dense result rows [T_loc][H] to write into (its dtype then is the output's)."""
+        if out is not None:
+            out_dtype = out.dtype
         if self.exchange == "dispatch":
-            return self._forward_dispatch(x, out_dtype)
-        if (self.exchange == "peer" and self.world > 1 and x.is_cuda and (x.shape[0] * self.top_k) % 4 == 0
+            res = self._forward_dispatch(x, out_dtype)
+        elif (self.exchange == "peer" and self.world > 1 and x.is_cuda and (x.shape[0] * self.top_k) % 4 == 0
                 and self._peer_ready(x)):
-            return self._forward_peer(x, out_dtype)
-        return self._forward_gather(x, out_dtype)
+            if self._layer_object(x):
+                return self._forward_layer_object(x, out_dtype, out)
+            res = self._forward_peer(x, out_dtype)
+        else:
+            res = self._forward_gather(x, out_dtype)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+
+    def _layer_object(self, x: torch.Tensor) -> bool:
+        """Buckets large enough for the tensor-core GEMMs take the library's layer object (knj_ep_*): one call per
+        step, no allocation, no collective. Smaller steps keep the f32-accurate kernels behind `_forward_peer`."""
+        cp = self.compute
+        return (hasattr(cp, "router") and x.shape[1] % 256 == 0 and
+                x.shape[0] * self.top_k >= getattr(cp, "tc_rows_per_expert", 1 << 30) * self.e_loc)
+
+    def _forward_layer_object(self, x, out_dtype, out):
+        T_loc, H = x.shape
+        cp = self.compute
+        ctx = ep_context(self.group, self.world, self.rank, T_loc, H, self.bank.ffn, self.E, self.top_k, x.device)
+        self.last_stats = {"tokens_gathered": int(T_loc * self.world), "layer_object": True}
+        self.context = ctx
+        if out is None:
+            return ctx.forward(x, cp.router, cp.bias, self.bank, False, out_dtype)
+        return ctx.forward_into(x, cp.router, cp.bias, self.bank, False, out)
 
     def _peer_ready(self, x: torch.Tensor) -> bool:
         """The peer mappings are set up once per shape, and the ranks agree on the outcome: if any rank cannot
@@ -275,8 +394,11 @@ class EpMoeLayer:
             return verdict[keys[0]]
         ok = 1
         try:
-            for (_, _, _, d) in keys:
-                peer_buffers(self.group, self.world, self.rank, T_loc, H, self.top_k, d, x.device)
+            if self._layer_object(x):
+                ep_context(self.group, self.world, self.rank, T_loc, H, self.bank.ffn, self.E, self.top_k, x.device)
+            else:
+                for (_, _, _, d) in keys:
+                    peer_buffers(self.group, self.world, self.rank, T_loc, H, self.top_k, d, x.device)
         except Exception as ex:  # noqa: BLE001 - any failure means "use the collectives"
             self.last_stats["peer_setup_error"] = repr(ex)
             ok = 0

@@ -93,7 +93,7 @@ class MoeFfnLayer:
         self.workspace = workspace
         self._need = need
 
-    def _args(self, x: torch.Tensor, out: torch.Tensor, taps=None, ordered_combine: bool = False) -> MoeFfnArgs:
+    def _args(self, x: torch.Tensor, out: torch.Tensor, taps=None, fused_combine: bool = False) -> MoeFfnArgs:
         b = self.bank
         T, H = x.shape
         assert H == b.hidden and T <= self.max_tokens and x.is_contiguous() and out.is_contiguous()
@@ -107,21 +107,21 @@ class MoeFfnLayer:
         a.norm_w = b.norm_w.data_ptr() if self.use_norm else None
         a.rms_eps = b.rms_eps
         a.residual = 1 if self.residual else 0
-        a.ordered_combine = 1 if ordered_combine else 0
+        a.fused_combine = 1 if fused_combine else 0
         a.out, a.out_dtype, a.ldo = out.data_ptr(), _DT[out.dtype], H
         a.workspace, a.workspace_bytes = self.workspace.data_ptr(), self.workspace.numel()
         if taps is not None:
             a.tap_pair_exp, a.tap_pair_w = taps[0].data_ptr(), taps[1].data_ptr()
         return a
 
-    def _run(self, fn, x, out, out_dtype, return_routing, ordered_combine=False):
+    def _run(self, fn, x, out, out_dtype, return_routing, fused_combine=False):
         if out is None:
             out = torch.empty(x.shape, dtype=out_dtype or torch.float32, device=x.device)
         taps = None
         if return_routing:
             P = x.shape[0] * self.top_k
             taps = (torch.empty(P, dtype=torch.int32, device=x.device), torch.empty(P, dtype=torch.float32, device=x.device))
-        args = self._args(x, out, taps, ordered_combine)
+        args = self._args(x, out, taps, fused_combine)
         check(fn(C.byref(args), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return (out, taps[0], taps[1]) if return_routing else out
 
@@ -129,10 +129,11 @@ class MoeFfnLayer:
         """f32-accurate path (batch <= 64 is the intended use)."""
         return self._run(lib().knj_moe_ffn_decode_launch, x, out, out_dtype, return_routing)
 
-    def prefill(self, x, out=None, out_dtype=None, return_routing=False, ordered_combine=False):
-        """Grouped-GEMM path over per-expert token buckets. ordered_combine=False: the weighted sum is fused into
-        the down GEMM's epilogue (f32 reductions, unordered); True: per-pair rows + the ordered combine kernel."""
-        return self._run(lib().knj_moe_ffn_prefill_launch, x, out, out_dtype, return_routing, ordered_combine)
+    def prefill(self, x, out=None, out_dtype=None, return_routing=False, fused_combine=False):
+        """Grouped-GEMM path over per-expert token buckets. fused_combine=False: per-pair rows + the ordered combine
+        kernel (reproducible, and the faster form); True: the weighted sum fused into the down GEMM's epilogue
+        (f32 reductions, unordered)."""
+        return self._run(lib().knj_moe_ffn_prefill_launch, x, out, out_dtype, return_routing, fused_combine)
 
 
 class MoeStack:

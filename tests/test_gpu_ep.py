@@ -114,3 +114,78 @@ def test_two_ranks_peer_exchange_fp16_rows_repeated(tmp_path):
     got = np.concatenate([np.load(tmp_path / f"out{r}.npy") for r in range(world)])
     st = report(got, want, "expert-parallel layer (peer exchange, fp16 rows, 3 steps), 2 NCCL ranks")
     assert st["rel_rmse"] <= TOL_TC
+
+
+def _emulated_ranks(world, T, cfg=403):
+    """`world` layer objects inside one process on one GPU: every rank's exchange buffers are ordinary device
+    tensors, so a "peer" store is a local store. Each rank's own flag words are preset far ahead of the epochs the
+    test reaches and its arrivals at the other ranks go to a sink, so no barrier ever waits: the ranks' steps run
+    one after another on one stream instead."""
+    from kanjoos_b200 import ep
+    from kanjoos_b200.moe import ExpertBank
+    bank, wr, hx = problem(cfg, T)
+    hx = synth.bf16_round(hx)
+    e_loc, t_loc = E // world, T // world
+    dev = torch.device("cuda")
+    bufs = [dict(x=torch.zeros((T, H), dtype=torch.float16, device=dev), pe=torch.zeros(T * K, dtype=torch.int32, device=dev),
+                 pw=torch.zeros(T * K, dtype=torch.float32, device=dev),
+                 parts=torch.zeros((world, t_loc, H), dtype=torch.float32, device=dev),
+                 flags=torch.full((64,), 1 << 20, dtype=torch.int32, device=dev)) for _ in range(world)]
+    sink = torch.zeros(64, dtype=torch.int32, device=dev)  # where a rank's arrivals at its "peers" go
+    ranks = []
+    for r in range(world):
+        ptrs = [[b[name].data_ptr() for b in bufs] for name in ("x", "pe", "pw", "parts")]
+        ptrs.append([bufs[j]["flags"].data_ptr() if j == r else sink.data_ptr() for j in range(world)])
+        local = {k: np.ascontiguousarray(v[r * e_loc:(r + 1) * e_loc]) for k, v in bank.items()}
+        bk = ExpertBank.from_numpy(local, wr)
+        ctx = ep.EpPeerContext.from_pointers(world, r, t_loc, H, F, E, K, ptrs, keep=(bufs, sink))
+        x = torch.from_numpy(hx[r * t_loc:(r + 1) * t_loc].copy()).cuda().to(torch.bfloat16)
+        ranks.append((ctx, bk, x))
+    return bank, wr, hx, ranks, bufs
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_layer_object_two_emulated_ranks_one_gpu(world):
+    """The whole data path of knj_ep_forward_launch (row and table stores into every rank's buffers, plan over
+    the rank's experts, grouped GEMMs, partial sums into the owners' buffers, rank-ordered sum) with the ranks
+    stepped in turn; a rank's result is complete once every rank has stepped after it published its rows, so the
+    second round's outputs are the layer's."""
+    from gpu_util import report
+    T = 320
+    bank, wr, hx, ranks, _ = _emulated_ranks(world, T)
+    want, _, _ = ol.moe(wr, bank, hx, K)
+    outs = [None] * world
+    for _ in range(2):
+        for r, (ctx, bk, x) in enumerate(ranks):
+            outs[r] = ctx.forward(x, bk.router, None, bk, False, torch.float32)
+    # the first rank's second step summed partial rows the later ranks stored one round earlier: same inputs, same rows
+    for ctx, _, _ in ranks:
+        ctx.status()
+    got = np.concatenate([o.cpu().numpy() for o in outs])
+    st = report(got, want, f"layer object, {world} emulated ranks on one GPU, T={T}")
+    assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_TC
+    for ctx, _, _ in ranks:
+        ctx.close()
+
+
+def test_layer_object_barrier_gives_up_and_recovers():
+    """A rank barrier whose peer never arrives (a flag word that nothing sets) ends at its wait limit with the
+    status word raised -- KNJ_E_TIMEOUT on the host -- and the context stays usable: once the peer's word is
+    there the next barrier passes and the status is clean."""
+    from kanjoos_b200._lib import KnjError
+    _, _, _, ranks, bufs = _emulated_ranks(2, 64)
+    ctx = ranks[0][0]
+    for b in bufs:
+        b["flags"].zero_()
+    ctx.set_wait(2_000_000)  # about a millisecond
+    ctx.barrier()
+    with pytest.raises(KnjError) as ei:
+        ctx.status()
+    assert ei.value.code == -5
+    bufs[0]["flags"][1] = 1 << 20  # the peer's arrival, far ahead of this rank's epoch
+    ctx.set_wait(0)
+    bk, x = ranks[0][1], ranks[0][2]
+    ctx.forward(x, bk.router, None, bk, False, torch.float32)  # resets the status words, two barriers
+    ctx.status()
+    for c, _, _ in ranks:
+        c.close()

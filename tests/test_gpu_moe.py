@@ -263,7 +263,7 @@ def test_config5_prefill_sampled_tokens(cfg5, T, routing):
     hx = synth.bf16_round(synth.hidden_rows(5, T))
     layer = make_layer(bank, wr, 8, T, bias=bias)
     x = dev(hx).to(torch.bfloat16)
-    out, pe, pw = layer.prefill(x, return_routing=True)
+    out, pe, pw = layer.prefill(x, return_routing=True, fused_combine=True)
     ch, wts = pe.cpu().numpy().reshape(T, 8), pw.cpu().numpy().reshape(T, 8)
     cnt = np.bincount(ch.ravel(), minlength=128)
     print(f"T={T} {routing}: bucket sizes max {cnt.max()} min {cnt.min()}")
@@ -272,7 +272,7 @@ def test_config5_prefill_sampled_tokens(cfg5, T, routing):
     got = out.cpu().numpy()
     st = report(got[sample], want, f"cfg5 prefill T={T} {routing}, fused combine, 256 sampled tokens")
     assert (got == SENTINEL).sum() == 0 and st["rel_rmse"] <= TOL_PREFILL
-    ordered = layer.prefill(x, ordered_combine=True).cpu().numpy()
+    ordered = layer.prefill(x).cpu().numpy()
     st = report(ordered[sample], want, f"cfg5 prefill T={T} {routing}, ordered combine")
     assert st["rel_rmse"] <= TOL_PREFILL
     # the two combine forms differ by the order of eight f32 additions per output only
@@ -290,9 +290,9 @@ def test_prefill_combine_forms_with_residual_and_bf16_output(cfg2):
     hx = synth.bf16_round(synth.hidden_rows(2, 300, layer=7))
     layer = make_layer(bank, wr, 8, 300, residual=True)
     x = dev(hx).to(torch.bfloat16)
-    fused = layer.prefill(x, out_dtype=torch.bfloat16).float().cpu().numpy()
-    o1 = layer.prefill(x, out_dtype=torch.bfloat16, ordered_combine=True).float().cpu().numpy()
-    o2 = layer.prefill(x, out_dtype=torch.bfloat16, ordered_combine=True).float().cpu().numpy()
+    fused = layer.prefill(x, out_dtype=torch.bfloat16, fused_combine=True).float().cpu().numpy()
+    o1 = layer.prefill(x, out_dtype=torch.bfloat16).float().cpu().numpy()
+    o2 = layer.prefill(x, out_dtype=torch.bfloat16).float().cpu().numpy()
     assert np.array_equal(o1, o2)
     assert np.mean(fused != o1) < 0.01 and report(fused, o1, "fused vs ordered, bf16 out + residual")["rel_rmse"] <= 5e-3
     want, _, _ = ol.moe(wr, bank, hx)
