@@ -513,7 +513,9 @@ def run_gpu(args):
     if world == 1:
         launches = 2 + n_perm + 1 + 2 + 1
     elif args.exchange == "peer":
-        launches = 2 + 1 + 3 + n_perm + 2 + 2      # + 3 peer gathers, partial combine to peers, rank reduce
+        # row stores, router (2), table stores, barrier, local expert ids, plan, gate+up, down, partial sums
+        # to the owners, barrier, rank reduce
+        launches = 1 + 2 + 1 + 1 + 1 + n_perm + 2 + 1 + 1 + 1
     elif args.exchange == "gather":
         launches = 2 + 1 + n_perm + 2 + 2
     else:

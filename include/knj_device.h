@@ -547,25 +547,39 @@ int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, 
  * symmetric memory or any other peer mapping made by the host) and passed as HOST
  * arrays of `world` device pointers, entry r = rank r's buffer, entry `rank` =
  * this rank's own:
- *   xall_ptrs  fp16 [world*n_tokens_local][hidden]  every rank's rows, by global token
+ *   xall_ptrs  fp16 [world*n_tokens_local][hidden]  every rank's rows
  *   pe_ptrs    int32 [world*n_tokens_local*top_k]   every rank's expert ids
  *   pw_ptrs    f32   [world*n_tokens_local*top_k]   every rank's routing weights
  *   parts_ptrs f32   [world][n_tokens_local][hidden] partial sums of this rank's tokens, by contributing rank
- *   flag_ptrs  uint32 [world]                       barrier words, zero before the first step
+ *   flag_ptrs  uint32 [KNJ_EP_FLAG_WORDS]            flag words, zero before the first step
  * knj_ep_create allocates the rank's private scratch (plan tables, the activation
  * and per-pair output rows) once; knj_ep_forward_launch allocates nothing and calls
- * no collective library: rows and routing tables are STORED into the peers'
- * buffers, the ranks meet at a flag barrier in peer memory (bounded spin; a wait
- * that gives up raises the status word read by knj_ep_status -> KNJ_E_TIMEOUT and
- * the step's output is then undefined), each rank runs the grouped tensor-core
- * GEMMs over its experts and stores its weighted partial sums into the token
- * owners' buffers, a second barrier, and the rank-ordered sum (+ residual = x).
- * All ranks must call knj_ep_forward_launch the same number of times.
- * hidden, ffn multiples of 256; n_tokens_local*top_k a multiple of 4; experts
- * split contiguously, n_experts / world <= 256.
+ * no collective library. A step runs in n_chunks chunks of the local tokens
+ * (chunk c = local tokens [c, c+1) * n_tokens_local / n_chunks of EVERY rank; the
+ * gathered buffers are chunk-major: rows [n_chunks][world][chunk tokens][hidden],
+ * likewise the tables and the partial sums) over the caller's stream and a copy
+ * stream of the context:
+ *   copy stream : per chunk the rank's rows (fp16) and routing tables are STORED
+ *                 into every rank's buffers, then an arrival word into every rank's
+ *                 flags; later the chunk's weighted partial sums go to the token
+ *                 owners the same way
+ *   caller's    : router over the local tokens; per chunk: wait until every rank's
+ *                 arrival word is there (bounded spin; a wait that gives up raises
+ *                 the status word read by knj_ep_status -> KNJ_E_TIMEOUT and the
+ *                 step's output is then undefined), plan, the grouped tensor-core
+ *                 GEMMs over the rank's experts, and -- one chunk behind -- the
+ *                 rank-ordered sum of the partial rows (+ residual = x)
+ * so that a chunk's transfers overlap the neighbouring chunks' GEMMs. When the
+ * call returns the caller's stream is ordered after everything it launched.
+ * All ranks must call knj_ep_forward_launch the same number of times (the flag
+ * words carry the step number).
+ * hidden, ffn multiples of 256; (n_tokens_local / n_chunks) * top_k a multiple of
+ * 4; experts split contiguously, n_experts / world <= 256; n_chunks 0 or 1 = one.
  * ------------------------------------------------------------------------- */
+#define KNJ_EP_FLAG_WORDS 4096
+#define KNJ_EP_MAX_CHUNKS 8
 typedef struct knj_ep_desc {
-  int32_t world, rank, n_tokens_local, hidden, ffn, n_experts, top_k, reserved;
+  int32_t world, rank, n_tokens_local, hidden, ffn, n_experts, top_k, n_chunks;
   void *const *xall_ptrs;
   int32_t *const *pe_ptrs;
   float *const *pw_ptrs;
@@ -580,9 +594,9 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out);
 int knj_ep_forward_launch(knj_ep_ctx *ctx, const void *x, int x_dtype, int64_t ldx, const uint16_t *w_router,
                           const float *router_bias, const uint8_t *w_gate, const uint8_t *w_up, const uint8_t *w_down,
                           int residual, void *out, int out_dtype, knj_stream_t s);
-/* the rank barrier alone (what knj_ep_forward_launch runs twice per step) */
+/* a barrier over the ranks on the stream (arrival + bounded wait in one launch, on flag words of its own) */
 int knj_ep_barrier_launch(knj_ep_ctx *ctx, knj_stream_t s);
-/* limit of the barrier's spin in SM clock cycles (<= 0 restores the default, about a second) */
+/* limit of every rank wait in SM clock cycles (<= 0 restores the default, about a second) */
 int knj_ep_set_wait(knj_ep_ctx *ctx, long long wait_cycles);
 /* synchronises the stream; KNJ_E_TIMEOUT if a barrier or a GEMM pipeline wait gave up since the last step began */
 int knj_ep_status(knj_ep_ctx *ctx, knj_stream_t s);

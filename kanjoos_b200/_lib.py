@@ -14,6 +14,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("KNJ_DEVICE_LIB") or os.path.join(PKG, "libknj_device.so")
 
 DT_F32, DT_BF16, DT_F16 = 0, 1, 2
+EP_FLAG_WORDS, EP_MAX_CHUNKS = 4096, 8  # KNJ_EP_FLAG_WORDS, KNJ_EP_MAX_CHUNKS
 
 
 class KnjError(RuntimeError):
@@ -44,7 +45,7 @@ class MoeFfnArgs(C.Structure):
 
 class EpDescC(C.Structure):
     _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("n_tokens_local", C.c_int32), ("hidden", C.c_int32),
-                ("ffn", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32), ("reserved", C.c_int32),
+                ("ffn", C.c_int32), ("n_experts", C.c_int32), ("top_k", C.c_int32), ("n_chunks", C.c_int32),
                 ("xall_ptrs", C.POINTER(C.c_void_p)), ("pe_ptrs", C.POINTER(C.c_void_p)),
                 ("pw_ptrs", C.POINTER(C.c_void_p)), ("parts_ptrs", C.POINTER(C.c_void_p)),
                 ("flag_ptrs", C.POINTER(C.c_void_p))]

@@ -25,6 +25,7 @@
 // kernels only, the GEMMs read local memory.
 #include "knj_common.cuh"
 #include "knj_q4k.h"
+#include "knj_q4k_engine.cuh"
 
 using namespace knj;
 
@@ -40,16 +41,16 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 }
 
 // Barrier over the ranks, on the stream: thread j tells rank j that this rank has reached epoch e (a store into
-// slot `rank` of j's flag array) and waits until rank j has told this rank the same (slot j of the own array).
+// slot `rank` of j's flag words) and waits until rank j has told this rank the same (slot j of the own words).
 // Everything this rank stored into peer memory before the launch is visible to a peer that leaves its barrier.
 // A wait that runs out of time raises *status and the kernel returns; nothing spins without a limit.
-__global__ void ep_barrier_kernel(uint32_t *const *flags, int world, int rank, uint32_t *epoch, long long limit, int *status) {
+__global__ void ep_barrier_kernel(uint32_t *const *flags, int slot, int world, int rank, uint32_t *epoch, long long limit, int *status) {
   const int j = threadIdx.x;
   const uint32_t e = *epoch + 1u;
   __threadfence_system();
   if (j < world) {
-    st_release_sys(flags[j] + rank, e);
-    const uint32_t *mine = flags[rank] + j;
+    st_release_sys(flags[j] + slot + rank, e);
+    const uint32_t *mine = flags[rank] + slot + j;
     const long long t0 = clock64();
     unsigned polls = 0;
     while ((int32_t)(ld_acquire_sys(mine) - e) < 0) {
@@ -63,16 +64,36 @@ __global__ void ep_barrier_kernel(uint32_t *const *flags, int world, int rank, u
   if (j == 0) *epoch = e;
 }
 
-// The rank's rows as fp16 into every rank's gathered-rows buffer at row offset rank * T_loc (16 bytes = 8 values
-// per thread and step, one store per destination).
+// The two halves of that barrier as launches of their own, so that they can sit on different streams: the arrival
+// follows the kernel whose peer stores it announces (the copy stream), the wait precedes the kernel that reads
+// what the peers stored (the compute stream). e is the step number, the same on every rank.
+__global__ void ep_arrive_kernel(uint32_t *const *flags, int slot, int world, int rank, uint32_t e) {
+  __threadfence_system();
+  if ((int)threadIdx.x < world) st_release_sys(flags[threadIdx.x] + slot + rank, e);
+}
+__global__ void ep_wait_kernel(const uint32_t *mine, int world, uint32_t e, long long limit, int *status) {
+  if ((int)threadIdx.x < world) {
+    const long long t0 = clock64();
+    unsigned polls = 0;
+    while ((int32_t)(ld_acquire_sys(mine + threadIdx.x) - e) < 0) {
+      if ((++polls & 255u) == 0u && clock64() - t0 > limit) {
+        atomicExch(status, 1);
+        break;
+      }
+    }
+  }
+  __threadfence_system();
+}
+
+// The rank's rows [r0, r0 + rows) as fp16 into every rank's gathered-rows buffer at element dst_off (16 bytes = 8
+// values per thread and step, one store per destination).
 template <int DT>
 __global__ void __launch_bounds__(256) ep_push_rows_kernel(const void *__restrict__ x, int64_t ldx, int H8, int64_t n8,
                                                            __half *const *__restrict__ dst, int world, int64_t dst_off) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
     const int64_t r = i / H8, c = 8 * (i - r * H8);
     float v[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = load_as_f32(x, DT, r * ldx + c + j);
+    knj::q4e::load8_f32(x, DT, r * ldx + c, v);
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -84,16 +105,17 @@ __global__ void __launch_bounds__(256) ep_push_rows_kernel(const void *__restric
   }
 }
 
-// The rank's slice of the routing tables from its own gathered tables to the peers' (16 bytes per thread).
-__global__ void __launch_bounds__(256) ep_push_tables_kernel(int32_t *const *__restrict__ pe, float *const *__restrict__ pw, int world,
-                                                             int rank, int64_t off, int64_t n4) {
-  const uint4 *spe = reinterpret_cast<const uint4 *>(pe[rank] + off), *spw = reinterpret_cast<const uint4 *>(pw[rank] + off);
+// The rank's routing tables (local order, [T_loc*k]) into every rank's gathered tables: the slice of chunk c goes
+// to element c*chunk_stride + rank_off (16 bytes per thread).
+__global__ void __launch_bounds__(256) ep_push_tables_kernel(const int32_t *__restrict__ pe_loc, const float *__restrict__ pw_loc,
+                                                             int32_t *const *__restrict__ pe, float *const *__restrict__ pw, int world,
+                                                             int64_t n4, int64_t n4_chunk, int64_t chunk_stride, int64_t rank_off) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
-    const uint4 a = spe[i], b = spw[i];
+    const uint4 a = reinterpret_cast<const uint4 *>(pe_loc)[i], b = reinterpret_cast<const uint4 *>(pw_loc)[i];
+    const int64_t c = i / n4_chunk, at = c * chunk_stride + rank_off + 4 * (i - c * n4_chunk);
     for (int d = 0; d < world; ++d) {
-      if (d == rank) continue;
-      reinterpret_cast<uint4 *>(pe[d] + off)[i] = a;
-      reinterpret_cast<uint4 *>(pw[d] + off)[i] = b;
+      *reinterpret_cast<uint4 *>(pe[d] + at) = a;
+      *reinterpret_cast<uint4 *>(pw[d] + at) = b;
     }
   }
 }
@@ -112,8 +134,9 @@ inline size_t up256(size_t n) { return (n + 255) & ~(size_t)255; }
 
 struct knj_ep_ctx {
   knj_ep_desc d{};
-  int T = 0, P = 0, e_loc = 0;
-  char *block = nullptr;  // one device allocation, carved below
+  int C = 1;                      // chunks of a step
+  int Tc_loc = 0, Tc = 0, Pc = 0, e_loc = 0;  // per chunk: local tokens, tokens of all ranks, pairs of all ranks
+  char *block = nullptr;          // one device allocation, carved below
   // device copies of the pointer tables
   __half **xall_ptrs = nullptr;
   int32_t **pe_ptrs = nullptr;
@@ -125,17 +148,37 @@ struct knj_ep_ctx {
   int32_t *pe_all = nullptr;
   float *pw_all = nullptr;
   float *parts = nullptr;
+  uint32_t *flags = nullptr;
   // local scratch
-  float *logits = nullptr, *Y = nullptr;
-  int32_t *local_ids = nullptr, *pair_idx = nullptr, *pair_cnt = nullptr, *exp_list = nullptr, *n_active = nullptr;
+  float *logits = nullptr, *pw_loc = nullptr, *Y[2] = {nullptr, nullptr};
+  int32_t *pe_loc = nullptr, *local_ids = nullptr, *pair_idx = nullptr, *pair_cnt = nullptr, *exp_list = nullptr, *n_active = nullptr;
   void *perm_scratch = nullptr, *ah = nullptr;
   size_t perm_bytes = 0;
   uint32_t *epoch = nullptr;
-  int *status = nullptr;  // [0] barrier, [1] GEMMs
+  int *status = nullptr;  // [0] rank waits, [1] GEMMs
   long long wait_cycles = kMaxWaitCycles;
+  uint32_t step = 0;      // steps launched so far: the epoch the flag words of a step carry
   cudaStream_t side = nullptr;
-  cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_router = nullptr, ev_side = nullptr;
+  cudaEvent_t ev_down[KNJ_EP_MAX_CHUNKS] = {}, ev_sent[KNJ_EP_MAX_CHUNKS] = {};
+#ifdef KNJ_TRACE
+  cudaEvent_t stamp[12] = {};
+#endif
 };
+
+#ifdef KNJ_TRACE
+#define KNJ_EP_STAMP(i)                                                        \
+  do {                                                                         \
+    if (!c->stamp[i]) cudaEventCreate(&c->stamp[i]);                           \
+    cudaEventRecord(c->stamp[i], st);                                          \
+  } while (0)
+#else
+#define KNJ_EP_STAMP(i) ((void)0)
+#endif
+
+// flag words of a rank: [0, C*world) rows and tables of chunk c have been stored; [C*world, 2*C*world) partial
+// sums of chunk c have been stored; kBarrierSlot.. the stand-alone barrier
+static constexpr int kBarrierSlot = KNJ_EP_FLAG_WORDS - 64;
 
 extern "C" {
 
@@ -143,13 +186,16 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
   KNJ_REQUIRE(desc && out, "knj_ep_create: null argument");
   *out = nullptr;
   const knj_ep_desc &d = *desc;
+  const int C = d.n_chunks <= 0 ? 1 : d.n_chunks;
   KNJ_REQUIRE(d.world >= 1 && d.world <= 64 && d.rank >= 0 && d.rank < d.world, "knj_ep_create: rank %d of %d", d.rank, d.world);
   KNJ_REQUIRE(d.n_experts >= d.world && d.n_experts % d.world == 0 && d.n_experts / d.world <= 256,
               "knj_ep_create: %d experts do not split over %d ranks", d.n_experts, d.world);
-  KNJ_REQUIRE(d.n_tokens_local >= 1 && d.hidden % 256 == 0 && d.ffn % 256 == 0 && d.hidden % 128 == 0 && d.ffn % 128 == 0,
+  KNJ_REQUIRE(d.n_tokens_local >= 1 && d.hidden > 0 && d.ffn > 0 && d.hidden % 256 == 0 && d.ffn % 256 == 0,
               "knj_ep_create: bad token count / hidden / ffn");
-  KNJ_REQUIRE(d.top_k >= 1 && d.top_k <= 8 && ((int64_t)d.n_tokens_local * d.top_k) % 4 == 0,
-              "knj_ep_create: top_k out of range or local pairs not a multiple of 4");
+  KNJ_REQUIRE(C <= KNJ_EP_MAX_CHUNKS && d.n_tokens_local % C == 0 && 2 * C * d.world <= kBarrierSlot,
+              "knj_ep_create: %d local tokens do not split into %d chunks", d.n_tokens_local, C);
+  KNJ_REQUIRE(d.top_k >= 1 && d.top_k <= 8 && ((int64_t)(d.n_tokens_local / C) * d.top_k) % 4 == 0,
+              "knj_ep_create: top_k out of range or a chunk's local pairs not a multiple of 4");
   KNJ_REQUIRE(d.xall_ptrs && d.pe_ptrs && d.pw_ptrs && d.parts_ptrs && d.flag_ptrs, "knj_ep_create: null pointer table");
   for (int r = 0; r < d.world; ++r)
     KNJ_REQUIRE(d.xall_ptrs[r] && d.pe_ptrs[r] && d.pw_ptrs[r] && d.parts_ptrs[r] && d.flag_ptrs[r] && aligned16(d.xall_ptrs[r]) &&
@@ -157,28 +203,36 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
                 "knj_ep_create: rank %d's buffers are missing or not 16-byte aligned", r);
   knj_ep_ctx *c = new knj_ep_ctx();
   c->d = d;
-  c->T = d.n_tokens_local * d.world;
-  c->P = c->T * d.top_k;
+  c->C = C;
+  c->Tc_loc = d.n_tokens_local / C;
+  c->Tc = c->Tc_loc * d.world;
+  c->Pc = c->Tc * d.top_k;
   c->e_loc = d.n_experts / d.world;
-  const size_t T = c->T, P = c->P, H = d.hidden, F = d.ffn, W = d.world;
-  c->perm_bytes = knj_moe_permute_scratch_bytes(c->P, c->e_loc);
+  const size_t Tc = c->Tc, Pc = c->Pc, H = d.hidden, F = d.ffn, W = d.world, Pl = (size_t)d.n_tokens_local * d.top_k;
+  c->perm_bytes = knj_moe_permute_scratch_bytes(c->Pc, c->e_loc);
   size_t off = 0;
   auto take = [&](size_t bytes) { const size_t at = off; off += up256(bytes); return at; };
   const size_t o_tab = take(5 * W * sizeof(void *));
   const size_t o_logits = take((size_t)d.n_tokens_local * d.n_experts * 4);
-  const size_t o_ids = take(P * 4);
-  const size_t o_pidx = take((size_t)c->e_loc * T * 4);
+  const size_t o_pe = take(Pl * 4), o_pw = take(Pl * 4);
+  const size_t o_ids = take(Pc * 4);
+  const size_t o_pidx = take((size_t)c->e_loc * Tc * 4);
   const size_t o_small = take((size_t)(2 * c->e_loc + 16) * 4);
   const size_t o_perm = take(c->perm_bytes);
-  const size_t o_ah = take(P * F * 2);
-  const size_t o_y = take(P * H * 4);
+  const size_t o_ah = take(Pc * F * 2);
+  const size_t o_y0 = take(Pc * H * 4);
+  const size_t o_y1 = C > 1 ? take(Pc * H * 4) : o_y0;
   const size_t o_words = take(64);
   cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->block), off);
   if (e == cudaSuccess) e = cudaMemset(c->block + o_words, 0, 64);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming);
-  if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming);
-  void **tab = reinterpret_cast<void **>(c->block + o_tab);
+  cudaEvent_t *evs[3] = {&c->ev_fork, &c->ev_router, &c->ev_side};
+  for (int i = 0; i < 3 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(evs[i], cudaEventDisableTiming);
+  for (int i = 0; i < C && e == cudaSuccess; ++i) {
+    e = cudaEventCreateWithFlags(&c->ev_down[i], cudaEventDisableTiming);
+    if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_sent[i], cudaEventDisableTiming);
+  }
+  void **tab = c->block ? reinterpret_cast<void **>(c->block + o_tab) : nullptr;
   const void *const *src[5] = {d.xall_ptrs, reinterpret_cast<const void *const *>(d.pe_ptrs), reinterpret_cast<const void *const *>(d.pw_ptrs),
                                reinterpret_cast<const void *const *>(d.parts_ptrs), reinterpret_cast<const void *const *>(d.flag_ptrs)};
   for (int i = 0; i < 5 && e == cudaSuccess; ++i) e = cudaMemcpy(tab + i * W, src[i], W * sizeof(void *), cudaMemcpyHostToDevice);
@@ -197,7 +251,10 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
   c->pe_all = d.pe_ptrs[d.rank];
   c->pw_all = d.pw_ptrs[d.rank];
   c->parts = d.parts_ptrs[d.rank];
+  c->flags = d.flag_ptrs[d.rank];
   c->logits = reinterpret_cast<float *>(c->block + o_logits);
+  c->pe_loc = reinterpret_cast<int32_t *>(c->block + o_pe);
+  c->pw_loc = reinterpret_cast<float *>(c->block + o_pw);
   c->local_ids = reinterpret_cast<int32_t *>(c->block + o_ids);
   c->pair_idx = reinterpret_cast<int32_t *>(c->block + o_pidx);
   c->pair_cnt = reinterpret_cast<int32_t *>(c->block + o_small);
@@ -205,7 +262,8 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
   c->n_active = c->exp_list + c->e_loc;
   c->perm_scratch = c->block + o_perm;
   c->ah = c->block + o_ah;
-  c->Y = reinterpret_cast<float *>(c->block + o_y);
+  c->Y[0] = reinterpret_cast<float *>(c->block + o_y0);
+  c->Y[1] = reinterpret_cast<float *>(c->block + o_y1);
   c->epoch = reinterpret_cast<uint32_t *>(c->block + o_words);
   c->status = reinterpret_cast<int *>(c->block + o_words + 16);
   *out = c;
@@ -220,7 +278,7 @@ int knj_ep_set_wait(knj_ep_ctx *c, long long wait_cycles) {
 
 int knj_ep_barrier_launch(knj_ep_ctx *c, knj_stream_t s) {
   KNJ_REQUIRE(c && c->block, "knj_ep_barrier: null context");
-  ep_barrier_kernel<<<1, 64, 0, as_stream(s)>>>(c->flag_ptrs, c->d.world, c->d.rank, c->epoch, c->wait_cycles, c->status);
+  ep_barrier_kernel<<<1, 64, 0, as_stream(s)>>>(c->flag_ptrs, kBarrierSlot, c->d.world, c->d.rank, c->epoch, c->wait_cycles, c->status);
   return launch_status("ep_barrier_kernel");
 }
 
@@ -231,59 +289,114 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
   KNJ_REQUIRE(x_dtype == KNJ_DT_F32 || x_dtype == KNJ_DT_BF16 || x_dtype == KNJ_DT_F16, "knj_ep_forward: unknown x dtype");
   KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_ep_forward: out must be f32 or bf16");
   const knj_ep_desc &d = c->d;
-  const int T_loc = d.n_tokens_local, H = d.hidden, F = d.ffn, k = d.top_k, W = d.world, rank = d.rank, T = c->T, P = c->P;
-  KNJ_REQUIRE(ldx >= H && ldx % 8 == 0 && aligned16(x), "knj_ep_forward: rows of x must be 16-byte aligned");
-  cudaStream_t st = as_stream(s);
+  const int T_loc = d.n_tokens_local, H = d.hidden, F = d.ffn, k = d.top_k, W = d.world, rank = d.rank, C = c->C;
+  const int Tc_loc = c->Tc_loc, Tc = c->Tc, Pc = c->Pc;
+  KNJ_REQUIRE(ldx >= H && ldx % 8 == 0 && aligned16(x) && (!residual || ldx == H), "knj_ep_forward: rows of x must be 16-byte aligned (dense with residual)");
+  cudaStream_t st = as_stream(s), side = c->side;
+  const size_t x_el = x_dtype == KNJ_DT_F32 ? 4 : 2, o_el = out_dtype == KNJ_DT_F32 ? 4 : 2;
+  const uint32_t epoch = ++c->step;
   int rc;
-  // ---- rows to every rank (side stream) while the router runs (main stream)
+  KNJ_EP_STAMP(0);
+  KNJ_CUDA(cudaMemsetAsync(c->status, 0, 2 * sizeof(int), st));
   KNJ_CUDA(cudaEventRecord(c->ev_fork, st));
-  KNJ_CUDA(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
-  {
-    const int64_t n8 = (int64_t)T_loc * H / 8, blocks = (n8 + 255) / 256, cap = (int64_t)sm_count() * 4;
+  KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_fork, 0));
+  // ---- main stream: the router over all local tokens (tables in local order)
+  rc = knj_router_topk_launch(x, x_dtype, ldx, w_router, router_bias, T_loc, H, d.n_experts, k, c->logits, c->pe_loc, c->pw_loc, s);
+  if (rc) return rc;
+  KNJ_CUDA(cudaEventRecord(c->ev_router, st));
+  KNJ_EP_STAMP(1);
+  // ---- copy stream: chunk by chunk the rows to every rank, the tables once, an arrival per chunk
+  for (int ch = 0; ch < C; ++ch) {
+    const int64_t n8 = (int64_t)Tc_loc * H / 8, blocks = (n8 + 255) / 256, cap = (int64_t)sm_count() * 4;
     const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
-    const int64_t off = (int64_t)rank * T_loc * H;
-    if (x_dtype == KNJ_DT_F32) ep_push_rows_kernel<KNJ_DT_F32><<<grid, 256, 0, c->side>>>(x, ldx, H / 8, n8, c->xall_ptrs, W, off);
-    else if (x_dtype == KNJ_DT_BF16) ep_push_rows_kernel<KNJ_DT_BF16><<<grid, 256, 0, c->side>>>(x, ldx, H / 8, n8, c->xall_ptrs, W, off);
-    else ep_push_rows_kernel<KNJ_DT_F16><<<grid, 256, 0, c->side>>>(x, ldx, H / 8, n8, c->xall_ptrs, W, off);
+    const int64_t off = ((int64_t)ch * Tc + (int64_t)rank * Tc_loc) * H;
+    const void *xc = static_cast<const char *>(x) + (size_t)ch * Tc_loc * ldx * x_el;
+    if (x_dtype == KNJ_DT_F32) ep_push_rows_kernel<KNJ_DT_F32><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
+    else if (x_dtype == KNJ_DT_BF16) ep_push_rows_kernel<KNJ_DT_BF16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
+    else ep_push_rows_kernel<KNJ_DT_F16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
     rc = launch_status("ep_push_rows_kernel");
     if (rc) return rc;
-    KNJ_CUDA(cudaEventRecord(c->ev_join, c->side));
-  }
-  KNJ_CUDA(cudaMemsetAsync(c->status, 0, 2 * sizeof(int), st));
-  const int64_t toff = (int64_t)rank * T_loc * k;
-  rc = knj_router_topk_launch(x, x_dtype, ldx, w_router, router_bias, T_loc, H, d.n_experts, k, c->logits, c->pe_all + toff,
-                              c->pw_all + toff, s);
-  if (rc) return rc;
-  if (W > 1) {
-    const int64_t n4 = (int64_t)T_loc * k / 4;
-    ep_push_tables_kernel<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(c->pe_ptrs, c->pw_ptrs, W, rank, toff, n4);
-    rc = launch_status("ep_push_tables_kernel");
+    if (ch == 0) {
+      KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_router, 0));
+      const int64_t n4 = (int64_t)T_loc * k / 4, n4c = (int64_t)Tc_loc * k / 4;
+      ep_push_tables_kernel<<<(unsigned)((n4 + 255) / 256 < 592 ? (n4 + 255) / 256 : 592), 256, 0, side>>>(
+          c->pe_loc, c->pw_loc, c->pe_ptrs, c->pw_ptrs, W, n4, n4c, (int64_t)Pc, (int64_t)rank * Tc_loc * k);
+      rc = launch_status("ep_push_tables_kernel");
+      if (rc) return rc;
+    }
+    ep_arrive_kernel<<<1, 64, 0, side>>>(c->flag_ptrs, ch * W, W, rank, epoch);
+    rc = launch_status("ep_arrive_kernel");
     if (rc) return rc;
   }
-  KNJ_CUDA(cudaStreamWaitEvent(st, c->ev_join, 0));
-  rc = knj_ep_barrier_launch(c, s);  // every rank's rows and tables have landed here
-  if (rc) return rc;
-  // ---- this rank's experts over all tokens
+  // ---- main stream: per chunk the rank's experts over the chunk's tokens of all ranks; the partial sums leave
+  //      on the copy stream while the next chunk's GEMMs run
   const int lo = rank * c->e_loc;
-  ep_local_ids_kernel<<<(unsigned)((P + 255) / 256 < 1184 ? (P + 255) / 256 : 1184), 256, 0, st>>>(c->pe_all, lo, c->e_loc, P, c->local_ids);
-  rc = launch_status("ep_local_ids_kernel");
-  if (rc) return rc;
-  rc = knj_moe_permute_ws_launch(c->local_ids, P, c->e_loc, T, c->pair_idx, c->pair_cnt, c->exp_list, c->n_active, c->perm_scratch,
-                                 c->perm_bytes, s);
-  if (rc) return rc;
-  rc = knj_q4k_gateup_tc_launch(c->x_all, w_gate, w_up, c->pair_idx, c->pair_cnt, nullptr, c->ah, F, H, H / 256 * KNJ_Q4K_BYTES, T,
-                                c->e_loc, k, P, c->status + 1, s);
-  if (rc) return rc;
-  rc = knj_q4k_down_tc_launch(c->ah, w_down, c->pair_idx, c->pair_cnt, nullptr, c->Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, c->e_loc, P,
-                              c->status + 1, s);
-  if (rc) return rc;
-  // ---- weighted partial sums to the token owners, then the sum over the contributing ranks
-  rc = knj_ep_combine_partial_peer_launch(c->Y, c->pe_all, c->pw_all, T, H, k, lo, lo + c->e_loc, c->parts_ptrs, rank, T_loc, s);
-  if (rc) return rc;
-  rc = knj_ep_barrier_launch(c, s);
-  if (rc) return rc;
-  return knj_ep_reduce_sel_launch(c->parts, W, T_loc, H, c->pe_all + toff, k, c->e_loc, residual ? x : nullptr, x_dtype, out, out_dtype, s);
+  auto reduce_chunk = [&](int ch) -> int {
+    ep_wait_kernel<<<1, 64, 0, st>>>(c->flags + (C + ch) * W, W, epoch, c->wait_cycles, c->status);
+    int r2 = launch_status("ep_wait_kernel");
+    if (r2) return r2;
+    return knj_ep_reduce_sel_launch(c->parts + (size_t)ch * Tc * H, W, Tc_loc, H, c->pe_loc + (size_t)ch * Tc_loc * k, k, c->e_loc,
+                                    residual ? static_cast<const char *>(x) + (size_t)ch * Tc_loc * ldx * x_el : nullptr, x_dtype,
+                                    static_cast<char *>(out) + (size_t)ch * Tc_loc * H * o_el, out_dtype, s);
+  };
+  for (int ch = 0; ch < C; ++ch) {
+    const __half *xa = c->x_all + (size_t)ch * Tc * H;
+    const int32_t *pe = c->pe_all + (size_t)ch * Pc;
+    const float *pw = c->pw_all + (size_t)ch * Pc;
+    float *Y = c->Y[ch & 1];
+    if (ch == 0) KNJ_EP_STAMP(2);
+    ep_wait_kernel<<<1, 64, 0, st>>>(c->flags + ch * W, W, epoch, c->wait_cycles, c->status);
+    rc = launch_status("ep_wait_kernel");
+    if (rc) return rc;
+    if (ch == 0) KNJ_EP_STAMP(3);
+    ep_local_ids_kernel<<<(unsigned)((Pc + 255) / 256 < 1184 ? (Pc + 255) / 256 : 1184), 256, 0, st>>>(pe, lo, c->e_loc, Pc, c->local_ids);
+    rc = launch_status("ep_local_ids_kernel");
+    if (rc) return rc;
+    rc = knj_moe_permute_ws_launch(c->local_ids, Pc, c->e_loc, Tc, c->pair_idx, c->pair_cnt, c->exp_list, c->n_active, c->perm_scratch,
+                                   c->perm_bytes, s);
+    if (rc) return rc;
+    if (ch == 0) KNJ_EP_STAMP(4);
+    rc = knj_q4k_gateup_tc_launch(xa, w_gate, w_up, c->pair_idx, c->pair_cnt, nullptr, c->ah, F, H, H / 256 * KNJ_Q4K_BYTES, Tc, c->e_loc, k,
+                                  Pc, c->status + 1, s);
+    if (rc) return rc;
+    if (ch == 0) KNJ_EP_STAMP(5);
+    if (ch >= 2) KNJ_CUDA(cudaStreamWaitEvent(st, c->ev_sent[ch - 2], 0));  // the rows of Y[ch & 1] have left
+    rc = knj_q4k_down_tc_launch(c->ah, w_down, c->pair_idx, c->pair_cnt, nullptr, Y, H, F, F / 256 * KNJ_Q4K_BYTES, Tc, c->e_loc, Pc,
+                                c->status + 1, s);
+    if (rc) return rc;
+    if (ch == 0) KNJ_EP_STAMP(6);
+    KNJ_CUDA(cudaEventRecord(c->ev_down[ch], st));
+    // copy stream: weighted partial sums of the chunk to the token owners, then the arrival
+    KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_down[ch], 0));
+    rc = ep_combine_partial_peer_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, rank, Tc_loc, side);
+    if (rc) return rc;
+    KNJ_CUDA(cudaEventRecord(c->ev_sent[ch], side));
+    ep_arrive_kernel<<<1, 64, 0, side>>>(c->flag_ptrs, (C + ch) * W, W, rank, epoch);
+    rc = launch_status("ep_arrive_kernel");
+    if (rc) return rc;
+    if (ch >= 1) {
+      rc = reduce_chunk(ch - 1);
+      if (rc) return rc;
+    }
+  }
+  KNJ_EP_STAMP(7);
+  KNJ_CUDA(cudaEventRecord(c->ev_side, side));
+  KNJ_CUDA(cudaStreamWaitEvent(st, c->ev_side, 0));  // the caller's stream owns everything the step launched
+  KNJ_EP_STAMP(8);
+  rc = reduce_chunk(C - 1);
+  KNJ_EP_STAMP(9);
+  return rc;
 }
+
+#ifdef KNJ_TRACE
+// measurement builds only: milliseconds between the stamps of the last step (router | - | wait for the first
+// chunk's rows | plan | gate+up | down (first chunk) | the remaining chunks | wait for the copy stream | last reduce)
+int knj_trace_ep_times(knj_ep_ctx *c, float *ms9) {
+  cudaDeviceSynchronize();
+  for (int i = 0; i < 9; ++i) cudaEventElapsedTime(ms9 + i, c->stamp[i], c->stamp[i + 1]);
+  return 0;
+}
+#endif
 
 int knj_ep_status(knj_ep_ctx *c, knj_stream_t s) {
   KNJ_REQUIRE(c && c->block, "knj_ep_status: null context");
@@ -291,7 +404,7 @@ int knj_ep_status(knj_ep_ctx *c, knj_stream_t s) {
   KNJ_CUDA(cudaMemcpyAsync(words, c->status, sizeof(words), cudaMemcpyDeviceToHost, as_stream(s)));
   KNJ_CUDA(cudaStreamSynchronize(as_stream(s)));
   if (words[0] != 0 || words[1] != 0) {
-    set_error("knj_ep: a bounded wait gave up (rank barrier %d, GEMMs %d)", words[0], words[1]);
+    set_error("knj_ep: a bounded wait gave up (rank waits %d, GEMMs %d)", words[0], words[1]);
     return KNJ_E_TIMEOUT;
   }
   return KNJ_OK;
@@ -300,8 +413,13 @@ int knj_ep_status(knj_ep_ctx *c, knj_stream_t s) {
 void knj_ep_destroy(knj_ep_ctx *c) {
   if (!c) return;
   if (c->side) cudaStreamDestroy(c->side);
-  if (c->ev_fork) cudaEventDestroy(c->ev_fork);
-  if (c->ev_join) cudaEventDestroy(c->ev_join);
+  cudaEvent_t evs[3] = {c->ev_fork, c->ev_router, c->ev_side};
+  for (cudaEvent_t e : evs)
+    if (e) cudaEventDestroy(e);
+  for (int i = 0; i < KNJ_EP_MAX_CHUNKS; ++i) {
+    if (c->ev_down[i]) cudaEventDestroy(c->ev_down[i]);
+    if (c->ev_sent[i]) cudaEventDestroy(c->ev_sent[i]);
+  }
   if (c->block) cudaFree(c->block);
   delete c;
 }

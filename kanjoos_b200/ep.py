@@ -41,6 +41,7 @@ CPU ranks with a stand-in compute in the tests.
 from __future__ import annotations
 
 import ctypes as C
+import os
 
 import torch
 import torch.distributed as dist
@@ -233,38 +234,39 @@ class EpPeerContext:
     whose per-rank addresses are handed to the library once; a step is one knj_ep_forward_launch, which
     allocates nothing and calls no collective."""
 
-    def __init__(self, group, world, rank, T_loc, H, F, E, k, device):
+    def __init__(self, group, world, rank, T_loc, H, F, E, k, device, n_chunks=1):
         import torch.distributed._symmetric_memory as symm
+        from ._lib import EP_FLAG_WORDS
         g = group if group is not None else dist.group.WORLD
         T = T_loc * world
         self.x_all = symm.empty((T, H), dtype=torch.float16, device=device)
         self.pe_all = symm.empty((T * k,), dtype=torch.int32, device=device)
         self.pw_all = symm.empty((T * k,), dtype=torch.float32, device=device)
         self.parts = symm.empty((world, T_loc, H), dtype=torch.float32, device=device)
-        self.flags = symm.empty((64,), dtype=torch.int32, device=device)
+        self.flags = symm.empty((EP_FLAG_WORDS,), dtype=torch.int32, device=device)
         self.flags.zero_()
         bufs = (self.x_all, self.pe_all, self.pw_all, self.parts, self.flags)
         self._handles = [symm.rendezvous(t, g) for t in bufs]
         torch.cuda.synchronize(device)
         dist.barrier(group=group)  # every rank's flag words are zero before anyone's first step
-        self._bind(world, rank, T_loc, H, F, E, k, [[int(p) for p in h.buffer_ptrs] for h in self._handles])
+        self._bind(world, rank, T_loc, H, F, E, k, [[int(p) for p in h.buffer_ptrs] for h in self._handles], n_chunks)
 
-    def _bind(self, world, rank, T_loc, H, F, E, k, ptrs):
+    def _bind(self, world, rank, T_loc, H, F, E, k, ptrs, n_chunks=1):
         """ptrs: five lists (rows, expert ids, weights, partial sums, flags) of `world` device addresses."""
         from ._lib import EpDescC, check, lib
         self._tables = [C.cast((C.c_void_p * world)(*p), C.POINTER(C.c_void_p)) for p in ptrs]
-        d = EpDescC(world, rank, T_loc, H, F, E, k, 0, *self._tables)
+        d = EpDescC(world, rank, T_loc, H, F, E, k, n_chunks, *self._tables)
         self._ctx = C.c_void_p()
         check(lib().knj_ep_create(C.byref(d), C.byref(self._ctx)))
         self.shape = (T_loc, H)
 
     @classmethod
-    def from_pointers(cls, world, rank, T_loc, H, F, E, k, ptrs, keep=None):
+    def from_pointers(cls, world, rank, T_loc, H, F, E, k, ptrs, keep=None, n_chunks=1):
         """A layer object over exchange buffers the caller mapped itself (any peer mapping; the tests emulate two
         ranks inside one process this way). `keep` holds whatever owns the memory."""
         self = cls.__new__(cls)
         self._keep = keep
-        self._bind(world, rank, T_loc, H, F, E, k, ptrs)
+        self._bind(world, rank, T_loc, H, F, E, k, ptrs, n_chunks)
         return self
 
     def forward(self, x, router, bias, bank, residual, out_dtype):
@@ -318,12 +320,23 @@ def peer_buffers(group, world, rank, T_loc, H, k, row_dtype, device) -> PeerBuff
 _EP_CONTEXTS = {}
 
 
-def ep_context(group, world, rank, T_loc, H, F, E, k, device) -> EpPeerContext:
+def ep_chunks(T_loc: int, k: int, world: int, e_loc: int) -> int:
+    """Chunks of a step: as many (up to four) as leave every local expert 256 rows per chunk on average."""
+    n = 1
+    while (n < 4 and T_loc % (2 * n) == 0 and ((T_loc // (2 * n)) * k) % 4 == 0
+           and (T_loc // (2 * n)) * world * k >= 256 * e_loc * world):
+        n *= 2
+    return n
+
+
+def ep_context(group, world, rank, T_loc, H, F, E, k, device, n_chunks=None) -> EpPeerContext:
     """One layer object per (group, shape), shared by the layers of a stack (the weights are per-call arguments):
     creation is a collective, so every rank asks in the same order."""
-    key = (id(group), world, T_loc, H, F, E, k, str(device))
+    if n_chunks is None:
+        n_chunks = int(os.environ.get("KNJ_EP_CHUNKS", "0")) or ep_chunks(T_loc, k, world, E // world)
+    key = (id(group), world, T_loc, H, F, E, k, str(device), n_chunks)
     if key not in _EP_CONTEXTS:
-        _EP_CONTEXTS[key] = EpPeerContext(group, world, rank, T_loc, H, F, E, k, device)
+        _EP_CONTEXTS[key] = EpPeerContext(group, world, rank, T_loc, H, F, E, k, device, n_chunks)
     return _EP_CONTEXTS[key]
 
 

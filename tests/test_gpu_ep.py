@@ -116,11 +116,21 @@ def test_two_ranks_peer_exchange_fp16_rows_repeated(tmp_path):
     assert st["rel_rmse"] <= TOL_TC
 
 
-def _emulated_ranks(world, T, cfg=403):
+FLAG_WORDS, BARRIER_SLOT, FAR = 4096, 4096 - 64, 1 << 20
+
+
+def _preset_flags(flags, r, world):
+    """Every word far ahead of any epoch the test reaches, except the words this rank writes itself."""
+    flags.fill_(FAR)
+    flags[r:BARRIER_SLOT:world] = 0
+    flags[BARRIER_SLOT + r] = 0
+
+
+def _emulated_ranks(world, T, cfg=403, n_chunks=1):
     """`world` layer objects inside one process on one GPU: every rank's exchange buffers are ordinary device
-    tensors, so a "peer" store is a local store. Each rank's own flag words are preset far ahead of the epochs the
-    test reaches and its arrivals at the other ranks go to a sink, so no barrier ever waits: the ranks' steps run
-    one after another on one stream instead."""
+    tensors, so a "peer" store is a local store. In each rank's flag words the peers' arrivals are preset far ahead
+    of the epochs the test reaches and the rank's arrivals at the other ranks go to a sink, so no wait depends on
+    another rank's launches (only on the rank's own copy stream): the ranks' steps run one after another."""
     from kanjoos_b200 import ep
     from kanjoos_b200.moe import ExpertBank
     bank, wr, hx = problem(cfg, T)
@@ -130,29 +140,31 @@ def _emulated_ranks(world, T, cfg=403):
     bufs = [dict(x=torch.zeros((T, H), dtype=torch.float16, device=dev), pe=torch.zeros(T * K, dtype=torch.int32, device=dev),
                  pw=torch.zeros(T * K, dtype=torch.float32, device=dev),
                  parts=torch.zeros((world, t_loc, H), dtype=torch.float32, device=dev),
-                 flags=torch.full((64,), 1 << 20, dtype=torch.int32, device=dev)) for _ in range(world)]
-    sink = torch.zeros(64, dtype=torch.int32, device=dev)  # where a rank's arrivals at its "peers" go
+                 flags=torch.zeros((FLAG_WORDS,), dtype=torch.int32, device=dev)) for _ in range(world)]
+    for r, b in enumerate(bufs):
+        _preset_flags(b["flags"], r, world)
+    sink = torch.zeros(FLAG_WORDS, dtype=torch.int32, device=dev)  # where a rank's arrivals at its "peers" go
     ranks = []
     for r in range(world):
         ptrs = [[b[name].data_ptr() for b in bufs] for name in ("x", "pe", "pw", "parts")]
         ptrs.append([bufs[j]["flags"].data_ptr() if j == r else sink.data_ptr() for j in range(world)])
         local = {k: np.ascontiguousarray(v[r * e_loc:(r + 1) * e_loc]) for k, v in bank.items()}
         bk = ExpertBank.from_numpy(local, wr)
-        ctx = ep.EpPeerContext.from_pointers(world, r, t_loc, H, F, E, K, ptrs, keep=(bufs, sink))
+        ctx = ep.EpPeerContext.from_pointers(world, r, t_loc, H, F, E, K, ptrs, keep=(bufs, sink), n_chunks=n_chunks)
         x = torch.from_numpy(hx[r * t_loc:(r + 1) * t_loc].copy()).cuda().to(torch.bfloat16)
         ranks.append((ctx, bk, x))
     return bank, wr, hx, ranks, bufs
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_layer_object_two_emulated_ranks_one_gpu(world):
+@pytest.mark.parametrize("world,n_chunks", [(2, 1), (4, 1), (2, 2), (2, 4), (4, 2)])
+def test_layer_object_emulated_ranks_one_gpu(world, n_chunks):
     """The whole data path of knj_ep_forward_launch (row and table stores into every rank's buffers, plan over
     the rank's experts, grouped GEMMs, partial sums into the owners' buffers, rank-ordered sum) with the ranks
     stepped in turn; a rank's result is complete once every rank has stepped after it published its rows, so the
     second round's outputs are the layer's."""
     from gpu_util import report
     T = 320
-    bank, wr, hx, ranks, _ = _emulated_ranks(world, T)
+    bank, wr, hx, ranks, _ = _emulated_ranks(world, T, n_chunks=n_chunks)
     want, _, _ = ol.moe(wr, bank, hx, K)
     outs = [None] * world
     for _ in range(2):
@@ -162,7 +174,7 @@ def test_layer_object_two_emulated_ranks_one_gpu(world):
     for ctx, _, _ in ranks:
         ctx.status()
     got = np.concatenate([o.cpu().numpy() for o in outs])
-    st = report(got, want, f"layer object, {world} emulated ranks on one GPU, T={T}")
+    st = report(got, want, f"layer object, {world} emulated ranks on one GPU, T={T}, {n_chunks} chunks")
     assert st["unwritten"] == 0 and st["rel_rmse"] <= TOL_TC
     for ctx, _, _ in ranks:
         ctx.close()
@@ -182,7 +194,7 @@ def test_layer_object_barrier_gives_up_and_recovers():
     with pytest.raises(KnjError) as ei:
         ctx.status()
     assert ei.value.code == -5
-    bufs[0]["flags"][1] = 1 << 20  # the peer's arrival, far ahead of this rank's epoch
+    _preset_flags(bufs[0]["flags"], 0, 2)  # the peer's arrivals, far ahead of this rank's epochs
     ctx.set_wait(0)
     bk, x = ranks[0][1], ranks[0][2]
     ctx.forward(x, bk.router, None, bk, False, torch.float32)  # resets the status words, two barriers
