@@ -559,7 +559,7 @@ int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, 
  * gathered buffers are chunk-major: rows [n_chunks][world][chunk tokens][hidden],
  * likewise the tables and the partial sums) over the caller's stream and a copy
  * stream of the context:
- *   copy stream : per chunk the rank's rows (fp16) and routing tables are STORED
+ *   copy streams: per chunk the rank's rows (fp16) and routing tables are written
  *                 into every rank's buffers, then an arrival word into every rank's
  *                 flags; later the chunk's weighted partial sums go to the token
  *                 owners the same way
@@ -576,6 +576,9 @@ int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, 
  * hidden, ffn multiples of 256; (n_tokens_local / n_chunks) * top_k a multiple of
  * 4; experts split contiguously, n_experts / world <= 256; n_chunks 0 or 1 = one.
  * ------------------------------------------------------------------------- */
+#define KNJ_EP_COPY_ENGINES 0 /* rows and partial sums travel as block copies (one cudaMemcpyAsync per peer) */
+#define KNJ_EP_SM_ROWS 1      /* the rows travel as 16-byte stores of this library's kernels */
+#define KNJ_EP_SM_PARTIALS 2  /* the partial sums travel as 16-byte stores of the kernel that forms them */
 #define KNJ_EP_FLAG_WORDS 4096
 #define KNJ_EP_MAX_CHUNKS 8
 typedef struct knj_ep_desc {
@@ -596,6 +599,12 @@ int knj_ep_forward_launch(knj_ep_ctx *ctx, const void *x, int x_dtype, int64_t l
                           int residual, void *out, int out_dtype, knj_stream_t s);
 /* a barrier over the ranks on the stream (arrival + bounded wait in one launch, on flag words of its own) */
 int knj_ep_barrier_launch(knj_ep_ctx *ctx, knj_stream_t s);
+/* How rows and partial sums reach the peers: an OR of KNJ_EP_SM_ROWS and KNJ_EP_SM_PARTIALS, 0 = block copies for
+ * both (the routing tables and the flag words always go as stores of the library's kernels). With block copies the
+ * SMs stay with the GEMMs while a chunk travels; partial sums then travel as dense blocks per owner, rows of tokens
+ * without an expert on the sender included (never read). Default KNJ_EP_SM_PARTIALS: block copies for the rows, the
+ * partial sums stored by the kernel that forms them (only contributing rows travel). Every rank must use the same. */
+int knj_ep_set_transport(knj_ep_ctx *ctx, int transport);
 /* limit of every rank wait in SM clock cycles (<= 0 restores the default, about a second) */
 int knj_ep_set_wait(knj_ep_ctx *ctx, long long wait_cycles);
 /* synchronises the stream; KNJ_E_TIMEOUT if a barrier or a GEMM pipeline wait gave up since the last step began */

@@ -153,6 +153,7 @@ SIGNATURES = {
     "knj_ep_forward_launch": (_i, [_vp, _vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _vp]),
     "knj_ep_barrier_launch": (_i, [_vp, _vp]),
     "knj_ep_set_wait": (_i, [_vp, C.c_longlong]),
+    "knj_ep_set_transport": (_i, [_vp, _i]),
     "knj_ep_status": (_i, [_vp, _vp]),
     "knj_ep_destroy": (None, [_vp]),
     "knj_moe_combine_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i64, _vp, _i, _i64, _i, _i, _i, _vp]),

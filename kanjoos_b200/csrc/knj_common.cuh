@@ -39,9 +39,10 @@ inline int launch_status(const char *what) {
 inline cudaStream_t as_stream(knj_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 int sm_count();  // SMs of the current device (cached per device)
-// knj_ep_combine_partial_peer_launch with every owner's array entered at element `parts_off`
+// knj_ep_combine_partial_peer_launch with every owner's array entered at element `parts_off`; with `stage` (f32
+// [T][H], local) the rows of other ranks' tokens are written there instead, one dense block per owner
 int ep_combine_partial_peer_at(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k, int exp_lo, int exp_hi,
-                               float *const *parts_ptrs, int64_t parts_off, int my_rank, int T_loc, cudaStream_t s);
+                               float *const *parts_ptrs, int64_t parts_off, float *stage, int my_rank, int T_loc, cudaStream_t s);
 
 // Launch of a kernel that belongs to a chain of dependent launches on one stream (the decode layer). With
 // overlap on, the launch carries the programmatic-stream-serialization attribute: the grid may be scheduled

@@ -193,11 +193,15 @@ __global__ void __launch_bounds__(256) ep_combine_partial_peer_kernel(const floa
                                                                       const float *__restrict__ pair_w, int exp_lo,
                                                                       int exp_hi, float *const *__restrict__ parts,
                                                                       int my_rank, int T_loc, int T, int H, int k,
-                                                                      int64_t parts_off) {
+                                                                      int64_t parts_off, float *__restrict__ stage) {
   // one warp per token: lanes 0..k-1 hold the token's slots, the local ones are ranked by expert id
+  // The grid walks the tokens starting with those of the next higher rank: at any moment every rank is sending
+  // to a different owner instead of all ranks to the same one.
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  int t = blockIdx.x * 8 + (threadIdx.x >> 5);
   if (t >= T) return;
+  t += ((my_rank + 1) * T_loc) % T;
+  if (t >= T) t -= T;
   const int e = lane < k ? pair_exp[t * k + lane] : -1;
   const float w = lane < k ? pair_w[t * k + lane] : 0.f;
   const bool mine = lane < k && e >= exp_lo && e < exp_hi;
@@ -218,7 +222,9 @@ __global__ void __launch_bounds__(256) ep_combine_partial_peer_kernel(const floa
     row[sl] = t * k + src;
     ws[sl] = __shfl_sync(0xffffffffu, w, src);
   }
-  float *out = parts[t / T_loc] + parts_off + ((size_t)my_rank * T_loc + (t % T_loc)) * H;
+  const int owner = t / T_loc;
+  float *out = (stage && owner != my_rank) ? stage + (size_t)t * H  // staged by owner for a later block copy
+                                           : parts[owner] + parts_off + ((size_t)my_rank * T_loc + (t % T_loc)) * H;
   for (int h = lane * 4; h < H; h += 128) {
     float4 y[8];
 #pragma unroll
@@ -285,14 +291,16 @@ int knj_ep_peer_gather_launch(const void *const *src_ptrs, int n_ranks, int64_t 
 
 }  // extern "C"
 
-// the same with every owner's array entered at element `parts_off` (one chunk of a chunked step)
+// the same with every owner's array entered at element `parts_off` (one chunk of a chunked step); with `stage`
+// (f32 [T][H], local) the rows of other ranks' tokens go there, in token order = one dense block per owner
 int knj::ep_combine_partial_peer_at(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k, int exp_lo,
-                                    int exp_hi, float *const *parts_ptrs, int64_t parts_off, int my_rank, int T_loc, cudaStream_t s) {
+                                    int exp_hi, float *const *parts_ptrs, int64_t parts_off, float *stage, int my_rank, int T_loc,
+                                    cudaStream_t s) {
   KNJ_REQUIRE(Y && pair_exp && pair_w && parts_ptrs, "knj_ep_combine_partial_peer: null pointer");
   KNJ_REQUIRE(k >= 1 && k <= 8 && H > 0 && H % 4 == 0 && exp_lo <= exp_hi && T_loc >= 1 && my_rank >= 0 && parts_off % 4 == 0,
               "knj_ep_combine_partial_peer: bad k / H / expert range / rank");
   if (T <= 0) return KNJ_OK;
-  ep_combine_partial_peer_kernel<<<(T + 7) / 8, 256, 0, s>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, T, H, k, parts_off);
+  ep_combine_partial_peer_kernel<<<(T + 7) / 8, 256, 0, s>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, T, H, k, parts_off, stage);
   return launch_status("ep_combine_partial_peer_kernel");
 }
 
@@ -301,7 +309,7 @@ extern "C" {
 int knj_ep_combine_partial_peer_launch(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k,
                                        int exp_lo, int exp_hi, float *const *parts_ptrs, int my_rank, int T_loc,
                                        knj_stream_t s) {
-  return knj::ep_combine_partial_peer_at(Y, pair_exp, pair_w, T, H, k, exp_lo, exp_hi, parts_ptrs, 0, my_rank, T_loc, as_stream(s));
+  return knj::ep_combine_partial_peer_at(Y, pair_exp, pair_w, T, H, k, exp_lo, exp_hi, parts_ptrs, 0, nullptr, my_rank, T_loc, as_stream(s));
 }
 
 int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, const int32_t *pair_exp, int k,

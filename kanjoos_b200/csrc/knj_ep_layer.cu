@@ -27,6 +27,8 @@
 #include "knj_q4k.h"
 #include "knj_q4k_engine.cuh"
 
+#include <vector>
+
 using namespace knj;
 
 namespace {
@@ -158,8 +160,12 @@ struct knj_ep_ctx {
   int *status = nullptr;  // [0] rank waits, [1] GEMMs
   long long wait_cycles = kMaxWaitCycles;
   uint32_t step = 0;      // steps launched so far: the epoch the flag words of a step carry
-  cudaStream_t side = nullptr;
-  cudaEvent_t ev_fork = nullptr, ev_router = nullptr, ev_side = nullptr;
+  int transport = KNJ_EP_SM_PARTIALS;
+  std::vector<__half *> h_xall;  // host copies of two pointer tables, for the block copies
+  std::vector<float *> h_parts;
+  float *stage[2] = {nullptr, nullptr};  // partial rows of other ranks' tokens before their block copies, by chunk parity
+  cudaStream_t side = nullptr, side2 = nullptr;
+  cudaEvent_t ev_fork = nullptr, ev_router = nullptr, ev_side = nullptr, ev_a = nullptr, ev_b = nullptr;
   cudaEvent_t ev_down[KNJ_EP_MAX_CHUNKS] = {}, ev_sent[KNJ_EP_MAX_CHUNKS] = {};
 #ifdef KNJ_TRACE
   cudaEvent_t stamp[12] = {};
@@ -222,12 +228,15 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
   const size_t o_ah = take(Pc * F * 2);
   const size_t o_y0 = take(Pc * H * 4);
   const size_t o_y1 = C > 1 ? take(Pc * H * 4) : o_y0;
+  const size_t o_st0 = take(Tc * H * 4);
+  const size_t o_st1 = C > 1 ? take(Tc * H * 4) : o_st0;
   const size_t o_words = take(64);
   cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->block), off);
   if (e == cudaSuccess) e = cudaMemset(c->block + o_words, 0, 64);
   if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking);
-  cudaEvent_t *evs[3] = {&c->ev_fork, &c->ev_router, &c->ev_side};
-  for (int i = 0; i < 3 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(evs[i], cudaEventDisableTiming);
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&c->side2, cudaStreamNonBlocking);
+  cudaEvent_t *evs[5] = {&c->ev_fork, &c->ev_router, &c->ev_side, &c->ev_a, &c->ev_b};
+  for (int i = 0; i < 5 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(evs[i], cudaEventDisableTiming);
   for (int i = 0; i < C && e == cudaSuccess; ++i) {
     e = cudaEventCreateWithFlags(&c->ev_down[i], cudaEventDisableTiming);
     if (e == cudaSuccess) e = cudaEventCreateWithFlags(&c->ev_sent[i], cudaEventDisableTiming);
@@ -264,6 +273,12 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
   c->ah = c->block + o_ah;
   c->Y[0] = reinterpret_cast<float *>(c->block + o_y0);
   c->Y[1] = reinterpret_cast<float *>(c->block + o_y1);
+  c->stage[0] = reinterpret_cast<float *>(c->block + o_st0);
+  c->stage[1] = reinterpret_cast<float *>(c->block + o_st1);
+  for (int r = 0; r < d.world; ++r) {
+    c->h_xall.push_back(static_cast<__half *>(d.xall_ptrs[r]));
+    c->h_parts.push_back(d.parts_ptrs[r]);
+  }
   c->epoch = reinterpret_cast<uint32_t *>(c->block + o_words);
   c->status = reinterpret_cast<int *>(c->block + o_words + 16);
   *out = c;
@@ -273,6 +288,12 @@ int knj_ep_create(const knj_ep_desc *desc, knj_ep_ctx **out) {
 int knj_ep_set_wait(knj_ep_ctx *c, long long wait_cycles) {
   KNJ_REQUIRE(c, "knj_ep_set_wait: null context");
   c->wait_cycles = wait_cycles > 0 ? wait_cycles : kMaxWaitCycles;
+  return KNJ_OK;
+}
+
+int knj_ep_set_transport(knj_ep_ctx *c, int transport) {
+  KNJ_REQUIRE(c && transport >= 0 && transport <= (KNJ_EP_SM_ROWS | KNJ_EP_SM_PARTIALS), "knj_ep_set_transport: unknown transport");
+  c->transport = transport;
   return KNJ_OK;
 }
 
@@ -298,24 +319,50 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
   int rc;
   KNJ_EP_STAMP(0);
   KNJ_CUDA(cudaMemsetAsync(c->status, 0, 2 * sizeof(int), st));
+  // ---- main stream: the first chunk's rows as fp16 (ahead of the router, so that their copies run beside it), then
+  //      the router over all local tokens (tables in local order)
+  const bool ce = !(c->transport & KNJ_EP_SM_ROWS), ce_parts = !(c->transport & KNJ_EP_SM_PARTIALS);
+  if (ce) {
+    rc = knj_to_f16_launch(x, x_dtype, ldx, Tc_loc, H, c->x_all + (int64_t)rank * Tc_loc * H, s);
+    if (rc) return rc;
+  }
   KNJ_CUDA(cudaEventRecord(c->ev_fork, st));
   KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_fork, 0));
-  // ---- main stream: the router over all local tokens (tables in local order)
+  KNJ_CUDA(cudaStreamWaitEvent(c->side2, c->ev_fork, 0));
   rc = knj_router_topk_launch(x, x_dtype, ldx, w_router, router_bias, T_loc, H, d.n_experts, k, c->logits, c->pe_loc, c->pw_loc, s);
   if (rc) return rc;
   KNJ_CUDA(cudaEventRecord(c->ev_router, st));
   KNJ_EP_STAMP(1);
-  // ---- copy stream: chunk by chunk the rows to every rank, the tables once, an arrival per chunk
+  // ---- copy streams: chunk by chunk the rows to every rank, the tables once, an arrival per chunk
+  cudaStream_t side2 = c->side2;
+  // block copies go to the nearest higher rank first (at any moment a rank receives from one sender), alternating
+  // over the two copy streams so that one copy's start-up hides behind the other's transfer; joined on `side`
   for (int ch = 0; ch < C; ++ch) {
-    const int64_t n8 = (int64_t)Tc_loc * H / 8, blocks = (n8 + 255) / 256, cap = (int64_t)sm_count() * 4;
-    const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
     const int64_t off = ((int64_t)ch * Tc + (int64_t)rank * Tc_loc) * H;
     const void *xc = static_cast<const char *>(x) + (size_t)ch * Tc_loc * ldx * x_el;
-    if (x_dtype == KNJ_DT_F32) ep_push_rows_kernel<KNJ_DT_F32><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
-    else if (x_dtype == KNJ_DT_BF16) ep_push_rows_kernel<KNJ_DT_BF16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
-    else ep_push_rows_kernel<KNJ_DT_F16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
-    rc = launch_status("ep_push_rows_kernel");
-    if (rc) return rc;
+    if (ce) {
+      if (ch > 0) {
+        rc = knj_to_f16_launch(xc, x_dtype, ldx, Tc_loc, H, c->x_all + off, side);
+        if (rc) return rc;
+      }
+    } else {
+      const int64_t n8 = (int64_t)Tc_loc * H / 8, blocks = (n8 + 255) / 256, cap = (int64_t)sm_count() * 4;
+      const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
+      if (x_dtype == KNJ_DT_F32) ep_push_rows_kernel<KNJ_DT_F32><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
+      else if (x_dtype == KNJ_DT_BF16) ep_push_rows_kernel<KNJ_DT_BF16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
+      else ep_push_rows_kernel<KNJ_DT_F16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
+      rc = launch_status("ep_push_rows_kernel");
+      if (rc) return rc;
+    }
+    if (ce && W > 1) {  // the block copies start before the tables below wait for the router
+      KNJ_CUDA(cudaEventRecord(c->ev_a, side));
+      KNJ_CUDA(cudaStreamWaitEvent(side2, c->ev_a, 0));
+      for (int i = 1; i < W; ++i) {
+        const int dr = (rank + i) % W;
+        KNJ_CUDA(cudaMemcpyAsync(c->h_xall[dr] + off, c->x_all + off, (size_t)Tc_loc * H * 2, cudaMemcpyDeviceToDevice, (i & 1) ? side2 : side));
+      }
+      KNJ_CUDA(cudaEventRecord(c->ev_b, side2));
+    }
     if (ch == 0) {
       KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_router, 0));
       const int64_t n4 = (int64_t)T_loc * k / 4, n4c = (int64_t)Tc_loc * k / 4;
@@ -324,6 +371,7 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
       rc = launch_status("ep_push_tables_kernel");
       if (rc) return rc;
     }
+    if (ce && W > 1) KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_b, 0));
     ep_arrive_kernel<<<1, 64, 0, side>>>(c->flag_ptrs, ch * W, W, rank, epoch);
     rc = launch_status("ep_arrive_kernel");
     if (rc) return rc;
@@ -360,16 +408,33 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
                                   Pc, c->status + 1, s);
     if (rc) return rc;
     if (ch == 0) KNJ_EP_STAMP(5);
-    if (ch >= 2) KNJ_CUDA(cudaStreamWaitEvent(st, c->ev_sent[ch - 2], 0));  // the rows of Y[ch & 1] have left
+    if (ch >= 2) KNJ_CUDA(cudaStreamWaitEvent(st, c->ev_sent[ch - 2], 0));  // the rows of Y[ch & 1] / stage[ch & 1] have left
     rc = knj_q4k_down_tc_launch(c->ah, w_down, c->pair_idx, c->pair_cnt, nullptr, Y, H, F, F / 256 * KNJ_Q4K_BYTES, Tc, c->e_loc, Pc,
                                 c->status + 1, s);
     if (rc) return rc;
     if (ch == 0) KNJ_EP_STAMP(6);
-    KNJ_CUDA(cudaEventRecord(c->ev_down[ch], st));
-    // copy stream: weighted partial sums of the chunk to the token owners, then the arrival
-    KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_down[ch], 0));
-    rc = ep_combine_partial_peer_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, rank, Tc_loc, side);
-    if (rc) return rc;
+    // weighted partial sums of the chunk to the token owners, then the arrival
+    if (ce_parts) {
+      // the sums on this stream: own tokens' rows into the own array, the others' staged by owner; block copies follow
+      float *stg = c->stage[ch & 1];
+      rc = ep_combine_partial_peer_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, stg, rank, Tc_loc, st);
+      if (rc) return rc;
+      KNJ_CUDA(cudaEventRecord(c->ev_down[ch], st));
+      KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_down[ch], 0));
+      KNJ_CUDA(cudaStreamWaitEvent(side2, c->ev_down[ch], 0));
+      for (int i = 1; i < W; ++i) {
+        const int dr = (rank + i) % W;
+        KNJ_CUDA(cudaMemcpyAsync(c->h_parts[dr] + ((size_t)ch * Tc + (size_t)rank * Tc_loc) * H, stg + (size_t)dr * Tc_loc * H,
+                                 (size_t)Tc_loc * H * 4, cudaMemcpyDeviceToDevice, (i & 1) ? side2 : side));
+      }
+      KNJ_CUDA(cudaEventRecord(c->ev_b, side2));
+      KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_b, 0));
+    } else {
+      KNJ_CUDA(cudaEventRecord(c->ev_down[ch], st));
+      KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_down[ch], 0));
+      rc = ep_combine_partial_peer_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, nullptr, rank, Tc_loc, side);
+      if (rc) return rc;
+    }
     KNJ_CUDA(cudaEventRecord(c->ev_sent[ch], side));
     ep_arrive_kernel<<<1, 64, 0, side>>>(c->flag_ptrs, (C + ch) * W, W, rank, epoch);
     rc = launch_status("ep_arrive_kernel");
@@ -413,7 +478,8 @@ int knj_ep_status(knj_ep_ctx *c, knj_stream_t s) {
 void knj_ep_destroy(knj_ep_ctx *c) {
   if (!c) return;
   if (c->side) cudaStreamDestroy(c->side);
-  cudaEvent_t evs[3] = {c->ev_fork, c->ev_router, c->ev_side};
+  if (c->side2) cudaStreamDestroy(c->side2);
+  cudaEvent_t evs[5] = {c->ev_fork, c->ev_router, c->ev_side, c->ev_a, c->ev_b};
   for (cudaEvent_t e : evs)
     if (e) cudaEventDestroy(e);
   for (int i = 0; i < KNJ_EP_MAX_CHUNKS; ++i) {

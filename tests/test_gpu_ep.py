@@ -156,8 +156,9 @@ def _emulated_ranks(world, T, cfg=403, n_chunks=1):
     return bank, wr, hx, ranks, bufs
 
 
+@pytest.mark.parametrize("sm_stores", [(False, False), (False, True), (True, True)], ids=["copies", "default", "stores"])
 @pytest.mark.parametrize("world,n_chunks", [(2, 1), (4, 1), (2, 2), (2, 4), (4, 2)])
-def test_layer_object_emulated_ranks_one_gpu(world, n_chunks):
+def test_layer_object_emulated_ranks_one_gpu(world, n_chunks, sm_stores):
     """The whole data path of knj_ep_forward_launch (row and table stores into every rank's buffers, plan over
     the rank's experts, grouped GEMMs, partial sums into the owners' buffers, rank-ordered sum) with the ranks
     stepped in turn; a rank's result is complete once every rank has stepped after it published its rows, so the
@@ -166,6 +167,8 @@ def test_layer_object_emulated_ranks_one_gpu(world, n_chunks):
     T = 320
     bank, wr, hx, ranks, _ = _emulated_ranks(world, T, n_chunks=n_chunks)
     want, _, _ = ol.moe(wr, bank, hx, K)
+    for ctx, _, _ in ranks:
+        ctx.set_transport(*sm_stores)
     outs = [None] * world
     for _ in range(2):
         for r, (ctx, bk, x) in enumerate(ranks):
