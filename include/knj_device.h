@@ -236,12 +236,6 @@ int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t
                          int32_t *pair_exp, float *pair_w, int32_t *pair_idx, int idx_stride, int32_t *pair_cnt,
                          int32_t *exp_list, int32_t *n_active, float *xn, uint32_t *counter, knj_stream_t s);
 
-/* Measurement hook (no reference counterpart): a device buffer of 16 uint64 that
- * receives global-timer stamps (ns) of the front kernel's phases -- start,
- * logits done, vectors prepared, group complete, top-k done, all groups
- * complete, tables done -- written by the CTA that finishes last. NULL = off. */
-void knj_moe_front_trace(void *dev_buf);
-
 /* Second half of the permutation step alone: exp_list / n_active from pair_cnt. */
 int knj_active_list_launch(const int32_t *pair_cnt, int E, int32_t *exp_list, int32_t *n_active, knj_stream_t s);
 
@@ -332,25 +326,16 @@ int knj_q4k_matmul_noalloc_launch(const uint8_t *W, int n_in, int n_out, const v
  * saturated to the fp16 range: the token operand of the grouped GEMMs. */
 int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s);
 
-/* Measurement hook (no reference counterpart): a device buffer of
- * 256 + 4 * cta_slots uint64. SM-clock stamps of CTA 0 of the grouped GEMMs:
- * [4k..4k+3], k < 12: unpacker starts K-slab k, stage free, stage published,
- * MMA thread sees the slab; [48..61] epilogue phases; [64+4k..64+4k+3]: loader
- * reaches slab k, stage free, rows stored, published. From [256] on, 4 uint64
- * per CTA b < cta_slots: global-timer ns at start, accumulator complete, end,
- * and (SM id << 32 | tokens of the CTA's bucket). NULL = off. */
-void knj_tc_trace(void *dev_buf, int cta_slots);
-
-/* Experiment hook (no reference counterpart): 1 = run every tile of the grouped
- * GEMMs on a single SM (tcgen05 cta_group::1) even where CTA pairs apply;
- * 0 = automatic (pairs whenever a bucket has an even number of row tiles). */
-void knj_tc_tuning(int force_single_sm);
+/* 1 = run every bucket of the grouped GEMMs in the single-SM form (tcgen05
+ * cta_group::1), the form buckets with an odd number of row tiles always take;
+ * 0 (default) = CTA pairs wherever the tile count is even. Process-wide. */
+void knj_q4k_tc_single_sm(int on);
 
 /* Launch mode of the kernels of a decode layer (no reference counterpart).
  * 1 (default): programmatic stream serialization -- each grid may be scheduled
  * while its predecessor on the stream drains and waits on the device for the
  * predecessor's completion before reading its results; 0: plain launches. */
-void knj_chain_overlap(int on);
+void knj_launch_overlap(int on);
 
 /* Grouped gate+up GEMM over per-expert token buckets on the tensor cores
  * (tools/bench/q4k_moe_ffn.hip:164-241 knj_q4k_gateup fused with

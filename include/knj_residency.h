@@ -3,8 +3,9 @@
  * SlotAllocator :144-172, TransferEngine :174-203, HostArena :205-215). The state
  * machine itself is host code that needs no change; what it lacked on this
  * hardware were implementations of the gates. Names, arguments and meanings of
- * the virtual functions are the reference's, so its ResidencyManager can be
- * constructed over these objects unchanged.
+ * the virtual functions are the reference's, so its ResidencyManager is
+ * constructed over these objects unchanged (oracle/ref_residency_check.cpp does
+ * exactly that with the reference's residency.cpp).
  *
  * All experts fit in HBM on a B200, so none of this is on the timed path; it
  * exists so that the "experts streamed through a few slots" mode produces the
@@ -19,6 +20,16 @@
 #include <memory>
 
 namespace knj {
+
+/* The reference's own header (src/residency/residency.h, include guard KNJ_RESIDENCY_H) declares the same three
+ * abstract classes and their enums under the same names. A translation unit that constructs the reference's
+ * ResidencyManager over these back ends includes the reference header FIRST (or defines
+ * KNJ_HAVE_REFERENCE_RESIDENCY, which makes this header include it by its project-relative path); the
+ * declarations below are then skipped and the factories return implementations of the reference's classes. */
+#if defined(KNJ_HAVE_REFERENCE_RESIDENCY) && !defined(KNJ_RESIDENCY_H)
+#include "src/residency/residency.h"
+#endif
+#ifndef KNJ_RESIDENCY_H
 
 using SlotHandle = int32_t;
 constexpr SlotHandle kNoSlot = -1;
@@ -65,16 +76,24 @@ class HostArena {
   virtual void free(void *p) = 0;
 };
 
-/* The CUDA slot pool additionally learns which transfers fill a slot. */
+#endif /* !KNJ_RESIDENCY_H: the interface declarations */
+
+/* The CUDA slot pool additionally learns which transfers read or fill a slot: a slot's load event has fired, and
+ * a released slot is reusable, only when all of them have finished. Not synchronised: one host thread drives a
+ * pool (the thread that drives the state machine); the engine's worker thread never touches it. */
 class CudaSlotAllocator : public SlotAllocator {
  public:
   virtual void watch(SlotHandle slot, const TransferEngine *engine, TransferId id) = 0;
+  /* the held or retiring slot that contains device address p, else kNoSlot */
+  virtual SlotHandle slot_of(const void *p) const = 0;
 };
 
 std::unique_ptr<HostArena> make_cuda_host_arena();
 std::unique_ptr<CudaSlotAllocator> make_cuda_slot_allocator(int n_slots, uint64_t slot_bytes);
-/* backing_path may be null: then the NVMe calls return kNoTransfer. */
-std::unique_ptr<TransferEngine> make_cuda_transfer_engine(const char *backing_path);
+/* backing_path may be null: then the NVMe calls return kNoTransfer. With `slots`, every device copy whose device
+ * side lies in one of the pool's slots registers itself there (watch), which is the bookkeeping the state machine
+ * expects from the pool; the pool must outlive the engine's last submit. */
+std::unique_ptr<TransferEngine> make_cuda_transfer_engine(const char *backing_path, CudaSlotAllocator *slots = nullptr);
 
 }  // namespace knj
 

@@ -103,7 +103,6 @@ SIGNATURES = {
     "knj_moe_permute_ws_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "knj_moe_front_launch": (_i, [_vp, _i, _i64, _vp, _f, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp,
                                   _vp, _vp, _vp, _vp]),
-    "knj_moe_front_trace": (None, [_vp]),
     "knj_active_list_launch": (_i, [_vp, _i, _vp, _vp, _vp]),
     "knj_moe_stack_create": (_i, [_vp, _i, C.POINTER(_vp)]),
     "knj_moe_stack_decode_launch": (_i, [_vp, _vp]),
@@ -161,9 +160,8 @@ SIGNATURES = {
                                    _i, _i, _vp, _vp]),
     "knj_q4k_proj_launch": (_i, [_vp, _i, _i64, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _vp, _vp]),
     "knj_decode_wait_limit": (None, [C.c_longlong]),
-    "knj_tc_trace": (None, [_vp, _i]),
-    "knj_tc_tuning": (None, [_i]),
-    "knj_chain_overlap": (None, [_i]),
+    "knj_q4k_tc_single_sm": (None, [_i]),
+    "knj_launch_overlap": (None, [_i]),
     "knj_to_f16_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp]),
     "knj_q4k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),

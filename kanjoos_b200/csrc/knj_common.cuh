@@ -47,7 +47,7 @@ int ep_combine_partial_peer_at(const float *Y, const int32_t *pair_exp, const fl
 // Launch of a kernel that belongs to a chain of dependent launches on one stream (the decode layer). With
 // overlap on, the launch carries the programmatic-stream-serialization attribute: the grid may be scheduled
 // while its predecessor drains, and it must call grid_dep_wait() before it touches anything the predecessor
-// wrote. Off (knj_chain_overlap(0)): a plain launch; grid_dep_wait() is then a no-op.
+// wrote. Off (knj_launch_overlap(0)): a plain launch; grid_dep_wait() is then a no-op.
 extern int g_chain_overlap;
 template <class... KArgs, class... Args>
 inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {

@@ -2,23 +2,33 @@
 // tensor cores: Q4_K weights are unpacked to fp16 in shared memory and consumed
 // by tcgen05.mma with f32 accumulators in tensor memory.
 //
-// Roles (swap-AB): the MMA "M" side is 128 weight rows of one expert, the "N"
-// side is a bucket of up to 256 routed tokens, K runs over the hidden (or ffn)
-// dimension in slabs of 64. Per CTA one (expert, 128-row tile, token bucket):
-//   warps 0..7  unpackers: per-row bulk async copies bring the raw 144-byte
-//               superblocks into a staging buffer (one copy per row and
-//               superblock, contiguous in HBM); each slab they rebuild
-//               w = (d*sc)*q - dmin*m in fp16 and store it into the K-major
-//               128-byte-swizzled operand tile;
-//   warp 8      one elected thread issues tcgen05.mma (kind::f16, 128 x N x 16)
-//               over the four 16-wide steps of a slab and commits the stage
-//               back to the producers through an mbarrier;
-//   warps 9..12 loaders: gather the token rows of the slab (16-byte pieces,
-//               one slab ahead in registers) into the second operand tile;
+// Roles (swap-AB): the MMA "M" side is weight rows of one expert, the "N" side is
+// a bucket of up to 256 routed tokens (a multiple of 16), K runs over the hidden
+// (or ffn) dimension in slabs of 64 (one 128-byte swizzle row of fp16). Per CTA
+// one (expert, 128-row tile, token bucket); where a bucket has an even number of
+// row tiles, CTAs 2i and 2i+1 form a cluster and share one cta_group::2 MMA
+// (M = 256 over the pair, each CTA gathers half of the bucket's token rows):
+//   warps 0..7  unpackers: 2-D TMA boxes (32 rows x 144 B) bring the raw
+//               superblocks into a double-buffered staging area; per superblock
+//               the eight (d*sc, -dmin*m) pairs are formed in fp16 (exact), per
+//               slab each thread turns 16 code bytes into 32 fp16 weights and
+//               stores them into the K-major 128-byte-swizzled operand tile
+//               (three operand stages);
+//   warp 8      one elected thread issues tcgen05.mma (kind::f16) over the four
+//               16-wide steps of a slab and commits the stage back to the
+//               producers; in a pair the even CTA issues for both and its commit
+//               arrives on the barriers of both CTAs (tcgen05.commit with the
+//               multicast::cluster qualifier: a barrier arrival, no data moves);
+//   warps 9..12 loaders: gather the token rows of the slab with 16-byte cp.async
+//               straight into the swizzled tile; completion arrives on the stage
+//               barrier (cp.async.mbarrier.arrive.noinc), so several slabs are in
+//               flight with no registers held;
 //   warps 0..7  epilogue: tcgen05.ld of the accumulators (lane = weight row,
-//               column = token), SiLU(gate)*up or the plain projection, stores.
-// Gate and up share the token operand: two accumulators (columns [0,256) and
-// [256,512)) are fed from two weight tiles per slab.
+//               column = token), SiLU(gate)*up or the plain projection (or the
+//               weighted reduction into the token's sum), transposed through the
+//               idle operand stages, 16-byte row stores.
+// Gate and up share the token operand: two accumulators (TMEM columns [0,256)
+// and [256,512)) are fed from two weight tiles per slab.
 //
 // Precision. Operands are fp16, not bf16: a Q4_K weight rounded to fp16 is off
 // by <= 2^-12 relative, which keeps the layer's relative RMSE well inside the
@@ -61,14 +71,26 @@ struct TcParams {
   const float *cmb_w;
   float *cmb_acc;
   int cmb_div;
-  unsigned long long *trace;  // optional: SM-clock stamps of CTA 0's first slabs (measurement hook)
+#ifdef KNJ_TRACE
+  unsigned long long *trace;  // measurement builds: SM-clock stamps of CTA 0's first slabs
   int trace_ctas;             // per-CTA records that fit behind the 64 slab stamps
+#endif
   CUtensorMap map0, map1;     // TMA descriptors of W0 / W1, box = one superblock (36 words) x 32 rows
 };
 
+#ifdef KNJ_TRACE
 unsigned long long *g_tc_trace = nullptr;
 int g_tc_trace_ctas = 0;
-int g_tc_force_single = 0;  // experiment hook: 1 = never pair CTAs
+#define KNJ_TC_STAMP(cond, slot)              \
+  do {                                        \
+    if (p.trace && (cond)) p.trace[slot] = clock64(); \
+  } while (0)
+#define KNJ_TC_SET_TRACE(p) ((p).trace = g_tc_trace, (p).trace_ctas = g_tc_trace_ctas)
+#else
+#define KNJ_TC_STAMP(cond, slot) ((void)0)
+#define KNJ_TC_SET_TRACE(p) ((void)0)
+#endif
+int g_tc_force_single = 0;  // 1 = never pair CTAs (knj_q4k_tc_single_sm)
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -262,6 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     }
   }
   if (e < 0) return;  // the same for both CTAs of a pair: nothing allocated yet, no barrier touched
+#ifdef KNJ_TRACE
   unsigned long long *cta_rec = (p.trace && (int)blockIdx.x < p.trace_ctas) ? p.trace + 256 + 4 * (size_t)blockIdx.x : nullptr;
   if (cta_rec && tid == 0) {
     unsigned smid;
@@ -269,6 +292,13 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     cta_rec[0] = global_timer_ns();
     cta_rec[3] = ((unsigned long long)smid << 32) | (unsigned)(cnt - tok0 < kMaxTok ? cnt - tok0 : kMaxTok);
   }
+#define KNJ_TC_REC(i)                                   \
+  do {                                                  \
+    if (cta_rec && tid == 0) cta_rec[i] = global_timer_ns(); \
+  } while (0)
+#else
+#define KNJ_TC_REC(i) ((void)0)
+#endif
   const int ntok = min(kMaxTok, cnt - tok0);
   const int n_mma = (ntok + 15) & ~15;  // MMA N: multiple of 16
   const int n_cta = n_mma / CG;         // token rows staged by this CTA: [rank * n_cta, (rank + 1) * n_cta)
@@ -386,10 +416,10 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
       for (int G = 0; G < 4; ++G) {
         if (!ok) break;
         const int ks = b * 4 + G, stage = ks % kStages;
-        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 0] = clock64();
+        KNJ_TC_STAMP(blockIdx.x == 0 && tid == 0 && ks < 12, 4 * ks + 0);
         if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
         tc_fence_after();
-        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 1] = clock64();
+        KNJ_TC_STAMP(blockIdx.x == 0 && tid == 0 && ks < 12, 4 * ks + 1);
         // ---- weight operand(s): 16 code bytes -> 16 low-nibble + 16 high-nibble weights of this row
 #pragma unroll
         for (int mat = 0; mat < NMAT; ++mat) {
@@ -423,7 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
           if (CG == 2) mbar_arrive_cluster(cluster_addr(&full[stage], 0));
           else mbar_arrive(&full[stage]);
         }
-        if (p.trace && blockIdx.x == 0 && tid == 0 && ks < 12) p.trace[4 * ks + 2] = clock64();
+        KNJ_TC_STAMP(blockIdx.x == 0 && tid == 0 && ks < 12, 4 * ks + 2);
       }
     }
   } else if (warp >= 9) {
@@ -445,10 +475,10 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     }
     for (int ks = 0; ks < nslab && ok; ++ks) {  // loaders meet no CTA barrier before the final one
       const int stage = ks % kStages;
-      const bool ltr = p.trace && blockIdx.x == 0 && lt == 0 && ks < 12;
-      if (ltr) p.trace[64 + 4 * ks] = clock64();
+      [[maybe_unused]] const bool ltr = blockIdx.x == 0 && lt == 0 && ks < 12;
+      KNJ_TC_STAMP(ltr, 64 + 4 * ks);
       if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
-      if (ltr) p.trace[64 + 4 * ks + 1] = clock64();
+      KNJ_TC_STAMP(ltr, 64 + 4 * ks + 1);
       uint8_t *bt = smem + S::kOffB + stage * S::kBTile;
 #pragma unroll
       for (int j = 0; j < kRpt; ++j) {
@@ -458,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
                      rowp[j] ? 16u : 0u);
       }
       cp_async_arrive(rank == 0 ? &full[stage] : &locB[stage]);
-      if (ltr) p.trace[64 + 4 * ks + 3] = clock64();
+      KNJ_TC_STAMP(ltr, 64 + 4 * ks + 3);
     }
   } else if (CG == 2 && warp == 8 && lane == 0 && rank == 1) {
     // =========================== relay (odd CTA) ===========================
@@ -481,7 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
       // complete when their copies' arrivals are (the hand-off CUTLASS' cp.async tcgen05 main loop relies on),
       // and a fence.proxy.async in this thread would wait for the shared-memory reads of every MMA in flight.
       tc_fence_after();
-      if (p.trace && blockIdx.x == 0 && ks < 12) p.trace[4 * ks + 3] = clock64();
+      KNJ_TC_STAMP(blockIdx.x == 0 && ks < 12, 4 * ks + 3);
       const uint32_t b_addr = smem_u32(smem + S::kOffB + st * S::kBTile);
       const uint32_t a_addr = smem_u32(smem + S::kOffA + st * NMAT * S::kATile);
 #pragma unroll
@@ -493,7 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
       }
       if (CG == 2) tc_commit_pair(smem_u32(&empty[st]));
       else tc_commit_addr<CG>(smem_u32(&empty[st]));
-      if (p.trace && blockIdx.x == 0 && ks < 12) p.trace[128 + ks] = clock64();
+      KNJ_TC_STAMP(blockIdx.x == 0 && ks < 12, 128 + ks);
     }
     if (ok) {
       if (CG == 2) tc_commit_pair(smem_u32(acc_full));
@@ -509,12 +539,12 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     const int slot = warp < 8 ? (warp >> 2) : 2;        // which of the three warps of a lane group
     if (ok && !mbar_wait(acc_full, 0, s_fail)) ok = false;
     tc_fence_after();
-    if (cta_rec && tid == 0) cta_rec[1] = global_timer_ns();
+    KNJ_TC_REC(1);
     // The accumulator rows are output indices (one per thread) and the columns tokens, while the outputs are
     // token-major: transpose through the operand stages (idle now), then write whole 256- or 512-byte row
     // segments, 16 bytes per lane. Every unpacker thread takes part in the barriers even after a failed wait.
-    const bool tr = p.trace && blockIdx.x == 0 && tid == 0;
-    if (tr) p.trace[48] = clock64();
+    [[maybe_unused]] const bool tr = blockIdx.x == 0 && tid == 0;
+    KNJ_TC_STAMP(tr, 48);
     const int lane_base = 32 * (warp & 3);
     uint8_t *stg = smem + S::kOffA;
     constexpr int kEpiMats = GATEUP ? 1 : NMAT;
@@ -543,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
           }
         }
       }
-      if (tr) p.trace[49 + 2 * mat] = clock64();
+      KNJ_TC_STAMP(tr, 49 + 2 * mat);
       asm volatile("bar.sync 5, 384;" ::: "memory");
       if (ok) {
         constexpr int kLanesPerRow = kRowB / 16;            // 16 (fp16) or 32 (f32)
@@ -567,7 +597,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
           *reinterpret_cast<uint4 *>(dst + l16 * 16) = v;
         }
       }
-      if (tr) p.trace[50 + 2 * mat] = clock64();
+      KNJ_TC_STAMP(tr, 50 + 2 * mat);
       if (mat + 1 < kEpiMats) asm volatile("bar.sync 5, 384;" ::: "memory");
     }
   }
@@ -578,7 +608,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   // operands or arrives on its barriers
   if (CG == 2) cluster_sync_all();
   if (warp == 8) tmem_dealloc<CG>(tmem_base, kTmemCols);
-  if (cta_rec && tid == 0) cta_rec[2] = global_timer_ns();
+  KNJ_TC_REC(2);
 }
 
 // x (f32 / bf16 / f16) -> fp16 with saturation, rows dense
@@ -689,19 +719,21 @@ int launch_tc(const TcParams &p, int max_pairs, cudaStream_t st) {
 
 extern "C" {
 
+#ifdef KNJ_TRACE
 // Measurement hook (no reference counterpart): device buffer of 256 + 4 * cta_slots u64. SM-clock stamps of
 // CTA 0: [4k..4k+3], k < 12: unpacker starts slab k, stage free, stage published, MMA sees the slab;
 // [48..61] epilogue phases; [64+4k..], k < 12: loader reaches slab k, stage free, rows stored, published.
 // From [256] on, per CTA b < cta_slots: global-timer ns at start, accumulator complete, end, and
 // (SM id << 32 | tokens of its bucket).
-void knj_tc_trace(void *dev_buf, int cta_slots) {
+void knj_trace_tc(void *dev_buf, int cta_slots) {
   g_tc_trace = static_cast<unsigned long long *>(dev_buf);
   g_tc_trace_ctas = dev_buf ? cta_slots : 0;
 }
+#endif
 
-// Experiment hook (no reference counterpart): 1 = run every tile on a single SM (cta_group::1) even where
-// CTA pairs apply; 0 = automatic.
-void knj_tc_tuning(int force_single_sm) { g_tc_force_single = force_single_sm & 1; }
+// 1 = run every bucket in the single-SM form (cta_group::1), the form buckets with an odd number of row tiles
+// always take; 0 = CTA pairs wherever the tile count is even (default). Process-wide.
+void knj_q4k_tc_single_sm(int on) { g_tc_force_single = on & 1; }
 
 int knj_to_f16_launch(const void *x, int x_dtype, int64_t ldx, int rows, int K, void *out_f16, knj_stream_t s) {
   KNJ_REQUIRE(x && out_f16, "knj_to_f16: null pointer");
@@ -734,7 +766,7 @@ int knj_q4k_gateup_tc_launch(const void *Xh, const uint8_t *Wg, const uint8_t *W
   TcParams p{};
   p.X = static_cast<const __half *>(Xh); p.W0 = Wg; p.W1 = Wu; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
   p.row_map = pair_tok; p.out = A_f16; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = top_k > 0 ? top_k : 1;
-  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = kActPrescale; p.status = status; p.trace = g_tc_trace; p.trace_ctas = g_tc_trace_ctas;
+  p.n_experts = n_experts; p.m_tiles = N / kRowsM; p.idxStride = idxStride; p.out_scale = kActPrescale; p.status = status; KNJ_TC_SET_TRACE(p);
   return launch_tc<2, true>(p, max_pairs, as_stream(s));
 }
 
@@ -751,7 +783,7 @@ int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pai
   TcParams p{};
   p.X = static_cast<const __half *>(Ah); p.W0 = Wd; p.W1 = nullptr; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
   p.row_map = pair_row; p.out = Y; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
-  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; p.trace = g_tc_trace; p.trace_ctas = g_tc_trace_ctas;
+  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; KNJ_TC_SET_TRACE(p);
   if (N % (2 * kRowsM) == 0) {  // two row tiles per CTA share every gathered token tile
     p.m_tiles = N / (2 * kRowsM);
     return launch_tc<2, false>(p, max_pairs, as_stream(s));
@@ -773,7 +805,7 @@ int knj_q4k_down_combine_tc_launch(const void *Ah, const uint8_t *Wd, const int3
   TcParams p{};
   p.X = static_cast<const __half *>(Ah); p.W0 = Wd; p.W1 = nullptr; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
   p.row_map = pair_row; p.out = nullptr; p.N = N; p.K = K; p.rowBytes = rowBytes; p.row_div = 1;
-  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; p.trace = g_tc_trace; p.trace_ctas = g_tc_trace_ctas;
+  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; KNJ_TC_SET_TRACE(p);
   p.cmb_w = pair_w; p.cmb_acc = acc; p.cmb_div = top_k;
   if (N % (2 * kRowsM) == 0) {
     p.m_tiles = N / (2 * kRowsM);

@@ -96,6 +96,13 @@ class SlotPool final : public CudaSlotAllocator {
   void watch(SlotHandle h, const TransferEngine *engine, TransferId id) override {
     if (valid(h) && engine && id != kNoTransfer) slots_[h].loads.push_back({engine, id});
   }
+  SlotHandle slot_of(const void *p) const override {
+    if (!base_ || !p || slot_bytes_ == 0) return kNoSlot;
+    const char *c = static_cast<const char *>(p), *b = static_cast<const char *>(base_);
+    if (c < b || c >= b + slots_.size() * slot_bytes_) return kNoSlot;
+    const SlotHandle h = (SlotHandle)((c - b) / slot_bytes_);
+    return slots_[h].state != kFree ? h : kNoSlot;
+  }
 
  private:
   enum State { kFree, kHeld, kRetiring };
@@ -128,7 +135,7 @@ class SlotPool final : public CudaSlotAllocator {
 
 class CopyEngine final : public TransferEngine {
  public:
-  explicit CopyEngine(const char *path) {
+  explicit CopyEngine(const char *path, CudaSlotAllocator *slots = nullptr) : slots_(slots) {
     int lo = 0, hi = 0;
     cudaDeviceGetStreamPriorityRange(&lo, &hi);  // hi is the numerically smallest = most urgent
     ok_ = cudaStreamCreateWithPriority(&demand_, cudaStreamNonBlocking, hi) == cudaSuccess &&
@@ -162,10 +169,10 @@ class CopyEngine final : public TransferEngine {
     return fd_ >= 0 && src ? enqueue_file({true, nullptr, src, off, bytes}, io) : kNoTransfer;
   }
   TransferId submit_h2d(void *dst, const void *src, uint64_t bytes, IoClass io) override {
-    return device_copy(dst, src, bytes, cudaMemcpyHostToDevice, io);
+    return note(dst, device_copy(dst, src, bytes, cudaMemcpyHostToDevice, io));
   }
   TransferId submit_d2h(void *dst, const void *src, uint64_t bytes, IoClass io) override {
-    return device_copy(dst, src, bytes, cudaMemcpyDeviceToHost, io);
+    return note(src, device_copy(dst, src, bytes, cudaMemcpyDeviceToHost, io));
   }
   TransferState poll(TransferId id) const override {
     std::lock_guard<std::mutex> g(m_);
@@ -216,6 +223,15 @@ class CopyEngine final : public TransferEngine {
     TransferId id;
     FileOp op;
   };
+  // a copy whose device side lies in a slot of the bound pool is registered with that slot
+  TransferId note(const void *dev, TransferId id) {
+    if (slots_ && id != kNoTransfer) {
+      const SlotHandle h = slots_->slot_of(dev);
+      if (h != kNoSlot) slots_->watch(h, this, id);
+    }
+    return id;
+  }
+  CudaSlotAllocator *slots_ = nullptr;
   TransferId device_copy(void *dst, const void *src, uint64_t bytes, cudaMemcpyKind kind, IoClass io) {
     if (!ok_ || !dst || !src) return kNoTransfer;
     cudaStream_t st = io == IoClass::DEMAND ? demand_ : prefetch_;
@@ -304,8 +320,8 @@ std::unique_ptr<HostArena> make_cuda_host_arena() { return std::unique_ptr<HostA
 std::unique_ptr<CudaSlotAllocator> make_cuda_slot_allocator(int n_slots, uint64_t slot_bytes) {
   return std::unique_ptr<CudaSlotAllocator>(new SlotPool(n_slots, slot_bytes));
 }
-std::unique_ptr<TransferEngine> make_cuda_transfer_engine(const char *backing_path) {
-  return std::unique_ptr<TransferEngine>(new CopyEngine(backing_path));
+std::unique_ptr<TransferEngine> make_cuda_transfer_engine(const char *backing_path, CudaSlotAllocator *slots) {
+  return std::unique_ptr<TransferEngine>(new CopyEngine(backing_path, slots));
 }
 
 }  // namespace knj

@@ -531,7 +531,9 @@ struct FrontParams {
   int32_t *pair_idx, *pair_cnt, *exp_list, *n_active;
   float *xn;  // [T][H]: the rows the experts see (normalised where norm_w is given)
   unsigned int *counter;  // [0, 1 + token groups) zero before the launch
-  unsigned long long *trace;  // optional [8]: global-timer stamps of the phases of the CTA that finishes last
+#ifdef KNJ_TRACE
+  unsigned long long *trace;  // measurement builds, [10]: global-timer stamps of the phases of the CTA that finishes last
+#endif
   int tpc;  // tokens per CTA: ceil(T / 8), the logits being a serial walk over a CTA's tokens
 };
 
@@ -561,9 +563,14 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   const int nslice = p.H / 256;
   const int e = eg * 8 + warp;
   const int t0 = tg * p.tpc;
+#ifdef KNJ_TRACE
   unsigned long long stamp[9];
   stamp[6] = stamp[7] = stamp[8] = 0;
-  stamp[0] = gtime_ns();
+#define KNJ_FRONT_STAMP(i) (stamp[i] = gtime_ns())
+#else
+#define KNJ_FRONT_STAMP(i) ((void)0)
+#endif
+  KNJ_FRONT_STAMP(0);
 
   // ---- logits (and the rows' scales)
   {
@@ -642,21 +649,21 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
     // the router and norm weights above do not depend on the previous launch and are already on their way;
     // the token rows are the previous layer's output
     grid_dep_wait();
-    stamp[6] = gtime_ns();
+    KNJ_FRONT_STAMP(6);
     if (nt > 0) fetch(t0, ra);
     for (int i = 0; i < nt; i += 2) {
       if (i + 1 < nt) fetch(t0 + i + 1, rb);
       reduce_store(i, ra);
-      if (i == 0) stamp[7] = gtime_ns();
+      if (i == 0) KNJ_FRONT_STAMP(7);
       if (i + 1 < nt) {
         if (i + 2 < nt) fetch(t0 + i + 2, ra);
         reduce_store(i + 1, rb);
       }
-      if (i == 0) stamp[8] = gtime_ns();
+      if (i == 0) KNJ_FRONT_STAMP(8);
     }
   }
   __syncthreads();
-  stamp[1] = gtime_ns();
+  KNJ_FRONT_STAMP(1);
 
   // ---- the rows the experts see: CTA (eg, tg) writes tokens t0 + eg, t0 + eg + n_eg, ...
   for (int i = eg; i < p.tpc; i += n_eg) {
@@ -671,14 +678,14 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   }
 
   // ---- did this CTA complete its token group?
-  stamp[2] = gtime_ns();
+  KNJ_FRONT_STAMP(2);
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) s_flag = (atomicAdd(p.counter + 1 + tg, 1u) == (unsigned)n_eg - 1) ? 1 : 0;
   __syncthreads();
   if (!s_flag) return;
   __threadfence();
-  stamp[3] = gtime_ns();
+  KNJ_FRONT_STAMP(3);
 
   // ---- top-k of the group's tokens, one warp each
   {
@@ -699,14 +706,14 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   }
 
   // ---- did this CTA complete the last group?
-  stamp[4] = gtime_ns();
+  KNJ_FRONT_STAMP(4);
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) s_flag = (atomicAdd(p.counter, 1u) == (unsigned)n_tg - 1) ? 1 : 0;
   __syncthreads();
   if (!s_flag) return;
   __threadfence();
-  stamp[5] = gtime_ns();
+  KNJ_FRONT_STAMP(5);
 
   // ---- permutation tables. Pairs are taken in chunks of 32 (one per warp pass):
   // count per (chunk, expert), scan over chunks, then every pair knows its rank.
@@ -765,6 +772,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
   if (threadIdx.x == 0) {
     p.n_active[0] = tot;
     p.n_active[1] = mxc;
+#ifdef KNJ_TRACE
     if (p.trace) {
       for (int i = 0; i < 6; ++i) p.trace[i] = stamp[i];
       p.trace[6] = gtime_ns();
@@ -772,6 +780,7 @@ __global__ void __launch_bounds__(256) moe_front_kernel(const FrontParams p) {
       p.trace[8] = stamp[7];
       p.trace[9] = stamp[8];
     }
+#endif
   }
 }
 
@@ -868,10 +877,11 @@ int knj_moe_permute_launch(const int32_t *pair_exp, int P, int E, int idx_stride
   return launch_status("active_list_kernel");
 }
 
+#ifdef KNJ_TRACE
 static unsigned long long *g_front_trace = nullptr;
-// Measurement hook (no reference counterpart): device buffer of 16 u64 that receives
-// global-timer stamps of the front kernel's phases; NULL switches it off.
-void knj_moe_front_trace(void *dev_buf) { g_front_trace = static_cast<unsigned long long *>(dev_buf); }
+// measurement builds only: device buffer of 16 u64 that receives global-timer stamps of the front kernel's phases
+void knj_trace_front(void *dev_buf) { g_front_trace = static_cast<unsigned long long *>(dev_buf); }
+#endif
 
 int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t *norm_w, float eps,
                          const uint16_t *Wr_bf16, const float *bias, int T, int H, int E, int k, float *logits,
@@ -891,7 +901,9 @@ int knj_moe_front_launch(const void *x, int x_dtype, int64_t ldx, const uint16_t
   p.idx_stride = idx_stride; p.logits = logits; p.pair_exp = pair_exp; p.pair_w = pair_w; p.pair_idx = pair_idx;
   p.pair_cnt = pair_cnt; p.exp_list = exp_list; p.n_active = n_active; p.xn = xn;
   p.counter = counter;
+#ifdef KNJ_TRACE
   p.trace = g_front_trace;
+#endif
   p.tpc = (T + 7) / 8;  // eight token groups at most: ~128 CTAs at every batch, and the serial walk over a CTA's tokens stays short
   const int n_tg = (T + p.tpc - 1) / p.tpc;
   KNJ_CUDA(cudaMemsetAsync(counter, 0, sizeof(uint32_t) * (1 + n_tg), as_stream(s)));

@@ -81,7 +81,7 @@ extern "C" {
 
 // 1 (default): the kernels of a decode layer are launched with programmatic stream serialization, so each
 // grid is scheduled while its predecessor drains; 0: plain launches.
-void knj_chain_overlap(int on) { g_chain_overlap = on ? 1 : 0; }
+void knj_launch_overlap(int on) { g_chain_overlap = on ? 1 : 0; }
 
 
 const char *knj_last_error_string(void) { return g_err; }

@@ -330,12 +330,9 @@ _EP_CONTEXTS = {}
 
 
 def ep_chunks(T_loc: int, k: int, world: int, e_loc: int) -> int:
-    """Chunks of a step: as many (up to four) as leave every local expert 256 rows per chunk on average."""
-    n = 1
-    while (n < 4 and T_loc % (2 * n) == 0 and ((T_loc // (2 * n)) * k) % 4 == 0
-           and (T_loc // (2 * n)) * world * k >= 256 * e_loc * world):
-        n *= 2
-    return n
+    """Chunks of a step. One: on 2 and 4 B200s two chunks were slower than one at the benchmark's size (the two
+    half-size GEMM launches lose more than the overlapped transfers save); more can be asked for explicitly."""
+    return 1
 
 
 def ep_context(group, world, rank, T_loc, H, F, E, k, device, n_chunks=None) -> EpPeerContext:

@@ -38,11 +38,11 @@ def ragged_problem(E, F, H, counts, seed):
 ])
 def test_grouped_gemms(E, F, H, counts, single_sm):
     from kanjoos_b200 import ops, _lib
-    _lib.lib().knj_tc_tuning(single_sm)
+    _lib.lib().knj_q4k_tc_single_sm(single_sm)
     try:
         _grouped_gemms(ops, E, F, H, counts)
     finally:
-        _lib.lib().knj_tc_tuning(0)
+        _lib.lib().knj_q4k_tc_single_sm(0)
 
 
 def _grouped_gemms(ops, E, F, H, counts):
