@@ -195,7 +195,7 @@ def workload_config(args, world):
 
 # --------------------------------------------------------------------------- GPU arm
 
-def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64)):
+def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64), inputs=("chained", "fresh")):
     """Resident stack (48 layers by default): tokens/s and HBM roofline of the decode path, one cooperative launch
     per step (knj_moe_stack_*). Two inputs per batch: `chained` feeds each layer the previous layer's output (the
     decode loop as it runs; with random-init weights the residual stream concentrates the routing on a third of
@@ -208,7 +208,7 @@ def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64)):
         g = torch.Generator(device="cuda")
         g.manual_seed(B)
         x = torch.randn((B, H), device="cuda", generator=g).to(torch.bfloat16)
-        for mode in ("chained", "fresh"):
+        for mode in inputs:
             if mode == "fresh" and B == 1:
                 continue  # one token routes to eight experts whatever its row is
             ins = ([torch.randn((B, H), device="cuda", generator=g).to(torch.bfloat16) for _ in range(layers)]
@@ -297,7 +297,7 @@ def run_gpu(args):
     if args.section == "decode":
         # decode-only run (used for profiling captures): one line about the resident stack
         dec = decode_section(torch, args.steps, args.warmup, pk, args.decode_layers,
-                             tuple(int(b) for b in args.decode_batches.split(",")))
+                             tuple(int(b) for b in args.decode_batches.split(",")), tuple(args.decode_inputs.split(",")))
         print(json.dumps({"metric": "moe_ffn_decode", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                           "data": "synthetic", "decode": dec}))
         return
@@ -549,6 +549,8 @@ def main():
     ap.add_argument("--section", default="all", choices=["all", "decode"])
     ap.add_argument("--decode-layers", type=int, default=LAYERS, dest="decode_layers")
     ap.add_argument("--decode-batches", default="1,8,64", dest="decode_batches")
+    ap.add_argument("--decode-inputs", default="chained,fresh", dest="decode_inputs",
+                    help="per-layer inputs of the decode section: chained (each layer feeds the next), fresh, or both")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

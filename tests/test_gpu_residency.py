@@ -83,3 +83,19 @@ def test_streamed_equals_resident_bit_for_bit():
         assert layer.loads > 6 and layer.evictions > 0      # the slots were recycled along the way
     finally:
         layer.close()
+
+
+def test_reference_residency_manager_over_the_cuda_gates():
+    """The reference's own ResidencyManager (its residency.cpp, compiled where it lies into
+    oracle/_ref/knj_ref_residency_check together with oracle/ref_residency_check.cpp) constructed over this
+    library's slot pool, copy engine and pinned arena, driven through demand, pool-full fallback, eviction,
+    pinning, reload and prefetch with real asynchronous copies. The binary is built where the reference tree
+    exists (make -C oracle ref); it is test infrastructure and travels prebuilt."""
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "oracle", "_ref", "knj_ref_residency_check")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/knj_ref_residency_check was not built (no reference tree on the build machine)")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    print(r.stdout, r.stderr)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failed" in r.stdout
