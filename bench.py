@@ -464,15 +464,14 @@ def run_gpu(args):
         flops = rows * 2 * 2 * H * F
         t_tensor = flops / (pk["bf16_tflops"] * 1e12)
         assert int(status.item()) == 0, "a bounded wait inside the grouped GEMM gave up"
-        # DRAM bytes per launch from the ncu capture of the 512-token case (weights 229.55 - 3.06 MB, which do not
-        # depend on the token count while every expert is active, + 3.06 MB read and 7.80 MB written per 512
-        # tokens), scaled to this launch's rows
+        # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum of this kernel) as ncu counted them on
+        # this workload in a one-pass capture of the same command: at T=16384 532.3 + 184.3 MB, at T=4096
+        # 261.5 + 38.7 MB (uniform router, N=1); other sizes have no capture
         w_bytes = int((pair_cnt > 0).sum().item()) * 2 * F * (H // 256) * 144
-        traffic = None
-        traffic_note = None
-        if world == 1:
-            traffic = w_bytes + (3.06e6 + 7.80e6) * (rows / 4096.0)
-            traffic_note = "ncu dram bytes of the T=512 capture: weight stream as measured, token-proportional part scaled by rows"
+        measured = {(16384, "uniform"): 716.6e6, (4096, "uniform"): 300.2e6}
+        traffic = measured.get((T, args.routing)) if world == 1 else None
+        traffic_note = ("ncu one-pass DRAM counters of this kernel on this workload; algorithmic bytes (weights once + fp16 rows "
+                        "in + fp16 rows out) = %.1f MB" % ((w_bytes + rows // TOPK * H * 2 + rows * F * 2) / 1e6)) if traffic else None
         roof = {"kernel": "q4k_grouped_tc_kernel<2,true,2> (gate+up, tcgen05 cta_group::2)", "bound": "tensor", "achieved": flops / (ms_k * 1e-3) / 1e12,
                 "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": flops / (ms_k * 1e-3) / 1e12 / pk["bf16_tflops"],
                 "peak_source": pk["_source"], "traffic": traffic, "traffic_note": traffic_note, "ms_per_launch": ms_k,

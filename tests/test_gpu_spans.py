@@ -66,3 +66,20 @@ def test_captured_launches_record_nothing():
         g.replay()
         torch.cuda.synchronize()
     assert spans.rows == [] and spans.dropped == 0
+
+
+def test_reference_profiler_fed_from_the_span_ring():
+    """The reference's own Profiler (its profiler.cpp, compiled where it lies into oracle/_ref/knj_ref_profiler_check
+    together with oracle/ref_profiler_check.cpp) receives the spans of three eager layer launches through
+    knj_spans_flush -> Profiler::device_span and reports them: Device domain, all spans counted, none dropped,
+    rows named as the CPU path's stages. The binary is built where the reference tree exists (make -C oracle ref)
+    and travels prebuilt; it is test infrastructure."""
+    import os
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "oracle", "_ref", "knj_ref_profiler_check")
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/knj_ref_profiler_check was not built (no reference tree on the build machine)")
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=300)
+    print(r.stdout, r.stderr)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "0 failed" in r.stdout
