@@ -273,3 +273,32 @@ def test_stack_create_refuses_bad_arguments(L):
     assert L.knj_moe_stack_create(a, 1, C.byref(h)) == -1 and b"null tensor" in L.knj_last_error_string()
     assert L.knj_moe_stack_decode_launch(None, None) == -1
     L.knj_moe_stack_destroy(None)
+
+
+def _run_ref_binary(name):
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "oracle", "_ref", name)
+    if not os.path.exists(exe):
+        pytest.skip(f"oracle/_ref/{name} was not built (no reference tree on the build machine)")
+    env = {k: v for k, v in os.environ.items() if k != "KNJ_BUILD_ARCH"}
+    return subprocess.run([exe], capture_output=True, text=True, timeout=120, env=env).stdout
+
+
+def test_reference_device_unit_test_passes_on_its_own_headers():
+    """Baseline: the reference's tests/unit/test_c2_device.cpp, compiled unmodified against the reference's own
+    src/device headers and backend.cpp with its gfx1201 build definitions: 91 assertions, none failing."""
+    out = _run_ref_binary("knj_ref_c2_test")
+    assert "tests passed: 91" in out and "tests failed: 0" in out, out[-2000:]
+
+
+def test_reference_device_unit_test_compiled_unmodified_against_this_library():
+    """The same source file, unmodified, compiled against include/device_caps.h + include/backend.h and linked
+    with libknj_device.so: arch guard, capability table, labels, cap line, host probe, Backend::create /
+    from_caps / would_instantiate / the four launches and the doctor header all answer as the reference's own
+    implementation does. One assertion of 91 differs, and must: the dot-product label of a device without the
+    sdot4 builtin names the instruction this hardware has (dp4a) instead of the gfx one."""
+    out = _run_ref_binary("knj_ref_c2_on_this_library")
+    assert "tests passed: 90" in out and "tests failed: 1" in out, out[-2000:]
+    fails = [ln for ln in out.splitlines() if "FAIL" in ln and "RESULT" not in ln]
+    assert len(fails) == 1 and "dot label mismatch" in fails[0], fails
+    assert 'expected: "asm(v_dot4_i32_i8)", got: "intrinsic(dp4a)"' in out
