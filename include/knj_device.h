@@ -564,6 +564,8 @@ int knj_ep_reduce_sel_launch(const float *parts, int n_ranks, int T_loc, int H, 
 #define KNJ_EP_COPY_ENGINES 0 /* rows and partial sums travel as block copies (one cudaMemcpyAsync per peer) */
 #define KNJ_EP_SM_ROWS 1      /* the rows travel as 16-byte stores of this library's kernels */
 #define KNJ_EP_SM_PARTIALS 2  /* the partial sums travel as 16-byte stores of the kernel that forms them */
+#define KNJ_EP_F16_PARTIALS 4 /* with KNJ_EP_SM_PARTIALS, hidden <= 2048: the partial rows travel as fp16 under a per-row
+                                 power-of-two scale (half the bytes; 2^-11 relative to the row's largest element) */
 #define KNJ_EP_FLAG_WORDS 4096
 #define KNJ_EP_MAX_CHUNKS 8
 typedef struct knj_ep_desc {
@@ -584,11 +586,14 @@ int knj_ep_forward_launch(knj_ep_ctx *ctx, const void *x, int x_dtype, int64_t l
                           int residual, void *out, int out_dtype, knj_stream_t s);
 /* a barrier over the ranks on the stream (arrival + bounded wait in one launch, on flag words of its own) */
 int knj_ep_barrier_launch(knj_ep_ctx *ctx, knj_stream_t s);
-/* How rows and partial sums reach the peers: an OR of KNJ_EP_SM_ROWS and KNJ_EP_SM_PARTIALS, 0 = block copies for
- * both (the routing tables and the flag words always go as stores of the library's kernels). With block copies the
+/* How rows and partial sums reach the peers: an OR of KNJ_EP_SM_ROWS, KNJ_EP_SM_PARTIALS and KNJ_EP_F16_PARTIALS,
+ * 0 = block copies for both (the routing tables and the flag words always go as stores of the library's kernels). With block copies the
  * SMs stay with the GEMMs while a chunk travels; partial sums then travel as dense blocks per owner, rows of tokens
- * without an expert on the sender included (never read). Default KNJ_EP_SM_PARTIALS: block copies for the rows, the
- * partial sums stored by the kernel that forms them (only contributing rows travel). Every rank must use the same. */
+ * without an expert on the sender included (never read). Default KNJ_EP_SM_PARTIALS | KNJ_EP_F16_PARTIALS: block copies
+ * for the rows, the partial sums stored by the kernel that forms them (only contributing rows travel) as fp16 under
+ * a per-row power-of-two scale -- the sums themselves are formed and added in f32; the stored form costs about
+ * 1e-4 relative RMSE of the layer output, inside the 1e-3 budget of the tensor-core path. Without the flag the rows
+ * travel as f32 and the result equals the single-GPU layer's to ~5e-8. Every rank must use the same transport. */
 int knj_ep_set_transport(knj_ep_ctx *ctx, int transport);
 /* limit of every rank wait in SM clock cycles (<= 0 restores the default, about a second) */
 int knj_ep_set_wait(knj_ep_ctx *ctx, long long wait_cycles);

@@ -43,6 +43,12 @@ int sm_count();  // SMs of the current device (cached per device)
 // [T][H], local) the rows of other ranks' tokens are written there instead, one dense block per owner
 int ep_combine_partial_peer_at(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k, int exp_lo, int exp_hi,
                                float *const *parts_ptrs, int64_t parts_off, float *stage, int my_rank, int T_loc, cudaStream_t s);
+// the partial rows as fp16 under a per-row power-of-two scale (the slot keeps its f32 stride; H <= 2048, H % 256 == 0),
+// and the rank-ordered sum over such slots
+int ep_combine_partial_peer_f16_at(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k, int exp_lo,
+                                   int exp_hi, float *const *parts_ptrs, int64_t parts_off, int my_rank, int T_loc, cudaStream_t s);
+int ep_reduce_sel_f16(const float *parts, int n_ranks, int T_loc, int H, const int32_t *pair_exp, int k, int experts_per_rank,
+                      const void *resid, int resid_dtype, void *out, int out_dtype, cudaStream_t s);
 
 // Launch of a kernel that belongs to a chain of dependent launches on one stream (the decode layer). With
 // overlap on, the launch carries the programmatic-stream-serialization attribute: the grid may be scheduled

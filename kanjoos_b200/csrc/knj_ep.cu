@@ -273,6 +273,124 @@ __global__ void __launch_bounds__(256) ep_reduce_sel_kernel(const float *__restr
   }
 }
 
+// ep_combine_partial_peer with the row stored as fp16 under a per-row power-of-two scale (half the bytes over
+// NVLink): the row's slot keeps its f32 stride, the first 2H bytes hold the scaled halves and the float at element
+// H/2 the inverse scale. The sum itself is formed in f32 exactly as above; only its stored form is rounded (2^-11
+// relative to the row's largest element). H <= 2048, a multiple of 256; lane l covers elements 256 it + 8 l .. + 7.
+__global__ void __launch_bounds__(256) ep_combine_partial_peer_f16_kernel(const float *__restrict__ Y,
+                                                                          const int32_t *__restrict__ pair_exp,
+                                                                          const float *__restrict__ pair_w, int exp_lo,
+                                                                          int exp_hi, float *const *__restrict__ parts,
+                                                                          int my_rank, int T_loc, int T, int H, int k,
+                                                                          int64_t parts_off) {
+  const int lane = threadIdx.x & 31;
+  int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (t >= T) return;
+  t += ((my_rank + 1) * T_loc) % T;
+  if (t >= T) t -= T;
+  const int e = lane < k ? pair_exp[t * k + lane] : -1;
+  const float w = lane < k ? pair_w[t * k + lane] : 0.f;
+  const bool mine = lane < k && e >= exp_lo && e < exp_hi;
+  const unsigned m = __ballot_sync(0xffffffffu, mine);
+  const int n = __popc(m);
+  if (n == 0) return;
+  int rank = 0;
+  for (int j = 0; j < k; ++j) {
+    const int ej = __shfl_sync(0xffffffffu, e, j);
+    if (((m >> j) & 1u) && ej < e) ++rank;
+  }
+  int row[8];
+  float ws[8];
+#pragma unroll
+  for (int sl = 0; sl < 8; ++sl) {
+    const unsigned b = __ballot_sync(0xffffffffu, mine && rank == sl);
+    const int src = b ? __ffs(b) - 1 : 0;
+    row[sl] = t * k + src;
+    ws[sl] = __shfl_sync(0xffffffffu, w, src);
+  }
+  const int nit = H >> 8;
+  float acc[8][8];
+  float amax = 0.f;
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[it][j] = 0.f;
+    if (it < nit) {
+      const int h = 256 * it + 8 * lane;
+#pragma unroll
+      for (int sl = 0; sl < 8; ++sl) {
+        if (sl < n) {
+          const float4 a = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)row[sl] * H + h));
+          const float4 b = __ldg(reinterpret_cast<const float4 *>(Y + (size_t)row[sl] * H + h + 4));
+          const float y[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[it][j] = __fadd_rn(acc[it][j], __fmul_rn(ws[sl], y[j]));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(acc[it][j]));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  // power-of-two scale that puts the largest magnitude in [2^14, 2^15); an all-zero, infinite or NaN row keeps 1
+  const int be = (int)((__float_as_uint(amax) >> 23) & 0xffu);
+  int ex = 0;
+  if (be != 0 && be != 0xff) ex = max(-100, min(100, 141 - be));
+  const float scale = __uint_as_float((uint32_t)(ex + 127) << 23), inv = __uint_as_float((uint32_t)(127 - ex) << 23);
+  float *slot = parts[t / T_loc] + parts_off + ((size_t)my_rank * T_loc + (t % T_loc)) * H;
+  __half *out = reinterpret_cast<__half *>(slot);
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    if (it < nit) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 h2 = __floats2half2_rn(fminf(fmaxf(acc[it][2 * j] * scale, -65504.f), 65504.f),
+                                             fminf(fmaxf(acc[it][2 * j + 1] * scale, -65504.f), 65504.f));
+        o[j] = *reinterpret_cast<const uint32_t *>(&h2);
+      }
+      *reinterpret_cast<uint4 *>(out + 256 * it + 8 * lane) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+  if (lane == 0) slot[H / 2] = inv;
+}
+
+// ep_reduce_sel over slots written by ep_combine_partial_peer_f16_kernel
+template <int ODT>
+__global__ void __launch_bounds__(256) ep_reduce_sel_f16_kernel(const float *__restrict__ parts, int n_ranks, int T_loc,
+                                                                const int32_t *__restrict__ pair_exp, int k, int e_loc,
+                                                                const void *__restrict__ resid, int resid_dtype,
+                                                                void *__restrict__ out, int H) {
+  const int t = blockIdx.x;
+  unsigned long long mask = 0;
+  for (int s = 0; s < k; ++s) mask |= 1ull << (pair_exp[t * k + s] / e_loc);
+  for (int h = threadIdx.x * 8; h < H; h += 2048) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int r = 0; r < n_ranks; ++r) {
+      if (!((mask >> r) & 1ull)) continue;
+      const float *slot = parts + ((size_t)r * T_loc + t) * H;
+      const float inv = __ldg(slot + H / 2);
+      const uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(slot) + h));
+      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 h2 = *reinterpret_cast<const __half2 *>(&u[j]);
+        acc[2 * j] = __fadd_rn(acc[2 * j], __low2float(h2) * inv);
+        acc[2 * j + 1] = __fadd_rn(acc[2 * j + 1], __high2float(h2) * inv);
+      }
+    }
+    if (resid) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = __fadd_rn(load_as_f32(resid, resid_dtype, (int64_t)t * H + h + j), acc[j]);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) store_from_f32(out, ODT, (int64_t)t * H + h + j, acc[j]);
+  }
+}
+
 }  // namespace
 
 extern "C" {
@@ -302,6 +420,31 @@ int knj::ep_combine_partial_peer_at(const float *Y, const int32_t *pair_exp, con
   if (T <= 0) return KNJ_OK;
   ep_combine_partial_peer_kernel<<<(T + 7) / 8, 256, 0, s>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, T, H, k, parts_off, stage);
   return launch_status("ep_combine_partial_peer_kernel");
+}
+
+// fp16 form of the partial rows (see the kernels): H <= 2048, a multiple of 256
+int knj::ep_combine_partial_peer_f16_at(const float *Y, const int32_t *pair_exp, const float *pair_w, int T, int H, int k, int exp_lo,
+                                        int exp_hi, float *const *parts_ptrs, int64_t parts_off, int my_rank, int T_loc, cudaStream_t s) {
+  KNJ_REQUIRE(Y && pair_exp && pair_w && parts_ptrs, "knj_ep_combine_partial_peer: null pointer");
+  KNJ_REQUIRE(k >= 1 && k <= 8 && H > 0 && H % 256 == 0 && H <= 2048 && exp_lo <= exp_hi && T_loc >= 1 && my_rank >= 0 && parts_off % 4 == 0,
+              "knj_ep_combine_partial_peer (fp16 rows): bad k / H / expert range / rank");
+  if (T <= 0) return KNJ_OK;
+  ep_combine_partial_peer_f16_kernel<<<(T + 7) / 8, 256, 0, s>>>(Y, pair_exp, pair_w, exp_lo, exp_hi, parts_ptrs, my_rank, T_loc, T, H, k, parts_off);
+  return launch_status("ep_combine_partial_peer_f16_kernel");
+}
+
+int knj::ep_reduce_sel_f16(const float *parts, int n_ranks, int T_loc, int H, const int32_t *pair_exp, int k, int experts_per_rank,
+                           const void *resid, int resid_dtype, void *out, int out_dtype, cudaStream_t s) {
+  KNJ_REQUIRE(parts && pair_exp && out, "knj_ep_reduce_sel: null pointer");
+  KNJ_REQUIRE(n_ranks >= 1 && n_ranks <= 64 && H > 0 && H % 256 == 0 && H <= 2048 && k >= 1 && k <= 8 && experts_per_rank >= 1,
+              "knj_ep_reduce_sel (fp16 rows): bad sizes");
+  KNJ_REQUIRE(out_dtype == KNJ_DT_F32 || out_dtype == KNJ_DT_BF16, "knj_ep_reduce_sel: out must be f32 or bf16");
+  if (T_loc <= 0) return KNJ_OK;
+  if (out_dtype == KNJ_DT_F32)
+    ep_reduce_sel_f16_kernel<KNJ_DT_F32><<<T_loc, 256, 0, s>>>(parts, n_ranks, T_loc, pair_exp, k, experts_per_rank, resid, resid_dtype, out, H);
+  else
+    ep_reduce_sel_f16_kernel<KNJ_DT_BF16><<<T_loc, 256, 0, s>>>(parts, n_ranks, T_loc, pair_exp, k, experts_per_rank, resid, resid_dtype, out, H);
+  return launch_status("ep_reduce_sel_f16_kernel");
 }
 
 extern "C" {

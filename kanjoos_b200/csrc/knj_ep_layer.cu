@@ -160,7 +160,7 @@ struct knj_ep_ctx {
   int *status = nullptr;  // [0] rank waits, [1] GEMMs
   long long wait_cycles = kMaxWaitCycles;
   uint32_t step = 0;      // steps launched so far: the epoch the flag words of a step carry
-  int transport = KNJ_EP_SM_PARTIALS;
+  int transport = KNJ_EP_SM_PARTIALS | KNJ_EP_F16_PARTIALS;
   std::vector<__half *> h_xall;  // host copies of two pointer tables, for the block copies
   std::vector<float *> h_parts;
   float *stage[2] = {nullptr, nullptr};  // partial rows of other ranks' tokens before their block copies, by chunk parity
@@ -292,7 +292,7 @@ int knj_ep_set_wait(knj_ep_ctx *c, long long wait_cycles) {
 }
 
 int knj_ep_set_transport(knj_ep_ctx *c, int transport) {
-  KNJ_REQUIRE(c && transport >= 0 && transport <= (KNJ_EP_SM_ROWS | KNJ_EP_SM_PARTIALS), "knj_ep_set_transport: unknown transport");
+  KNJ_REQUIRE(c && transport >= 0 && transport <= (KNJ_EP_SM_ROWS | KNJ_EP_SM_PARTIALS | KNJ_EP_F16_PARTIALS), "knj_ep_set_transport: unknown transport");
   c->transport = transport;
   return KNJ_OK;
 }
@@ -322,6 +322,8 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
   // ---- main stream: the first chunk's rows as fp16 (ahead of the router, so that their copies run beside it), then
   //      the router over all local tokens (tables in local order)
   const bool ce = !(c->transport & KNJ_EP_SM_ROWS), ce_parts = !(c->transport & KNJ_EP_SM_PARTIALS);
+  // partial rows as fp16 under a per-row scale: only in the form the combining kernel stores itself
+  const bool f16p = (c->transport & KNJ_EP_F16_PARTIALS) && !ce_parts && H <= 2048;
   if (ce) {
     rc = knj_to_f16_launch(x, x_dtype, ldx, Tc_loc, H, c->x_all + (int64_t)rank * Tc_loc * H, s);
     if (rc) return rc;
@@ -383,9 +385,13 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
     ep_wait_kernel<<<1, 64, 0, st>>>(c->flags + (C + ch) * W, W, epoch, c->wait_cycles, c->status);
     int r2 = launch_status("ep_wait_kernel");
     if (r2) return r2;
-    return knj_ep_reduce_sel_launch(c->parts + (size_t)ch * Tc * H, W, Tc_loc, H, c->pe_loc + (size_t)ch * Tc_loc * k, k, c->e_loc,
-                                    residual ? static_cast<const char *>(x) + (size_t)ch * Tc_loc * ldx * x_el : nullptr, x_dtype,
-                                    static_cast<char *>(out) + (size_t)ch * Tc_loc * H * o_el, out_dtype, s);
+    const void *res = residual ? static_cast<const char *>(x) + (size_t)ch * Tc_loc * ldx * x_el : nullptr;
+    void *o = static_cast<char *>(out) + (size_t)ch * Tc_loc * H * o_el;
+    if (f16p)
+      return ep_reduce_sel_f16(c->parts + (size_t)ch * Tc * H, W, Tc_loc, H, c->pe_loc + (size_t)ch * Tc_loc * k, k, c->e_loc, res, x_dtype, o,
+                               out_dtype, st);
+    return knj_ep_reduce_sel_launch(c->parts + (size_t)ch * Tc * H, W, Tc_loc, H, c->pe_loc + (size_t)ch * Tc_loc * k, k, c->e_loc, res,
+                                    x_dtype, o, out_dtype, s);
   };
   for (int ch = 0; ch < C; ++ch) {
     const __half *xa = c->x_all + (size_t)ch * Tc * H;
@@ -432,7 +438,8 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
     } else {
       KNJ_CUDA(cudaEventRecord(c->ev_down[ch], st));
       KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_down[ch], 0));
-      rc = ep_combine_partial_peer_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, nullptr, rank, Tc_loc, side);
+      rc = f16p ? ep_combine_partial_peer_f16_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, rank, Tc_loc, side)
+                : ep_combine_partial_peer_at(Y, pe, pw, Tc, H, k, lo, lo + c->e_loc, c->parts_ptrs, (int64_t)ch * Tc * H, nullptr, rank, Tc_loc, side);
       if (rc) return rc;
     }
     KNJ_CUDA(cudaEventRecord(c->ev_sent[ch], side));

@@ -260,8 +260,8 @@ class EpPeerContext:
         check(lib().knj_ep_create(C.byref(d), C.byref(self._ctx)))
         self.shape = (T_loc, H)
         if os.environ.get("KNJ_EP_TRANSPORT"):  # measurement override: two letters, c(opy) or s(tores), rows then partials
-            t = os.environ["KNJ_EP_TRANSPORT"]
-            self.set_transport(t[0] == "s", t[1] == "s")
+            t = os.environ["KNJ_EP_TRANSPORT"]  # third letter h: partial rows as fp16
+            self.set_transport(t[0] == "s", t[1] == "s", t[2:3] == "h")
 
     @classmethod
     def from_pointers(cls, world, rank, T_loc, H, F, E, k, ptrs, keep=None, n_chunks=1):
@@ -297,11 +297,11 @@ class EpPeerContext:
         from ._lib import check, lib
         check(lib().knj_ep_set_wait(self._ctx, int(cycles)))
 
-    def set_transport(self, sm_rows: bool, sm_partials: bool):
+    def set_transport(self, sm_rows: bool, sm_partials: bool, f16_partials: bool = False):
         """How rows / partial sums reach the peers: stores of the library's kernels (True) or block copies by the
-        copy engines (False). Default: rows as block copies, partial sums as stores."""
+        copy engines (False); f16_partials: the stored partial rows travel as fp16 under a per-row scale."""
         from ._lib import check, lib
-        check(lib().knj_ep_set_transport(self._ctx, (1 if sm_rows else 0) | (2 if sm_partials else 0)))
+        check(lib().knj_ep_set_transport(self._ctx, (1 if sm_rows else 0) | (2 if sm_partials else 0) | (4 if f16_partials else 0)))
 
     def status(self):
         """Synchronises; raises KnjError (KNJ_E_TIMEOUT) if a bounded device-side wait gave up in the last step."""

@@ -156,7 +156,8 @@ def _emulated_ranks(world, T, cfg=403, n_chunks=1):
     return bank, wr, hx, ranks, bufs
 
 
-@pytest.mark.parametrize("sm_stores", [(False, False), (False, True), (True, True)], ids=["copies", "default", "stores"])
+@pytest.mark.parametrize("sm_stores", [(False, False), (False, True), (True, True), (False, True, True)],
+                         ids=["copies", "f32_partials", "stores_both_ways", "default"])
 @pytest.mark.parametrize("world,n_chunks", [(2, 1), (4, 1), (2, 2), (2, 4), (4, 2)])
 def test_layer_object_emulated_ranks_one_gpu(world, n_chunks, sm_stores):
     """The whole data path of knj_ep_forward_launch (row and table stores into every rank's buffers, plan over
