@@ -87,23 +87,25 @@ __global__ void ep_wait_kernel(const uint32_t *mine, int world, uint32_t e, long
   __threadfence_system();
 }
 
-// The rank's rows [r0, r0 + rows) as fp16 into every rank's gathered-rows buffer at element dst_off (16 bytes = 8
-// values per thread and step, one store per destination).
-template <int DT>
-__global__ void __launch_bounds__(256) ep_push_rows_kernel(const void *__restrict__ x, int64_t ldx, int H8, int64_t n8,
-                                                           __half *const *__restrict__ dst, int world, int64_t dst_off) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t r = i / H8, c = 8 * (i - r * H8);
-    float v[8];
-    knj::q4e::load8_f32(x, DT, r * ldx + c, v);
-    uint32_t o[4];
+// The rank's fp16 rows (already in its own slot of the gathered-rows buffer) to the same place in every peer's
+// buffer, as 16-byte stores. The grid is cut into world-1 phases of `cpp` CTAs; phase i stores to rank
+// (rank + 1 + i) % world, and CTAs start in block order, so at any moment every rank is writing to a different peer
+// (all ranks storing to the same peer at once shares that peer's ingress: measured 2x slower).
+__global__ void __launch_bounds__(256) ep_push_rows_kernel(const uint4 *__restrict__ src, __half *const *__restrict__ dst, int64_t off16,
+                                                           int64_t n16, int world, int rank, int cpp) {
+  const int phase = blockIdx.x / cpp, b = blockIdx.x - phase * cpp;
+  int d = rank + 1 + phase;
+  if (d >= world) d -= world;
+  uint4 *out = reinterpret_cast<uint4 *>(dst[d]) + off16;
+  const int64_t stride = (int64_t)cpp * 256;
+  for (int64_t i = (int64_t)b * 256 + threadIdx.x; i < n16; i += 4 * stride) {
+    uint4 v[4];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const __half2 h = __floats2half2_rn(fminf(fmaxf(v[2 * j], -65504.0f), 65504.0f), fminf(fmaxf(v[2 * j + 1], -65504.0f), 65504.0f));
-      o[j] = *reinterpret_cast<const uint32_t *>(&h);
-    }
-    const uint4 u = make_uint4(o[0], o[1], o[2], o[3]);
-    for (int d = 0; d < world; ++d) *reinterpret_cast<uint4 *>(dst[d] + dst_off + r * (int64_t)H8 * 8 + c) = u;
+    for (int u = 0; u < 4; ++u)
+      if (i + u * stride < n16) v[u] = __ldg(src + i + u * stride);
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (i + u * stride < n16) out[i + u * stride] = v[u];
   }
 }
 
@@ -324,10 +326,8 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
   const bool ce = !(c->transport & KNJ_EP_SM_ROWS), ce_parts = !(c->transport & KNJ_EP_SM_PARTIALS);
   // partial rows as fp16 under a per-row scale: only in the form the combining kernel stores itself
   const bool f16p = (c->transport & KNJ_EP_F16_PARTIALS) && !ce_parts && H <= 2048;
-  if (ce) {
-    rc = knj_to_f16_launch(x, x_dtype, ldx, Tc_loc, H, c->x_all + (int64_t)rank * Tc_loc * H, s);
-    if (rc) return rc;
-  }
+  rc = knj_to_f16_launch(x, x_dtype, ldx, Tc_loc, H, c->x_all + (int64_t)rank * Tc_loc * H, s);
+  if (rc) return rc;
   KNJ_CUDA(cudaEventRecord(c->ev_fork, st));
   KNJ_CUDA(cudaStreamWaitEvent(side, c->ev_fork, 0));
   KNJ_CUDA(cudaStreamWaitEvent(c->side2, c->ev_fork, 0));
@@ -342,17 +342,16 @@ int knj_ep_forward_launch(knj_ep_ctx *c, const void *x, int x_dtype, int64_t ldx
   for (int ch = 0; ch < C; ++ch) {
     const int64_t off = ((int64_t)ch * Tc + (int64_t)rank * Tc_loc) * H;
     const void *xc = static_cast<const char *>(x) + (size_t)ch * Tc_loc * ldx * x_el;
-    if (ce) {
-      if (ch > 0) {
-        rc = knj_to_f16_launch(xc, x_dtype, ldx, Tc_loc, H, c->x_all + off, side);
-        if (rc) return rc;
-      }
-    } else {
-      const int64_t n8 = (int64_t)Tc_loc * H / 8, blocks = (n8 + 255) / 256, cap = (int64_t)sm_count() * 4;
-      const unsigned grid = (unsigned)(blocks < cap ? blocks : cap);
-      if (x_dtype == KNJ_DT_F32) ep_push_rows_kernel<KNJ_DT_F32><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
-      else if (x_dtype == KNJ_DT_BF16) ep_push_rows_kernel<KNJ_DT_BF16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
-      else ep_push_rows_kernel<KNJ_DT_F16><<<grid, 256, 0, side>>>(xc, ldx, H / 8, n8, c->xall_ptrs, W, off);
+    if (ch > 0) {
+      rc = knj_to_f16_launch(xc, x_dtype, ldx, Tc_loc, H, c->x_all + off, side);
+      if (rc) return rc;
+    }
+    if (!ce && W > 1) {  // staggered stores of the library's own kernel
+      const int64_t n16 = (int64_t)Tc_loc * H / 8;
+      int cpp = (int)((n16 + 1023) / 1024);
+      if (cpp > 2 * sm_count()) cpp = 2 * sm_count();
+      ep_push_rows_kernel<<<(unsigned)(cpp * (W - 1)), 256, 0, side>>>(reinterpret_cast<const uint4 *>(c->x_all + off), c->xall_ptrs, off / 8, n16, W,
+                                                                      rank, cpp);
       rc = launch_status("ep_push_rows_kernel");
       if (rc) return rc;
     }
