@@ -83,24 +83,29 @@ class StreamedMoeLayer:
 
     def _ensure(self, experts, stream):
         """Make every expert in `experts` slot-resident; evict least-recently-used experts that are not needed."""
+        n_slots = self.pools["gate"].n_slots
+        if len(experts) > n_slots:
+            raise ValueError(f"a step routes to {len(experts)} distinct experts but the pools hold {n_slots} slots: "
+                             "split the step or give the layer more slots")
         need = [e for e in experts if e not in self.slot_of]
+        # victims for ALL three pools leave before any slot is acquired, so the pools stay in lockstep
+        n_evict = max(0, len(self.slot_of) + len(need) - n_slots)
+        victims = sorted((x for x in self.slot_of if x not in experts), key=lambda x: self.last_use[x])[:n_evict]
+        for victim in victims:
+            for kd in ("gate", "up", "down"):
+                pv = self.pools[kd]
+                self.L.knj_res_slot_release(pv.h, self.slot_of[victim])
+                while not self.L.knj_res_slot_released(pv.h, self.slot_of[victim]):
+                    pass  # its loads finished long ago; release completes at once
+            del self.slot_of[victim]
+            self.evictions += 1
         waits = []
         for e in need:
             slots = {}
             for kind in ("gate", "up", "down"):
                 p = self.pools[kind]
                 h = self.L.knj_res_slot_acquire(p.h, self.layer_id, e, p.slot_bytes)
-                if h < 0:
-                    victim = min((x for x in self.slot_of if x not in experts), key=lambda x: self.last_use[x])
-                    for kd in ("gate", "up", "down"):
-                        pv = self.pools[kd]
-                        self.L.knj_res_slot_release(pv.h, self.slot_of[victim])
-                        while not self.L.knj_res_slot_released(pv.h, self.slot_of[victim]):
-                            pass  # its loads finished long ago; release completes at once
-                    del self.slot_of[victim]
-                    self.evictions += 1
-                    h = self.L.knj_res_slot_acquire(p.h, self.layer_id, e, p.slot_bytes)
-                assert h >= 0
+                assert h >= 0, "a slot was freed for every expert that has to come in"
                 slots[kind] = h
             assert len(set(slots.values())) == 1, "the three pools evolve in lockstep"
             for kind, h in slots.items():

@@ -81,6 +81,13 @@ def test_streamed_equals_resident_bit_for_bit():
             torch.cuda.synchronize()
             assert torch.equal(got.view(torch.int32), want.view(torch.int32)), f"step {step}: streamed != resident"
         assert layer.loads > 6 and layer.evictions > 0      # the slots were recycled along the way
+        # a step that routes to more distinct experts than there are slots is refused up front, and the pools stay
+        # usable afterwards
+        many = torch.from_numpy(synth.hidden_rows(799, 12, H)).cuda()
+        with pytest.raises(ValueError):
+            layer.forward(many)
+        x = torch.from_numpy(synth.hidden_rows(701, 3, H)).cuda()
+        assert torch.equal(layer.forward(x).view(torch.int32), layer.forward(x, resident_bank=resident).view(torch.int32))
     finally:
         layer.close()
 
