@@ -44,7 +44,10 @@ namespace q4e {
 
 constexpr int kTileRows = 16;
 constexpr int kStageBytes = kTileRows * KNJ_Q4K_BYTES;  // 2304: one superblock column of a 16-row tile
-constexpr int kJobTok = 8;                              // tokens of one job: one or two groups of 4 (x 2 planes = the MMA's n)
+constexpr int kJobTok = 4;                              // tokens of one job = one MMA column group (4 tokens x 2 planes = the MMA's n).
+                                                        // 8 (two column groups for jobs of five and more tokens) is supported by the code
+                                                        // below and measured slower: a two-group round costs twice a one-group round, so
+                                                        // CTAs that drew such jobs ran 25 % above the mean of a phase
 // Panel of one (token, superblock): eight 128-byte units u = 4 * (sub-block & 1) + (16-byte piece of the
 // sub-block's plane); inside a unit, 16 bytes per (plane, t) at 16 * (4 * plane + t): the eight lanes of a
 // quarter-warp (planes 0/1 of one token, t = 0..3) read one unit without bank conflicts. Then the per-32
@@ -388,7 +391,7 @@ __device__ __forceinline__ void run_phase(const PhaseShape &sh, const PhaseSmem 
       if (sb == 0 && lane == 0) sm.pair[tk] = live ? pair : -1;
     }
     __syncthreads();
-    const bool two = sm.pair[4] >= 0;  // tokens fill the slots from 0 up: a fifth token means a second group
+    const bool two = kJobTok > 4 && sm.pair[kJobTok > 4 ? 4 : 0] >= 0;  // tokens fill the slots from 0 up: a fifth token means a second group
 
     int stage = 0;
     int n0 = (r0 + slot - job * tiles) * rows_per_tile;  // first output row of the tile in progress
