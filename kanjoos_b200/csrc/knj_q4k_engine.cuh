@@ -18,8 +18,9 @@
 //   * the min term is one more MMA per superblock: A = the eight 6-bit m_sb,
 //     B = the per-32 sums of the token's planes.
 //
-// Work split. A JOB is one expert with up to eight of its tokens (one or two MMA
-// column groups of four; the unpacked weights serve both groups); its activations
+// Work split. A JOB is one expert with up to kJobTok of its tokens: four, i.e. one
+// MMA column group (the code also carries the eight-token form, two column groups
+// served by the same unpacked weights, which was measured slower); its activations
 // are converted once per CTA into a PANEL in shared memory, laid out so that a
 // warp's fragment loads are 128 contiguous bytes per quarter-warp. A warp owns a
 // 16-row tile (8 gate + 8 up rows of the same output indices, or 16 rows of one
