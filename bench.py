@@ -512,9 +512,9 @@ def run_gpu(args):
     if world == 1:
         launches = 2 + n_perm + 1 + 2 + 1
     elif args.exchange == "peer":
-        # row stores, router (2), table stores, barrier, local expert ids, plan, gate+up, down, partial sums
-        # to the owners, barrier, rank reduce
-        launches = 1 + 2 + 1 + 1 + 1 + n_perm + 2 + 1 + 1 + 1
+        # rows to fp16, router (2), table stores, arrival, wait, local expert ids, plan, gate+up, down, partial sums to
+        # the owners, arrival, wait, rank reduce (the rows themselves travel as copy-engine copies, not kernels)
+        launches = 1 + 2 + 1 + 1 + 1 + 1 + n_perm + 2 + 1 + 1 + 1 + 1
     elif args.exchange == "gather":
         launches = 2 + 1 + n_perm + 2 + 2
     else:
