@@ -11,8 +11,9 @@
  *     name + `_launch`, same arguments in the same order, plus a trailing
  *     stream (a __global__ symbol cannot be launched by a foreign compiler);
  *   - the Q4_K bench kernels' argument lists (the de-facto ExpertPlan) become
- *     knj_q4k_gateup_launch / knj_q4k_down_launch / knj_q4k_proj_launch /
- *     knj_fuse_gateup_silu_launch;
+ *     knj_q4k_gateup_launch / knj_q4k_proj_launch / knj_q6k_proj_launch /
+ *     knj_fuse_gateup_silu_launch (decode class) and knj_q4k_gateup_tc_launch /
+ *     knj_q4k_down_tc_launch (prefill class);
  *   - the host routing plan and weighted combine of the benches become device
  *     kernels (knj_router_topk_launch, knj_moe_permute_launch,
  *     knj_moe_combine_launch) and the whole layer is one call
@@ -24,9 +25,10 @@
  *     last error on the calling thread.
  *   - All buffers are owned by the caller. The kernel launches allocate no
  *     device memory: those that need scratch take an explicit workspace whose
- *     size a *_workspace_bytes function reports. Three object constructors do
+ *     size a *_workspace_bytes function reports. The object constructors do
  *     allocate and say so where they are declared: knj_moe_stack_create (the
- *     stack launch's scratch), the residency slot pool and the pinned arena
+ *     stack launch's scratch), knj_ep_create (the rank's private scratch of the
+ *     expert-parallel layer), the residency slot pool and the pinned arena
  *     (knj_residency.h). The library image also carries a 64 KiB device array
  *     per GPU, the scratch of knj_q4k_matmul_noalloc_launch.
  *   - Quantized weights are borrowed and immutable: Q4_K superblocks of 144
