@@ -396,7 +396,7 @@ typedef struct knj_moe_ffn_args {
   int32_t *tap_pair_exp;     /* [T*k] */
   float *tap_pair_w;         /* [T*k] */
   /* format of w_down: 0 = Q4_K as above, 1 = Q6_K [E][hidden][ffn/256][210] (the
-   * mixed-format layers of Q4_K_M checkpoints; decode launch only) */
+   * mixed-format layers of Q4_K_M checkpoints; decode launch and whole-stack launch, not the prefill launch) */
   int32_t down_format;
   /* prefill launch: 0 = per-pair rows + the ordered combine kernel (bit-reproducible, the CPU path's summation
    * order; the faster form on B200 at every measured size); 1 = the weighted combine fused into the down GEMM's
@@ -422,7 +422,8 @@ int knj_moe_ffn_status(const knj_moe_ffn_args *a, int mode, knj_stream_t s);
 
 /* The resident decode stack for a decode batch of 1..64 tokens in ONE cooperative
  * launch: n_layers layer descriptions (layer l's out is normally layer l+1's x; out
- * must not alias x within a layer), all of one shape, Q4_K down matrices. The loop
+ * must not alias x within a layer), all of one shape; a layer's down matrices are
+ * Q4_K or Q6_K (down_format, per layer: the mixed-format stacks of Q4_K_M files). The loop
  * the reference runs on the host per layer (src/model/model.cpp:399-510) becomes
  * grid barriers inside one kernel. Same arithmetic class as
  * knj_moe_ffn_decode_launch (f32, <= 1e-5 rel-RMSE vs the CPU path; routing

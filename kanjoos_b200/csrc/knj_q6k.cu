@@ -14,13 +14,14 @@
 // superblock, the warp sums meet in shuffles.
 #include "knj_common.cuh"
 #include "knj_q4k.h"
+#include "knj_q6k_block.cuh"
 
 using namespace knj;
 
 namespace {
 
-constexpr int kQ6Tok = 8;     // tokens per pass (accumulators per lane)
-constexpr int kQ6Rows = 64;   // output rows per work item
+constexpr int kQ6Tok = q6b::kTok;     // tokens per pass (accumulators per lane)
+constexpr int kQ6Rows = q6b::kRows;   // output rows per work item
 constexpr int kQ6Threads = 256;
 
 struct Q6Params {
@@ -31,70 +32,6 @@ struct Q6Params {
   int N, K;
   int64_t idxStride;
 };
-
-// four weights of lane `lane` in half `hf` of a superblock, as sc * (q - 32): positions lane, +32, +64, +96
-__device__ __forceinline__ void q6k_four(const uint8_t *blk, int hf, int lane, float (&w)[4]) {
-  const uint32_t a = blk[64 * hf + lane], b = blk[64 * hf + 32 + lane], h = blk[128 + 32 * hf + lane];
-  const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * hf) + (lane >> 4);
-  w[0] = (float)((int)sc[0] * ((int)((a & 15u) | ((h & 3u) << 4)) - 32));
-  w[1] = (float)((int)sc[2] * ((int)((b & 15u) | (((h >> 2) & 3u) << 4)) - 32));
-  w[2] = (float)((int)sc[4] * ((int)((a >> 4) | (((h >> 4) & 3u) << 4)) - 32));
-  w[3] = (float)((int)sc[6] * ((int)((b >> 4) | (((h >> 6) & 3u) << 4)) - 32));
-}
-
-// Rows of the staged block against NT staged activation rows: a warp takes rows (r, r + 8) together, so that an
-// activation value read from shared memory meets two weights.
-template <int NT>
-__device__ __forceinline__ void q6k_rows(const Q6Params &p, const uint8_t *wbuf, const float *abuf, const int *s_pair, int n0, int rows,
-                                         int nt, int lane, int warp) {
-  constexpr int kW = kQ6Threads / 32;
-  const int nsb = p.K / KNJ_QK_K, row_bytes = nsb * KNJ_Q6K_BYTES;
-  for (int r = warp; r < rows; r += 2 * kW) {
-    const bool two = r + kW < rows;
-    const int r2 = two ? r + kW : r;
-    float acc[2][NT];
-#pragma unroll
-    for (int t = 0; t < NT; ++t) acc[0][t] = acc[1][t] = 0.f;
-    for (int sb = 0; sb < nsb; ++sb) {
-      const uint8_t *b0 = wbuf + (size_t)r * row_bytes + sb * KNJ_Q6K_BYTES, *b1 = wbuf + (size_t)r2 * row_bytes + sb * KNJ_Q6K_BYTES;
-      float part[2][NT];
-#pragma unroll
-      for (int t = 0; t < NT; ++t) part[0][t] = part[1][t] = 0.f;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        float w0[4], w1[4];
-        q6k_four(b0, hf, lane, w0);
-        q6k_four(b1, hf, lane, w1);
-        const float *x = abuf + sb * KNJ_QK_K + hf * 128 + lane;
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          const float *xt = x + (size_t)t * p.K;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float xv = xt[32 * j];
-            part[0][t] = fmaf(w0[j], xv, part[0][t]);
-            part[1][t] = fmaf(w1[j], xv, part[1][t]);
-          }
-        }
-      }
-      const float d0 = knj_half_bits_to_float((uint16_t)(b0[208] | ((uint16_t)b0[209] << 8)));
-      const float d1 = knj_half_bits_to_float((uint16_t)(b1[208] | ((uint16_t)b1[209] << 8)));
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        acc[0][t] = fmaf(d0, part[0][t], acc[0][t]);
-        acc[1][t] = fmaf(d1, part[1][t], acc[1][t]);
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      const float v0 = warp_sum(acc[0][t]), v1 = warp_sum(acc[1][t]);
-      if (lane == 0 && t < nt) {
-        p.Y[(size_t)s_pair[t] * p.N + n0 + r] = v0;
-        if (two) p.Y[(size_t)s_pair[t] * p.N + n0 + r2] = v1;
-      }
-    }
-  }
-}
 
 __global__ void __launch_bounds__(kQ6Threads) q6k_proj_kernel(const Q6Params p) {
   extern __shared__ __align__(16) uint8_t s_raw[];  // [kQ6Rows][row bytes] weights, then [kQ6Tok][K] f32 activations
@@ -110,19 +47,9 @@ __global__ void __launch_bounds__(kQ6Threads) q6k_proj_kernel(const Q6Params p) 
     const int a = it / chunks, chunk = it - a * chunks;
     const int e = p.exp_list[a];
     const int cnt = p.pair_cnt[e];
-    const int n0 = chunk * kQ6Rows, rows = min(kQ6Rows, p.N - n0);
+    const int n0 = chunk * kQ6Rows, n_rows = min(kQ6Rows, p.N - n0);
     __syncthreads();  // the previous item is done with both buffers
-    {  // the block's superblocks: contiguous bytes; 16-byte pieces where the start allows it
-      const uint8_t *src = p.W + ((size_t)e * p.N + n0) * row_bytes;
-      const int bytes = rows * row_bytes;
-      if (((reinterpret_cast<uintptr_t>(src) | (uintptr_t)bytes) & 15u) == 0) {
-        for (int i = threadIdx.x; i < bytes / 16; i += kQ6Threads)
-          reinterpret_cast<uint4 *>(wbuf)[i] = __ldcs(reinterpret_cast<const uint4 *>(src) + i);
-      } else {
-        for (int i = threadIdx.x; i < bytes / 2; i += kQ6Threads)
-          reinterpret_cast<uint16_t *>(wbuf)[i] = reinterpret_cast<const uint16_t *>(src)[i];
-      }
-    }
+    q6b::stage_block(wbuf, p.W + ((size_t)e * p.N + n0) * row_bytes, n_rows * row_bytes, threadIdx.x, kQ6Threads);
     for (int tok0 = 0; tok0 < cnt; tok0 += kQ6Tok) {
       const int nt = min(kQ6Tok, cnt - tok0);
       if (tok0) __syncthreads();  // the previous pass is done with the staged rows
@@ -133,17 +60,8 @@ __global__ void __launch_bounds__(kQ6Threads) q6k_proj_kernel(const Q6Params p) 
         reinterpret_cast<float4 *>(abuf + (size_t)t * p.K)[k4] = __ldg(reinterpret_cast<const float4 *>(p.A + (size_t)s_pair[t] * p.K) + k4);
       }
       __syncthreads();
-      if (nt == 1) q6k_rows<1>(p, wbuf, abuf, s_pair, n0, rows, nt, lane, warp);
-      else if (nt == 2) q6k_rows<2>(p, wbuf, abuf, s_pair, n0, rows, nt, lane, warp);
-      else if (nt <= 4) {
-        for (int i = threadIdx.x; i < (4 - nt) * p.K; i += kQ6Threads) abuf[(size_t)nt * p.K + i] = 0.f;
-        __syncthreads();
-        q6k_rows<4>(p, wbuf, abuf, s_pair, n0, rows, nt, lane, warp);
-      } else {
-        for (int i = threadIdx.x; i < (kQ6Tok - nt) * p.K; i += kQ6Threads) abuf[(size_t)nt * p.K + i] = 0.f;
-        __syncthreads();
-        q6k_rows<kQ6Tok>(p, wbuf, abuf, s_pair, n0, rows, nt, lane, warp);
-      }
+      q6b::rows_any<kQ6Threads / 32>(wbuf, abuf, p.K, n_rows, nt, lane, warp,
+                                     [&](int r, int t, float v) { p.Y[(size_t)s_pair[t] * p.N + n0 + r] = v; });
     }
   }
 }

@@ -24,8 +24,10 @@
 #include "knj_common.cuh"
 #include "knj_q4k.h"
 #include "knj_q4k_engine.cuh"
+#include "knj_q6k_block.cuh"
 #include "knj_topk.cuh"
 
+#include <algorithm>
 #include <vector>
 
 using namespace knj;
@@ -46,6 +48,7 @@ struct LayerDesc {  // copied to shared memory one layer ahead
   const __nv_bfloat16 *Wr;
   const float *bias;
   const __nv_bfloat16 *norm_w;
+  const uint8_t *w_down6;  // non-null: the layer's down matrices are Q6_K [E][H][F/256][210] (no TMA map for them)
   int32_t *tap_exp;
   float *tap_w;
   int64_t ldx, ldo;
@@ -327,9 +330,61 @@ __device__ __noinline__ void stage_plan(const StackParams &p, const LayerDesc &L
       }
       __syncwarp();
       q4e::job_prefix(jbase, lane);
+      if (lane == 0) jbase[259] = total;  // active experts (behind the job table, inside its padding)
     }
     __syncthreads();
 
+}
+
+// Down phase of a layer whose down matrices are Q6_K: (active expert, block of 64 output rows) units dealt round
+// robin over the CTAs; the block's superblocks and the SiLU*up rows of up to eight of the expert's tokens are
+// staged in the (idle) ring area, the arithmetic is knj_q6k_block.cuh's, i.e. the stand-alone projection's.
+__device__ __noinline__ void stage_down_q6k(const StackParams &p, const LayerDesc &L, const Plan &pl, uint8_t *smem) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int H = p.H, F = p.F, k = p.k, c = blockIdx.x, G = gridDim.x;
+  const int *sel_e = reinterpret_cast<const int *>(smem + pl.sel_e);
+  const unsigned long long *mask = reinterpret_cast<const unsigned long long *>(smem + pl.mask);
+  const int *jbase = reinterpret_cast<const int *>(smem + pl.jbase), *uexp = reinterpret_cast<const int *>(smem + pl.uexp);
+  int *s_pair = reinterpret_cast<int *>(smem + pl.inv);  // eight ints: the pass's output rows (the phase engine is idle)
+  const int row_bytes = F / KNJ_QK_K * KNJ_Q6K_BYTES;
+  uint8_t *wbuf = smem + pl.ring;
+  float *abuf = reinterpret_cast<float *>(wbuf + (((size_t)q6b::kRows * row_bytes + 15) & ~(size_t)15));
+  const int blocks = (H + q6b::kRows - 1) / q6b::kRows, n_act = jbase[259];
+  for (int u = c; u < n_act * blocks; u += G) {
+    const int a = u / blocks, rb = u - a * blocks;
+    const int e = uexp[a];
+    const int n0 = rb * q6b::kRows, n_rows = min(q6b::kRows, H - n0);
+    __syncthreads();  // the previous unit is done with both buffers
+    q6b::stage_block(wbuf, L.w_down6 + ((size_t)e * H + n0) * row_bytes, n_rows * row_bytes, threadIdx.x, kThreads);
+    unsigned long long m = mask[e];
+    bool first = true;
+    while (m) {
+      if (!first) __syncthreads();  // the previous pass is done with the staged rows
+      first = false;
+      int nt = 0;
+      unsigned long long mm = m;
+      if (threadIdx.x == 0) {
+        for (; nt < q6b::kTok && mm; ++nt) {
+          const int tok = __ffsll((long long)mm) - 1;
+          mm &= mm - 1;
+          int slot = 0;
+          for (int j = 0; j < k; ++j) slot = sel_e[tok * k + j] == e ? j : slot;
+          s_pair[nt] = tok * k + slot;
+        }
+      }
+      nt = min(q6b::kTok, __popcll(m));
+      for (int i = 0; i < nt; ++i) m &= m - 1;
+      __syncthreads();
+      for (int i = threadIdx.x; i < nt * (F / 4); i += kThreads) {
+        const int t = i / (F / 4), k4 = i - t * (F / 4);
+        reinterpret_cast<float4 *>(abuf + (size_t)t * F)[k4] = __ldcg(reinterpret_cast<const float4 *>(p.act + (size_t)s_pair[t] * F) + k4);
+      }
+      __syncthreads();
+      q6b::rows_any<q4e::kWarps>(wbuf, abuf, F, n_rows, nt, lane, warp,
+                                 [&](int r, int t, float v) { p.Y[(size_t)s_pair[t] * H + n0 + r] = v; });
+    }
+  }
+  __syncthreads();  // the ring area returns to the projection phases
 }
 
 __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParams p) {
@@ -453,7 +508,8 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     KNJ_STAMP(5);
 
     // ---- stage 4: down -> Y (one row per pair)
-    {
+    if (L.w_down6) stage_down_q6k(p, L, pl, smem);
+    else {
       const long long U = (long long)jbase[256] * p.dn.tiles;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
       q4e::run_phase<false>(
@@ -545,7 +601,9 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   const knj_moe_ffn_args &a0 = layers[0];
   const int T = a0.n_tokens, H = a0.hidden, F = a0.ffn, E = a0.n_experts, k = a0.top_k;
   KNJ_REQUIRE(T >= 1 && T <= kMaxT, "knj_moe_stack_create: n_tokens=%d, this launch takes 1..%d", T, kMaxT);
-  if (T <= kSmallStackMaxTokens && !g_force_big_stack) {
+  bool any_q6k = false;  // the scalar kernel of the smallest batches takes Q4_K down matrices only
+  for (int l = 0; l < n_layers; ++l) any_q6k = any_q6k || layers[l].down_format == 1;
+  if (T <= kSmallStackMaxTokens && !g_force_big_stack && !any_q6k) {
     SmallStack *sm = nullptr;
     const int rc = small_stack_create(layers, n_layers, &sm);
     if (rc) return rc;
@@ -570,7 +628,7 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
     KNJ_REQUIRE(a.n_tokens == T && a.hidden == H && a.ffn == F && a.n_experts == E && a.top_k == k,
                 "knj_moe_stack_create: layer %d differs in shape from layer 0", l);
     KNJ_REQUIRE(a.x && a.out && a.w_router && a.w_gate && a.w_up && a.w_down, "knj_moe_stack_create: layer %d: null tensor pointer", l);
-    KNJ_REQUIRE(a.down_format == 0, "knj_moe_stack_create: layer %d: Q6_K down matrices are not taken by this launch", l);
+    KNJ_REQUIRE(a.down_format == 0 || a.down_format == 1, "knj_moe_stack_create: layer %d: unknown format of the down matrices", l);
     KNJ_REQUIRE(a.x_dtype == KNJ_DT_F32 || a.x_dtype == KNJ_DT_BF16, "knj_moe_stack_create: layer %d: x must be f32 or bf16", l);
     KNJ_REQUIRE(a.out_dtype == KNJ_DT_F32 || a.out_dtype == KNJ_DT_BF16, "knj_moe_stack_create: layer %d: out must be f32 or bf16", l);
     KNJ_REQUIRE(a.ldx >= H && a.ldo >= H && a.ldx % 8 == 0 && a.ldo % 4 == 0, "knj_moe_stack_create: layer %d: bad row strides", l);
@@ -583,8 +641,10 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
     LayerMaps &m = maps[l];
     int rc = make_row_tensor_map(&m.mg, a.w_gate, (uint64_t)E * F, (uint32_t)sp.gu.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.gu.sbs * KNJ_Q4K_BYTES, 8);
     if (!rc) rc = make_row_tensor_map(&m.mu, a.w_up, (uint64_t)E * F, (uint32_t)sp.gu.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.gu.sbs * KNJ_Q4K_BYTES, 8);
-    if (!rc) rc = make_row_tensor_map(&m.md, a.w_down, (uint64_t)E * H, (uint32_t)sp.dn.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.dn.sbs * KNJ_Q4K_BYTES, 16);
+    if (!rc && a.down_format == 0)
+      rc = make_row_tensor_map(&m.md, a.w_down, (uint64_t)E * H, (uint32_t)sp.dn.nsb * KNJ_Q4K_BYTES, (uint32_t)sp.dn.sbs * KNJ_Q4K_BYTES, 16);
     if (rc) return rc;
+    s.w_down6 = a.down_format == 1 ? a.w_down : nullptr;
     s.x = a.x;
     s.out = a.out;
     s.Wr = reinterpret_cast<const __nv_bfloat16 *>(a.w_router);
@@ -615,6 +675,11 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
     else --sp.gu.stages;
   }
   const size_t smem = total();
+  if (any_q6k) {  // a Q6_K down phase stages a 64-row block and eight activation rows in the ring area
+    const size_t need = (((size_t)q6b::kRows * (F / 256) * KNJ_Q6K_BYTES + 15) & ~(size_t)15) + (size_t)q6b::kTok * F * 4;
+    const size_t ring = std::max(q4e::phase_ring_bytes(sp.gu.sbs, sp.gu.stages), q4e::phase_ring_bytes(sp.dn.sbs, sp.dn.stages));
+    KNJ_REQUIRE(need <= ring, "knj_moe_stack_create: ffn=%d is too long for the Q6_K down phase's staging (%zu > %zu bytes)", F, need, ring);
+  }
   if (!prop.cooperativeLaunch || smem > (size_t)prop.sharedMemPerBlockOptin) {
     set_error("knj_moe_stack_create: the device lacks cooperative launch or %zu bytes of shared memory per block", smem);
     return KNJ_E_REFUSE;

@@ -85,6 +85,37 @@ def test_stack_follows_layer_by_layer_launches_larger_batches(T):
     st.close()
 
 
+def _q6k_down(cfg, E, H, F):
+    rng = np.random.Generator(np.random.Philox(cfg))
+    W6 = rng.integers(0, 256, size=(E, H, F // 256, 210), dtype=np.uint8)
+    W6[..., 208:210] = (np.abs(rng.standard_normal((E, H, F // 256, 1))) * 0.01).astype(np.float16).view(np.uint8)
+    return W6
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 37, 64])
+def test_mixed_format_stack_q6k_down_follows_the_layer_launches(T):
+    """A stack as Q4_K_M files hold it: the down matrices of every other layer are Q6_K. The whole-stack launch
+    takes them through its own down phase; the layer-by-layer launches (whose Q6_K projection is checked against
+    the CPU decoder) are the comparison, f32 stream so that nothing but summation order may differ."""
+    from kanjoos_b200.moe import ExpertBank, FusedMoeStack, MoeStack
+    L, E, H, F, k = 4, 16, 512, 512, 4
+    banks = []
+    for l in range(L):
+        bank = synth.expert_bank(806, l, n_experts=E, hidden=H, ffn=F)
+        if l % 2 == 1:
+            bank = dict(bank, down=_q6k_down(806 + l, E, H, F))
+        wr, _ = synth.router_weight(806, l, n_experts=E, hidden=H)
+        banks.append(ExpertBank.from_numpy(bank, wr, None, synth.norm_weight(806, l, H)))
+    x = dev(synth.hidden_rows(806, T, H))
+    ref = MoeStack(banks, top_k=k, max_tokens=T).step(x).cpu().numpy()
+    st = FusedMoeStack(banks, top_k=k, n_tokens=T, dtype=torch.float32)
+    got = st.step(x).cpu().numpy()
+    st.status()
+    s = report(got, ref, f"mixed-format stack (Q6_K down in layers 1 and 3), T={T}, fused vs layer launches")
+    assert s["unwritten"] == 0 and s["rel_rmse"] <= 1e-5
+    st.close()
+
+
 @pytest.mark.parametrize("B", [1, 8, 64])
 def test_config4_full_size_stack_checked_layers(B):
     """Config 4: the 48-layer resident stack at full size (about 15 GiB of random-init Q4_K experts), f32 residual
