@@ -357,6 +357,13 @@ int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pai
                            const int32_t *pair_row, float *Y, int N, int K, int rowBytes, int64_t idxStride,
                            int n_experts, int max_pairs, int *status, knj_stream_t s);
 
+/* Grouped down GEMM over Q6_K weights (tools/bench/q4k_stream_ffn.hip:780-829 knj_q6k_down with dq4 = 0; the
+ * mixed-format layers of Q4_K_M files): as knj_q4k_down_tc_launch with W6 [E][N][K/256][210]. The tile's rows are
+ * staged whole in shared memory, so K <= 1024. */
+int knj_q6k_down_tc_launch(const void *Ah, const uint8_t *W6, const int32_t *pair_idx, const int32_t *pair_cnt,
+                           const int32_t *pair_row, float *Y, int N, int K, int64_t idxStride, int n_experts, int max_pairs,
+                           int *status, knj_stream_t s);
+
 /* Grouped down GEMM with the weighted scatter-combine in its epilogue (the sum the
  * reference does on the host, tools/bench/q4k_moe_ffn.hip:682-694, residual
  * tools/bench/q4k_stream_ffn.hip:1305-1313): acc[p / top_k][n] += pair_w[p] * 2^6 *
@@ -396,7 +403,7 @@ typedef struct knj_moe_ffn_args {
   int32_t *tap_pair_exp;     /* [T*k] */
   float *tap_pair_w;         /* [T*k] */
   /* format of w_down: 0 = Q4_K as above, 1 = Q6_K [E][hidden][ffn/256][210] (the
-   * mixed-format layers of Q4_K_M checkpoints; decode launch and whole-stack launch, not the prefill launch) */
+   * mixed-format layers of Q4_K_M checkpoints; the prefill launch takes them for ffn <= 1024) */
   int32_t down_format;
   /* prefill launch: 0 = per-pair rows + the ordered combine kernel (bit-reproducible, the CPU path's summation
    * order; the faster form on B200 at every measured size); 1 = the weighted combine fused into the down GEMM's

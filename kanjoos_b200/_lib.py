@@ -165,6 +165,7 @@ SIGNATURES = {
     "knj_to_f16_launch": (_i, [_vp, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_gateup_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _i, _vp, _vp]),
     "knj_q4k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),
+    "knj_q6k_down_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i, _i, _vp, _vp]),
     "knj_q4k_down_combine_tc_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _i, _i, _i, _i64, _i, _i, _vp, _vp]),
     "knj_moe_acc_init_launch": (_i, [_vp, _i, _i64, _i, _i, _i, _vp, _vp]),
     "knj_moe_acc_finish_launch": (_i, [_vp, _vp, _i, _i64, _i, _i, _vp]),

@@ -189,7 +189,8 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   if (rc) return rc;
   const int T = a->n_tokens, H = a->hidden, F = a->ffn, E = a->n_experts, k = a->top_k;
   KNJ_REQUIRE(H % 128 == 0 && F % 128 == 0, "knj_moe_ffn_prefill: hidden and ffn must be multiples of 128");
-  KNJ_REQUIRE(a->down_format == 0, "knj_moe_ffn_prefill: Q6_K down matrices have no tensor-core form yet; use knj_moe_ffn_decode_launch");
+  KNJ_REQUIRE(a->down_format == 0 || (a->ffn <= 1024 && !a->fused_combine),
+              "knj_moe_ffn_prefill: Q6_K down matrices need ffn <= 1024 and the ordered combine");
   const size_t need = knj_moe_ffn_workspace_bytes(T, H, F, E, k, 1);
   if (!a->workspace || a->workspace_bytes < need) {
     set_error("knj_moe_ffn_prefill: workspace of %zu bytes needed, %zu given", need, a->workspace_bytes);
@@ -252,8 +253,10 @@ int knj_moe_ffn_prefill_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   }
   {
     StageSpan sp("moe-down", s);
-    rc = knj_q4k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, E,
-                                P, w.status, s);
+    rc = a->down_format == 1
+             ? knj_q6k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, T, E, P, w.status, s)
+             : knj_q4k_down_tc_launch(w.ah, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.Y, H, F, F / 256 * KNJ_Q4K_BYTES, T, E,
+                                      P, w.status, s);
     if (rc) return rc;
   }
   StageSpan sp("moe-scatter", s);

@@ -208,7 +208,9 @@ __device__ __forceinline__ uint32_t instr_desc_f16(int m, int n) {
 // the two unpacker warps that own the same 32 weight rows (one per 16-byte half) meet on their own barrier
 __device__ __forceinline__ void pair_sync(int pair) { asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory"); }
 
-template <int NMAT, int CG>
+constexpr int kQ6MaxSb = 4;  // Q6_K form: superblocks per weight row that the whole-tile staging holds (K <= 1024)
+
+template <int NMAT, int CG, int FMT = 0>
 struct Smem {
   // operand tiles: 1024-byte aligned for the swizzle pattern
   static constexpr int kStages = CG == 2 ? 3 : 2;   // operand stages (weights and token rows advance together)
@@ -216,15 +218,24 @@ struct Smem {
   static constexpr int kTokCta = kMaxTok / CG;   // token rows this CTA stages per slab
   static constexpr int kATile = kRowsM * 128;    // 16 KB per matrix per stage
   static constexpr int kBTile = kTokCta * 128;   // 32 KB (16 KB in a pair) per stage
-  static constexpr int kRawBuf = NMAT * kRowsM * KNJ_Q4K_BYTES;
+  // raw weights: Q4_K two buffers of one superblock per row; Q6_K the tile's rows whole, once (its 210-byte
+  // superblocks cannot be fetched as boxes: rows are only 2-byte aligned)
+  static constexpr int kRawBuf = FMT == 1 ? kRowsM * kQ6MaxSb * KNJ_Q6K_BYTES : NMAT * kRowsM * KNJ_Q4K_BYTES;
   static constexpr int kOffA = 0;
   static constexpr int kOffB = kOffA + kStagesA * NMAT * kATile;
   static constexpr int kOffRaw = kOffB + kStagesB * kBTile;
-  static constexpr int kOffPairs = kOffRaw + 2 * kRawBuf;       // int32 pair id per token of the bucket
+  static constexpr int kOffPairs = kOffRaw + (FMT == 1 ? kRawBuf : 2 * kRawBuf);  // int32 pair id per token of the bucket
   static constexpr int kOffRows = kOffPairs + kMaxTok * 4;      // int32 activation row per token
   static constexpr int kOffBars = kOffRows + kMaxTok * 4;       // mbarriers
   static constexpr int kBytes = kOffBars + 256 + 1024;          // + alignment slack
 };
+
+// sixteen bytes from a 2-byte aligned shared-memory address as four words
+__device__ __forceinline__ void lds16_u16(const uint8_t *p, uint32_t (&w)[4]) {
+  const uint16_t *h = reinterpret_cast<const uint16_t *>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w[i] = (uint32_t)h[2 * i] | ((uint32_t)h[2 * i + 1] << 16);
+}
 
 // NMAT = 2 with GATEUP: gate and up tiles of the same 128 output indices (one shared token operand, SiLU*up
 // epilogue). NMAT = 2 without: two consecutive 128-row tiles of one matrix (halves the token-operand traffic
@@ -233,9 +244,13 @@ struct Smem {
 // each CTA unpacks its own weight tiles and stages half of the bucket's token rows, so the token operand
 // crosses L2 -> shared memory once per 256 weight rows instead of once per 128. The even CTA issues the MMAs;
 // producers of both CTAs arrive on its "full" barriers, and it commits to the "empty" barriers of both.
-template <int NMAT, bool GATEUP, int CG>
+// FMT = 1: the weights are Q6_K (single matrix, NMAT = 1): the tile's 128 rows are staged whole with 16-byte loads
+// by the unpackers themselves and decoded per slab (w = d * sc * (q - 32), formed in fp16 as (1024 + q - 1056) *
+// fp16(d * sc)); everything downstream of the operand tile is the Q4_K form's.
+template <int NMAT, bool GATEUP, int CG, int FMT = 0>
 __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __grid_constant__ TcParams p) {
-  using S = Smem<NMAT, CG>;
+  static_assert(FMT == 0 || (NMAT == 1 && !GATEUP), "the Q6_K form is the single-matrix projection");
+  using S = Smem<NMAT, CG, FMT>;
   constexpr int kStages = S::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -351,7 +366,61 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;  // once false this thread skips all work and waits but still meets every barrier
 
-  if (warp < 8) {
+  if (FMT == 1 && warp < 8) {
+    // =========================== producers, Q6_K ===========================
+    const int row = tid & 127, half = tid >> 7;  // weight row, which 16 of a quadrant's 32 weights
+    const int row_bytes = nsb * KNJ_Q6K_BYTES;
+    uint8_t *rawq = smem + S::kOffRaw;
+    {  // the tile's rows: contiguous in HBM, on a 16-byte boundary (tiles start at multiples of 128 rows)
+      const uint4 *src = reinterpret_cast<const uint4 *>(p.W0 + ((size_t)e * p.N + m0) * row_bytes);
+      for (int i = tid; i < kRowsM * row_bytes / 16; i += kProducerThreads) reinterpret_cast<uint4 *>(rawq)[i] = __ldcs(src + i);
+    }
+    asm volatile("bar.sync 6, 256;" ::: "memory");
+    const uint8_t *rrow = rawq + (size_t)row * row_bytes;
+    const __half2 k1056 = __float2half2_rn(1056.0f);  // 1024 (the byte-to-fp16 trick) + 32 (the code's offset)
+    for (int ks = 0; ks < nslab; ++ks) {
+      if (*s_fail) ok = false;
+      if (!ok) break;
+      const int stage = ks % kStages;
+      if (ks >= kStages && !mbar_wait(&empty[stage], ((ks / kStages) - 1) & 1, s_fail)) { ok = false; break; }
+      tc_fence_after();
+      const int sl = ks & 3, hf = sl >> 1;
+      const uint8_t *blk = rrow + (ks >> 2) * KNJ_Q6K_BYTES;
+      const float d = __half2float(__ushort_as_half(*reinterpret_cast<const uint16_t *>(blk + 208)));
+      uint32_t qh[4];
+      lds16_u16(blk + 128 + 32 * hf + 16 * half, qh);
+      uint8_t *at = smem + S::kOffA + stage * S::kATile + row * 128;
+#pragma unroll
+      for (int par = 0; par < 2; ++par) {
+        const int c = 2 * (sl & 1) + par;  // quadrant of the 128-weight half: weights 32 c + l, l = 16 half + [0, 16)
+        uint32_t ql[4];
+        lds16_u16(blk + 64 * hf + 32 * par + 16 * half, ql);
+        const float sc = (float)reinterpret_cast<const int8_t *>(blk)[192 + 8 * hf + half + 2 * c];
+        const __half2 ds = __float2half2_rn(d * sc);
+        uint32_t o[8];
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint32_t nib = ((sl & 1) ? (ql[w] >> 4) : ql[w]) & 0x0f0f0f0fu;
+          const uint32_t q4 = nib | (((qh[w] >> (2 * c)) & 0x03030303u) << 4);
+          const uint32_t e01 = __byte_perm(q4, 0x64646464u, 0x4140);
+          const uint32_t e23 = __byte_perm(q4, 0x64646464u, 0x4342);
+          const __half2 h01 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&e01), k1056), ds);
+          const __half2 h23 = __hmul2(__hsub2(*reinterpret_cast<const __half2 *>(&e23), k1056), ds);
+          o[2 * w] = *reinterpret_cast<const uint32_t *>(&h01);
+          o[2 * w + 1] = *reinterpret_cast<const uint32_t *>(&h23);
+        }
+        const int c0 = 4 * par + 2 * half;
+        *reinterpret_cast<uint4 *>(at + (((c0) ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4 *>(at + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) {
+        if (CG == 2) mbar_arrive_cluster(cluster_addr(&full[stage], 0));
+        else mbar_arrive(&full[stage]);
+      }
+    }
+  } else if (warp < 8) {
     // =========================== producers ===========================
     const int row = tid & 127, half = tid >> 7;  // weight row, which 16 of the slab's 32 code bytes
     const int pair = warp & 3;                   // rows 32*pair .. 32*pair+31: this warp and warp ^ 4
@@ -668,18 +737,18 @@ __global__ void __launch_bounds__(256) acc_finish_kernel(const float *__restrict
   }
 }
 
-template <int NMAT, bool GATEUP, int CG>
+template <int NMAT, bool GATEUP, int CG, int FMT = 0>
 int launch_tc_cg(TcParams p, int max_pairs, cudaStream_t st) {
-  using S = Smem<NMAT, CG>;
+  using S = Smem<NMAT, CG, FMT>;
   int dev = 0;
   KNJ_CUDA(cudaGetDevice(&dev));
-  auto kern = q4k_grouped_tc_kernel<NMAT, GATEUP, CG>;
+  auto kern = q4k_grouped_tc_kernel<NMAT, GATEUP, CG, FMT>;
   static bool opted[64] = {false};
   if (dev >= 0 && dev < 64 && !opted[dev]) {
     KNJ_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kBytes));
     opted[dev] = true;
   }
-  {
+  if (FMT == 0) {
     const uint64_t rows = (uint64_t)p.n_experts * p.N;
     int rc = make_row_tensor_map(&p.map0, p.W0, rows, (uint32_t)p.rowBytes, KNJ_Q4K_BYTES, 32);
     if (rc) return rc;
@@ -790,6 +859,26 @@ int knj_q4k_down_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pai
   }
   p.m_tiles = N / kRowsM;
   return launch_tc<1, false>(p, max_pairs, as_stream(s));
+}
+
+// Grouped down GEMM over Q6_K weights (the mixed-format layers of Q4_K_M files): as knj_q4k_down_tc_launch with
+// W6 [E][N][K/256][210]; K <= 1024 (the tile's rows are staged whole).
+int knj_q6k_down_tc_launch(const void *Ah, const uint8_t *W6, const int32_t *pair_idx, const int32_t *pair_cnt,
+                           const int32_t *pair_row, float *Y, int N, int K, int64_t idxStride, int n_experts, int max_pairs,
+                           int *status, knj_stream_t s) {
+  KNJ_REQUIRE(Ah && W6 && pair_idx && pair_cnt && Y, "knj_q6k_down_tc: null pointer");
+  KNJ_REQUIRE(K > 0 && K % 256 == 0 && K <= 256 * kQ6MaxSb, "knj_q6k_down_tc: K=%d must be a multiple of 256, at most %d", K, 256 * kQ6MaxSb);
+  KNJ_REQUIRE(N > 0 && N % kRowsM == 0, "knj_q6k_down_tc: N=%d must be a multiple of 128", N);
+  KNJ_REQUIRE(aligned16(W6) && aligned16(Ah), "knj_q6k_down_tc: bases must be 16-byte aligned");
+  KNJ_REQUIRE(n_experts >= 1 && n_experts <= 256 && max_pairs >= 0, "knj_q6k_down_tc: bad expert / pair counts");
+  if (max_pairs == 0) return KNJ_OK;
+  TcParams p{};
+  p.X = static_cast<const __half *>(Ah); p.W0 = W6; p.W1 = nullptr; p.pair_idx = pair_idx; p.pair_cnt = pair_cnt;
+  p.row_map = pair_row; p.out = Y; p.N = N; p.K = K; p.rowBytes = K / 256 * KNJ_Q6K_BYTES; p.row_div = 1;
+  p.n_experts = n_experts; p.idxStride = idxStride; p.out_scale = 1.0f / kActPrescale; p.status = status; KNJ_TC_SET_TRACE(p);
+  p.m_tiles = N / kRowsM;
+  if (p.m_tiles % 2 == 0 && !g_tc_force_single) return launch_tc_cg<1, false, 2, 1>(p, max_pairs, as_stream(s));
+  return launch_tc_cg<1, false, 1, 1>(p, max_pairs, as_stream(s));
 }
 
 int knj_q4k_down_combine_tc_launch(const void *Ah, const uint8_t *Wd, const int32_t *pair_idx, const int32_t *pair_cnt,

@@ -221,6 +221,18 @@ def q4k_gateup_tc(xh, Wg, Wu, pair_idx, pair_cnt, P: int, top_k: int, pair_tok=N
     return A, status
 
 
+def q6k_down_tc(ah, W6, pair_idx, pair_cnt, P: int, pair_row=None):
+    """Grouped down GEMM over Q6_K weights [E][N][K/256][210] (K <= 1024): fp16 activations as the gate+up GEMM
+    writes them -> Y f32 [P][N]."""
+    _need(ah, torch.float16), _need(W6, torch.uint8)
+    E, N, nsb, _ = W6.shape
+    Y = torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    check(lib().knj_q6k_down_tc_launch(_p(ah), _p(W6), _p(pair_idx), _p(pair_cnt), _p(pair_row), _p(Y), N, nsb * 256,
+                                       pair_idx.shape[1], E, P, _p(status), _stream()))
+    return Y, status
+
+
 def q4k_down_tc(ah, Wd, pair_idx, pair_cnt, P: int, pair_row=None, poison: bool = True):
     _need(ah, torch.float16)
     E, N, nsb, _ = Wd.shape

@@ -77,3 +77,43 @@ def _grouped_gemms(ops, E, F, H, counts):
             want_y[rows] = ol.matmul_q4k(Wd[e], np.ascontiguousarray(A_host[rows]))
     sty = report(Y.cpu().numpy(), want_y, "tc down")
     assert sty["unwritten"] == 0 and sty["rel_rmse"] <= TOL
+
+
+@pytest.mark.parametrize("E,F,H,counts,single_sm", [
+    (3, 256, 512, [16, 300, 0], 0),    # CTA pairs, a ragged and a two-bucket expert, an empty one
+    (2, 768, 2048, [33, 7], 0),        # the full-size down shape: three superblocks per row
+    (2, 512, 384, [130, 9], 0),        # 384 = 3 x 128 rows: odd tile count, single-SM form
+    (2, 1024, 256, [256, 255], 1),     # four superblocks per row (the staging's limit), single SMs forced
+])
+def test_q6k_down_gemm(E, F, H, counts, single_sm):
+    """The grouped down GEMM over Q6_K weights (whole-tile staging, per-slab decode) against the CPU decoder and
+    a double-precision product, on fp16 activations scaled as the gate+up GEMM writes them."""
+    from kanjoos_b200 import ops, _lib
+    rng = np.random.Generator(np.random.Philox([E, F, H, 6]))
+    T = int(sum(counts))
+    pe = np.concatenate([np.full(c, e, np.int32) for e, c in enumerate(counts)])
+    pe = pe[rng.permutation(T)]
+    nsb = F // 256
+    W6 = rng.integers(0, 256, size=(E, H, nsb, 210), dtype=np.uint8)
+    W6[..., 208:210] = (np.abs(rng.standard_normal((E, H, nsb, 1))) * 0.01).astype(np.float16).view(np.uint8)
+    Wd = np.empty((E * H * nsb, 256), np.float32)
+    ol.oracle().knj_or_dequant_q6k(ol.ptr(W6, ol.u8p), ol.ptr(Wd, ol.f32p), Wd.size)
+    Wd = Wd.reshape(E, H, F)
+    a = (rng.standard_normal((T, F)) * 3.0).astype(np.float32)
+    ah = torch.from_numpy((a / 64.0).astype(np.float16)).cuda()      # the 2^-6 prescale of the stored activations
+    a_seen = ah.float().cpu().numpy() * 64.0
+    pair_idx, pair_cnt, _, _ = ops.moe_permute(dev(pe), E, T)
+    _lib.lib().knj_q4k_tc_single_sm(single_sm)
+    try:
+        Y, st = ops.q6k_down_tc(ah, dev(W6), pair_idx, pair_cnt, T)
+        torch.cuda.synchronize()
+    finally:
+        _lib.lib().knj_q4k_tc_single_sm(0)
+    assert int(st.item()) == 0, "a bounded wait inside the kernel gave up"
+    want = np.zeros((T, H), np.float32)
+    for e in range(E):
+        rows = np.nonzero(pe == e)[0]
+        if len(rows):
+            want[rows] = (a_seen[rows].astype(np.float64) @ Wd[e].astype(np.float64).T).astype(np.float32)
+    sty = report(Y.cpu().numpy(), want, f"tc down, Q6_K, E={E} F={F} H={H} counts={counts}")
+    assert sty["unwritten"] == 0 and sty["rel_rmse"] <= TOL
