@@ -230,11 +230,18 @@ struct Smem {
   static constexpr int kBytes = kOffBars + 256 + 1024;          // + alignment slack
 };
 
-// sixteen bytes from a 2-byte aligned shared-memory address as four words
+// sixteen bytes from a 2-byte aligned shared-memory address as four words: five aligned words, shifted by two
+// bytes where the address is odd in units of two (the word past the sixteen bytes is read but, when the address
+// is aligned, not used; callers keep it inside their own data)
 __device__ __forceinline__ void lds16_u16(const uint8_t *p, uint32_t (&w)[4]) {
-  const uint16_t *h = reinterpret_cast<const uint16_t *>(p);
+  const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+  const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+  const uint32_t sel = (a & 2) ? 0x5432u : 0x3210u;
+  uint32_t v[5];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) w[i] = (uint32_t)h[2 * i] | ((uint32_t)h[2 * i + 1] << 16);
+  for (int i = 0; i < 5; ++i) v[i] = q[i];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) w[i] = __byte_perm(v[i], v[i + 1], sel);
 }
 
 // NMAT = 2 with GATEUP: gate and up tiles of the same 128 output indices (one shared token operand, SiLU*up
@@ -344,6 +351,18 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     *s_fail = 0;
     if (CG == 2) asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     else mbar_init_fence();
+    if (FMT == 1) {
+      // Q6_K: the tile's 128 rows are contiguous in HBM and start on a 16-byte boundary (tiles start at multiples
+      // of 128 rows, 32 rows are a multiple of 16 bytes): four bulk copies, one per 32-row group, each on its own
+      // barrier, under way while the rest of the prologue runs
+      const uint32_t grp = 32u * (uint32_t)(p.K / KNJ_QK_K) * KNJ_Q6K_BYTES;
+      const uint8_t *src = p.W0 + ((size_t)e * p.N + m_tile * kRowsM) * (size_t)(grp / 32u);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        mbar_expect_tx(&raw_full[g], grp);
+        bulk_g2s(smem + S::kOffRaw + g * grp, src + (size_t)g * grp, grp, &raw_full[g]);
+      }
+    }
   }
   for (int i = tid; i < kMaxTok; i += kThreads) {
     int pr = -1, rw = -1;
@@ -371,11 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4k_grouped_tc_kernel(const __gri
     const int row = tid & 127, half = tid >> 7;  // weight row, which 16 of a quadrant's 32 weights
     const int row_bytes = nsb * KNJ_Q6K_BYTES;
     uint8_t *rawq = smem + S::kOffRaw;
-    {  // the tile's rows: contiguous in HBM, on a 16-byte boundary (tiles start at multiples of 128 rows)
-      const uint4 *src = reinterpret_cast<const uint4 *>(p.W0 + ((size_t)e * p.N + m0) * row_bytes);
-      for (int i = tid; i < kRowsM * row_bytes / 16; i += kProducerThreads) reinterpret_cast<uint4 *>(rawq)[i] = __ldcs(src + i);
-    }
-    asm volatile("bar.sync 6, 256;" ::: "memory");
+    if (!mbar_wait(&raw_full[warp & 3], 0, s_fail)) ok = false;  // this warp's 32 rows have landed
     const uint8_t *rrow = rawq + (size_t)row * row_bytes;
     const __half2 k1056 = __float2half2_rn(1056.0f);  // 1024 (the byte-to-fp16 trick) + 32 (the code's offset)
     for (int ks = 0; ks < nslab; ++ks) {
