@@ -187,8 +187,10 @@ def run_reference(args):
 
 
 def workload_config(args, world):
-    return {"workload": f"ep_moe_layer_T{args.tokens}_{args.routing}", "hidden": H, "ffn": F, "experts": E,
-            "top_k": TOPK, "tokens_per_step": args.tokens, "experts_per_gpu": E // world, "weight_format": "GGUF Q4_K",
+    q6 = getattr(args, "down_format", "q4k") == "q6k"
+    return {"workload": f"ep_moe_layer_T{args.tokens}_{args.routing}" + ("_q6k_down" if q6 else ""), "hidden": H, "ffn": F,
+            "experts": E, "top_k": TOPK, "tokens_per_step": args.tokens, "experts_per_gpu": E // world,
+            "weight_format": "GGUF Q4_K gate/up, Q6_K down" if q6 else "GGUF Q4_K",
             "l2_policy": "inputs larger than L2: steps rotate over distinct weight banks",
             "parallelism": f"ep{world}"}
 
@@ -261,7 +263,15 @@ def check_parity(torch, args, world, rank, e_loc, n_banks, banks, router, bias, 
             rows, slots = np.nonzero(ch == e)
             g = ol.matmul_q4k(bank["gate"][e], hx[rows])
             u = ol.matmul_q4k(bank["up"][e], hx[rows])
-            want[rows] += wts[rows, slots][:, None] * ol.matmul_q4k(bank["down"][e], ol.silu_mul(g, u))
+            a = ol.silu_mul(g, u)
+            if bank["down"].shape[-1] == 210:   # Q6_K: the CPU decoder and a double-precision product
+                w6 = np.ascontiguousarray(bank["down"][e])
+                wd = np.empty((w6.shape[0] * w6.shape[1], 256), np.float32)
+                ol.oracle().knj_or_dequant_q6k(ol.ptr(w6, ol.u8p), ol.ptr(wd, ol.f32p), wd.size)
+                y = (a.astype(np.float64) @ wd.reshape(w6.shape[0], -1).astype(np.float64).T).astype(np.float32)
+            else:
+                y = ol.matmul_q4k(bank["down"][e], a)
+            want[rows] += wts[rows, slots][:, None] * y
         ref_kind = "CPU path (oracle) on the device's routing decision"
     else:
         n = min(256, x.shape[0])
@@ -289,6 +299,8 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if args.down_format == "q6k" and world > 1:
+        raise SystemExit("--down-format q6k is a single-GPU measurement (the expert-parallel layer holds Q4_K banks)")
     from kanjoos_b200 import _lib, ops
     from kanjoos_b200.ep import CudaCompute, EpMoeLayer
     from kanjoos_b200.moe import ExpertBank, MoeFfnLayer
@@ -321,6 +333,13 @@ def run_gpu(args):
     for i in range(n_banks):
         bk = ExpertBank.random(n_experts=e_loc, seed=100 + 17 * i + 1000 * rank, with_norm=False)
         bk.router, bk.router_bias = router, bias
+        if args.down_format == "q6k":
+            g6 = torch.Generator(device="cuda")
+            g6.manual_seed(7000 + i)
+            w6 = torch.randint(0, 256, (e_loc, H, F // 256, 210), dtype=torch.uint8, device="cuda", generator=g6)
+            d6 = (torch.randn((e_loc, H, F // 256, 1), device="cuda", generator=g6).abs() * 0.002).to(torch.float16)
+            w6[..., 208:210] = d6.view(torch.uint8).reshape(e_loc, H, F // 256, 2)
+            bk.down = w6
         banks.append(bk)
     gx = torch.Generator(device="cuda")
     gx.manual_seed(11 + rank)
@@ -461,6 +480,29 @@ def run_gpu(args):
         e1.record()
         torch.cuda.synchronize()
         ms_k = e0.elapsed_time(e1) / args.steps
+        # the down GEMM alone, over the rows the gate+up launch has just left in A
+        Y = torch.empty((T_loc * TOPK, H), dtype=torch.float32, device="cuda")
+
+        def down(i):
+            bk = banks[i % n_banks]
+            common = (C.c_void_p(pair_idx.data_ptr()), C.c_void_p(pair_cnt.data_ptr()), None, C.c_void_p(Y.data_ptr()), H, F)
+            tail = (pair_idx.shape[1], e_loc, T_loc * TOPK, C.c_void_p(status.data_ptr()),
+                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
+            if bk.down.shape[-1] == 210:
+                _lib.check(_lib.lib().knj_q6k_down_tc_launch(C.c_void_p(A.data_ptr()), C.c_void_p(bk.down.data_ptr()), *common, *tail))
+            else:
+                _lib.check(_lib.lib().knj_q4k_down_tc_launch(C.c_void_p(A.data_ptr()), C.c_void_p(bk.down.data_ptr()), *common,
+                                                             (F // 256) * 144, *tail))
+        for i in range(3):
+            down(i)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(args.steps):
+            down(3 + i)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_d = e0.elapsed_time(e1) / args.steps
+        del Y
         flops = rows * 2 * 2 * H * F
         t_tensor = flops / (pk["bf16_tflops"] * 1e12)
         assert int(status.item()) == 0, "a bounded wait inside the grouped GEMM gave up"
@@ -477,7 +519,11 @@ def run_gpu(args):
                 "peak_source": pk["_source"], "traffic": traffic, "traffic_note": traffic_note, "ms_per_launch": ms_k,
                 "algorithmic_flops_per_launch": flops,
                 "weight_bytes_per_launch": int((pair_cnt > 0).sum().item()) * 2 * F * (H // 256) * 144,
-                "t_tensor_ms": t_tensor * 1e3}
+                "t_tensor_ms": t_tensor * 1e3,
+                "down": {"kernel": ("q4k_grouped_tc_kernel<1,false,2,1> (Q6_K down)" if args.down_format == "q6k"
+                                    else "q4k_grouped_tc_kernel<2,false,2> (Q4_K down)"),
+                         "ms_per_launch": ms_d, "achieved": rows * 2 * H * F / (ms_d * 1e-3) / 1e12, "unit": "TFLOP/s",
+                         "frac": rows * 2 * H * F / (ms_d * 1e-3) / 1e12 / pk["bf16_tflops"]}}
 
     # parity, outside the timed regions: the first rows of rank 0's shard against the CPU path (N = 1: 64 tokens on
     # the device's routing decision) or against the single-GPU layer over the same experts (N > 1: 256 tokens)
@@ -499,9 +545,9 @@ def run_gpu(args):
     cb = None
     dec = None
     if world == 1:
-        if args.cpu_sample > 0:
+        if args.cpu_sample > 0 and args.down_format == "q4k":   # the CPU arm is the Q4_K layer
             cb, _ = cpu_layer_tokens_per_s(args.cpu_sample, 3, 1, "uniform")
-        if not args.no_decode:
+        if not args.no_decode and args.down_format == "q4k":
             del banks, layers
             torch.cuda.empty_cache()
             dec = decode_section(torch, max(5, args.steps), args.warmup, pk)
@@ -544,6 +590,9 @@ def main():
     ap.add_argument("--routing", default="uniform", choices=["uniform", "zipf"])
     ap.add_argument("--cpu-sample", type=int, default=1024, dest="cpu_sample")
     ap.add_argument("--no-decode", action="store_true")
+    ap.add_argument("--down-format", default="q4k", choices=["q4k", "q6k"], dest="down_format",
+                    help="q6k: the layer's down matrices are Q6_K, as in the mixed-format layers of Q4_K_M files (N = 1, "
+                         "prefill section only)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "gather", "dispatch"], help="expert-parallel exchange (N > 1)")
     ap.add_argument("--section", default="all", choices=["all", "decode"])
     ap.add_argument("--decode-layers", type=int, default=LAYERS, dest="decode_layers")
