@@ -95,7 +95,7 @@ SIGNATURES = {
     "knj_dot_helpers_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "knj_q4k_dequant_launch": (_i, [_vp, _vp, _u64, _vp]),
     "knj_q6k_dequant_launch": (_i, [_vp, _vp, _u64, _vp]),
-    "knj_q6k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i, _vp]),
+    "knj_q6k_proj_launch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i64, _i, _vp, _vp]),
     "knj_rmsnorm_launch": (_i, [_vp, _i, _i64, _vp, _f, _i, _i, _vp, _vp]),
     "knj_router_topk_launch": (_i, [_vp, _i, _i64, _vp, _vp, _i, _i, _i, _i, _vp, _vp, _vp, _vp]),
     "knj_moe_permute_launch": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp]),

@@ -76,6 +76,9 @@ inline cudaError_t launch_chain(void (*kern)(KArgs...), dim3 grid, dim3 block, s
 int make_row_tensor_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t row_bytes, uint32_t box_bytes,
                         uint32_t box_rows);
 
+// Limit (SM clock cycles) of the bounded waits of the decode-class kernels, as set by knj_decode_wait_limit.
+long long decode_wait_cycles();
+
 // The cooperative stack launch for the smallest batches (knj_stack_small.cu), behind knj_moe_stack_*.
 struct SmallStack;
 constexpr int kSmallStackMaxTokens = 2;  // measured: from 3 tokens on the tensor-core kernel is the faster one

@@ -170,8 +170,8 @@ int knj_moe_ffn_decode_launch(const knj_moe_ffn_args *a, knj_stream_t s) {
   }
   StageSpan sp_down("moe-down", s);  // down projection and the weighted combine (to the end of the launch)
   if (a->down_format == 1) {
-    // mixed-format layer: Q6_K down matrices (210-byte superblocks) through the plain f32 projection
-    rc = knj_q6k_proj_launch(w.A, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F, T, E, s);
+    // mixed-format layer: Q6_K down matrices (210-byte superblocks) through their own decode-class projection
+    rc = knj_q6k_proj_launch(w.A, a->w_down, w.pair_idx, w.pair_cnt, w.exp_list, w.n_active, w.Y, H, F, T, E, w.status + 1, s);
     if (rc) return rc;
   } else {
     rc = knj_q4k_proj_launch(w.A, KNJ_DT_F32, F, a->w_down, w.pair_idx, w.pair_cnt, nullptr, w.exp_list, w.n_active, w.Y, H,

@@ -191,6 +191,10 @@ int check_rows(const void *X, int dtype, int64_t ld, int K, const char *who) {
 
 }  // namespace
 
+namespace knj {
+long long decode_wait_cycles() { return g_decode_wait_cycles; }
+}  // namespace knj
+
 extern "C" {
 
 #ifdef KNJ_TRACE

@@ -5,13 +5,14 @@
 // (tools/bench/q4k_stream_ffn.hip:780-829) and the CPU dot_q6_k
 // (src/loader/dequant.cpp:986-1022).
 //
-// f32 throughout. A CTA takes (expert, block of up to 64 output rows): the block's superblocks are contiguous in
-// HBM and start on a 16-byte boundary every eighth row (rows themselves are only 2-byte aligned, so there are no
-// TMA boxes here), and are staged into shared memory with 16-byte loads, once for all of the expert's tokens; the
-// activation rows of up to 8 tokens are staged beside them. A warp then walks a row: lane l decodes the four
-// weights l, l+32, l+64, l+96 of each 128-weight half (two code bytes, one byte of high bit pairs, four int8
-// scales), forms sc * (q - 32) in integers, and feeds one FMA per weight and token; d is applied once per
-// superblock, the warp sums meet in shuffles.
+// A CTA takes (expert, block of 64 output rows): a block's superblocks are contiguous in HBM and start
+// on a 16-byte boundary (rows themselves are only 2-byte aligned, so there are no TMA boxes here); they travel as one
+// bulk copy per block while the CTA prepares the activation side of up to 8 of the expert's tokens (two CTAs per SM:
+// one's block travels while the other computes). With one or two tokens a warp walks a
+// row: lane l decodes the four weights l, l+32, l+64, l+96 of each 128-weight half (two code bytes, one byte of high
+// bit pairs, four int8 scales), forms sc * (q - 32) in integers, and feeds one FMA per weight and token; d is applied
+// once per superblock, the warp sums meet in shuffles. From three tokens on the block runs on mma.sync.m16n8k16
+// (one k-step per 16-weight scale group, activations as two fp16 planes: knj_q6k_block.cuh).
 #include "knj_common.cuh"
 #include "knj_q4k.h"
 #include "knj_q6k_block.cuh"
@@ -20,9 +21,11 @@ using namespace knj;
 
 namespace {
 
-constexpr int kQ6Tok = q6b::kTok;     // tokens per pass (accumulators per lane)
-constexpr int kQ6Rows = q6b::kRows;   // output rows per work item
-constexpr int kQ6Threads = 256;
+constexpr int kQ6Tok = q6b::kTok;     // tokens per pass
+constexpr int kQ6Rows = q6b::kRows;   // output rows per staged block
+constexpr int kQ6MaxSub = 1;          // blocks per work item (the activation side is prepared once per item): with two CTAs
+                                      // per SM finer items measured faster (125 against 142 us at batch 64) than four blocks per item
+constexpr int kQ6Threads = 256;  // two CTAs per SM: one's block travels while the other computes
 
 struct Q6Params {
   const float *A;  // activation rows f32 [P][K]
@@ -31,37 +34,48 @@ struct Q6Params {
   float *Y;  // [P][N]
   int N, K;
   int64_t idxStride;
+  int *status;  // raised when the bounded wait for a weight block gave up (may be null)
+  long long wait_cycles;
+  int two_blocks;  // the shared memory holds two weight blocks (the next one travels while this one is worked on)
 };
 
-__global__ void __launch_bounds__(kQ6Threads) q6k_proj_kernel(const Q6Params p) {
-  extern __shared__ __align__(16) uint8_t s_raw[];  // [kQ6Rows][row bytes] weights, then [kQ6Tok][K] f32 activations
+__global__ void __launch_bounds__(kQ6Threads, 2) q6k_proj_kernel(const Q6Params p) {
+  extern __shared__ __align__(16) uint8_t s_raw[];  // weight block(s), then the activation side (q6b::carve)
   __shared__ int s_pair[kQ6Tok];
+  __shared__ uint64_t s_bars[2];  // the weight blocks' bulk copies
+  __shared__ int s_fail;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nsb = p.K / KNJ_QK_K, row_bytes = nsb * KNJ_Q6K_BYTES;
-  uint8_t *wbuf = s_raw;
-  float *abuf = reinterpret_cast<float *>(s_raw + (((size_t)kQ6Rows * row_bytes + 15) & ~(size_t)15));
-  const int chunks = (p.N + kQ6Rows - 1) / kQ6Rows;
+  if (threadIdx.x == 0) {
+    mbar_init(&s_bars[0], 1);
+    mbar_init(&s_bars[1], 1);
+    s_fail = 0;
+    mbar_init_fence();
+  }
+  const int row_bytes = p.K / KNJ_QK_K * KNJ_Q6K_BYTES;
+  const q6b::Bufs b = q6b::carve(s_raw, p.K, kQ6Threads / 32, p.two_blocks != 0, s_bars, &s_fail);
+  const int blocks = (p.N + kQ6Rows - 1) / kQ6Rows;
   const int n_act = p.n_active[0];
+  // blocks per item: as many as leave every CTA about two items (few experts: one block per item)
+  const int sub = max(1, min(kQ6MaxSub, n_act * blocks / (2 * (int)gridDim.x)));
+  const int chunks = (blocks + sub - 1) / sub;
   const int total = n_act * chunks;
+  const bool bulk = (reinterpret_cast<uintptr_t>(p.W) & 15u) == 0 && p.N % kQ6Rows == 0;
+  unsigned staged = 0;  // bulk copies waited for so far
   for (int it = blockIdx.x; it < total; it += gridDim.x) {
     const int a = it / chunks, chunk = it - a * chunks;
     const int e = p.exp_list[a];
     const int cnt = p.pair_cnt[e];
-    const int n0 = chunk * kQ6Rows, n_rows = min(kQ6Rows, p.N - n0);
-    __syncthreads();  // the previous item is done with both buffers
-    q6b::stage_block(wbuf, p.W + ((size_t)e * p.N + n0) * row_bytes, n_rows * row_bytes, threadIdx.x, kQ6Threads);
+    const int n0 = chunk * sub * kQ6Rows, n_rows = min(sub * kQ6Rows, p.N - n0);
     for (int tok0 = 0; tok0 < cnt; tok0 += kQ6Tok) {
       const int nt = min(kQ6Tok, cnt - tok0);
-      if (tok0) __syncthreads();  // the previous pass is done with the staged rows
+      __syncthreads();  // the previous pass is done with the shared buffers
       if ((int)threadIdx.x < kQ6Tok) s_pair[threadIdx.x] = (int)threadIdx.x < nt ? p.pair_idx[(size_t)e * p.idxStride + tok0 + threadIdx.x] : -1;
       __syncthreads();
-      for (int i = threadIdx.x; i < nt * (p.K / 4); i += kQ6Threads) {
-        const int t = i / (p.K / 4), k4 = i - t * (p.K / 4);
-        reinterpret_cast<float4 *>(abuf + (size_t)t * p.K)[k4] = __ldg(reinterpret_cast<const float4 *>(p.A + (size_t)s_pair[t] * p.K) + k4);
+      if (!q6b::chunk_pass<kQ6Threads / 32>(b, p.W + ((size_t)e * p.N + n0) * row_bytes, n_rows, p.K, p.A, p.Y + n0, p.N, s_pair, nt, staged,
+                                            bulk, p.wait_cycles, lane, warp)) {
+        if (threadIdx.x == 0 && p.status) atomicExch(p.status, 1);  // a copy that never completed: report and leave
+        return;
       }
-      __syncthreads();
-      q6b::rows_any<kQ6Threads / 32>(wbuf, abuf, p.K, n_rows, nt, lane, warp,
-                                     [&](int r, int t, float v) { p.Y[(size_t)s_pair[t] * p.N + n0 + r] = v; });
     }
   }
 }
@@ -72,11 +86,12 @@ extern "C" {
 
 int knj_q6k_proj_launch(const float *A, const uint8_t *W6, const int32_t *pair_idx, const int32_t *pair_cnt,
                         const int32_t *exp_list, const int32_t *n_active, float *Y, int N, int K, int64_t idxStride,
-                        int n_experts, knj_stream_t s) {
+                        int n_experts, int *status, knj_stream_t s) {
   KNJ_REQUIRE(A && W6 && pair_idx && pair_cnt && exp_list && n_active && Y, "knj_q6k_proj: null pointer");
   KNJ_REQUIRE(K > 0 && K % 256 == 0 && N > 0 && n_experts > 0, "knj_q6k_proj: K=%d must be a multiple of 256, N=%d positive", K, N);
-  const size_t row_bytes = (size_t)(K / 256) * KNJ_Q6K_BYTES;
-  const size_t smem = ((kQ6Rows * row_bytes + 15) & ~(size_t)15) + (size_t)kQ6Tok * K * sizeof(float);
+  const size_t one = q6b::block_bytes(K) + q6b::act_scratch_bytes(K, kQ6Threads / 32);
+  const bool two = false;  // one block buffer per CTA and two CTAs per SM measured faster than one CTA with two buffers
+  const size_t smem = one + (two ? q6b::block_bytes(K) : 0);
   KNJ_REQUIRE(smem <= 220 * 1024, "knj_q6k_proj: K=%d is too long for the staged rows", K);
   KNJ_REQUIRE(aligned16(A) && K % 4 == 0, "knj_q6k_proj: activation rows must be 16-byte aligned");
   int dev = 0;
@@ -87,9 +102,10 @@ int knj_q6k_proj_launch(const float *A, const uint8_t *W6, const int32_t *pair_i
     KNJ_CUDA(cudaFuncSetAttribute(q6k_proj_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
     opted[dev] = smem;
   }
-  Q6Params p{A, W6, pair_idx, pair_cnt, exp_list, n_active, Y, N, K, idxStride};
+  Q6Params p{A, W6, pair_idx, pair_cnt, exp_list, n_active, Y, N, K, idxStride, status, knj::decode_wait_cycles(), two ? 1 : 0};
   const long long items = (long long)n_experts * ((N + kQ6Rows - 1) / kQ6Rows);
-  const long long cap = (long long)sm_count() * (smem <= 72 * 1024 ? 3 : 1);
+  const long long per_sm = smem + 1024 <= 113 * 1024 ? 2 : 1;
+  const long long cap = (long long)sm_count() * per_sm;
   q6k_proj_kernel<<<(unsigned)(items < cap ? items : cap), kQ6Threads, smem, as_stream(s)>>>(p);
   return launch_status("q6k_proj_kernel");
 }

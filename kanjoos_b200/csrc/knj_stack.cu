@@ -127,7 +127,7 @@ __host__ __device__ inline Plan make_plan(const q4e::PhaseShape &gu, const q4e::
   pl.pair = take(q4e::kJobTok * 4);
   pl.scale = take((size_t)T * 4);
   pl.ord = take((size_t)T * k);
-  pl.fail = take(16);
+  pl.fail = take(32);   // fail word, then the two block barriers of the Q6_K down phase
   pl.desc = take(2 * sizeof(LayerDesc));
   // partial sums of warps that share a tile: only small batches have so few tiles that they do
   pl.red = T <= kSplitMaxT ? take((size_t)q4e::kWarps * 32 * sizeof(float4)) : 0;
@@ -336,10 +336,14 @@ __device__ __noinline__ void stage_plan(const StackParams &p, const LayerDesc &L
 
 }
 
-// Down phase of a layer whose down matrices are Q6_K: (active expert, block of 64 output rows) units dealt round
-// robin over the CTAs; the block's superblocks and the SiLU*up rows of up to eight of the expert's tokens are
-// staged in the (idle) ring area, the arithmetic is knj_q6k_block.cuh's, i.e. the stand-alone projection's.
-__device__ __noinline__ void stage_down_q6k(const StackParams &p, const LayerDesc &L, const Plan &pl, uint8_t *smem) {
+// Down phase of a layer whose down matrices are Q6_K: (active expert, one to four blocks of 64 output rows) units
+// dealt round robin over the CTAs; the blocks' superblocks and the activation side of up to eight of the expert's
+// tokens live in the (idle) ring area, the arithmetic is knj_q6k_block.cuh's, i.e. the stand-alone projection's.
+// Where the blocks can travel as bulk copies (16-byte aligned base, H a multiple of 64) and the ring area holds two
+// of them, the next block is under way while this one is worked on: two barriers behind the fail word, `staged`
+// counts this CTA's blocks over the whole launch.
+__device__ __noinline__ void stage_down_q6k(const StackParams &p, const LayerDesc &L, const Plan &pl, uint8_t *smem, unsigned &staged,
+                                            bool &ok) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int H = p.H, F = p.F, k = p.k, c = blockIdx.x, G = gridDim.x;
   const int *sel_e = reinterpret_cast<const int *>(smem + pl.sel_e);
@@ -347,41 +351,40 @@ __device__ __noinline__ void stage_down_q6k(const StackParams &p, const LayerDes
   const int *jbase = reinterpret_cast<const int *>(smem + pl.jbase), *uexp = reinterpret_cast<const int *>(smem + pl.uexp);
   int *s_pair = reinterpret_cast<int *>(smem + pl.inv);  // eight ints: the pass's output rows (the phase engine is idle)
   const int row_bytes = F / KNJ_QK_K * KNJ_Q6K_BYTES;
-  uint8_t *wbuf = smem + pl.ring;
-  float *abuf = reinterpret_cast<float *>(wbuf + (((size_t)q6b::kRows * row_bytes + 15) & ~(size_t)15));
+  const bool two = 2 * q6b::block_bytes(F) + q6b::act_scratch_bytes(F, q4e::kWarps) <= (size_t)(pl.panels - pl.ring);
+  const bool bulk = (reinterpret_cast<uintptr_t>(L.w_down6) & 15u) == 0 && H % q6b::kRows == 0;
+  const q6b::Bufs b = q6b::carve(smem + pl.ring, F, q4e::kWarps, two, reinterpret_cast<uint64_t *>(smem + pl.fail + 16),
+                                 reinterpret_cast<int *>(smem + pl.fail));
   const int blocks = (H + q6b::kRows - 1) / q6b::kRows, n_act = jbase[259];
-  for (int u = c; u < n_act * blocks; u += G) {
-    const int a = u / blocks, rb = u - a * blocks;
+  const int sub = max(1, min(4, n_act * blocks / (2 * G)));  // blocks per unit: the activation side is prepared once per unit
+  const int chunks = (blocks + sub - 1) / sub, total = n_act * chunks;
+  for (int u = c; u < total; u += G) {
+    const int a = u / chunks, ch = u - a * chunks;
     const int e = uexp[a];
-    const int n0 = rb * q6b::kRows, n_rows = min(q6b::kRows, H - n0);
-    __syncthreads();  // the previous unit is done with both buffers
-    q6b::stage_block(wbuf, L.w_down6 + ((size_t)e * H + n0) * row_bytes, n_rows * row_bytes, threadIdx.x, kThreads);
+    const int n0 = ch * sub * q6b::kRows, n_rows = min(sub * q6b::kRows, H - n0);
     unsigned long long m = mask[e];
-    bool first = true;
     while (m) {
-      if (!first) __syncthreads();  // the previous pass is done with the staged rows
-      first = false;
-      int nt = 0;
-      unsigned long long mm = m;
-      if (threadIdx.x == 0) {
-        for (; nt < q6b::kTok && mm; ++nt) {
+      __syncthreads();  // the previous pass is done with the shared buffers
+      // the pass's tokens are the lowest set bits of the mask: thread 8 i + j looks at slot j (+ 8, ...) of the i-th
+      const int nt = min(q6b::kTok, __popcll(m));
+      if (threadIdx.x < 8 * q6b::kTok) {
+        const int i = threadIdx.x >> 3;
+        unsigned long long mm = m;
+        for (int x = 0; x < i; ++x) mm &= mm - 1;
+        if (i < nt) {
           const int tok = __ffsll((long long)mm) - 1;
-          mm &= mm - 1;
-          int slot = 0;
-          for (int j = 0; j < k; ++j) slot = sel_e[tok * k + j] == e ? j : slot;
-          s_pair[nt] = tok * k + slot;
+          for (int j = threadIdx.x & 7; j < k; j += 8)
+            if (sel_e[tok * k + j] == e) s_pair[i] = tok * k + j;
         }
       }
-      nt = min(q6b::kTok, __popcll(m));
       for (int i = 0; i < nt; ++i) m &= m - 1;
       __syncthreads();
-      for (int i = threadIdx.x; i < nt * (F / 4); i += kThreads) {
-        const int t = i / (F / 4), k4 = i - t * (F / 4);
-        reinterpret_cast<float4 *>(abuf + (size_t)t * F)[k4] = __ldcg(reinterpret_cast<const float4 *>(p.act + (size_t)s_pair[t] * F) + k4);
+      if (!q6b::chunk_pass<q4e::kWarps>(b, L.w_down6 + ((size_t)e * H + n0) * row_bytes, n_rows, F, p.act, p.Y + n0, H, s_pair, nt, staged,
+                                        bulk, p.wait_cycles, lane, warp)) {
+        ok = false;  // a copy that never completes: bounded wait, the launch reports it
+        m = 0;
+        u = total;
       }
-      __syncthreads();
-      q6b::rows_any<q4e::kWarps>(wbuf, abuf, F, n_rows, nt, lane, warp,
-                                 [&](int r, int t, float v) { p.Y[(size_t)s_pair[t] * H + n0 + r] = v; });
     }
   }
   __syncthreads();  // the ring area returns to the projection phases
@@ -412,12 +415,18 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
 
   if (lane == 0)
     for (int s = 0; s < q4e::kMaxStages; ++s) mbar_init(&sm.bars[warp * q4e::kMaxStages + s], 1);
-  if (threadIdx.x == 0) *s_fail = 0;
+  if (threadIdx.x == 0) {
+    *s_fail = 0;
+    // the Q6_K down phase's two block barriers (behind the fail word)
+    mbar_init(reinterpret_cast<uint64_t *>(smem + pl.fail + 16), 1);
+    mbar_init(reinterpret_cast<uint64_t *>(smem + pl.fail + 24), 1);
+  }
   mbar_init_fence();
   __syncthreads();
 
   unsigned arrivals = 0, parity = 0;
   bool ok = true;
+  unsigned q6_staged = 0;  // Q6_K down blocks this CTA has staged so far (stage_down_q6k)
   // logits: CTA c < n_eg * n_tg takes experts epi * eg .. + epi - 1 for tokens 8 tg .. 8 tg + 7
   const int n_tg = (T + 7) / 8;
   int epi = 8;
@@ -508,7 +517,7 @@ __global__ void __launch_bounds__(kThreads, 1) moe_stack_kernel(const StackParam
     KNJ_STAMP(5);
 
     // ---- stage 4: down -> Y (one row per pair)
-    if (L.w_down6) stage_down_q6k(p, L, pl, smem);
+    if (L.w_down6) stage_down_q6k(p, L, pl, smem, q6_staged, ok);
     else {
       const long long U = (long long)jbase[256] * p.dn.tiles;
       const int u0 = (int)(U * c / G), u1 = (int)(U * (c + 1) / G);
@@ -676,7 +685,7 @@ int knj_moe_stack_create(const knj_moe_ffn_args *layers, int n_layers, knj_moe_s
   }
   const size_t smem = total();
   if (any_q6k) {  // a Q6_K down phase stages a 64-row block and eight activation rows in the ring area
-    const size_t need = (((size_t)q6b::kRows * (F / 256) * KNJ_Q6K_BYTES + 15) & ~(size_t)15) + (size_t)q6b::kTok * F * 4;
+    const size_t need = q6b::block_bytes(F) + q6b::act_scratch_bytes(F, q4e::kWarps);
     const size_t ring = std::max(q4e::phase_ring_bytes(sp.gu.sbs, sp.gu.stages), q4e::phase_ring_bytes(sp.dn.sbs, sp.dn.stages));
     KNJ_REQUIRE(need <= ring, "knj_moe_stack_create: ffn=%d is too long for the Q6_K down phase's staging (%zu > %zu bytes)", F, need, ring);
   }

@@ -165,8 +165,11 @@ def q6k_proj(A: torch.Tensor, W6: torch.Tensor, pair_idx, pair_cnt, exp_list, n_
     _need(A, torch.float32), _need(W6, torch.uint8)
     E, N, nblk, _ = W6.shape
     Y = torch.full((P, N), -12345.0, dtype=torch.float32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
     check(lib().knj_q6k_proj_launch(_p(A), _p(W6), _p(pair_idx), _p(pair_cnt), _p(exp_list), _p(n_active), _p(Y), N,
-                                    nblk * 256, pair_idx.shape[1], E, _stream()))
+                                    nblk * 256, pair_idx.shape[1], E, _p(status), _stream()))
+    if int(status.item()):
+        raise RuntimeError("knj_q6k_proj_launch: a bounded wait for a weight block gave up")
     return Y
 
 

@@ -126,9 +126,15 @@ def test_refusals_do_not_launch():
         ops.q4k_matmul(torch.zeros((16, 1, 144), dtype=torch.uint8, device="cuda")[1:], x)  # 15 rows: not a multiple of 16
 
 
-@pytest.mark.parametrize("E,N,K,counts", [(3, 80, 768, [5, 0, 11]), (2, 64, 256, [1, 9])])
+@pytest.mark.parametrize("E,N,K,counts", [
+    (3, 80, 768, [5, 0, 11]),     # ragged last block (loads instead of bulk copies), passes of 8 + 3 rows
+    (2, 64, 256, [1, 9]),         # one row (scalar form), 8 + 1
+    (2, 192, 768, [2, 4]),        # bulk copies over three blocks; two rows (scalar form), four (one MMA column group)
+    (2, 128, 1024, [7, 3]),       # four superblocks per row; two column groups, one
+])
 def test_q6k_projection(E, N, K, counts):
-    """Q6_K down projection of the mixed-format path against the CPU decoder + a double-precision product."""
+    """Q6_K down projection of the mixed-format path against the CPU decoder + a double-precision product, the
+    activation rows spread over six decades of magnitude (every row has its own power-of-two scale in the MMA form)."""
     from kanjoos_b200 import ops
     rng = np.random.Generator(np.random.Philox([E, N, K]))
     nblk = K // 256
@@ -140,10 +146,12 @@ def test_q6k_projection(E, N, K, counts):
     P = int(sum(counts))
     pe = np.concatenate([np.full(c, e, np.int32) for e, c in enumerate(counts)])
     pe = pe[rng.permutation(P)]
-    A = rng.standard_normal((P, K)).astype(np.float32)
+    A = (rng.standard_normal((P, K)) * (10.0 ** (np.arange(P) % 7 - 3))[:, None]).astype(np.float32)
     pair_idx, pair_cnt, exp_list, n_active = ops.moe_permute(dev(pe), E, P)
     Y = ops.q6k_proj(dev(A), dev(W), pair_idx, pair_cnt, exp_list, n_active, P).cpu().numpy()
     want = np.stack([(Wf[pe[p]].astype(np.float64) @ A[p].astype(np.float64)) for p in range(P)]).astype(np.float32)
     st = ol.compare(Y, want)
     print("[parity] q6k projection", st)
     assert (Y == -12345.0).sum() == 0 and st["rel_rmse"] <= 1e-5
+    row_err = np.sqrt(((Y.astype(np.float64) - want) ** 2).mean(1)) / np.sqrt((want.astype(np.float64) ** 2).mean(1))
+    assert row_err.max() <= 1e-5, f"worst row {row_err.argmax()}: {row_err.max():.3e}"
