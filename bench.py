@@ -197,7 +197,7 @@ def workload_config(args, world):
 
 # --------------------------------------------------------------------------- GPU arm
 
-def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64), inputs=("chained", "fresh")):
+def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64), inputs=("chained", "fresh"), down="q4k"):
     """Resident stack (48 layers by default): tokens/s and HBM roofline of the decode path, one cooperative launch
     per step (knj_moe_stack_*). Two inputs per batch: `chained` feeds each layer the previous layer's output (the
     decode loop as it runs; with random-init weights the residual stream concentrates the routing on a third of
@@ -205,7 +205,19 @@ def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64), 
     trained router: ~126 of 128 experts at batch 64). Algorithmic bytes use the distinct experts actually routed."""
     from kanjoos_b200.moe import ExpertBank, FusedMoeStack
     banks = [ExpertBank.random(seed=1000 + l) for l in range(layers)]
-    out = {"layers": layers, "resident_weight_gib": round(layers * E * EXPERT_BYTES / 2**30, 2), "batches": {}}
+    # down == "mixed": every second layer's down matrices are Q6_K, as Q4_K_M files hold them; "q6k": every layer's
+    q6_layers = [l for l in range(layers) if down == "q6k" or (down == "mixed" and l % 2 == 1)]
+    q6_down_bytes = H * (F // 256) * 210
+    for l in q6_layers:
+        g6 = torch.Generator(device="cuda")
+        g6.manual_seed(9000 + l)
+        w6 = torch.randint(0, 256, (E, H, F // 256, 210), dtype=torch.uint8, device="cuda", generator=g6)
+        d6 = (torch.randn((E, H, F // 256, 1), device="cuda", generator=g6).abs() * 0.002).to(torch.float16)
+        w6[..., 208:210] = d6.view(torch.uint8).reshape(E, H, F // 256, 2)
+        banks[l].down = w6
+    expert_bytes = [EXPERT_BYTES - F * (H // 256) * 144 + q6_down_bytes if l in q6_layers else EXPERT_BYTES for l in range(layers)]
+    out = {"layers": layers, "down_format": down, "q6k_down_layers": len(q6_layers),
+           "resident_weight_gib": round(E * sum(expert_bytes) / 2**30, 2), "batches": {}}
     for B in batches:
         g = torch.Generator(device="cuda")
         g.manual_seed(B)
@@ -219,7 +231,8 @@ def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64), 
             for _ in range(max(3, warmup)):
                 stack.step(x)
             stack.status()
-            distinct = sum(int(torch.unique(t[0]).numel()) for t in stack.taps)
+            per_layer = [int(torch.unique(t[0]).numel()) for t in stack.taps]
+            distinct = sum(per_layer)
             ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
             reps = max(steps, int(0.3 / max(1e-4, layers * 150e-6)))  # at least ~0.3 s of timed launches
             ev[0].record()
@@ -229,7 +242,7 @@ def decode_section(torch, steps, warmup, pk, layers=LAYERS, batches=(1, 8, 64), 
             torch.cuda.synchronize()
             stack.status()
             ms = ev[0].elapsed_time(ev[1]) / reps
-            alg = distinct * EXPERT_BYTES + layers * (E * H * 2 + H * 2 + B * H * 2 * 2)
+            alg = sum(d * eb for d, eb in zip(per_layer, expert_bytes)) + layers * (E * H * 2 + H * 2 + B * H * 2 * 2)
             key = str(B) if mode == "chained" else f"{B}_fresh"
             out["batches"][key] = {"tokens_per_s": B / (ms * 1e-3), "ms_per_step": ms, "timed_steps": reps,
                                    "path": "one cooperative launch per step (knj_moe_stack_decode_launch)",
@@ -309,7 +322,8 @@ def run_gpu(args):
     if args.section == "decode":
         # decode-only run (used for profiling captures): one line about the resident stack
         dec = decode_section(torch, args.steps, args.warmup, pk, args.decode_layers,
-                             tuple(int(b) for b in args.decode_batches.split(",")), tuple(args.decode_inputs.split(",")))
+                             tuple(int(b) for b in args.decode_batches.split(",")), tuple(args.decode_inputs.split(",")),
+                             args.decode_down)
         print(json.dumps({"metric": "moe_ffn_decode", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
                           "data": "synthetic", "decode": dec}))
         return
@@ -597,6 +611,9 @@ def main():
     ap.add_argument("--section", default="all", choices=["all", "decode"])
     ap.add_argument("--decode-layers", type=int, default=LAYERS, dest="decode_layers")
     ap.add_argument("--decode-batches", default="1,8,64", dest="decode_batches")
+    ap.add_argument("--decode-down", default="q4k", choices=["q4k", "q6k", "mixed"], dest="decode_down",
+                    help="--section decode: down matrices of the resident stack; mixed = Q6_K in every second layer, as "
+                         "Q4_K_M files hold them")
     ap.add_argument("--decode-inputs", default="chained,fresh", dest="decode_inputs",
                     help="per-layer inputs of the decode section: chained (each layer feeds the next), fresh, or both")
     args = ap.parse_args()
