@@ -188,9 +188,10 @@ int knj_q6k_dequant_launch(const uint8_t *blocks, float *out, uint64_t n_blocks,
  * Y[p][n] = sum_k W6[e][n][k] * A[p][k] for the pairs p of every active expert e
  * (tables as for knj_q4k_proj_launch). A f32 [P][K] dense, W6 uint8
  * [E][N][K/256][210] (rows need no alignment; a 16-byte aligned base with N a
- * multiple of 64 takes the bulk-copy staging), Y f32 [P][N]. One or two rows per
- * expert: f32 FMAs; three and more: mma.sync.m16n8k16 on exact fp16 codes with
- * the activations as two fp16 planes (f32-level accuracy). status (optional):
+ * multiple of 64 takes the bulk-copy staging), Y f32 [P][N]. mma.sync.m16n8k16
+ * on exact fp16 codes (q - 32), the activations as two fp16 planes under a
+ * power-of-two scale per row (f32-level accuracy), the int8 group scales and d
+ * applied in f32. status (optional):
  * set to 1 when a bounded wait for a weight block gave up. */
 int knj_q6k_proj_launch(const float *A, const uint8_t *W6, const int32_t *pair_idx, const int32_t *pair_cnt,
                         const int32_t *exp_list, const int32_t *n_active, float *Y, int N, int K, int64_t idxStride,

@@ -8,11 +8,10 @@
 // A CTA takes (expert, block of 64 output rows): a block's superblocks are contiguous in HBM and start
 // on a 16-byte boundary (rows themselves are only 2-byte aligned, so there are no TMA boxes here); they travel as one
 // bulk copy per block while the CTA prepares the activation side of up to 8 of the expert's tokens (two CTAs per SM:
-// one's block travels while the other computes). With one or two tokens a warp walks a
-// row: lane l decodes the four weights l, l+32, l+64, l+96 of each 128-weight half (two code bytes, one byte of high
-// bit pairs, four int8 scales), forms sc * (q - 32) in integers, and feeds one FMA per weight and token; d is applied
-// once per superblock, the warp sums meet in shuffles. From three tokens on the block runs on mma.sync.m16n8k16
-// (one k-step per 16-weight scale group, activations as two fp16 planes: knj_q6k_block.cuh).
+// one's block travels while the other computes). The block then runs on mma.sync.m16n8k16: one k-step per
+// 16-weight scale group, the codes as exact fp16 integers, the activations as two fp16 planes (f32-level accuracy:
+// knj_q6k_block.cuh). A scalar form (one FMA per weight and token on integer sc * (q - 32)) was the first version
+// and measured slower at every batch, one-token experts included.
 #include "knj_common.cuh"
 #include "knj_q4k.h"
 #include "knj_q6k_block.cuh"
@@ -24,7 +23,7 @@ namespace {
 constexpr int kQ6Tok = q6b::kTok;     // tokens per pass
 constexpr int kQ6Rows = q6b::kRows;   // output rows per staged block
 constexpr int kQ6MaxSub = 1;          // blocks per work item (the activation side is prepared once per item): with two CTAs
-                                      // per SM finer items measured faster (125 against 142 us at batch 64) than four blocks per item
+                                      // per SM two or four blocks per item measured no faster (118 us at batch 64 either way)
 constexpr int kQ6Threads = 256;  // two CTAs per SM: one's block travels while the other computes
 
 struct Q6Params {

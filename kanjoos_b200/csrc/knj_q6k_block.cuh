@@ -9,18 +9,8 @@
 namespace knj {
 namespace q6b {
 
-constexpr int kTok = 8;    // activation rows per pass (accumulators per lane and row)
+constexpr int kTok = 8;    // activation rows per pass: two MMA column groups of four
 constexpr int kRows = 64;  // output rows per staged block: a block starts on a 16-byte boundary of the weight stream
-
-// four weights of lane `lane` in half `hf` of a superblock, as sc * (q - 32): positions lane, +32, +64, +96
-__device__ __forceinline__ void four(const uint8_t *blk, int hf, int lane, float (&w)[4]) {
-  const uint32_t a = blk[64 * hf + lane], b = blk[64 * hf + 32 + lane], h = blk[128 + 32 * hf + lane];
-  const int8_t *sc = reinterpret_cast<const int8_t *>(blk + 192 + 8 * hf) + (lane >> 4);
-  w[0] = (float)((int)sc[0] * ((int)((a & 15u) | ((h & 3u) << 4)) - 32));
-  w[1] = (float)((int)sc[2] * ((int)((b & 15u) | (((h >> 2) & 3u) << 4)) - 32));
-  w[2] = (float)((int)sc[4] * ((int)((a >> 4) | (((h >> 4) & 3u) << 4)) - 32));
-  w[3] = (float)((int)sc[6] * ((int)((b >> 4) | (((h >> 6) & 3u) << 4)) - 32));
-}
 
 // The block's superblocks (rows x row_bytes contiguous bytes at src) into shared memory: 16-byte pieces where the
 // start and the length allow it, else 2-byte pieces (rows are 2-byte aligned). All `threads` threads of the CTA.
@@ -44,61 +34,7 @@ __device__ __forceinline__ void stage_block_bulk(uint8_t *wbuf, const uint8_t *s
   bulk_g2s(wbuf, src, (uint32_t)bytes, bar);
 }
 
-// Rows of the staged block against NT staged activation rows (f32 [NT][K] at abuf): a warp takes rows (r, r + WARPS)
-// together, so that an activation value read from shared memory meets two weights. store(r, t, value) receives the
-// finished sums of row r and activation row t < nt from lane 0. Lane l covers weights l, l+32, l+64, l+96 of every
-// 128-weight half; d is applied once per superblock; the warp's partial sums meet in shuffles.
-template <int NT, int WARPS, class Store>
-__device__ __forceinline__ void rows(const uint8_t *wbuf, const float *abuf, int K, int n_rows, int nt, int lane, int warp, Store store) {
-  const int nsb = K / KNJ_QK_K, row_bytes = nsb * KNJ_Q6K_BYTES;
-  for (int r = warp; r < n_rows; r += 2 * WARPS) {
-    const bool two = r + WARPS < n_rows;
-    const int r2 = two ? r + WARPS : r;
-    float acc[2][NT];
-#pragma unroll
-    for (int t = 0; t < NT; ++t) acc[0][t] = acc[1][t] = 0.f;
-    for (int sb = 0; sb < nsb; ++sb) {
-      const uint8_t *b0 = wbuf + (size_t)r * row_bytes + sb * KNJ_Q6K_BYTES, *b1 = wbuf + (size_t)r2 * row_bytes + sb * KNJ_Q6K_BYTES;
-      float part[2][NT];
-#pragma unroll
-      for (int t = 0; t < NT; ++t) part[0][t] = part[1][t] = 0.f;
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        float w0[4], w1[4];
-        four(b0, hf, lane, w0);
-        four(b1, hf, lane, w1);
-        const float *x = abuf + sb * KNJ_QK_K + hf * 128 + lane;
-#pragma unroll
-        for (int t = 0; t < NT; ++t) {
-          const float *xt = x + (size_t)t * K;
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const float xv = xt[32 * j];
-            part[0][t] = fmaf(w0[j], xv, part[0][t]);
-            part[1][t] = fmaf(w1[j], xv, part[1][t]);
-          }
-        }
-      }
-      const float d0 = knj_half_bits_to_float((uint16_t)(b0[208] | ((uint16_t)b0[209] << 8)));
-      const float d1 = knj_half_bits_to_float((uint16_t)(b1[208] | ((uint16_t)b1[209] << 8)));
-#pragma unroll
-      for (int t = 0; t < NT; ++t) {
-        acc[0][t] = fmaf(d0, part[0][t], acc[0][t]);
-        acc[1][t] = fmaf(d1, part[1][t], acc[1][t]);
-      }
-    }
-#pragma unroll
-    for (int t = 0; t < NT; ++t) {
-      const float v0 = warp_sum(acc[0][t]), v1 = warp_sum(acc[1][t]);
-      if (lane == 0 && t < nt) {
-        store(r, t, v0);
-        if (two) store(r2, t, v1);
-      }
-    }
-  }
-}
-
-// ---- three and more activation rows: mma.sync.m16n8k16 -------------------------------------------------------
+// ---- the arithmetic: mma.sync.m16n8k16 -----------------------------------------------------------------------
 // A 16-weight scale group of Q6_K is exactly one k-step of the MMA. A = the codes as exact fp16 integers q - 32
 // (byte under the exponent 0x64 = 1024 + q, minus 1056), B = the activations as two fp16 planes (x * s = hi + lo,
 // s a power of two per activation row that puts its largest magnitude in [2^13, 2^14); the planes are adjacent
@@ -310,7 +246,7 @@ __device__ __forceinline__ bool chunk_pass(const Bufs &b, const uint8_t *src, in
     reinterpret_cast<float4 *>(b.abuf + (size_t)t * K)[k4] = __ldcg(reinterpret_cast<const float4 *>(A + (size_t)rows_of[t] * K) + k4);
   }
   __syncthreads();
-  if (nt > 2) prepare_panel<WARPS>(b, K, nt, lane, warp);
+  prepare_panel<WARPS>(b, K, nt, lane, warp);
   for (int sub = 0; sub < nsub; ++sub) {
     const int r0 = sub * kRows, nr = min(kRows, n_rows - r0);
     const uint8_t *wbuf;
@@ -330,9 +266,7 @@ __device__ __forceinline__ bool chunk_pass(const Bufs &b, const uint8_t *src, in
       wbuf = b.w[0];
     }
     auto store = [&](int r, int t, float v) { Y[(size_t)rows_of[t] * ldy + r0 + r] = v; };
-    if (nt == 1) rows<1, WARPS>(wbuf, b.abuf, K, nr, nt, lane, warp, store);
-    else if (nt == 2) rows<2, WARPS>(wbuf, b.abuf, K, nr, nt, lane, warp, store);
-    else if (nt <= 4) block_mma<1, WARPS>(wbuf, b, K, nr, nt, lane, warp, store);
+    if (nt <= 4) block_mma<1, WARPS>(wbuf, b, K, nr, nt, lane, warp, store);
     else block_mma<2, WARPS>(wbuf, b, K, nr, nt, lane, warp, store);
     if (bulk && !two && sub + 1 < nsub) {  // one buffer: the next block can only start once this one is done with
       __syncthreads();
